@@ -1,0 +1,262 @@
+/*
+ * t0b200 — B200 (sm_100a) implementation of the T0-GPU GEMM hot path behind a C ABI.
+ *
+ * Every entry point is what a foreign-function binding in the reference
+ * (clearnature/rust-gpu, crate t0-gpu) would bind for this path; the comment
+ * above each one cites the Rust item it replaces (paths relative to that tree).
+ *
+ * Conventions
+ *   - every fallible call returns int: 0 = OK, non-zero = error code below;
+ *     the message is available from t0_last_error() (thread-local).  A Rust
+ *     `panic!`/`assert!` in the reference becomes T0_ERR_INVALID here.
+ *   - handles are opaque pointers owned by the caller until the matching free.
+ *   - plain pointers and sizes only; device addresses travel as uint64_t
+ *     exactly as the reference carries them in its kernarg blobs.
+ *   - there is no CPU fallback: compute entry points fail with T0_ERR_CUDA when
+ *     no B200-class device is present.
+ */
+#ifndef T0B200_H
+#define T0B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ errors */
+enum {
+    T0_OK = 0,
+    T0_ERR_INVALID = 1,      /* bad argument / a panic in the reference            */
+    T0_ERR_CUDA = 2,         /* CUDA runtime or driver call failed                 */
+    T0_ERR_POISONED = 3,     /* runtime poisoned by an earlier device failure      */
+    T0_ERR_TIMEOUT = 4,      /* a bounded device-side wait expired                 */
+    T0_ERR_BOUNDS = 5,       /* buffer too small for the requested operation       */
+    T0_ERR_UNSUPPORTED = 6,  /* shape/config this build has no kernel for          */
+    T0_ERR_IO = 7            /* tune-cache file problem                            */
+};
+/* Rust `Result<_, String>` error text of the last failing call on this thread. */
+const char* t0_last_error(void);
+/* Library/ABI version: major*10000 + minor*100 + patch. */
+int t0_version(void);
+
+/* ------------------------------------------------------- GemmConfig (a3) */
+/* src/t0/gemm_gen.rs:23-33 GemmTranspose */
+enum { T0_NT = 0, T0_NN = 1 };
+/* src/t0/gemm_gen.rs:40-49 EpilogueOp */
+enum { T0_EPI_STORE_F32 = 0, T0_EPI_BIAS_ADD_STORE_F32 = 1, T0_EPI_BIAS_ADD_RELU_STORE_F32 = 2 };
+
+/* src/t0/gemm_gen.rs:55-84 GemmConfig — same fields, same meaning.  On B200:
+ * tile_m/tile_n/tile_k are the CTA tile, wg_size the CTA thread count that
+ * compute_grid multiplies by, use_lds/double_buffer select the multi-stage
+ * shared-memory pipeline (always on), split_k 0 or 1 means None, wgp_mode
+ * selects the two-CTA pair tile, lds_pad and n_col_passes are accepted and
+ * ignored (no bank padding / column passes exist on this hardware). */
+typedef struct t0_gemm_config {
+    uint32_t tile_m, tile_n, tile_k, wg_size;
+    uint8_t use_lds, double_buffer;
+    uint8_t _pad0[2];
+    uint32_t split_k;
+    uint32_t lds_pad, n_col_passes;
+    uint8_t swap_grid, wgp_mode, transpose, epilogue;
+} t0_gemm_config;
+
+/* GemmConfig::tile_16x64_k16() ... tile_64x128_2pass() (gemm_gen.rs:86-145);
+ * `preset` is the Rust constructor name, e.g. "tile_128x64_k32". */
+int t0_gemm_config_preset(const char* preset, t0_gemm_config* out);
+/* GemmConfig::name() (gemm_gen.rs:215-235); writes a NUL-terminated string. */
+int t0_gemm_config_name(const t0_gemm_config* cfg, char* buf, size_t buf_len);
+/* GemmConfig::estimated_vgprs() (gemm_gen.rs:189-201), kept for callers that print it. */
+uint32_t t0_gemm_config_estimated_vgprs(const t0_gemm_config* cfg);
+/* GemmConfig::is_feasible() (gemm_gen.rs:203-213): 1 when this library can run the config. */
+int t0_gemm_config_is_feasible(const t0_gemm_config* cfg);
+/* GemmConfig::lds_total() (gemm_gen.rs:168-170): shared memory of the B200 pipeline for this config. */
+uint32_t t0_gemm_config_lds_total(const t0_gemm_config* cfg);
+/* sweep_configs() / standard_configs() (gemm_gen.rs:239-251,407-427): fills up
+ * to `cap` entries, returns the total count. */
+int t0_sweep_configs(t0_gemm_config* out, int cap);
+int t0_standard_configs(t0_gemm_config* out, int cap);
+
+/* ------------------------------------------------- selection (a6, a7, a8) */
+/* auto_select(m, k, n) (gemm_gen.rs:340-342 -> cost_model.rs:660-668). Argument order (m, k, n). */
+int t0_auto_select(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out);
+/* auto_select_legacy(m, k, n) (gemm_gen.rs:351-404): the hand-tuned table, verbatim semantics. */
+int t0_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out);
+/* auto_select_backward_data / _weight (gemm_gen.rs:510-549) */
+int t0_auto_select_backward_data(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0_gemm_config* out);
+int t0_auto_select_backward_weight(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0_gemm_config* out);
+/* cost_model::auto_schedule_gemm (cost_model.rs:464-534): ranked candidates for
+ * (m, n, k) with their predicted TFLOP/s; returns the number written (<= cap). */
+int t0_auto_schedule_gemm(uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* out, double* pred_tflops, int cap);
+/* prefill_spec_cache (prefill_spec_cache.rs:55-76,79-113,125-138) */
+int t0_cached_auto_select(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out);
+int t0_cached_auto_select_backward_data(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0_gemm_config* out);
+int t0_cached_auto_select_backward_weight(uint32_t m, uint32_t n_orig, uint32_t k_orig, t0_gemm_config* out);
+int t0_prewarm_cache(const uint32_t* mkn_triples, size_t n_triples);
+void t0_clear_cache(void);
+size_t t0_cache_size(void);
+
+/* ------------------------------------------------------- grids (a5) */
+/* compute_grid / compute_grid_split_k / compute_grid_auto (gemm_gen.rs:308-329,430-437):
+ * grid in THREADS: swap_grid ? (tiles_n*wg_size, tiles_m[*sk]) : (tiles_m*wg_size, tiles_n[*sk]). */
+int t0_compute_grid(const t0_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t* gx, uint32_t* gy);
+int t0_compute_grid_split_k(const t0_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t split_k, uint32_t* gx, uint32_t* gy);
+int t0_compute_grid_auto(const t0_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t* gx, uint32_t* gy);
+/* compute_grid_backward_data / _weight (gemm_gen.rs:533-536,567-570) */
+int t0_compute_grid_backward_data(const t0_gemm_config* cfg, uint32_t m, uint32_t k_orig, uint32_t* gx, uint32_t* gy);
+int t0_compute_grid_backward_weight(const t0_gemm_config* cfg, uint32_t n_orig, uint32_t k_orig, uint32_t* gx, uint32_t* gy);
+
+/* ------------------------------------------------------- kernargs (a9) */
+/* build_kernargs(x, wt, y, k, n, m, cfg) -> [u8;40] (gemm_gen.rs:442-458). Argument order kept. */
+int t0_build_kernargs(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                      const t0_gemm_config* cfg, uint8_t out[40]);
+/* build_kernargs_with_bias(..., bias) -> [u8;48] (gemm_gen.rs:466-484) */
+int t0_build_kernargs_with_bias(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                                const t0_gemm_config* cfg, uint64_t bias, uint8_t out[48]);
+/* build_kernargs_backward_data / _weight (gemm_gen.rs:523-530,557-564) */
+int t0_build_kernargs_backward_data(uint64_t dy, uint64_t w, uint64_t dx, uint32_t m, uint32_t n_orig, uint32_t k_orig,
+                                    const t0_gemm_config* cfg, uint8_t out[40]);
+int t0_build_kernargs_backward_weight(uint64_t dy_t, uint64_t x_t, uint64_t dw, uint32_t m, uint32_t n_orig, uint32_t k_orig,
+                                      const t0_gemm_config* cfg, uint8_t out[40]);
+
+/* ------------------------------------------------------- TileGemm (a11, a13) */
+/* src/t0/tile_ir.rs:41-62 EpilogueOp (TileIR chain) */
+enum { T0_TEPI_BIAS_ADD = 0, T0_TEPI_SCALE = 1, T0_TEPI_RELU = 2, T0_TEPI_SILU = 3,
+       T0_TEPI_GELU = 4, T0_TEPI_ABS = 5, T0_TEPI_NEG = 6, T0_TEPI_CLAMP = 7 };
+#define T0_TILE_MAX_EPILOGUE 8
+/* src/t0/tile_ir.rs:109-152 TileGemm.  waves_per_wg 0 = None; wmma_format 0 = BF16_F32
+ * (the only format this library computes). */
+typedef struct t0_tile_gemm {
+    uint32_t tile_m, tile_n, tile_k;
+    uint8_t wgp_mode, double_buffer, triple_buffer, swap_grid;
+    uint32_t split_k;
+    uint8_t transpose, acc_swap, persistent, n_epilogue;
+    uint8_t epilogue[T0_TILE_MAX_EPILOGUE];
+    uint32_t waves_per_wg;
+    uint32_t wmma_format;
+} t0_tile_gemm;
+/* TileGemm::tile_128x64_k16() ... (tile_ir.rs:156-604); `preset` is the Rust constructor name. */
+int t0_tile_gemm_preset(const char* preset, t0_tile_gemm* out);
+/* TileGemm::name() (tile_ir.rs:677-701) */
+int t0_tile_gemm_name(const t0_tile_gemm* spec, char* buf, size_t buf_len);
+/* TileGemm::wg_size() / lds_total() (tile_ir.rs:607-651) — the reference's arithmetic, kept for grid maths */
+uint32_t t0_tile_gemm_wg_size(const t0_tile_gemm* spec);
+uint32_t t0_tile_gemm_lds_total(const t0_tile_gemm* spec);
+/* tile_auto_select(m, k, n, transpose) (tile_ir.rs:740-870) */
+int t0_tile_auto_select(uint32_t m, uint32_t k, uint32_t n, int transpose, t0_tile_gemm* out);
+/* tile_ir::build_kernargs_m (tile_ir.rs:4595-4634): 44 bytes (64 in persistent mode);
+ * returns the length through out_len.  Extra epilogue arguments are appended in the
+ * order bias u64, scale f32, clamp_min f32, clamp_max f32 when the chain uses them
+ * (tile_ir.rs:1015-1026). */
+int t0_tile_build_kernargs_m(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                             const t0_tile_gemm* spec, uint8_t* out, size_t cap, size_t* out_len);
+int t0_tile_build_kernargs_epilogue(uint64_t x, uint64_t wt, uint64_t y, uint32_t k, uint32_t n, uint32_t m,
+                                    const t0_tile_gemm* spec, uint64_t bias, float scale, float clamp_min, float clamp_max,
+                                    uint8_t* out, size_t cap, size_t* out_len);
+/* tile_ir::compute_grid(&spec, m, n) -> [u32;3] (tile_ir.rs:4645-4665) */
+int t0_tile_compute_grid(const t0_tile_gemm* spec, uint32_t m, uint32_t n, uint32_t grid[3]);
+/* tile_ir::f32_to_bf16 (truncate) / bf16_to_f32 (tile_ir.rs:4677-4683) */
+uint16_t t0_f32_to_bf16(float v);
+float t0_bf16_to_f32(uint16_t v);
+
+/* ------------------------------------------------------- runtime (a17) */
+typedef struct t0_runtime t0_runtime;   /* GpuRuntime   src/ignis/gpu_context.rs:99-119 */
+typedef struct t0_buffer t0_buffer;     /* GpuBuffer    src/kfd/buffer.rs:9-123        */
+typedef struct t0_kernel t0_kernel;     /* GpuKernel    src/kfd/kernel.rs:8-19         */
+
+/* GpuRuntime::new() (gpu_context.rs:151-171): one CUDA stream (the in-order AQL queue), a buffer pool, a kernel cache. */
+int t0_rt_new(int device, t0_runtime** out);
+void t0_rt_free(t0_runtime* rt);
+/* is_poisoned / mark_poisoned (gpu_context.rs:190-198) */
+int t0_rt_is_poisoned(const t0_runtime* rt);
+void t0_rt_mark_poisoned(t0_runtime* rt);
+/* queue.synchronize() / wait_idle() (src/kfd/aql.rs:473): drain the stream; a device-side failure poisons the runtime. */
+int t0_rt_synchronize(t0_runtime* rt);
+int t0_rt_wait_idle(t0_runtime* rt);
+/* the CUDA stream handle (cudaStream_t) and device ordinal, for callers that time or order work themselves */
+void* t0_rt_stream(const t0_runtime* rt);
+int t0_rt_device(const t0_runtime* rt);
+int t0_rt_sm_count(const t0_runtime* rt);
+
+/* rt.alloc / alloc_zero / alloc_f32 / recycle (gpu_context.rs:508-530) with BufferPool semantics
+ * (gpu_context.rs:31-92): sizes rounded to 4 KiB, recycled buffers are zeroed on hand-out. */
+int t0_rt_alloc(t0_runtime* rt, size_t n_bytes, t0_buffer** out);
+int t0_rt_alloc_zero(t0_runtime* rt, size_t n_bytes, t0_buffer** out);
+int t0_rt_alloc_f32(t0_runtime* rt, size_t n_elems, t0_buffer** out);
+void t0_rt_recycle(t0_runtime* rt, t0_buffer* buf);
+size_t t0_rt_pool_cached_bytes(const t0_runtime* rt);
+void t0_rt_pool_clear(t0_runtime* rt);
+/* read_f32 / write_f32 / upload_f32 (gpu_context.rs:535-558) */
+int t0_rt_read_f32(t0_runtime* rt, const t0_buffer* buf, size_t n, float* out);
+int t0_rt_write_f32(t0_runtime* rt, t0_buffer* buf, const float* data, size_t n);
+int t0_rt_upload_f32(t0_runtime* rt, const float* data, size_t n, t0_buffer** out);
+
+/* GpuBuffer::{write, read, write_bytes, read_bytes, zero, gpu_addr, size} (src/kfd/buffer.rs:23-109), bounds-checked;
+ * Drop (buffer.rs:125-146) = t0_buf_free. */
+int t0_buf_write(t0_buffer* buf, const void* data, size_t len);
+int t0_buf_read(const t0_buffer* buf, void* out, size_t len);
+int t0_buf_write_bytes(t0_buffer* buf, size_t offset, const void* data, size_t len);
+int t0_buf_read_bytes(const t0_buffer* buf, size_t offset, void* out, size_t len);
+int t0_buf_zero(t0_buffer* buf);
+uint64_t t0_buf_gpu_addr(const t0_buffer* buf);
+size_t t0_buf_size(const t0_buffer* buf);
+void t0_buf_free(t0_buffer* buf);
+
+/* generate(&cfg) + rt.ensure_kernel_t0(name, builder, wg, lds) (gemm_gen.rs:261-297, gpu_context.rs:212-259):
+ * looks up the precompiled sm_100a kernel for the config, cached by cfg.name(). */
+int t0_rt_ensure_gemm_kernel(t0_runtime* rt, const t0_gemm_config* cfg, t0_kernel** out);
+/* lower_gemm(&spec) + ensure_kernel_t0 (tile_ir.rs:887, gpu_context.rs:212) */
+int t0_rt_ensure_tile_kernel(t0_runtime* rt, const t0_tile_gemm* spec, t0_kernel** out);
+/* GpuKernel.kernarg_size (src/kfd/kernel.rs:8-19) and the cache key */
+uint32_t t0_kernel_kernarg_size(const t0_kernel* k);
+const char* t0_kernel_name(const t0_kernel* k);
+size_t t0_rt_kernel_cache_size(const t0_runtime* rt);
+
+/* rt.dispatch(&kernel, grid, kernargs) (gpu_context.rs:305-356): submit + wait; checks poison, asserts
+ * kernargs.len() == kernel.kernarg_size, decodes the blob, validates every pointer against the live
+ * allocations of this runtime, launches, waits; a device failure poisons the runtime.
+ * The 40/48-byte gemm_gen blob carries no M: M = tiles_m * tile_m is taken from the grid, as the
+ * reference kernel implicitly does (every row of every launched tile is written). */
+int t0_rt_dispatch(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len);
+/* dispatch_async (gpu_context.rs:400-410): submit only; slot index through out_slot (may be NULL) */
+int t0_rt_dispatch_async(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len, size_t* out_slot);
+/* dispatch_bench (gpu_context.rs:363-374): submit + wait without validation */
+int t0_rt_dispatch_bench(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len);
+/* number of kernels this runtime has launched (all kinds) since creation */
+uint64_t t0_rt_launch_count(const t0_runtime* rt);
+/* CUDA-event stopwatch on the runtime's stream: start records an event, stop records another, waits and returns ms */
+int t0_rt_timer_start(t0_runtime* rt);
+int t0_rt_timer_stop(t0_runtime* rt, float* ms);
+
+/* ------------------------------------------------------- direct GEMM entry */
+/* The launch that generate()+dispatch() amounts to, with explicit arguments instead of a kernarg blob.
+ * y[M,N] (f32, or bf16 when out_bf16) = x[M,K] (bf16) * op(b): transpose T0_NT: b is [N,K]; T0_NN: b is [K,N].
+ * split_k > 1 with planes != 0 writes split_k f32 planes of M*N (gemm_gen.rs:447-448); with planes == 0 the
+ * partial sums are reduced on the device in split order into y.  epilogue as t0_gemm_config.epilogue. */
+typedef struct t0_gemm_args {
+    uint64_t x, b, y, bias;
+    uint32_t m, n, k;
+    uint32_t tile_n;        /* 0 = choose; else 32/64/128/256 */
+    uint32_t split_k;       /* 0/1 = none */
+    uint8_t transpose, epilogue, out_bf16, planes;
+    uint8_t swap_grid, pair_cta, _pad[2];
+    /* TileIR epilogue chain (used when n_tile_epilogue > 0; epilogue above is then ignored) */
+    uint8_t n_tile_epilogue;
+    uint8_t tile_epilogue[T0_TILE_MAX_EPILOGUE];
+    uint8_t _pad2[3];
+    float scale, clamp_min, clamp_max;
+} t0_gemm_args;
+int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
+
+/* ------------------------------------------------------- seeded inputs */
+/* Device-side generators for benchmark-sized inputs: element i of the stream (seed) gets the same bits as the
+ * host generator of the test oracle, so any sub-range can be checked on the CPU without a full download. */
+int t0_fill_uniform_bf16(t0_runtime* rt, uint64_t dst, uint64_t n, uint64_t seed, uint64_t first_index);
+int t0_fill_u32(t0_runtime* rt, uint64_t dst, uint64_t n, uint64_t seed, uint64_t first_index);
+int t0_fill_range_bf16(t0_runtime* rt, uint64_t dst, uint64_t n, uint64_t seed, uint64_t first_index, float lo, float hi);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T0B200_H */

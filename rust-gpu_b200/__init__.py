@@ -1,0 +1,581 @@
+"""Host-side mirror of the T0-GPU GEMM API over the t0b200 C ABI (ctypes).
+
+The names follow the reference crate (clearnature/rust-gpu): ``GemmConfig``, ``auto_select``,
+``compute_grid_auto``, ``build_kernargs``, ``TileGemm``, ``GpuRuntime``, ``GpuBuffer`` ... so that
+tests read like the reference's own.  This module is a binding only: every computation happens in
+``lib/libt0b200.so`` (hand-written sm_100a kernels).  There is no CPU fallback — if the library is
+missing the import of any compute entry point raises.
+
+The package directory name contains a hyphen; import it with
+``importlib.import_module("rust-gpu_b200")``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libt0b200.so")
+HEADER_PATH = os.path.join(_HERE, "..", "include", "t0b200.h")
+
+NT, NN = 0, 1
+EPI_STORE_F32, EPI_BIAS_ADD_STORE_F32, EPI_BIAS_ADD_RELU_STORE_F32 = 0, 1, 2
+TEPI = {"bias": 0, "scale": 1, "relu": 2, "silu": 3, "gelu": 4, "abs": 5, "neg": 6, "clamp": 7}
+ERR_NAMES = {0: "OK", 1: "INVALID", 2: "CUDA", 3: "POISONED", 4: "TIMEOUT", 5: "BOUNDS", 6: "UNSUPPORTED", 7: "IO"}
+
+
+class T0Error(RuntimeError):
+    """A failing C-ABI call: the Rust side's ``Err(String)`` / panic."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{ERR_NAMES.get(code, code)}] {message}")
+        self.code = code
+        self.message = message
+
+
+def build(force: bool = False) -> str:
+    """Compile the CUDA library in-tree (nvcc, sm_100a)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_t0b200_build", os.path.join(_HERE, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build(force=force)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded C-ABI library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise T0Error(2, f"{LIB_PATH} is missing: build it with `python rust-gpu_b200/build.py` "
+                             "(there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _declare(_lib)
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise T0Error(rc, lib().t0_last_error().decode())
+
+
+# --------------------------------------------------------------------------- records
+
+class GemmConfig(C.Structure):
+    """``GemmConfig`` (src/t0/gemm_gen.rs:55-84)."""
+    _fields_ = [("tile_m", C.c_uint32), ("tile_n", C.c_uint32), ("tile_k", C.c_uint32), ("wg_size", C.c_uint32),
+                ("use_lds", C.c_uint8), ("double_buffer", C.c_uint8), ("_pad0", C.c_uint8 * 2),
+                ("split_k", C.c_uint32), ("lds_pad", C.c_uint32), ("n_col_passes", C.c_uint32),
+                ("swap_grid", C.c_uint8), ("wgp_mode", C.c_uint8), ("transpose", C.c_uint8), ("epilogue", C.c_uint8)]
+
+    @classmethod
+    def preset(cls, name: str) -> "GemmConfig":
+        c = cls()
+        _check(lib().t0_gemm_config_preset(name.encode(), C.byref(c)))
+        return c
+
+    def copy(self, **kw) -> "GemmConfig":
+        c = GemmConfig.from_buffer_copy(self)
+        for k, v in kw.items():
+            setattr(c, k, v)
+        return c
+
+    def name(self) -> str:
+        buf = C.create_string_buffer(128)
+        _check(lib().t0_gemm_config_name(C.byref(self), buf, 128))
+        return buf.value.decode()
+
+    def is_feasible(self) -> bool:
+        return bool(lib().t0_gemm_config_is_feasible(C.byref(self)))
+
+    def estimated_vgprs(self) -> int:
+        return int(lib().t0_gemm_config_estimated_vgprs(C.byref(self)))
+
+    def lds_total(self) -> int:
+        return int(lib().t0_gemm_config_lds_total(C.byref(self)))
+
+    def split(self) -> int:
+        return self.split_k if self.split_k > 1 else 1
+
+
+for _n in ["tile_16x64_k16", "tile_32x64_direct", "tile_32x64_k16", "tile_32x64_k32", "tile_32x128_k16", "tile_64x64_k16",
+           "tile_64x64_k32", "tile_128x64_k16", "tile_64x128_k16", "tile_128x64_k32", "tile_128x128_k16", "tile_64x64_k64",
+           "tile_128x128_2pass", "tile_64x128_2pass"]:
+    setattr(GemmConfig, _n, classmethod(lambda cls, _n=_n: cls.preset(_n)))
+
+
+class TileGemm(C.Structure):
+    """``TileGemm`` (src/t0/tile_ir.rs:109-152)."""
+    _fields_ = [("tile_m", C.c_uint32), ("tile_n", C.c_uint32), ("tile_k", C.c_uint32),
+                ("wgp_mode", C.c_uint8), ("double_buffer", C.c_uint8), ("triple_buffer", C.c_uint8), ("swap_grid", C.c_uint8),
+                ("split_k", C.c_uint32),
+                ("transpose", C.c_uint8), ("acc_swap", C.c_uint8), ("persistent", C.c_uint8), ("n_epilogue", C.c_uint8),
+                ("epilogue", C.c_uint8 * 8), ("waves_per_wg", C.c_uint32), ("wmma_format", C.c_uint32)]
+
+    @classmethod
+    def preset(cls, name: str) -> "TileGemm":
+        s = cls()
+        _check(lib().t0_tile_gemm_preset(name.encode(), C.byref(s)))
+        return s
+
+    def copy(self, **kw) -> "TileGemm":
+        s = TileGemm.from_buffer_copy(self)
+        for k, v in kw.items():
+            setattr(s, k, v)
+        return s
+
+    def with_epilogue(self, ops: list[str]) -> "TileGemm":
+        s = self.copy()
+        s.n_epilogue = len(ops)
+        for i, o in enumerate(ops):
+            s.epilogue[i] = TEPI[o]
+        return s
+
+    def name(self) -> str:
+        buf = C.create_string_buffer(160)
+        _check(lib().t0_tile_gemm_name(C.byref(self), buf, 160))
+        return buf.value.decode()
+
+    def wg_size(self) -> int:
+        return int(lib().t0_tile_gemm_wg_size(C.byref(self)))
+
+    def lds_total(self) -> int:
+        return int(lib().t0_tile_gemm_lds_total(C.byref(self)))
+
+    def n_waves(self) -> int:
+        return self.waves_per_wg or self.tile_m // 32
+
+    def rows_per_wave(self) -> int:
+        return self.tile_m // self.n_waves()
+
+    def n_row_blocks(self) -> int:
+        return self.rows_per_wave() // 16
+
+    def k_sub_steps(self) -> int:
+        return self.tile_k // 16
+
+    def lds_per_buffer(self) -> int:
+        return self.tile_m * self.tile_k * 2 + self.tile_n * self.tile_k * 2
+
+
+TILE_PRESETS = ["tile_128x64_k16", "tile_64x64_k16", "tile_64x64_k32", "tile_64x64_k64", "tile_32x64_k16", "tile_128x64_k32",
+                "tile_64x128_k32", "tile_64x128_k16", "tile_128x128_k16", "tile_128x128_k32", "tile_128x128_k48",
+                "tile_128x128_k16_swap", "tile_128x128_k32_swap", "tile_256x64_k32_wgp", "tile_256x64_k64_wgp",
+                "tile_128x128_k64", "tile_128x64_k64", "tile_32x32_k16", "tile_32x128_k16", "tile_128x32_k16",
+                "tile_64x256_k32", "tile_128x256_k32", "tile_256x128_k32", "tile_persistent_decode",
+                "tile_persistent_128x64_k32", "tile_persistent_256x128_k32"]
+for _n in TILE_PRESETS:
+    setattr(TileGemm, _n, classmethod(lambda cls, _n=_n: cls.preset(_n)))
+
+
+class GemmArgs(C.Structure):
+    """``t0_gemm_args``: explicit-argument GEMM launch."""
+    _fields_ = [("x", C.c_uint64), ("b", C.c_uint64), ("y", C.c_uint64), ("bias", C.c_uint64),
+                ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32), ("tile_n", C.c_uint32), ("split_k", C.c_uint32),
+                ("transpose", C.c_uint8), ("epilogue", C.c_uint8), ("out_bf16", C.c_uint8), ("planes", C.c_uint8),
+                ("swap_grid", C.c_uint8), ("pair_cta", C.c_uint8), ("_pad", C.c_uint8 * 2),
+                ("n_tile_epilogue", C.c_uint8), ("tile_epilogue", C.c_uint8 * 8), ("_pad2", C.c_uint8 * 3),
+                ("scale", C.c_float), ("clamp_min", C.c_float), ("clamp_max", C.c_float)]
+
+
+# --------------------------------------------------------------------------- selection / grids / kernargs
+
+def auto_select(m: int, k: int, n: int) -> GemmConfig:
+    """``auto_select(m, k, n)`` (gemm_gen.rs:340) — note the (m, k, n) order."""
+    c = GemmConfig()
+    _check(lib().t0_auto_select(m, k, n, C.byref(c)))
+    return c
+
+
+def auto_select_legacy(m: int, k: int, n: int) -> GemmConfig:
+    c = GemmConfig()
+    _check(lib().t0_auto_select_legacy(m, k, n, C.byref(c)))
+    return c
+
+
+def cached_auto_select(m: int, k: int, n: int) -> GemmConfig:
+    c = GemmConfig()
+    _check(lib().t0_cached_auto_select(m, k, n, C.byref(c)))
+    return c
+
+
+def prewarm_cache(dims: list[tuple[int, int, int]]) -> None:
+    arr = (C.c_uint32 * (3 * len(dims)))(*[v for d in dims for v in d])
+    _check(lib().t0_prewarm_cache(arr, len(dims)))
+
+
+def clear_cache() -> None:
+    lib().t0_clear_cache()
+
+
+def cache_size() -> int:
+    return int(lib().t0_cache_size())
+
+
+def auto_schedule_gemm(m: int, n: int, k: int, cap: int = 64) -> list[tuple[GemmConfig, float]]:
+    cfgs = (GemmConfig * cap)()
+    tf = (C.c_double * cap)()
+    cnt = lib().t0_auto_schedule_gemm(m, n, k, cfgs, tf, cap)
+    return [(GemmConfig.from_buffer_copy(cfgs[i]), tf[i]) for i in range(cnt)]
+
+
+def compute_grid(cfg: GemmConfig, m: int, n: int) -> tuple[int, int]:
+    gx, gy = C.c_uint32(), C.c_uint32()
+    _check(lib().t0_compute_grid(C.byref(cfg), m, n, C.byref(gx), C.byref(gy)))
+    return gx.value, gy.value
+
+
+def compute_grid_split_k(cfg: GemmConfig, m: int, n: int, split_k: int) -> tuple[int, int]:
+    gx, gy = C.c_uint32(), C.c_uint32()
+    _check(lib().t0_compute_grid_split_k(C.byref(cfg), m, n, split_k, C.byref(gx), C.byref(gy)))
+    return gx.value, gy.value
+
+
+def compute_grid_auto(cfg: GemmConfig, m: int, n: int) -> tuple[int, int]:
+    gx, gy = C.c_uint32(), C.c_uint32()
+    _check(lib().t0_compute_grid_auto(C.byref(cfg), m, n, C.byref(gx), C.byref(gy)))
+    return gx.value, gy.value
+
+
+def build_kernargs(x: int, wt: int, y: int, k: int, n: int, m: int, cfg: GemmConfig) -> bytes:
+    """``build_kernargs(x, wt, y, k, n, m, &cfg) -> [u8; 40]`` (gemm_gen.rs:442-458)."""
+    out = (C.c_uint8 * 40)()
+    _check(lib().t0_build_kernargs(x, wt, y, k, n, m, C.byref(cfg), out))
+    return bytes(out)
+
+
+def build_kernargs_with_bias(x: int, wt: int, y: int, k: int, n: int, m: int, cfg: GemmConfig, bias: int) -> bytes:
+    out = (C.c_uint8 * 48)()
+    _check(lib().t0_build_kernargs_with_bias(x, wt, y, k, n, m, C.byref(cfg), bias, out))
+    return bytes(out)
+
+
+def tile_auto_select(m: int, k: int, n: int, transpose: int = NT) -> TileGemm:
+    s = TileGemm()
+    _check(lib().t0_tile_auto_select(m, k, n, transpose, C.byref(s)))
+    return s
+
+
+def tile_build_kernargs_m(x: int, wt: int, y: int, k: int, n: int, m: int, spec: TileGemm) -> bytes:
+    out = (C.c_uint8 * 96)()
+    ln = C.c_size_t()
+    _check(lib().t0_tile_build_kernargs_m(x, wt, y, k, n, m, C.byref(spec), out, 96, C.byref(ln)))
+    return bytes(out[: ln.value])
+
+
+def tile_build_kernargs_epilogue(x: int, wt: int, y: int, k: int, n: int, m: int, spec: TileGemm, bias: int = 0,
+                                 scale: float = 1.0, clamp_min: float = 0.0, clamp_max: float = 0.0) -> bytes:
+    out = (C.c_uint8 * 96)()
+    ln = C.c_size_t()
+    _check(lib().t0_tile_build_kernargs_epilogue(x, wt, y, k, n, m, C.byref(spec), bias, scale, clamp_min, clamp_max,
+                                                 out, 96, C.byref(ln)))
+    return bytes(out[: ln.value])
+
+
+def tile_compute_grid(spec: TileGemm, m: int, n: int) -> list[int]:
+    g = (C.c_uint32 * 3)()
+    _check(lib().t0_tile_compute_grid(C.byref(spec), m, n, g))
+    return list(g)
+
+
+def f32_to_bf16(v: float) -> int:
+    return int(lib().t0_f32_to_bf16(v))
+
+
+def bf16_to_f32(v: int) -> float:
+    return float(lib().t0_bf16_to_f32(v))
+
+
+# --------------------------------------------------------------------------- runtime
+
+class GpuBuffer:
+    """``GpuBuffer`` (src/kfd/buffer.rs:9-123)."""
+
+    def __init__(self, handle, rt: "GpuRuntime"):
+        self._h = handle
+        self._rt = rt
+
+    def gpu_addr(self) -> int:
+        return int(lib().t0_buf_gpu_addr(self._h))
+
+    @property
+    def size(self) -> int:
+        return int(lib().t0_buf_size(self._h))
+
+    def write(self, data) -> None:
+        a = np.ascontiguousarray(data)
+        _check(lib().t0_buf_write(self._h, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def write_bytes(self, offset: int, data) -> None:
+        a = np.ascontiguousarray(data)
+        _check(lib().t0_buf_write_bytes(self._h, offset, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def read(self, nbytes: int, dtype=np.uint8) -> np.ndarray:
+        out = np.empty(nbytes, dtype=np.uint8)
+        _check(lib().t0_buf_read(self._h, out.ctypes.data_as(C.c_void_p), nbytes))
+        return out.view(dtype)
+
+    def read_bytes(self, offset: int, nbytes: int, dtype=np.uint8) -> np.ndarray:
+        out = np.empty(nbytes, dtype=np.uint8)
+        _check(lib().t0_buf_read_bytes(self._h, offset, out.ctypes.data_as(C.c_void_p), nbytes))
+        return out.view(dtype)
+
+    def zero(self) -> None:
+        _check(lib().t0_buf_zero(self._h))
+
+    def free(self) -> None:
+        if self._h:
+            lib().t0_buf_free(self._h)
+            self._h = None
+
+
+class GpuKernel:
+    def __init__(self, handle):
+        self._h = handle
+
+    @property
+    def kernarg_size(self) -> int:
+        return int(lib().t0_kernel_kernarg_size(self._h))
+
+    @property
+    def name(self) -> str:
+        return lib().t0_kernel_name(self._h).decode()
+
+
+class GpuRuntime:
+    """``GpuRuntime`` (src/ignis/gpu_context.rs:99-597): stream, buffer pool, kernel cache, poison flag."""
+
+    def __init__(self, device: int = 0):
+        h = C.c_void_p()
+        _check(lib().t0_rt_new(device, C.byref(h)))
+        self._h = h
+
+    @classmethod
+    def new(cls, device: int = 0) -> "GpuRuntime":
+        return cls(device)
+
+    def close(self) -> None:
+        if self._h:
+            lib().t0_rt_free(self._h)
+            self._h = None
+
+    def is_poisoned(self) -> bool:
+        return bool(lib().t0_rt_is_poisoned(self._h))
+
+    def mark_poisoned(self) -> None:
+        lib().t0_rt_mark_poisoned(self._h)
+
+    def synchronize(self) -> None:
+        _check(lib().t0_rt_synchronize(self._h))
+
+    wait_idle = synchronize
+
+    def stream(self) -> int:
+        return int(lib().t0_rt_stream(self._h) or 0)
+
+    def sm_count(self) -> int:
+        return int(lib().t0_rt_sm_count(self._h))
+
+    def launch_count(self) -> int:
+        return int(lib().t0_rt_launch_count(self._h))
+
+    def alloc(self, n_bytes: int) -> GpuBuffer:
+        h = C.c_void_p()
+        _check(lib().t0_rt_alloc(self._h, n_bytes, C.byref(h)))
+        return GpuBuffer(h, self)
+
+    def alloc_zero(self, n_bytes: int) -> GpuBuffer:
+        h = C.c_void_p()
+        _check(lib().t0_rt_alloc_zero(self._h, n_bytes, C.byref(h)))
+        return GpuBuffer(h, self)
+
+    def alloc_f32(self, n: int) -> GpuBuffer:
+        h = C.c_void_p()
+        _check(lib().t0_rt_alloc_f32(self._h, n, C.byref(h)))
+        return GpuBuffer(h, self)
+
+    def recycle(self, buf: GpuBuffer) -> None:
+        lib().t0_rt_recycle(self._h, buf._h)
+        buf._h = None
+
+    def pool_cached_bytes(self) -> int:
+        return int(lib().t0_rt_pool_cached_bytes(self._h))
+
+    def upload(self, data) -> GpuBuffer:
+        a = np.ascontiguousarray(data)
+        b = self.alloc(max(a.nbytes, 1))
+        if a.nbytes:
+            b.write(a)
+        return b
+
+    def read_f32(self, buf: GpuBuffer, n: int) -> np.ndarray:
+        out = np.empty(n, dtype=np.float32)
+        _check(lib().t0_rt_read_f32(self._h, buf._h, n, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def write_f32(self, buf: GpuBuffer, data) -> None:
+        a = np.ascontiguousarray(data, dtype=np.float32)
+        _check(lib().t0_rt_write_f32(self._h, buf._h, a.ctypes.data_as(C.c_void_p), a.size))
+
+    def upload_f32(self, data) -> GpuBuffer:
+        a = np.ascontiguousarray(data, dtype=np.float32)
+        h = C.c_void_p()
+        _check(lib().t0_rt_upload_f32(self._h, a.ctypes.data_as(C.c_void_p), a.size, C.byref(h)))
+        return GpuBuffer(h, self)
+
+    def ensure_kernel_t0(self, spec) -> GpuKernel:
+        """``ensure_kernel_t0(name, || generate(&cfg) / lower_gemm(&spec), ..)`` (gpu_context.rs:212-259)."""
+        h = C.c_void_p()
+        if isinstance(spec, GemmConfig):
+            _check(lib().t0_rt_ensure_gemm_kernel(self._h, C.byref(spec), C.byref(h)))
+        else:
+            _check(lib().t0_rt_ensure_tile_kernel(self._h, C.byref(spec), C.byref(h)))
+        return GpuKernel(h)
+
+    def kernel_cache_size(self) -> int:
+        return int(lib().t0_rt_kernel_cache_size(self._h))
+
+    def dispatch(self, kernel: GpuKernel, grid, kernargs: bytes) -> None:
+        g = (C.c_uint32 * 3)(*grid)
+        ka = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
+        _check(lib().t0_rt_dispatch(self._h, kernel._h, g, ka, len(kernargs)))
+
+    def dispatch_async(self, kernel: GpuKernel, grid, kernargs: bytes) -> int:
+        g = (C.c_uint32 * 3)(*grid)
+        ka = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
+        slot = C.c_size_t()
+        _check(lib().t0_rt_dispatch_async(self._h, kernel._h, g, ka, len(kernargs), C.byref(slot)))
+        return slot.value
+
+    def dispatch_bench(self, kernel: GpuKernel, grid, kernargs: bytes) -> None:
+        g = (C.c_uint32 * 3)(*grid)
+        ka = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
+        _check(lib().t0_rt_dispatch_bench(self._h, kernel._h, g, ka, len(kernargs)))
+
+    def timer_start(self) -> None:
+        _check(lib().t0_rt_timer_start(self._h))
+
+    def timer_stop(self) -> float:
+        ms = C.c_float()
+        _check(lib().t0_rt_timer_stop(self._h, C.byref(ms)))
+        return ms.value
+
+    def gemm(self, x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
+             transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False, swap_grid: bool = True,
+             tile_epilogue: list[str] | None = None, scale: float = 1.0, clamp_min: float = 0.0,
+             clamp_max: float = 0.0) -> None:
+        """Explicit-argument launch (``t0_gemm_launch``); device addresses as integers."""
+        a = GemmArgs()
+        a.x, a.b, a.y, a.bias = x, b, y, bias
+        a.m, a.n, a.k, a.tile_n, a.split_k = m, n, k, tile_n, split_k
+        a.transpose, a.epilogue, a.out_bf16, a.planes, a.swap_grid = transpose, epilogue, int(out_bf16), int(planes), int(swap_grid)
+        ops = tile_epilogue or []
+        a.n_tile_epilogue = len(ops)
+        for i, o in enumerate(ops):
+            a.tile_epilogue[i] = TEPI[o]
+        a.scale, a.clamp_min, a.clamp_max = scale, clamp_min, clamp_max
+        _check(lib().t0_gemm_launch(self._h, C.byref(a)))
+
+    def fill_uniform_bf16(self, dst: int, n: int, seed: int, first_index: int = 0) -> None:
+        _check(lib().t0_fill_uniform_bf16(self._h, dst, n, seed, first_index))
+
+    def fill_u32(self, dst: int, n: int, seed: int, first_index: int = 0) -> None:
+        _check(lib().t0_fill_u32(self._h, dst, n, seed, first_index))
+
+    def fill_range_bf16(self, dst: int, n: int, seed: int, lo: float, hi: float, first_index: int = 0) -> None:
+        _check(lib().t0_fill_range_bf16(self._h, dst, n, seed, first_index, lo, hi))
+
+
+# --------------------------------------------------------------------------- ctypes signatures
+
+def _declare(L: C.CDLL) -> None:
+    u8p, u32, u64, sz, vp, i32 = C.POINTER(C.c_uint8), C.c_uint32, C.c_uint64, C.c_size_t, C.c_void_p, C.c_int
+    cfgp, tilep, u32p = C.POINTER(GemmConfig), C.POINTER(TileGemm), C.POINTER(C.c_uint32)
+
+    def sig(name, restype, *argtypes):
+        fn = getattr(L, name)
+        fn.restype = restype
+        fn.argtypes = list(argtypes)
+
+    sig("t0_last_error", C.c_char_p)
+    sig("t0_version", i32)
+    sig("t0_gemm_config_preset", i32, C.c_char_p, cfgp)
+    sig("t0_gemm_config_name", i32, cfgp, C.c_char_p, sz)
+    sig("t0_gemm_config_estimated_vgprs", u32, cfgp)
+    sig("t0_gemm_config_is_feasible", i32, cfgp)
+    sig("t0_gemm_config_lds_total", u32, cfgp)
+    sig("t0_sweep_configs", i32, cfgp, i32)
+    sig("t0_standard_configs", i32, cfgp, i32)
+    for n in ("t0_auto_select", "t0_auto_select_legacy", "t0_auto_select_backward_data", "t0_auto_select_backward_weight",
+              "t0_cached_auto_select", "t0_cached_auto_select_backward_data", "t0_cached_auto_select_backward_weight"):
+        sig(n, i32, u32, u32, u32, cfgp)
+    sig("t0_auto_schedule_gemm", i32, u32, u32, u32, cfgp, C.POINTER(C.c_double), i32)
+    sig("t0_prewarm_cache", i32, u32p, sz)
+    sig("t0_clear_cache", None)
+    sig("t0_cache_size", sz)
+    sig("t0_compute_grid", i32, cfgp, u32, u32, u32p, u32p)
+    sig("t0_compute_grid_split_k", i32, cfgp, u32, u32, u32, u32p, u32p)
+    sig("t0_compute_grid_auto", i32, cfgp, u32, u32, u32p, u32p)
+    sig("t0_compute_grid_backward_data", i32, cfgp, u32, u32, u32p, u32p)
+    sig("t0_compute_grid_backward_weight", i32, cfgp, u32, u32, u32p, u32p)
+    sig("t0_build_kernargs", i32, u64, u64, u64, u32, u32, u32, cfgp, u8p)
+    sig("t0_build_kernargs_with_bias", i32, u64, u64, u64, u32, u32, u32, cfgp, u64, u8p)
+    sig("t0_build_kernargs_backward_data", i32, u64, u64, u64, u32, u32, u32, cfgp, u8p)
+    sig("t0_build_kernargs_backward_weight", i32, u64, u64, u64, u32, u32, u32, cfgp, u8p)
+    sig("t0_tile_gemm_preset", i32, C.c_char_p, tilep)
+    sig("t0_tile_gemm_name", i32, tilep, C.c_char_p, sz)
+    sig("t0_tile_gemm_wg_size", u32, tilep)
+    sig("t0_tile_gemm_lds_total", u32, tilep)
+    sig("t0_tile_auto_select", i32, u32, u32, u32, i32, tilep)
+    sig("t0_tile_build_kernargs_m", i32, u64, u64, u64, u32, u32, u32, tilep, u8p, sz, C.POINTER(sz))
+    sig("t0_tile_build_kernargs_epilogue", i32, u64, u64, u64, u32, u32, u32, tilep, u64, C.c_float, C.c_float, C.c_float,
+        u8p, sz, C.POINTER(sz))
+    sig("t0_tile_compute_grid", i32, tilep, u32, u32, u32p)
+    sig("t0_f32_to_bf16", C.c_uint16, C.c_float)
+    sig("t0_bf16_to_f32", C.c_float, C.c_uint16)
+    sig("t0_rt_new", i32, i32, C.POINTER(vp))
+    sig("t0_rt_free", None, vp)
+    sig("t0_rt_is_poisoned", i32, vp)
+    sig("t0_rt_mark_poisoned", None, vp)
+    sig("t0_rt_synchronize", i32, vp)
+    sig("t0_rt_wait_idle", i32, vp)
+    sig("t0_rt_stream", vp, vp)
+    sig("t0_rt_device", i32, vp)
+    sig("t0_rt_sm_count", i32, vp)
+    sig("t0_rt_launch_count", u64, vp)
+    sig("t0_rt_timer_start", i32, vp)
+    sig("t0_rt_timer_stop", i32, vp, C.POINTER(C.c_float))
+    sig("t0_rt_alloc", i32, vp, sz, C.POINTER(vp))
+    sig("t0_rt_alloc_zero", i32, vp, sz, C.POINTER(vp))
+    sig("t0_rt_alloc_f32", i32, vp, sz, C.POINTER(vp))
+    sig("t0_rt_recycle", None, vp, vp)
+    sig("t0_rt_pool_cached_bytes", sz, vp)
+    sig("t0_rt_pool_clear", None, vp)
+    sig("t0_rt_read_f32", i32, vp, vp, sz, vp)
+    sig("t0_rt_write_f32", i32, vp, vp, vp, sz)
+    sig("t0_rt_upload_f32", i32, vp, vp, sz, C.POINTER(vp))
+    sig("t0_buf_write", i32, vp, vp, sz)
+    sig("t0_buf_read", i32, vp, vp, sz)
+    sig("t0_buf_write_bytes", i32, vp, sz, vp, sz)
+    sig("t0_buf_read_bytes", i32, vp, sz, vp, sz)
+    sig("t0_buf_zero", i32, vp)
+    sig("t0_buf_gpu_addr", u64, vp)
+    sig("t0_buf_size", sz, vp)
+    sig("t0_buf_free", None, vp)
+    sig("t0_rt_ensure_gemm_kernel", i32, vp, cfgp, C.POINTER(vp))
+    sig("t0_rt_ensure_tile_kernel", i32, vp, tilep, C.POINTER(vp))
+    sig("t0_kernel_kernarg_size", u32, vp)
+    sig("t0_kernel_name", C.c_char_p, vp)
+    sig("t0_rt_kernel_cache_size", sz, vp)
+    sig("t0_rt_dispatch", i32, vp, vp, u32p, u8p, sz)
+    sig("t0_rt_dispatch_async", i32, vp, vp, u32p, u8p, sz, C.POINTER(sz))
+    sig("t0_rt_dispatch_bench", i32, vp, vp, u32p, u8p, sz)
+    sig("t0_gemm_launch", i32, vp, C.POINTER(GemmArgs))
+    sig("t0_fill_uniform_bf16", i32, vp, u64, u64, u64, u64)
+    sig("t0_fill_u32", i32, vp, u64, u64, u64, u64)
+    sig("t0_fill_range_bf16", i32, vp, u64, u64, u64, u64, C.c_float, C.c_float)

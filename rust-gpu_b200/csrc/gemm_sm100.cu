@@ -1,0 +1,429 @@
+// K1 — dense bf16 GEMM for sm_100a: y[M,N] = x[M,K] * op(b), fp32 accumulation in tensor memory.
+//
+// Replaces the reference's generated RDNA kernels (src/t0/gemm_gen.rs:668-1438 generate_lds_db and
+// src/t0/tile_ir.rs:887-2459 lower_gemm).  Same contract: bf16 operands, NT (b = WT[N,K]) or NN
+// (b = B[K,N]) layout, f32 output, optional split-K planes at y + id*M*N (gemm_gen.rs:447-448),
+// ragged M/N/K handled by zero fill and predicated stores (tile_ir.rs:1142-1203,3699-3717), fused
+// epilogues (gemm_gen.rs:40-49, tile_ir.rs:3406-3533).
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128B-swizzled tiles of A (128 x 64) and B (BN x 64) into a ring of stages
+//   warp 1      UMMA issuer: four tcgen05.mma (128 x BN x 16) per stage, accumulator in tensor memory;
+//               owns the tensor-memory allocation (two accumulator buffers of BN columns)
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the epilogue, store to global,
+//               while the issuer already fills the other accumulator buffer
+// All inter-role hand-offs are mbarriers; every wait is bounded and a wait that expires writes an
+// error word the host turns into an error (no trap, no unbounded spin).
+#include "kernels.h"
+#include "ptx_sm100.cuh"
+
+#include <cuda_bf16.h>
+#include <mutex>
+
+namespace t0 {
+
+namespace {
+
+constexpr uint32_t BM = 128;
+constexpr uint32_t BK = 64;
+constexpr uint32_t kThreads = 192;
+constexpr uint32_t kAStageBytes = BM * BK * 2;   // 16 KiB
+
+__host__ __device__ constexpr uint32_t stages_for(uint32_t bn) { return bn == 256 ? 4 : bn == 128 ? 6 : 8; }
+
+struct KParams {
+    void* y;
+    const float* bias;
+    int* status;
+    uint64_t plane_stride;
+    uint32_t M, N, K;
+    uint32_t tiles_m, tiles_n, split_k;
+    uint32_t kb_per_split;
+    uint32_t swap_grid, raster_group;
+    uint32_t out_bf16, epilogue, n_ops;
+    float scale, clamp_min, clamp_max;
+    uint8_t ops[T0_TILE_MAX_EPILOGUE];
+};
+
+struct WorkItem { uint32_t m_blk, n_blk, split; };
+
+__device__ __forceinline__ WorkItem decode_work(uint32_t w, const KParams& p) {
+    WorkItem it;
+    it.split = w % p.split_k;
+    const uint32_t t = w / p.split_k;
+    const uint32_t tiles_fast = p.swap_grid ? p.tiles_n : p.tiles_m;
+    const uint32_t tiles_slow = p.swap_grid ? p.tiles_m : p.tiles_n;
+    const uint32_t group_size = p.raster_group * tiles_fast;
+    const uint32_t g = t / group_size;
+    const uint32_t first = g * p.raster_group;
+    const uint32_t gsz = min(p.raster_group, tiles_slow - first);
+    const uint32_t r = t - g * group_size;
+    const uint32_t slow = first + r % gsz;
+    const uint32_t fast = r / gsz;
+    it.m_blk = p.swap_grid ? slow : fast;
+    it.n_blk = p.swap_grid ? fast : slow;
+    return it;
+}
+
+__device__ __forceinline__ float sigmoid_seq(float x) {
+    // tile_ir.rs:3448-3477: negate, scale by log2(e), exp2, add one, reciprocal
+    const float e = exp2f((-x) * 1.44269504088896340736f);
+    return __frcp_rn(e + 1.0f);
+}
+
+__device__ __forceinline__ float apply_chain(float v, float bias, const KParams& p) {
+    for (uint32_t o = 0; o < p.n_ops; ++o) {
+        switch (p.ops[o]) {
+            case T0_TEPI_BIAS_ADD: v = v + bias; break;
+            case T0_TEPI_SCALE: v = v * p.scale; break;
+            case T0_TEPI_RELU: v = fmaxf(v, 0.0f); break;
+            case T0_TEPI_SILU: v = v * sigmoid_seq(v); break;
+            case T0_TEPI_GELU: v = v * sigmoid_seq(v * 1.702f); break;
+            case T0_TEPI_ABS: v = fabsf(v); break;
+            case T0_TEPI_NEG: v = -v; break;
+            case T0_TEPI_CLAMP: v = fminf(fmaxf(v, p.clamp_min), p.clamp_max); break;
+            default: break;
+        }
+    }
+    return v;
+}
+
+template <uint32_t BN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+    constexpr uint32_t kStages = stages_for(BN);
+    constexpr uint32_t kBStageBytes = BN * BK * 2;
+    constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;
+    constexpr uint32_t kTmemCols = 2 * BN;   // two accumulator buffers; 64..512, a power of two
+    constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(BM, BN, B_MN ? 1u : 0u);
+
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzled tiles need 1024-byte alignment
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* a_tiles = smem;
+    uint8_t* b_tiles = smem + kStages * kAStageBytes;
+    uint64_t* bars = (uint64_t*)(smem + kStages * kStageBytes);
+    uint64_t* full_bar = bars;                       // [kStages] TMA bytes landed
+    uint64_t* empty_bar = bars + kStages;            // [kStages] UMMAs finished reading the stage
+    uint64_t* tmem_full_bar = bars + 2 * kStages;    // [2] accumulator complete
+    uint64_t* tmem_empty_bar = bars + 2 * kStages + 2;  // [2] accumulator drained by the epilogue
+    uint32_t* tmem_holder = (uint32_t*)(bars + 2 * kStages + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t total_work = p.tiles_m * p.tiles_n * p.split_k;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
+        }
+        for (uint32_t b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&tmem_full_bar[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tmem_empty_bar[b]), 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::tma_prefetch_desc(&map_a);
+        ptx::tma_prefetch_desc(&map_b);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
+                const WorkItem wi = decode_work(w, p);
+                for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                        atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(w & 0xFFFFFF));
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+                    ptx::mbar_arrive_expect_tx(fb, kStageBytes);
+                    ptx::tma_load_3d(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
+                                     (int32_t)(kb * BK), (int32_t)(wi.m_blk * BM), (int32_t)wi.split);
+                    if constexpr (!B_MN) {
+                        ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b, fb,
+                                         (int32_t)(kb * BK), (int32_t)(wi.n_blk * BN), (int32_t)wi.split);
+                    } else {
+                        // B[K,N]: one 64(k) x 64(n) box per 64 columns; each box is an [k][128 B] block
+#pragma unroll
+                        for (uint32_t j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes + j * (BK * 128)), &map_b, fb,
+                                             (int32_t)(wi.n_blk * BN + j * 64), (int32_t)(kb * BK), (int32_t)wi.split);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++iter) {
+                const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
+                if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, abort_flag)) {
+                    atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(w & 0xFFFFFF));
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+                        atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000 | (int)(w & 0x7FFFFF));
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * kAStageBytes);
+                    const uint32_t b_addr = ptx::smem_u32(b_tiles + stage * kBStageBytes);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < BK / 16; ++k4) {
+                        // K-major, 128B swizzle: 8-row groups 1024 B apart; a 16-element K step is 32 B
+                        const uint64_t da = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024);
+                        // N-major B: 64-column atoms 8 KiB apart, 8-row k groups 1024 B apart; a K step is two groups
+                        const uint64_t db = B_MN ? ptx::make_smem_desc(b_addr + k4 * 2048, BK * 128, 1024)
+                                                 : ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024);
+                        ptx::umma_bf16_ss(tmem_d, da, db, kIdesc, (kb | k4) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(ptx::smem_u32(&empty_bar[stage]));
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) ptx::umma_commit(ptx::smem_u32(&tmem_full_bar[buf]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const uint32_t quarter = warp & 3;   // tensor-memory lanes 32*quarter .. +31 belong to this warp
+        const bool vec32 = (p.N % 4 == 0) && (((uintptr_t)p.y & 15) == 0);
+        const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
+        uint32_t iter = 0;
+        for (uint32_t w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
+            const WorkItem wi = decode_work(w, p);
+            const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
+            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(w & 0xFFFFFF));
+                break;
+            }
+            ptx::tc_fence_after_sync();
+            const uint32_t row = wi.m_blk * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                const uint32_t col0 = wi.n_blk * BN + c * 32;
+                if (col0 >= p.N) break;   // warp-uniform
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * BN + c * 32, r);
+                ptx::tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                if (p.n_ops) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float bj = (p.bias && col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
+                        v[j] = apply_chain(v[j], bj, p);
+                    }
+                } else if (p.epilogue != T0_EPI_STORE_F32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const float bj = (p.bias && col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
+                        v[j] += bj;
+                        if (p.epilogue == T0_EPI_BIAS_ADD_RELU_STORE_F32) v[j] = fmaxf(v[j], 0.0f);
+                    }
+                }
+                if (row_ok) {
+                    const size_t off = (size_t)wi.split * p.plane_stride + (size_t)row * p.N + col0;
+                    if (!p.out_bf16) {
+                        float* dst = (float*)p.y + off;
+                        if (vec32 && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                ((float4*)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) dst[j] = v[j];
+                        }
+                    } else {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)p.y + off;
+                        if (vec16 && col0 + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 q;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                                q.x = *(uint32_t*)&h0; q.y = *(uint32_t*)&h1; q.z = *(uint32_t*)&h2; q.w = *(uint32_t*)&h3;
+                                ((uint4*)dst)[j] = q;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tmem_empty_bar[buf]));
+        }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    __syncwarp();
+    if (*abort_flag) {
+        // give copies and UMMAs already in flight time to land before shared and tensor memory go away
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 3-D view [split][rows][k_per_split] of a row-major [rows][ld] bf16 matrix (K contiguous, ld >= K).
+int make_map_kmajor(CUtensorMap* map, const void* base, uint32_t rows, uint32_t ld, uint32_t k_per_split, uint32_t split,
+                    uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {k_per_split, rows, split};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)k_per_split * 2};
+    cuuint32_t box[3] = {BK, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (K-major, rows=%u ld=%u) failed: %d", rows, ld, (int)r);
+    return T0_OK;
+}
+
+// 3-D view [split][k_per_split][N] of a row-major [K][ld] bf16 matrix (N contiguous, ld >= N).
+int make_map_nmajor(CUtensorMap* map, const void* base, uint32_t N, uint32_t ld, uint32_t k_per_split, uint32_t split) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {N, k_per_split, split};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)k_per_split * ld * 2};
+    cuuint32_t box[3] = {64, BK, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (N-major, N=%u) failed: %d", N, (int)r);
+    return T0_OK;
+}
+
+template <uint32_t BN, bool B_MN>
+int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& p, uint32_t grid, cudaStream_t stream) {
+    auto kern = gemm_bf16_tcgen05_kernel<BN, B_MN>;
+    const uint32_t smem = gemm_smem_bytes(BN);
+    static bool attr_set[64] = {};   // per instantiation, per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaFuncSetAttribute(smem=%u): %s", smem, cudaGetErrorString(e));
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    kern<<<grid, kThreads, smem, stream>>>(ma, mb, p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
+    return T0_OK;
+}
+
+}  // namespace
+
+uint32_t gemm_stage_count(uint32_t tile_n) { return stages_for(snap_tile_n(tile_n)); }
+
+uint32_t gemm_smem_bytes(uint32_t tile_n) {
+    const uint32_t bn = snap_tile_n(tile_n);
+    // tiles + barriers/holder (256 B) + slack for the 1024-byte alignment of the dynamic segment
+    return stages_for(bn) * (kAStageBytes + bn * BK * 2) + 256 + 1024;
+}
+
+int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
+    if (g.m == 0 || g.n == 0) return T0_OK;
+    if (g.k == 0) return fail(T0_ERR_INVALID, "K must be positive");
+    const uint32_t split = g.split_k ? g.split_k : 1;
+    if (g.k % split) return fail(T0_ERR_UNSUPPORTED, "K=%u not divisible by split_k=%u", g.k, split);
+    const uint32_t kps = g.k / split;
+    const uint32_t ldx = g.ldx ? g.ldx : g.k;
+    const uint32_t ldb = g.ldb ? g.ldb : (g.nn ? g.n : g.k);
+    if ((ldx % 8) || (ldb % 8) || (split > 1 && (kps % 8)))
+        return fail(T0_ERR_UNSUPPORTED, "row strides (%u, %u) and, with split-K, K per split (%u) must be multiples of 8 for the TMA path", ldx, ldb, kps);
+    if (((uintptr_t)g.x & 15) || ((uintptr_t)g.b & 15)) return fail(T0_ERR_UNSUPPORTED, "operand pointers must be 16-byte aligned");
+    const uint32_t bn = snap_tile_n(g.tile_n);
+    if (g.nn && bn < 64) return fail(T0_ERR_UNSUPPORTED, "NN layout needs tile_n >= 64");
+
+    KParams p;
+    memset(&p, 0, sizeof p);
+    p.y = g.y; p.bias = g.bias; p.status = g.status; p.plane_stride = g.plane_stride;
+    p.M = g.m; p.N = g.n; p.K = g.k;
+    p.tiles_m = ceil_div(g.m, BM); p.tiles_n = ceil_div(g.n, bn); p.split_k = split;
+    p.kb_per_split = ceil_div(kps, BK);
+    p.swap_grid = g.swap_grid ? 1 : 0; p.raster_group = 8;
+    p.out_bf16 = g.out_bf16 ? 1 : 0; p.epilogue = g.epilogue; p.n_ops = g.n_ops;
+    p.scale = g.scale; p.clamp_min = g.clamp_min; p.clamp_max = g.clamp_max;
+    memcpy(p.ops, g.ops, sizeof p.ops);
+
+    CUtensorMap ma, mb;
+    int rc = make_map_kmajor(&ma, g.x, g.m, ldx, kps, split, BM);
+    if (rc != T0_OK) return rc;
+    rc = g.nn ? make_map_nmajor(&mb, g.b, g.n, ldb, kps, split) : make_map_kmajor(&mb, g.b, g.n, ldb, kps, split, bn);
+    if (rc != T0_OK) return rc;
+
+    const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * split;
+    if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, g.n_sms ? g.n_sms : 148);
+
+    if (g.nn) {
+        switch (bn) {
+            case 64: return launch_instance<64, true>(ma, mb, p, grid, stream);
+            case 128: return launch_instance<128, true>(ma, mb, p, grid, stream);
+            default: return launch_instance<256, true>(ma, mb, p, grid, stream);
+        }
+    }
+    switch (bn) {
+        case 32: return launch_instance<32, false>(ma, mb, p, grid, stream);
+        case 64: return launch_instance<64, false>(ma, mb, p, grid, stream);
+        case 128: return launch_instance<128, false>(ma, mb, p, grid, stream);
+        default: return launch_instance<256, false>(ma, mb, p, grid, stream);
+    }
+}
+
+}  // namespace t0

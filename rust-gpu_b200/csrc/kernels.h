@@ -1,0 +1,53 @@
+// Internal launch interface between the runtime (runtime.cu) and the sm_100a kernels.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "common.h"
+
+namespace t0 {
+
+// Error word written by a kernel whose bounded wait expired: role in the top byte.
+enum : int { kStatusOk = 0, kStatusProducerTimeout = 0x01000000, kStatusMmaTimeout = 0x02000000, kStatusEpilogueTimeout = 0x03000000 };
+
+struct GemmLaunch {
+    const void* x;        // bf16 [M,K]
+    const void* b;        // bf16 [N,K] (NT) or [K,N] (NN)
+    void* y;              // f32 [M,N] (or planes) / bf16 [M,N]
+    const float* bias;    // f32 [N] or null
+    uint32_t m, n, k;
+    uint32_t ldx, ldb;    // row strides in elements (0 = dense)
+    uint32_t tile_n;      // 32/64/128/256
+    uint32_t split_k;     // >= 1
+    uint64_t plane_stride;  // elements between split planes
+    bool nn, out_bf16, swap_grid;
+    uint8_t epilogue;     // T0_EPI_*
+    uint8_t n_ops;        // TileIR chain (overrides epilogue when > 0)
+    uint8_t ops[T0_TILE_MAX_EPILOGUE];
+    float scale, clamp_min, clamp_max;
+    int* status;          // device error word
+    uint32_t n_sms;
+};
+
+// Launches the tcgen05 GEMM. Requirements (checked): x and b 16-byte aligned, row strides and
+// K / split_k multiples of 8 elements, K % split_k == 0.  Returns a T0_* code.
+int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream);
+
+// y[i] = sum_s planes[s][i] in split order, then the epilogue; K4.
+int launch_splitk_reduce(const float* planes, void* y, const float* bias, uint32_t m, uint32_t n, uint32_t split_k,
+                         bool out_bf16, uint8_t epilogue, uint8_t n_ops, const uint8_t* ops, float scale, float clamp_min,
+                         float clamp_max, cudaStream_t stream);
+
+// dst[r][0..dst_cols) = src[r][0..cols) zero-extended, 16-bit elements (staging copy for shapes TMA cannot address).
+int launch_pad_copy_u16(const void* src, void* dst, uint32_t rows, uint32_t cols, uint32_t dst_cols, cudaStream_t stream);
+
+int launch_fill_uniform_bf16(void* dst, uint64_t n, uint64_t seed, uint64_t first, cudaStream_t stream);
+int launch_fill_u32(void* dst, uint64_t n, uint64_t seed, uint64_t first, cudaStream_t stream);
+int launch_fill_range_bf16(void* dst, uint64_t n, uint64_t seed, uint64_t first, float lo, float hi, cudaStream_t stream);
+
+// Shared-memory footprint of the GEMM pipeline for a tile width.
+uint32_t gemm_stage_count(uint32_t tile_n);
+uint32_t gemm_smem_bytes(uint32_t tile_n);
+
+}  // namespace t0

@@ -1,0 +1,694 @@
+// CUDA-runtime shim behind the reference's GpuRuntime / GpuBuffer / GpuKernel API
+// (src/ignis/gpu_context.rs:31-92,99-119,151-597; src/kfd/buffer.rs:9-146; src/kfd/kernel.rs:8-19):
+// one in-order stream stands in for the AQL queue, a size-keyed pool for BufferPool, a name-keyed
+// table of precompiled sm_100a kernels for the JIT kernel cache, and a poison flag with the same
+// fail-fast meaning.  The kernarg blobs the reference's builders produce are decoded here.
+#include "kernels.h"
+
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+using namespace t0;
+
+struct t0_buffer {
+    t0_runtime* rt;
+    void* dptr;
+    size_t size;       // pool size class (4 KiB multiple)
+};
+
+struct t0_kernel {
+    std::string name;
+    uint32_t kernarg_size;
+    int kind;          // 0 = gemm_gen config, 1 = TileIR spec
+    t0_gemm_config cfg;
+    t0_tile_gemm spec;
+};
+
+struct Scratch {
+    void* ptr = nullptr;
+    size_t size = 0;
+};
+
+struct t0_runtime {
+    int device = 0;
+    int sm_count = 148;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
+    std::mutex mu;
+    std::map<size_t, std::vector<t0_buffer*>> pool;       // BufferPool.cache
+    size_t cached_bytes = 0;
+    std::map<uintptr_t, size_t> live;                      // device allocations handed out (for kernarg validation)
+    std::map<std::string, std::unique_ptr<t0_kernel>> kernels;
+    std::atomic<bool> poisoned{false};
+    std::atomic<uint64_t> launches{0};
+    std::atomic<size_t> slot{0};
+    int* d_status = nullptr;     // device error word written by kernels whose bounded wait expired
+    int* h_status = nullptr;     // pinned mirror
+    Scratch scratch_a, scratch_b, scratch_planes;
+};
+
+namespace {
+
+#define T0_CUDA(expr)                                                                                  \
+    do {                                                                                               \
+        cudaError_t _e = (expr);                                                                       \
+        if (_e != cudaSuccess) return fail(T0_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e));      \
+    } while (0)
+
+struct DeviceGuard {
+    int prev = -1;
+    explicit DeviceGuard(int dev) {
+        cudaGetDevice(&prev);
+        if (prev != dev) cudaSetDevice(dev);
+        else prev = -1;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int check_rt(const t0_runtime* rt) {
+    if (!rt) return fail(T0_ERR_INVALID, "null runtime");
+    if (rt->poisoned.load(std::memory_order_relaxed))
+        return fail(T0_ERR_POISONED, "runtime poisoned after a device failure - refusing dispatch");   // gpu_context.rs:311-313
+    return T0_OK;
+}
+
+// Grow-only scratch areas (staging copies, split-K planes). Growing waits for the stream first.
+int ensure_scratch(t0_runtime* rt, Scratch& s, size_t bytes) {
+    if (bytes <= s.size) return T0_OK;
+    T0_CUDA(cudaStreamSynchronize(rt->stream));
+    if (s.ptr) cudaFree(s.ptr);
+    s.ptr = nullptr; s.size = 0;
+    size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
+    T0_CUDA(cudaMalloc(&s.ptr, want));
+    s.size = want;
+    return T0_OK;
+}
+
+// After a synchronising call: read the device error word; a non-zero value poisons the runtime.
+int check_status_after_sync(t0_runtime* rt) {
+    cudaError_t e = cudaMemcpyAsync(rt->h_status, rt->d_status, sizeof(int), cudaMemcpyDeviceToHost, rt->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
+    if (e != cudaSuccess) {
+        rt->poisoned.store(true);
+        return fail(T0_ERR_CUDA, "device failure while waiting: %s", cudaGetErrorString(e));
+    }
+    if (*rt->h_status != 0) {
+        int code = *rt->h_status;
+        rt->poisoned.store(true);
+        cudaMemsetAsync(rt->d_status, 0, sizeof(int), rt->stream);
+        return fail(T0_ERR_TIMEOUT, "a bounded device-side wait expired (status 0x%08x: role %d, work item %d)", code,
+                    (code >> 24) & 0xFF, code & 0xFFFFFF);
+    }
+    return T0_OK;
+}
+
+struct GemmRequest {
+    uint64_t x, b, y, bias;
+    uint32_t m, n, k;
+    uint32_t tile_n, split_k;
+    bool nn, out_bf16, planes, swap_grid;
+    uint64_t plane_stride;     // elements; only when planes
+    uint8_t epilogue, n_ops;
+    uint8_t ops[T0_TILE_MAX_EPILOGUE];
+    float scale, clamp_min, clamp_max;
+};
+
+uint32_t choose_tile_n(const t0_runtime* rt, uint32_t m, uint32_t n, uint32_t k, uint32_t split) {
+    // widest tile that still gives every SM work; HBM-bound skinny shapes want many CTAs in flight
+    const uint32_t tiles_m = ceil_div(m, 128);
+    static const uint32_t tns[] = {256, 128, 64, 32};
+    for (uint32_t tn : tns) {
+        if (tn > 32 && n <= tn / 2) continue;
+        if ((uint64_t)tiles_m * ceil_div(n, tn) * split >= (uint64_t)rt->sm_count) return tn;
+    }
+    (void)k;
+    return 32;   // nothing fills the machine: take the most CTAs
+}
+
+// The common path of every GEMM entry point: staging for shapes TMA cannot address, the tcgen05
+// kernel, and the device-side split-K reduction when the caller did not ask for planes.
+int run_gemm(t0_runtime* rt, const GemmRequest& q) {
+    if (q.m == 0 || q.n == 0) return T0_OK;
+    if (!q.x || !q.b || !q.y) return fail(T0_ERR_INVALID, "null device pointer in GEMM arguments");
+    const bool needs_bias = q.n_ops ? std::find(q.ops, q.ops + q.n_ops, (uint8_t)T0_TEPI_BIAS_ADD) != q.ops + q.n_ops
+                                    : q.epilogue != T0_EPI_STORE_F32;
+    if (needs_bias && !q.bias) return fail(T0_ERR_INVALID, "epilogue needs a bias vector but bias is null");
+    uint32_t split = q.split_k > 1 ? q.split_k : 1;
+    if (q.k == 0) {
+        // empty contraction: the sum is zero, the epilogue still applies
+        int rc0 = launch_splitk_reduce(nullptr, (void*)q.y, (const float*)q.bias, q.m, q.n, 0, q.out_bf16, q.epilogue, q.n_ops,
+                                       q.ops, q.scale, q.clamp_min, q.clamp_max, rt->stream);
+        if (rc0 == T0_OK) rt->launches.fetch_add(1);
+        return rc0;
+    }
+    if (q.k % split) return fail(T0_ERR_INVALID, "K=%u is not divisible by split_k=%u", q.k, split);   // gemm_gen callers filter this
+    if (q.planes && (q.out_bf16 || q.n_ops || q.epilogue != T0_EPI_STORE_F32) && split > 1)
+        return fail(T0_ERR_INVALID, "split-K planes are raw f32 partial sums: no epilogue or bf16 output");
+
+    GemmLaunch g;
+    memset(&g, 0, sizeof g);
+    g.x = (const void*)q.x; g.b = (const void*)q.b;
+    g.m = q.m; g.n = q.n; g.k = q.k;
+    g.nn = q.nn; g.swap_grid = q.swap_grid;
+    g.status = rt->d_status; g.n_sms = (uint32_t)rt->sm_count;
+    g.split_k = split;
+    g.tile_n = q.tile_n ? snap_tile_n(q.tile_n) : choose_tile_n(rt, q.m, q.n, q.k, split);
+    if (q.nn && g.tile_n < 64) g.tile_n = 64;
+
+    // --- staging for shapes the TMA path cannot address (row stride or base not 16-byte aligned)
+    const uint32_t kps = q.k / split;
+    const bool x_bad = (q.k % 8) || (q.x & 15);
+    const bool b_bad = q.nn ? ((q.n % 8) || (q.b & 15)) : ((q.k % 8) || (q.b & 15));
+    if ((x_bad || b_bad || (kps % 8)) && split > 1)
+        return fail(T0_ERR_UNSUPPORTED, "split-K needs K/split_k %% 8 == 0 and 16-byte aligned operands (K=%u, split_k=%u)", q.k, split);
+    const uint32_t k_pad = (q.k + 7) & ~7u;
+    if (x_bad) {
+        int rc = ensure_scratch(rt, rt->scratch_a, (size_t)q.m * k_pad * 2);
+        if (rc != T0_OK) return rc;
+        rc = launch_pad_copy_u16((const void*)q.x, rt->scratch_a.ptr, q.m, q.k, k_pad, rt->stream);
+        if (rc != T0_OK) return rc;
+        rt->launches.fetch_add(1);
+        g.x = rt->scratch_a.ptr; g.ldx = k_pad;
+    }
+    if (b_bad) {
+        if (q.nn) {
+            const uint32_t n_pad = (q.n + 7) & ~7u;
+            int rc = ensure_scratch(rt, rt->scratch_b, (size_t)q.k * n_pad * 2);
+            if (rc != T0_OK) return rc;
+            rc = launch_pad_copy_u16((const void*)q.b, rt->scratch_b.ptr, q.k, q.n, n_pad, rt->stream);
+            if (rc != T0_OK) return rc;
+            g.b = rt->scratch_b.ptr; g.ldb = n_pad;
+        } else {
+            int rc = ensure_scratch(rt, rt->scratch_b, (size_t)q.n * k_pad * 2);
+            if (rc != T0_OK) return rc;
+            rc = launch_pad_copy_u16((const void*)q.b, rt->scratch_b.ptr, q.n, q.k, k_pad, rt->stream);
+            if (rc != T0_OK) return rc;
+            g.b = rt->scratch_b.ptr; g.ldb = k_pad;
+        }
+        rt->launches.fetch_add(1);
+    }
+
+    const bool fused_reduce = split > 1 && !q.planes;
+    if (fused_reduce) {
+        // partial planes go to scratch; K4 sums them in split order and applies the epilogue
+        const size_t mn = (size_t)q.m * q.n;
+        int rc = ensure_scratch(rt, rt->scratch_planes, mn * split * sizeof(float));
+        if (rc != T0_OK) return rc;
+        g.y = rt->scratch_planes.ptr; g.plane_stride = mn;
+        g.out_bf16 = false; g.epilogue = T0_EPI_STORE_F32; g.n_ops = 0;
+        rc = launch_gemm_sm100(g, rt->stream);
+        if (rc != T0_OK) return rc;
+        rt->launches.fetch_add(1);
+        rc = launch_splitk_reduce((const float*)rt->scratch_planes.ptr, (void*)q.y, (const float*)q.bias, q.m, q.n, split,
+                                  q.out_bf16, q.epilogue, q.n_ops, q.ops, q.scale, q.clamp_min, q.clamp_max, rt->stream);
+        if (rc != T0_OK) return rc;
+        rt->launches.fetch_add(1);
+        return T0_OK;
+    }
+    g.y = (void*)q.y;
+    g.plane_stride = split > 1 ? (q.plane_stride ? q.plane_stride : (uint64_t)q.m * q.n) : 0;
+    g.bias = (const float*)q.bias;
+    g.out_bf16 = q.out_bf16; g.epilogue = q.epilogue; g.n_ops = q.n_ops;
+    memcpy(g.ops, q.ops, sizeof g.ops);
+    g.scale = q.scale; g.clamp_min = q.clamp_min; g.clamp_max = q.clamp_max;
+    int rc = launch_gemm_sm100(g, rt->stream);
+    if (rc != T0_OK) return rc;
+    rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+// Bytes available from `addr` to the end of the live allocation containing it, or SIZE_MAX when the
+// address belongs to no allocation of this runtime (foreign device memory).
+size_t extent_from(t0_runtime* rt, uint64_t addr) {
+    std::lock_guard<std::mutex> g(rt->mu);
+    auto it = rt->live.upper_bound((uintptr_t)addr);
+    if (it == rt->live.begin()) return SIZE_MAX;
+    --it;
+    if (addr >= it->first + it->second) return SIZE_MAX;
+    return (size_t)(it->first + it->second - addr);
+}
+
+uint32_t rd_u32(const uint8_t* p) { return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24); }
+uint64_t rd_u64(const uint8_t* p) { return (uint64_t)rd_u32(p) | ((uint64_t)rd_u32(p + 4) << 32); }
+float rd_f32(const uint8_t* p) { uint32_t b = rd_u32(p); float f; memcpy(&f, &b, 4); return f; }
+
+// Decode a kernarg blob + grid into a GEMM request (the work the reference's kernel would do).
+int decode_dispatch(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* ka, size_t len, bool validate,
+                    GemmRequest* out) {
+    // gpu_context.rs:319-322: assert_eq!(kernargs.len(), kernel.kernarg_size)
+    if (len != k->kernarg_size)
+        return fail(T0_ERR_INVALID, "kernarg mismatch: builder produced %zuB, kernel declares %uB", len, k->kernarg_size);
+    GemmRequest q;
+    memset(&q, 0, sizeof q);
+    q.x = rd_u64(ka); q.b = rd_u64(ka + 8); q.y = rd_u64(ka + 16);
+    q.k = rd_u32(ka + 24); q.n = rd_u32(ka + 28);
+    const uint32_t y_split_stride = rd_u32(ka + 36);
+    q.scale = 1.0f;
+    uint32_t tile_m, tile_n, wg, sk;
+    bool swap;
+    if (k->kind == 0) {
+        const t0_gemm_config& c = k->cfg;
+        tile_m = c.tile_m; tile_n = c.tile_n; wg = c.wg_size; sk = split_of(&c); swap = c.swap_grid;
+        q.nn = c.transpose == T0_NN; q.epilogue = c.epilogue;
+        if (c.epilogue != T0_EPI_STORE_F32) q.bias = rd_u64(ka + 40);
+    } else {
+        const t0_tile_gemm& s = k->spec;
+        tile_m = s.tile_m; tile_n = s.tile_n; wg = t0_tile_gemm_wg_size(&s); sk = s.split_k ? s.split_k : 1; swap = s.swap_grid;
+        q.nn = s.transpose == T0_NN;
+        q.m = rd_u32(ka + 40);
+        q.n_ops = s.n_epilogue;
+        memcpy(q.ops, s.epilogue, sizeof q.ops);
+        size_t off = s.persistent ? 64 : 44;
+        bool has_bias = false, has_scale = false, has_clamp = false;
+        for (uint32_t i = 0; i < s.n_epilogue; ++i) {
+            has_bias |= s.epilogue[i] == T0_TEPI_BIAS_ADD;
+            has_scale |= s.epilogue[i] == T0_TEPI_SCALE;
+            has_clamp |= s.epilogue[i] == T0_TEPI_CLAMP;
+        }
+        if (has_bias) { off = (off + 7) & ~(size_t)7; q.bias = rd_u64(ka + off); off += 8; }
+        if (has_scale) { q.scale = rd_f32(ka + off); off += 4; }
+        if (has_clamp) { q.clamp_min = rd_f32(ka + off); q.clamp_max = rd_f32(ka + off + 4); off += 8; }
+    }
+    if (wg == 0 || tile_m == 0 || tile_n == 0) return fail(T0_ERR_INVALID, "degenerate kernel configuration");
+    if (grid[2] != 1 && grid[2] != 0) return fail(T0_ERR_INVALID, "grid z must be 1");
+    uint32_t tiles_m, tiles_n;
+    if (k->kind == 1 && k->spec.persistent) {
+        // tile_ir.rs:4646-4655: one workgroup loops over every tile
+        tiles_m = ceil_div(q.m, tile_m); tiles_n = ceil_div(q.n, tile_n);
+    } else {
+        if (grid[0] % wg) return fail(T0_ERR_INVALID, "grid x=%u is not a multiple of the workgroup size %u", grid[0], wg);
+        if (grid[1] % sk) return fail(T0_ERR_INVALID, "grid y=%u is not a multiple of split_k=%u", grid[1], sk);
+        const uint32_t gx = grid[0] / wg, gy = grid[1] / sk;
+        tiles_n = swap ? gx : gy;
+        tiles_m = swap ? gy : gx;
+    }
+    if (k->kind == 0) {
+        // the 40/48-byte blob has no M: every row of every launched tile is computed
+        q.m = tiles_m * tile_m;
+        if (sk > 1 && y_split_stride && q.n) q.m = std::min<uint32_t>(q.m, y_split_stride / (4u * q.n));
+        q.planes = sk > 1;
+        q.plane_stride = y_split_stride / 4;
+    } else {
+        if ((uint64_t)tiles_m * tile_m < q.m) q.m = tiles_m * tile_m;   // rows no workgroup covers stay untouched
+        q.planes = false;   // y_split_stride is always 0 in TileIR blobs (tile_ir.rs:4613): reduce on the device
+    }
+    if ((uint64_t)tiles_n * tile_n < q.n)
+        return fail(T0_ERR_INVALID, "grid covers %u columns but N=%u", tiles_n * tile_n, q.n);
+    q.split_k = sk;
+    q.tile_n = tile_n;
+    q.swap_grid = swap;
+
+    // pointer validation against this runtime's live allocations (stronger than gpu_context.rs:380-395);
+    // rows that do not fit the caller's buffers are not computed
+    const bool strict = validate && getenv("T0_VALIDATE_KA") != nullptr;
+    const size_t ex = extent_from(rt, q.x), eb = extent_from(rt, q.b), ey = extent_from(rt, q.y);
+    if (strict && (ex == SIZE_MAX || eb == SIZE_MAX || ey == SIZE_MAX))
+        return fail(T0_ERR_INVALID, "kernarg pointer outside every live allocation of this runtime");
+    if (validate) {
+        if (eb != SIZE_MAX && (uint64_t)q.n * q.k * 2 > eb)
+            return fail(T0_ERR_BOUNDS, "weight buffer holds %zu bytes, N*K*2 = %llu", eb, (unsigned long long)q.n * q.k * 2);
+        if (ex != SIZE_MAX && q.k) q.m = (uint32_t)std::min<uint64_t>(q.m, ex / ((uint64_t)q.k * 2));
+        if (ey != SIZE_MAX && q.n) {
+            const uint64_t per_row = (uint64_t)q.n * 4;
+            if (q.planes && q.plane_stride) {
+                if ((uint64_t)(sk - 1) * q.plane_stride * 4 + (uint64_t)q.m * per_row > ey)
+                    return fail(T0_ERR_BOUNDS, "output buffer too small for %u split-K planes", sk);
+            } else {
+                q.m = (uint32_t)std::min<uint64_t>(q.m, ey / per_row);
+            }
+        }
+        if (q.bias) {
+            const size_t ebias = extent_from(rt, q.bias);
+            if (ebias != SIZE_MAX && (uint64_t)q.n * 4 > ebias) return fail(T0_ERR_BOUNDS, "bias buffer shorter than N floats");
+        }
+    }
+    *out = q;
+    return T0_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ------------------------------------------------------------------ runtime
+
+int t0_rt_new(int device, t0_runtime** out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    *out = nullptr;
+    int n_dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n_dev);
+    if (e != cudaSuccess || n_dev == 0)
+        return fail(T0_ERR_CUDA, "no CUDA device available (%s); this library has no CPU fallback", cudaGetErrorString(e));
+    if (device < 0 || device >= n_dev) return fail(T0_ERR_INVALID, "device %d out of range (0..%d)", device, n_dev - 1);
+    cudaDeviceProp prop;
+    T0_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(T0_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a (B200) only", device, prop.major, prop.minor);
+    DeviceGuard guard(device);
+    std::unique_ptr<t0_runtime> rt(new t0_runtime());
+    rt->device = device;
+    rt->sm_count = prop.multiProcessorCount;
+    T0_CUDA(cudaStreamCreateWithFlags(&rt->stream, cudaStreamNonBlocking));
+    T0_CUDA(cudaEventCreate(&rt->ev_start));
+    T0_CUDA(cudaEventCreate(&rt->ev_stop));
+    T0_CUDA(cudaMalloc(&rt->d_status, sizeof(int)));
+    T0_CUDA(cudaMemset(rt->d_status, 0, sizeof(int)));
+    T0_CUDA(cudaMallocHost(&rt->h_status, sizeof(int)));
+    *rt->h_status = 0;
+    *out = rt.release();
+    return T0_OK;
+}
+
+void t0_rt_free(t0_runtime* rt) {
+    if (!rt) return;
+    DeviceGuard guard(rt->device);
+    cudaStreamSynchronize(rt->stream);
+    t0_rt_pool_clear(rt);
+    for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes})
+        if (s->ptr) cudaFree(s->ptr);
+    if (rt->d_status) cudaFree(rt->d_status);
+    if (rt->h_status) cudaFreeHost(rt->h_status);
+    if (rt->ev_start) cudaEventDestroy(rt->ev_start);
+    if (rt->ev_stop) cudaEventDestroy(rt->ev_stop);
+    if (rt->stream) cudaStreamDestroy(rt->stream);
+    delete rt;
+}
+
+int t0_rt_is_poisoned(const t0_runtime* rt) { return rt && rt->poisoned.load() ? 1 : 0; }
+
+void t0_rt_mark_poisoned(t0_runtime* rt) {
+    if (!rt) return;
+    rt->poisoned.store(true);
+    fprintf(stderr, "[t0b200] runtime POISONED - all subsequent dispatches will fail fast\n");   // gpu_context.rs:195-198
+}
+
+int t0_rt_synchronize(t0_runtime* rt) {
+    if (!rt) return fail(T0_ERR_INVALID, "null runtime");
+    DeviceGuard guard(rt->device);
+    return check_status_after_sync(rt);
+}
+
+int t0_rt_wait_idle(t0_runtime* rt) { return t0_rt_synchronize(rt); }
+void* t0_rt_stream(const t0_runtime* rt) { return rt ? (void*)rt->stream : nullptr; }
+int t0_rt_device(const t0_runtime* rt) { return rt ? rt->device : -1; }
+int t0_rt_sm_count(const t0_runtime* rt) { return rt ? rt->sm_count : 0; }
+uint64_t t0_rt_launch_count(const t0_runtime* rt) { return rt ? rt->launches.load() : 0; }
+
+int t0_rt_timer_start(t0_runtime* rt) {
+    if (!rt) return fail(T0_ERR_INVALID, "null runtime");
+    DeviceGuard guard(rt->device);
+    T0_CUDA(cudaEventRecord(rt->ev_start, rt->stream));
+    return T0_OK;
+}
+
+int t0_rt_timer_stop(t0_runtime* rt, float* ms) {
+    if (!rt || !ms) return fail(T0_ERR_INVALID, "null argument");
+    DeviceGuard guard(rt->device);
+    T0_CUDA(cudaEventRecord(rt->ev_stop, rt->stream));
+    T0_CUDA(cudaEventSynchronize(rt->ev_stop));
+    T0_CUDA(cudaEventElapsedTime(ms, rt->ev_start, rt->ev_stop));
+    return T0_OK;
+}
+
+// ------------------------------------------------------------------ buffers
+
+int t0_rt_alloc(t0_runtime* rt, size_t n_bytes, t0_buffer** out) {
+    if (!rt || !out) return fail(T0_ERR_INVALID, "null argument");
+    *out = nullptr;
+    DeviceGuard guard(rt->device);
+    const size_t aligned = std::max<size_t>(4096, (n_bytes + 4095) / 4096 * 4096);   // gpu_context.rs:55
+    {
+        std::unique_lock<std::mutex> g(rt->mu);
+        auto it = rt->pool.find(aligned);
+        if (it != rt->pool.end() && !it->second.empty()) {
+            t0_buffer* b = it->second.back();
+            it->second.pop_back();
+            rt->cached_bytes -= aligned;
+            rt->live[(uintptr_t)b->dptr] = b->size;
+            g.unlock();
+            // gpu_context.rs:57-62: a reused buffer is zeroed before the new owner sees it
+            T0_CUDA(cudaMemsetAsync(b->dptr, 0, b->size, rt->stream));
+            *out = b;
+            return T0_OK;
+        }
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, aligned);
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaMalloc(%zu): %s", aligned, cudaGetErrorString(e));
+    t0_buffer* b = new t0_buffer{rt, p, aligned};
+    {
+        std::lock_guard<std::mutex> g(rt->mu);
+        rt->live[(uintptr_t)p] = aligned;
+    }
+    *out = b;
+    return T0_OK;
+}
+
+int t0_rt_alloc_zero(t0_runtime* rt, size_t n_bytes, t0_buffer** out) {
+    int rc = t0_rt_alloc(rt, n_bytes, out);
+    if (rc != T0_OK) return rc;
+    return t0_buf_zero(*out);
+}
+
+int t0_rt_alloc_f32(t0_runtime* rt, size_t n_elems, t0_buffer** out) {
+    const size_t bytes = (std::max<size_t>(n_elems * 4, 512) + 511) & ~(size_t)511;   // gpu_context.rs:521
+    return t0_rt_alloc_zero(rt, bytes, out);
+}
+
+void t0_rt_recycle(t0_runtime* rt, t0_buffer* buf) {
+    if (!rt || !buf) return;
+    std::lock_guard<std::mutex> g(rt->mu);
+    rt->live.erase((uintptr_t)buf->dptr);
+    rt->pool[buf->size].push_back(buf);
+    rt->cached_bytes += buf->size;
+}
+
+size_t t0_rt_pool_cached_bytes(const t0_runtime* rt) { return rt ? rt->cached_bytes : 0; }
+
+void t0_rt_pool_clear(t0_runtime* rt) {
+    if (!rt) return;
+    DeviceGuard guard(rt->device);
+    cudaStreamSynchronize(rt->stream);
+    std::lock_guard<std::mutex> g(rt->mu);
+    for (auto& kv : rt->pool)
+        for (t0_buffer* b : kv.second) { cudaFree(b->dptr); delete b; }
+    rt->pool.clear();
+    rt->cached_bytes = 0;
+}
+
+void t0_buf_free(t0_buffer* buf) {
+    if (!buf) return;
+    t0_runtime* rt = buf->rt;
+    DeviceGuard guard(rt->device);
+    cudaStreamSynchronize(rt->stream);
+    {
+        std::lock_guard<std::mutex> g(rt->mu);
+        rt->live.erase((uintptr_t)buf->dptr);
+    }
+    cudaFree(buf->dptr);
+    delete buf;
+}
+
+int t0_buf_write_bytes(t0_buffer* buf, size_t offset, const void* data, size_t len) {
+    if (!buf || (!data && len)) return fail(T0_ERR_INVALID, "null argument");
+    // src/kfd/buffer.rs:76: assert!(offset + data.len() <= self.size)
+    if (offset > buf->size || len > buf->size - offset)
+        return fail(T0_ERR_BOUNDS, "write of %zu bytes at offset %zu exceeds buffer size %zu", len, offset, buf->size);
+    if (len == 0) return T0_OK;
+    DeviceGuard guard(buf->rt->device);
+    T0_CUDA(cudaMemcpyAsync((uint8_t*)buf->dptr + offset, data, len, cudaMemcpyHostToDevice, buf->rt->stream));
+    T0_CUDA(cudaStreamSynchronize(buf->rt->stream));
+    return T0_OK;
+}
+
+int t0_buf_read_bytes(const t0_buffer* buf, size_t offset, void* out, size_t len) {
+    if (!buf || (!out && len)) return fail(T0_ERR_INVALID, "null argument");
+    if (offset > buf->size || len > buf->size - offset)
+        return fail(T0_ERR_BOUNDS, "read of %zu bytes at offset %zu exceeds buffer size %zu", len, offset, buf->size);
+    if (len == 0) return T0_OK;
+    DeviceGuard guard(buf->rt->device);
+    T0_CUDA(cudaMemcpyAsync(out, (const uint8_t*)buf->dptr + offset, len, cudaMemcpyDeviceToHost, buf->rt->stream));
+    T0_CUDA(cudaStreamSynchronize(buf->rt->stream));
+    return T0_OK;
+}
+
+int t0_buf_write(t0_buffer* buf, const void* data, size_t len) { return t0_buf_write_bytes(buf, 0, data, len); }
+int t0_buf_read(const t0_buffer* buf, void* out, size_t len) { return t0_buf_read_bytes(buf, 0, out, len); }
+
+int t0_buf_zero(t0_buffer* buf) {
+    if (!buf) return fail(T0_ERR_INVALID, "null buffer");
+    DeviceGuard guard(buf->rt->device);
+    T0_CUDA(cudaMemsetAsync(buf->dptr, 0, buf->size, buf->rt->stream));
+    return T0_OK;
+}
+
+uint64_t t0_buf_gpu_addr(const t0_buffer* buf) { return buf ? (uint64_t)(uintptr_t)buf->dptr : 0; }
+size_t t0_buf_size(const t0_buffer* buf) { return buf ? buf->size : 0; }
+
+int t0_rt_read_f32(t0_runtime* rt, const t0_buffer* buf, size_t n, float* out) {
+    if (!rt || !buf) return fail(T0_ERR_INVALID, "null argument");
+    int rc = t0_rt_wait_idle(rt);   // gpu_context.rs:536
+    if (rc != T0_OK) return rc;
+    return t0_buf_read(buf, out, n * 4);
+}
+
+int t0_rt_write_f32(t0_runtime* rt, t0_buffer* buf, const float* data, size_t n) {
+    if (!rt || !buf) return fail(T0_ERR_INVALID, "null argument");
+    return t0_buf_write(buf, data, n * 4);
+}
+
+int t0_rt_upload_f32(t0_runtime* rt, const float* data, size_t n, t0_buffer** out) {
+    int rc = t0_rt_alloc_f32(rt, n, out);
+    if (rc != T0_OK) return rc;
+    return t0_rt_write_f32(rt, *out, data, n);
+}
+
+// ------------------------------------------------------------------ kernels
+
+int t0_rt_ensure_gemm_kernel(t0_runtime* rt, const t0_gemm_config* cfg, t0_kernel** out) {
+    if (!rt || !cfg || !out) return fail(T0_ERR_INVALID, "null argument");
+    // gemm_gen.rs:270-281 panics on an infeasible config; here that is an error code
+    if (!t0_gemm_config_is_feasible(cfg)) return fail(T0_ERR_INVALID, "[gemm_gen] config '%s' is not feasible", gemm_config_name(*cfg).c_str());
+    std::string name = gemm_config_name(*cfg);
+    std::lock_guard<std::mutex> g(rt->mu);
+    auto it = rt->kernels.find(name);
+    if (it == rt->kernels.end()) {
+        std::unique_ptr<t0_kernel> k(new t0_kernel());
+        k->name = name;
+        k->kind = 0;
+        k->cfg = *cfg;
+        memset(&k->spec, 0, sizeof k->spec);
+        k->kernarg_size = cfg->epilogue == T0_EPI_STORE_F32 ? 40 : 48;   // gemm_gen.rs:442,466
+        it = rt->kernels.emplace(name, std::move(k)).first;
+    }
+    *out = it->second.get();
+    return T0_OK;
+}
+
+int t0_rt_ensure_tile_kernel(t0_runtime* rt, const t0_tile_gemm* spec, t0_kernel** out) {
+    if (!rt || !spec || !out) return fail(T0_ERR_INVALID, "null argument");
+    if (spec->tile_m < 16 || spec->tile_m % 16 || spec->tile_n < 16 || spec->tile_n % 16 || spec->tile_k < 16 ||
+        spec->n_epilogue > T0_TILE_MAX_EPILOGUE || spec->wmma_format != 0)
+        return fail(T0_ERR_INVALID, "TileGemm spec is not supported (tile %ux%ux%u, format %u)", spec->tile_m, spec->tile_n,
+                    spec->tile_k, spec->wmma_format);
+    uint32_t sk = spec->split_k ? spec->split_k : 1;
+    if (sk & (sk - 1)) return fail(T0_ERR_INVALID, "split_k=%u must be a power of 2", sk);
+    std::string name = tile_gemm_name(*spec);
+    std::lock_guard<std::mutex> g(rt->mu);
+    auto it = rt->kernels.find(name);
+    if (it == rt->kernels.end()) {
+        std::unique_ptr<t0_kernel> k(new t0_kernel());
+        k->name = name;
+        k->kind = 1;
+        k->spec = *spec;
+        memset(&k->cfg, 0, sizeof k->cfg);
+        uint8_t tmp[96];
+        size_t len = 0;
+        t0_tile_build_kernargs_epilogue(0, 0, 0, 0, 0, 0, spec, 0, 1.0f, 0.0f, 0.0f, tmp, sizeof tmp, &len);
+        k->kernarg_size = (uint32_t)len;
+        it = rt->kernels.emplace(name, std::move(k)).first;
+    }
+    *out = it->second.get();
+    return T0_OK;
+}
+
+uint32_t t0_kernel_kernarg_size(const t0_kernel* k) { return k ? k->kernarg_size : 0; }
+const char* t0_kernel_name(const t0_kernel* k) { return k ? k->name.c_str() : ""; }
+size_t t0_rt_kernel_cache_size(const t0_runtime* rt) {
+    if (!rt) return 0;
+    std::lock_guard<std::mutex> g(const_cast<t0_runtime*>(rt)->mu);
+    return rt->kernels.size();
+}
+
+// ------------------------------------------------------------------ dispatch
+
+static int dispatch_impl(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* ka, size_t len, bool validate,
+                         bool wait) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!k || !grid || !ka) return fail(T0_ERR_INVALID, "null argument");
+    DeviceGuard guard(rt->device);
+    GemmRequest q;
+    rc = decode_dispatch(rt, k, grid, ka, len, validate, &q);
+    if (rc != T0_OK) return rc;
+    if (getenv("T0_DEBUG_DISPATCH"))   // gpu_context.rs:335-349
+        fprintf(stderr, "[DISPATCH] %s x=0x%llx wt=0x%llx y=0x%llx M=%u N=%u K=%u split_k=%u\n", k->name.c_str(),
+                (unsigned long long)q.x, (unsigned long long)q.b, (unsigned long long)q.y, q.m, q.n, q.k, q.split_k);
+    rc = run_gemm(rt, q);
+    if (rc != T0_OK) return rc;
+    rt->slot.fetch_add(1);
+    if (wait) return check_status_after_sync(rt);
+    return T0_OK;
+}
+
+int t0_rt_dispatch(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len) {
+    return dispatch_impl(rt, k, grid, kernargs, len, true, true);
+}
+
+int t0_rt_dispatch_async(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len, size_t* out_slot) {
+    if (rt && out_slot) *out_slot = rt->slot.load() % 256;   // gpu_context.rs:296-298
+    return dispatch_impl(rt, k, grid, kernargs, len, true, false);
+}
+
+int t0_rt_dispatch_bench(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len) {
+    return dispatch_impl(rt, k, grid, kernargs, len, false, true);
+}
+
+int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* a) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!a) return fail(T0_ERR_INVALID, "null arguments");
+    if (a->transpose > T0_NN || a->epilogue > T0_EPI_BIAS_ADD_RELU_STORE_F32 || a->n_tile_epilogue > T0_TILE_MAX_EPILOGUE)
+        return fail(T0_ERR_INVALID, "bad enum value in GEMM arguments");
+    uint32_t sk = a->split_k > 1 ? a->split_k : 1;
+    if (sk & (sk - 1)) return fail(T0_ERR_INVALID, "split_k=%u must be power of 2", sk);
+    DeviceGuard guard(rt->device);
+    GemmRequest q;
+    memset(&q, 0, sizeof q);
+    q.x = a->x; q.b = a->b; q.y = a->y; q.bias = a->bias;
+    q.m = a->m; q.n = a->n; q.k = a->k;
+    q.tile_n = a->tile_n; q.split_k = sk;
+    q.nn = a->transpose == T0_NN; q.out_bf16 = a->out_bf16; q.planes = a->planes && sk > 1; q.swap_grid = a->swap_grid;
+    q.plane_stride = (uint64_t)a->m * a->n;
+    q.epilogue = a->epilogue; q.n_ops = a->n_tile_epilogue;
+    memcpy(q.ops, a->tile_epilogue, sizeof q.ops);
+    q.scale = a->scale; q.clamp_min = a->clamp_min; q.clamp_max = a->clamp_max;
+    return run_gemm(rt, q);
+}
+
+// ------------------------------------------------------------------ seeded inputs
+
+int t0_fill_uniform_bf16(t0_runtime* rt, uint64_t dst, uint64_t n, uint64_t seed, uint64_t first_index) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    DeviceGuard guard(rt->device);
+    rc = launch_fill_uniform_bf16((void*)dst, n, seed, first_index, rt->stream);
+    if (rc == T0_OK) rt->launches.fetch_add(1);
+    return rc;
+}
+
+int t0_fill_u32(t0_runtime* rt, uint64_t dst, uint64_t n, uint64_t seed, uint64_t first_index) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    DeviceGuard guard(rt->device);
+    rc = launch_fill_u32((void*)dst, n, seed, first_index, rt->stream);
+    if (rc == T0_OK) rt->launches.fetch_add(1);
+    return rc;
+}
+
+int t0_fill_range_bf16(t0_runtime* rt, uint64_t dst, uint64_t n, uint64_t seed, uint64_t first_index, float lo, float hi) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    DeviceGuard guard(rt->device);
+    rc = launch_fill_range_bf16((void*)dst, n, seed, first_index, lo, hi, rt->stream);
+    if (rc == T0_OK) rt->launches.fetch_add(1);
+    return rc;
+}
+
+}  // extern "C"
