@@ -1,0 +1,329 @@
+"""Benchmark of the B200 GEMM hot path (one JSON line on rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+N = 1   workload `gemm_bf16_4096`: bf16 4096^3 GEMM, fp32 accumulate and output (the configuration the
+        headline metric is quoted on).  A step is one GEMM over one of several resident input sets.
+N > 1   workload `gemm_bf16_16384_sharded`: the 16384^3 GEMM sharded by N-column blocks, A replicated,
+        each rank computes C[:, N/g slice]; no data-path collective (strong scaling).
+`value` is whole-job TFLOP/s with inputs resident in HBM, timed with CUDA events on the launching
+stream, max over ranks.  `e2e` is the same metric through the C-ABI call with pinned HOST buffers:
+host->device copies of the step's operands and the device->host read of its result are inside the
+timed region.  `--impl reference` times the CPU restatement of the reference's own CPU GEMM on the
+host cores for the same config (the reference's GPU path targets AMD RDNA through /dev/kfd and its Rust
+toolchain is absent, so its CPU reference GEMM is the only part of it that can run on this box).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "gemm_bf16_4096": dict(m=4096, n=4096, k=4096),
+    "gemm_bf16_2048": dict(m=2048, n=2048, k=2048),
+    "gemm_bf16_8192": dict(m=8192, n=8192, k=8192),
+    "gemm_bf16_16384_sharded": dict(m=16384, n=16384, k=16384),
+}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from the ncu capture summarised
+# in profiles/ (bytes); None until a capture of that workload exists.
+NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": None}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                 "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                 "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                 "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self.nv:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=1.0)
+        return {"sm_mhz": int(statistics.median(self.samples)) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def cpu_baseline(oracle, m, n, k, rows, threads=0):
+    """Times the oracle's reference GEMM on `rows` rows of the workload; returns (TFLOP/s, seconds, cores)."""
+    a = oracle.fill_uniform_bf16(rows * k, 42 + m)
+    b = oracle.fill_uniform_bf16(n * k, 137 + n)
+    oracle.gemm_nt(a[: 8 * k], b, 8, k, n, threads)   # page in, spin up
+    best = float("inf")
+    for _ in range(3):                                # BASELINE plan: steady clock around the region, best of 3
+        t = time.perf_counter()
+        oracle.gemm_nt(a, b, rows, k, n, threads)
+        best = min(best, time.perf_counter() - t)
+    cores = threads if threads > 0 else oracle.host_threads()
+    return 2.0 * rows * n * k / best / 1e12, best, cores
+
+
+def run_reference_arm(args, rank, world):
+    """`--impl reference`: the reference's own CPU reference GEMM (src/t0/tile_ir.rs:5021-5038), restated in
+    oracle/oracle.c, on all host cores.  Rank 0 alone runs it."""
+    if rank != 0:
+        return
+    import oracle
+    oracle.build()
+    name = args.workload or ("gemm_bf16_4096" if world == 1 else "gemm_bf16_16384_sharded")
+    w = WORKLOADS[name]
+    m, n, k = w["m"], w["n"], w["k"]
+    # bounded sample: the whole matrix when it is 4096^3-sized, else a row block with the same work (extrapolated)
+    rows = max(32, min(m, int(m * (2.0 * 4096 ** 3) / (2.0 * m * n * k))))
+    a = oracle.fill_uniform_bf16(rows * k, 42 + m)
+    b = oracle.fill_uniform_bf16(n * k, 137 + n)
+    for _ in range(args.warmup):
+        oracle.gemm_nt(a, b, rows, k, n)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.gemm_nt(a, b, rows, k, n)
+    dt = time.perf_counter() - t
+    tflops = 2.0 * rows * n * k * args.steps / dt / 1e12
+    full_ms = dt / args.steps * (m / rows) * 1e3
+    sample = (f"the full {m}x{n}x{k} GEMM per step" if rows == m else
+              f"rows 0..{rows - 1} of {m} per step, full-matrix time extrapolated linearly")
+    line = {"impl": "reference", "metric": "bf16_gemm_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": full_ms, "higher_is_better": True,
+            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, "m": m, "n": n, "k": k, "layout": "NT", "out": "f32"},
+            "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": oracle.host_threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--tile-n", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        print(f"bench.py --gpus {args.gpus} must be launched through torch.distributed.run", file=sys.stderr)
+        sys.exit(2)
+
+    if args.impl == "reference":
+        args.steps = args.steps if args.steps is not None else 3
+        args.warmup = args.warmup if args.warmup is not None else 1
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    t0 = importlib.import_module("rust-gpu_b200")
+    t0.lib()   # raises if the CUDA library is missing: there is no fallback path
+
+    name = args.workload or ("gemm_bf16_4096" if world == 1 else "gemm_bf16_16384_sharded")
+    sharded = name.endswith("_sharded")
+    w = WORKLOADS[name]
+    M, N_total, K = w["m"], w["n"], w["k"]
+    N = N_total // world if sharded else N_total
+    steps = args.steps if args.steps is not None else (200 if not sharded else 5)
+    warmup = max(3, args.warmup if args.warmup is not None else (10 if not sharded else 3))
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    rt = t0.GpuRuntime(local_rank)
+
+    # resident inputs: several sets so consecutive steps do not find their operands in L2 (126 MB)
+    set_bytes = M * K * 2 + N * K * 2 + M * N * 4
+    n_sets = 1 if sharded else max(2, min(4, -(-3 * 126 * 2 ** 20 // set_bytes)))
+    sets = []
+    for s in range(n_sets):
+        xa, xb, y = rt.alloc(M * K * 2), rt.alloc(N * K * 2), rt.alloc(M * N * 4)
+        rt.fill_uniform_bf16(xa.gpu_addr(), M * K, 42 + M + 1000 * s)
+        # rank r owns rows [r*N, (r+1)*N) of WT[N_total, K]: the same stream, offset by its first element
+        rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N_total + 1000 * s, rank * N * K if sharded else 0)
+        sets.append((xa, xb, y))
+    cfg = t0.auto_select(M, K, N)
+    tile_n = args.tile_n or cfg.tile_n
+    split_k = cfg.split()
+    pair = 1 if (cfg.wgp_mode and cfg.tile_m == 256 and not args.tile_n) else 2
+    gemm_kw = dict(tile_n=tile_n, split_k=split_k, swap_grid=bool(cfg.swap_grid), pair_cta=pair)
+    step_args = [rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K, **gemm_kw) for (xa, xb, y) in sets]
+
+    def step(i):
+        rt.gemm_batch([step_args[i % n_sets]])
+
+    def barrier():
+        rt.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        rt.synchronize()
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches_before = rt.launch_count()
+    timed = [step_args[i % n_sets] for i in range(steps)]
+    rt.timer_start()
+    rt.gemm_batch(timed)          # the K steps are submitted back to back from native code, then one wait
+    ms = rt.timer_stop()
+    barrier()
+    clocks = sampler.stop()
+    launches = rt.launch_count() - launches_before
+    kernel_mhz, _ = rt.last_kernel_clock()
+    clocks["sm_mhz_in_kernel"] = round(kernel_mhz)   # cycle counter / nanosecond timer inside the last timed kernel
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    flops_per_step = 2.0 * M * N_total * K
+    value = flops_per_step * steps / (ms_max * 1e-3) / 1e12
+
+    # parity spot check on rank 0 (the full parity suite is tests/ -m gpu)
+    parity = None
+    if rank == 0:
+        import oracle
+        oracle.build()
+        xa, xb, y = sets[(steps - 1) % n_sets]
+        s_idx = (steps - 1) % n_sets
+        rows = [0, M // 2 + 1, M - 1]
+        b_host = oracle.fill_uniform_bf16(N * K, 137 + N_total + 1000 * s_idx)
+        worst = 0.0
+        for r in rows:
+            a_row = oracle.fill_uniform_bf16(K, 42 + M + 1000 * s_idx, r * K)
+            ref = oracle.gemm_nt(a_row, b_host, 1, K, N)
+            got = y.read_bytes(r * N * 4, N * 4, np.float32)
+            worst = max(worst, float(np.abs(ref[0] - got).max()))
+        parity = {"sampled_rows": rows, "max_abs_err": worst, "tol": 5e-3 * (K / 256) ** 0.5}
+        if worst > parity["tol"]:
+            print(json.dumps({"error": "parity check failed", "parity": parity}), flush=True)
+            sys.exit(1)
+
+    # ---- end to end through the C ABI with pinned host buffers (copies inside the timed region)
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(1, min(steps, 10 if not sharded else 2))
+        a_host = torch.empty(M * K, dtype=torch.int16).pin_memory()
+        b_host_t = torch.empty(N * K, dtype=torch.int16).pin_memory()
+        y_host = torch.empty(M * N, dtype=torch.float32).pin_memory()
+        xa, xb, y = sets[0]
+        a_host.numpy()[:] = xa.read(M * K * 2, np.int16)
+        b_host_t.numpy()[:] = xb.read(N * K * 2, np.int16)
+        a_np, b_np, y_np = a_host.numpy(), b_host_t.numpy(), y_host.numpy()
+        C = __import__("ctypes")
+
+        def e2e_step():
+            xa.write(a_np)
+            xb.write(b_np)
+            rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K, **gemm_kw)
+            t0._check(t0.lib().t0_rt_read_f32(rt._h, y._h, M * N, y_np.ctypes.data_as(C.c_void_p)))
+
+        e2e_step()
+        barrier()
+        t_start = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        dt = time.perf_counter() - t_start
+        td = torch.tensor([dt], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(td, op=dist.ReduceOp.MAX)
+        e2e = {"value": flops_per_step * e2e_steps / float(td.item()) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": (M * K * 2 + N * K * 2) * (world if sharded else 1),
+               "d2h_bytes_per_step": M * N * 4 * (world if sharded else 1), "steps": e2e_steps}
+
+    if rank == 0:
+        peaks = measured_peaks()
+        # the kernel is timed inside a run of back-to-back launches: a burst for the default run, a long step when sharded
+        peak = peaks["bf16_tflops_sustained"] if sharded else peaks["bf16_tflops"]
+        per_launch_ms = ms_max / steps
+        achieved = 2.0 * M * N * K / (per_launch_ms * 1e-3) / 1e12     # this rank's kernel: algorithmic FLOPs / event time
+        line = {"metric": "bf16_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": ms_max / steps, "higher_is_better": True,
+                "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": name, "m": M, "n": N_total, "k": K, "layout": "NT", "out": "f32",
+                           "kernel": (cfg if not args.tile_n else cfg.copy(tile_m=128, tile_n=tile_n, wgp_mode=0)).name(), "per_rank_n": N, "input_sets": n_sets,
+                           "l2": f"{n_sets} resident operand sets of {set_bytes >> 20} MiB rotate (> 126 MB L2)" if n_sets > 1
+                                 else f"operands {set_bytes >> 20} MiB per rank (> 126 MB L2)",
+                           "pct_of_nominal_dense_peak": round(100.0 * value / world / 2250.0, 1)},
+                "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                             "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peaks['source']} "
+                             f"({'sustained' if sharded else 'burst'} cuBLAS bf16)"},
+                "clocks": clocks, "gpu_launches": int(launches), "parity": parity}
+        if e2e:
+            line["e2e"] = e2e
+        if not args.no_cpu and world == 1:
+            import oracle
+            rows = max(32, min(M, int(M * (2.0 * 4096 ** 3) / (2.0 * M * N_total * K))))
+            tf, sec, cores = cpu_baseline(oracle, M, N_total, K, rows)
+            what = f"the full {M}x{N_total}x{K} GEMM" if rows == M else f"rows 0..{rows - 1} of {M} (extrapolate linearly)"
+            line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"{what}, best of 3, {sec:.2f} s per pass"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    rt.close()
+
+
+if __name__ == "__main__":
+    main()

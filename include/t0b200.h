@@ -223,8 +223,16 @@ int t0_rt_dispatch(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], c
 int t0_rt_dispatch_async(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len, size_t* out_slot);
 /* dispatch_bench (gpu_context.rs:363-374): submit + wait without validation */
 int t0_rt_dispatch_bench(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len);
+/* prefill_dispatch::DispatchQueue::{submit, flush} (src/t0/prefill_dispatch.rs:61-206): fire-and-forget submits that only
+ * check the poison flag, then one wait.  The stream is the queue, so a "queue" is the runtime itself. */
+int t0_rt_submit(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len);
+int t0_rt_flush(t0_runtime* rt);
 /* number of kernels this runtime has launched (all kinds) since creation */
 uint64_t t0_rt_launch_count(const t0_runtime* rt);
+/* Tracing aid (the reference reads SHADER_CYCLES for the same purpose, src/t0/ir.rs:571): CTA 0 of every GEMM kernel
+ * stamps the SM cycle counter and the nanosecond timer at entry and exit.  Returns the SM clock (MHz) the last GEMM kernel
+ * actually ran at and, optionally, that CTA's lifetime in microseconds.  Waits for the stream. */
+int t0_rt_last_kernel_clock(t0_runtime* rt, double* sm_mhz, double* kernel_us);
 /* CUDA-event stopwatch on the runtime's stream: start records an event, stop records another, waits and returns ms */
 int t0_rt_timer_start(t0_runtime* rt);
 int t0_rt_timer_stop(t0_runtime* rt, float* ms);
@@ -240,7 +248,9 @@ typedef struct t0_gemm_args {
     uint32_t tile_n;        /* 0 = choose; else 32/64/128/256 */
     uint32_t split_k;       /* 0/1 = none */
     uint8_t transpose, epilogue, out_bf16, planes;
-    uint8_t swap_grid, pair_cta, _pad[2];
+    uint8_t swap_grid;
+    uint8_t pair_cta;       /* 0 = choose by shape, 1 = two-CTA pair kernel (256 x 256 tiles, NT only), 2 = single-CTA kernel */
+    uint8_t _pad[2];
     /* TileIR epilogue chain (used when n_tile_epilogue > 0; epilogue above is then ignored) */
     uint8_t n_tile_epilogue;
     uint8_t tile_epilogue[T0_TILE_MAX_EPILOGUE];
@@ -248,6 +258,9 @@ typedef struct t0_gemm_args {
     float scale, clamp_min, clamp_max;
 } t0_gemm_args;
 int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
+/* `count` launches from an array, submitted back to back from native code (the batch form of the above; the reference's
+ * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
+int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 
 /* ------------------------------------------------------- seeded inputs */
 /* Device-side generators for benchmark-sized inputs: element i of the stream (seed) gets the same bits as the

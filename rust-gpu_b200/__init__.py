@@ -457,6 +457,12 @@ class GpuRuntime:
         ka = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
         _check(lib().t0_rt_dispatch_bench(self._h, kernel._h, g, ka, len(kernargs)))
 
+    def last_kernel_clock(self) -> tuple[float, float]:
+        """(SM MHz, microseconds) measured inside the last GEMM kernel by its CTA 0."""
+        mhz, us = C.c_double(), C.c_double()
+        _check(lib().t0_rt_last_kernel_clock(self._h, C.byref(mhz), C.byref(us)))
+        return mhz.value, us.value
+
     def timer_start(self) -> None:
         _check(lib().t0_rt_timer_start(self._h))
 
@@ -465,15 +471,47 @@ class GpuRuntime:
         _check(lib().t0_rt_timer_stop(self._h, C.byref(ms)))
         return ms.value
 
+    def submit(self, kernel: GpuKernel, grid, kernargs: bytes) -> None:
+        """``DispatchQueue::submit`` (prefill_dispatch.rs:61-100): no wait, no pointer validation."""
+        g = (C.c_uint32 * 3)(*grid)
+        ka = (C.c_uint8 * len(kernargs)).from_buffer_copy(kernargs)
+        _check(lib().t0_rt_submit(self._h, kernel._h, g, ka, len(kernargs)))
+
+    def flush(self) -> None:
+        _check(lib().t0_rt_flush(self._h))
+
+    @staticmethod
+    def gemm_args(x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
+                  transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False,
+                  swap_grid: bool = True, pair_cta: int = 0, tile_epilogue: list[str] | None = None, scale: float = 1.0,
+                  clamp_min: float = 0.0, clamp_max: float = 0.0) -> GemmArgs:
+        a = GemmArgs()
+        a.x, a.b, a.y, a.bias = x, b, y, bias
+        a.m, a.n, a.k, a.tile_n, a.split_k = m, n, k, tile_n, split_k
+        a.transpose, a.epilogue, a.out_bf16, a.planes, a.swap_grid = transpose, epilogue, int(out_bf16), int(planes), int(swap_grid)
+        a.pair_cta = pair_cta
+        ops = tile_epilogue or []
+        a.n_tile_epilogue = len(ops)
+        for i, o in enumerate(ops):
+            a.tile_epilogue[i] = TEPI[o]
+        a.scale, a.clamp_min, a.clamp_max = scale, clamp_min, clamp_max
+        return a
+
+    def gemm_batch(self, args_list: list[GemmArgs]) -> None:
+        """``t0_gemm_launch_batch``: the launches are submitted back to back from native code."""
+        arr = (GemmArgs * len(args_list))(*args_list)
+        _check(lib().t0_gemm_launch_batch(self._h, arr, len(args_list)))
+
     def gemm(self, x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
              transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False, swap_grid: bool = True,
-             tile_epilogue: list[str] | None = None, scale: float = 1.0, clamp_min: float = 0.0,
+             pair_cta: int = 0, tile_epilogue: list[str] | None = None, scale: float = 1.0, clamp_min: float = 0.0,
              clamp_max: float = 0.0) -> None:
         """Explicit-argument launch (``t0_gemm_launch``); device addresses as integers."""
         a = GemmArgs()
         a.x, a.b, a.y, a.bias = x, b, y, bias
         a.m, a.n, a.k, a.tile_n, a.split_k = m, n, k, tile_n, split_k
         a.transpose, a.epilogue, a.out_bf16, a.planes, a.swap_grid = transpose, epilogue, int(out_bf16), int(planes), int(swap_grid)
+        a.pair_cta = pair_cta
         ops = tile_epilogue or []
         a.n_tile_epilogue = len(ops)
         for i, o in enumerate(ops):
@@ -548,6 +586,7 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_device", i32, vp)
     sig("t0_rt_sm_count", i32, vp)
     sig("t0_rt_launch_count", u64, vp)
+    sig("t0_rt_last_kernel_clock", i32, vp, C.POINTER(C.c_double), C.POINTER(C.c_double))
     sig("t0_rt_timer_start", i32, vp)
     sig("t0_rt_timer_stop", i32, vp, C.POINTER(C.c_float))
     sig("t0_rt_alloc", i32, vp, sz, C.POINTER(vp))
@@ -576,6 +615,9 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_dispatch_async", i32, vp, vp, u32p, u8p, sz, C.POINTER(sz))
     sig("t0_rt_dispatch_bench", i32, vp, vp, u32p, u8p, sz)
     sig("t0_gemm_launch", i32, vp, C.POINTER(GemmArgs))
+    sig("t0_gemm_launch_batch", i32, vp, C.POINTER(GemmArgs), sz)
+    sig("t0_rt_submit", i32, vp, vp, u32p, u8p, sz)
+    sig("t0_rt_flush", i32, vp)
     sig("t0_fill_uniform_bf16", i32, vp, u64, u64, u64, u64)
     sig("t0_fill_u32", i32, vp, u64, u64, u64, u64)
     sig("t0_fill_range_bf16", i32, vp, u64, u64, u64, u64, C.c_float, C.c_float)

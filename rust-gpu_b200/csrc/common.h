@@ -23,11 +23,11 @@ struct B200Limits {
     uint32_t n_sms = 148;
     uint32_t smem_per_cta = 227 * 1024;
     uint32_t tmem_cols = 512;
-    double sm_clock_ghz = 1.75;          // typical clock under a dense tensor load
+    double sm_clock_ghz = 1.6;           // typical clock under a dense tensor load (power management, not the 1.965 max)
     double hbm_gbs = 6500.0;             // measured copy bandwidth of this class of part
     double mma_flops_per_clk = 8192.0;   // dense bf16 per SM per clock
-    double smem_bytes_per_clk = 128.0;
-    double launch_us = 3.0;
+    double smem_bytes_per_clk = 100.0;   // effective operand feed per SM; 128x128 tiles measure ~0.76 of 128x256
+    double launch_us = 8.0;              // launch + prologue + drain between dependent kernels, measured
 };
 
 // The tile the sm_100a kernel actually runs for a requested (tile_m, tile_n):

@@ -3,10 +3,11 @@
 // roofline/occupancy model), the legacy hand table (src/t0/gemm_gen.rs:351-404), TileIR's static
 // selector (src/t0/tile_ir.rs:740-870) and the process-level memo (src/t0/prefill_spec_cache.rs).
 //
-// The search space is re-derived for B200: a CTA always owns 128 output rows (one UMMA M=128
-// instruction shape, accumulator in tensor memory), tile_n is 32/64/128/256 columns, tile_k is one
-// 128-byte swizzle atom (64 bf16), split-K is 1..8.  The score is predicted time =
-// max(tensor time with wave quantisation over 148 SMs, HBM time on the algorithmic bytes) + launch.
+// The search space is re-derived for B200: a CTA owns 128 output rows (one UMMA M=128 instruction
+// shape, accumulator in tensor memory) or a CTA pair owns 256 x 256 (`wgp_mode`); tile_n is
+// 32/64/128/256 columns, tile_k is one 128-byte swizzle atom (64 bf16), split-K is 1..8.  The score
+// is predicted time = max(tensor time with wave quantisation over the SMs, HBM time on the
+// algorithmic bytes) + launch (+ the split-K reduction pass).
 #include "common.h"
 
 #include <algorithm>
@@ -24,23 +25,36 @@ struct Candidate {
     double pred_tflops;
 };
 
-static double predict_us(const B200Limits& hw, uint32_t m, uint32_t n, uint32_t k, uint32_t tn, uint32_t sk) {
-    const double tiles = (double)ceil_div(m, 128) * ceil_div(n, tn) * sk;
-    const double waves = std::ceil(tiles / hw.n_sms);
+// Measured main-loop cost per 64-deep k-block on B200 (SM cycles, from the in-kernel cycle probe at 2048^3..8192^3):
+// the tensor pipe needs tn/2 cycles per UMMA and four UMMAs per k-block, but narrow tiles are bound by the
+// shared-memory operand feed (A is re-read for every UMMA) and the single-CTA 128x256 tile by L2->SM latency with
+// only four stages in flight.  The CTA pair (256x256 over two SMs) comes closest to the pipe's 512 cycles.
+static double kblock_cycles(uint32_t tn, bool pair) {
+    if (pair) return 590.0;
+    switch (tn) {
+        case 256: return 740.0;
+        case 128: return 540.0;
+        case 64: return 400.0;
+        default: return 330.0;
+    }
+}
+
+static double predict_us(const B200Limits& hw, uint32_t m, uint32_t n, uint32_t k, uint32_t tn, uint32_t sk, bool pair) {
+    const double tiles = (double)ceil_div(m, pair ? 256 : 128) * ceil_div(n, tn) * sk;
+    const double slots = pair ? hw.n_sms / 2 : hw.n_sms;
+    const double rounds = std::ceil(tiles / slots);
     const double kb = std::ceil((double)k / sk / 64.0);
-    // one k-block = four UMMA 128 x tn x 16 instructions; the tensor pipe needs tn/2 clocks each,
-    // the shared-memory read port (A 4 KiB + B tn*32 B per instruction) may need more
-    const double mma_clk = std::max(tn / 2.0, (4096.0 + tn * 32.0) / hw.smem_bytes_per_clk);
-    const double tile_clk = kb * 4.0 * mma_clk + 1500.0;
-    const double tensor_us = waves * tile_clk / (hw.sm_clock_ghz * 1e3);
-    // memory: A once per column of tiles is an L2 hit after the first; count algorithmic bytes,
-    // plus the partial planes a split-K reduction writes and re-reads
+    const double tile_clk = kb * kblock_cycles(tn, pair) + 3000.0;   // + pipeline fill and the exposed part of the epilogue
+    const double tensor_us = rounds * tile_clk / (hw.sm_clock_ghz * 1e3);
+    // memory: count algorithmic bytes, plus the partial planes a split-K reduction writes and re-reads
     double bytes = 2.0 * m * k + 2.0 * (double)n * k + 4.0 * (double)m * n;
-    if (sk > 1) bytes += 2.0 * 4.0 * (double)m * n * sk;
+    if (sk > 1) bytes += 4.0 * (double)m * n * sk;
     const double mem_us = bytes / (hw.hbm_gbs * 1e3);
     // a partially filled machine cannot pull full bandwidth: scale by the fraction of SMs busy
-    const double fill = std::min(1.0, tiles / hw.n_sms);
-    return std::max(tensor_us, mem_us / std::max(fill, 0.05)) + hw.launch_us;
+    const double fill = std::min(1.0, tiles * (pair ? 2.0 : 1.0) / hw.n_sms);
+    // split-K runs a second, serialised kernel: it reads sk planes and writes y
+    const double reduce_us = sk > 1 ? hw.launch_us + (sk + 1.0) * 4.0 * (double)m * n / (hw.hbm_gbs * 1e3) : 0.0;
+    return std::max(tensor_us, mem_us / std::max(fill, 0.05)) + hw.launch_us + reduce_us;
 }
 
 static std::vector<Candidate> schedule(uint32_t m, uint32_t n, uint32_t k) {
@@ -49,23 +63,28 @@ static std::vector<Candidate> schedule(uint32_t m, uint32_t n, uint32_t k) {
     if (m == 0 || n == 0 || k == 0) return out;
     static const uint32_t tns[] = {256, 128, 64, 32};
     static const uint32_t sks[] = {1, 2, 4, 8};
-    for (uint32_t tn : tns) {
-        if (tn > 32 && tn / 2 >= n && n > 0) continue;   // a tile more than twice as wide as N wastes the pipe
-        for (uint32_t sk : sks) {
-            if (sk > 1) {
-                if (k % (sk * 64) != 0) continue;        // same rule as cost_model.rs:500-502 with tile_k = 64
-                if (sk > k / 64) continue;
-            }
-            for (int swap = 1; swap >= 0; --swap) {
-                Candidate c;
-                c.cfg = b200_default_config(tn, sk, swap != 0);
-                c.pred_us = predict_us(hw, m, n, k, tn, sk);
-                // prefer N-fastest rasterisation when A (the M side) is the larger operand to keep
-                // resident, M-fastest otherwise; a tie-break only
-                const bool want_swap = m >= n;
-                if ((swap != 0) != want_swap) c.pred_us *= 1.001;
-                c.pred_tflops = 2.0 * m * (double)n * k / (c.pred_us * 1e6);
-                out.push_back(c);
+    for (int pair = 1; pair >= 0; --pair) {
+        for (uint32_t tn : tns) {
+            if (pair && tn != 256) continue;                 // the pair kernel is worth it with 256-wide tiles only
+            if (pair && (m <= 128 || n <= 128)) continue;
+            if (tn > 32 && tn / 2 >= n && n > 0) continue;   // a tile more than twice as wide as N wastes the pipe
+            for (uint32_t sk : sks) {
+                if (sk > 1) {
+                    if (k % (sk * 64) != 0) continue;        // same rule as cost_model.rs:500-502 with tile_k = 64
+                    if (sk > k / 64) continue;
+                }
+                for (int swap = 1; swap >= 0; --swap) {
+                    Candidate c;
+                    c.cfg = b200_default_config(tn, sk, swap != 0);
+                    if (pair) { c.cfg.tile_m = 256; c.cfg.wgp_mode = 1; }
+                    c.pred_us = predict_us(hw, m, n, k, tn, sk, pair != 0);
+                    // prefer N-fastest rasterisation when A (the M side) is the larger operand to keep
+                    // resident, M-fastest otherwise; a tie-break only
+                    const bool want_swap = m >= n;
+                    if ((swap != 0) != want_swap) c.pred_us *= 1.001;
+                    c.pred_tflops = 2.0 * m * (double)n * k / (c.pred_us * 1e6);
+                    out.push_back(c);
+                }
             }
         }
     }

@@ -1,0 +1,220 @@
+// Pieces shared by the single-CTA and the CTA-pair GEMM kernels: launch parameters, the persistent
+// tile schedule, the epilogue/store of one accumulator chunk, and the TMA tensor-map builders.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cstdlib>
+#include <mutex>
+
+#include "kernels.h"
+#include "ptx_sm100.cuh"
+
+namespace t0 {
+namespace gemm {
+
+constexpr uint32_t BM = 128;            // accumulator rows per CTA (one UMMA M=128 half or whole)
+constexpr uint32_t BK = 64;             // one 128-byte swizzle atom of bf16
+constexpr uint32_t kAStageBytes = BM * BK * 2;
+
+struct KParams {
+    void* y;
+    const float* bias;
+    int* status;
+    unsigned long long* probe;   // optional: {SM cycles, nanoseconds} of CTA 0, for the in-kernel clock estimate
+    uint64_t plane_stride;
+    uint32_t M, N, K;
+    uint32_t tiles_m, tiles_n, split_k;
+    uint32_t kb_per_split;
+    uint32_t swap_grid, raster_group;
+    uint32_t out_bf16, epilogue, n_ops;
+    float scale, clamp_min, clamp_max;
+    uint8_t ops[T0_TILE_MAX_EPILOGUE];
+};
+
+struct WorkItem { uint32_t m_blk, n_blk, split; };
+
+__device__ __forceinline__ WorkItem decode_work(uint32_t w, const KParams& p) {
+    WorkItem it;
+    it.split = w % p.split_k;
+    const uint32_t t = w / p.split_k;
+    const uint32_t tiles_fast = p.swap_grid ? p.tiles_n : p.tiles_m;
+    const uint32_t tiles_slow = p.swap_grid ? p.tiles_m : p.tiles_n;
+    const uint32_t group_size = p.raster_group * tiles_fast;
+    const uint32_t g = t / group_size;
+    const uint32_t first = g * p.raster_group;
+    const uint32_t gsz = min(p.raster_group, tiles_slow - first);
+    const uint32_t r = t - g * group_size;
+    const uint32_t slow = first + r % gsz;
+    const uint32_t fast = r / gsz;
+    it.m_blk = p.swap_grid ? slow : fast;
+    it.n_blk = p.swap_grid ? fast : slow;
+    return it;
+}
+
+__device__ __forceinline__ float sigmoid_seq(float x) {
+    // tile_ir.rs:3448-3477: negate, scale by log2(e), exp2, add one, reciprocal
+    const float e = exp2f((-x) * 1.44269504088896340736f);
+    return __frcp_rn(e + 1.0f);
+}
+
+__device__ __forceinline__ float apply_chain(float v, float bias, const KParams& p) {
+    for (uint32_t o = 0; o < p.n_ops; ++o) {
+        switch (p.ops[o]) {
+            case T0_TEPI_BIAS_ADD: v = v + bias; break;
+            case T0_TEPI_SCALE: v = v * p.scale; break;
+            case T0_TEPI_RELU: v = fmaxf(v, 0.0f); break;
+            case T0_TEPI_SILU: v = v * sigmoid_seq(v); break;
+            case T0_TEPI_GELU: v = v * sigmoid_seq(v * 1.702f); break;
+            case T0_TEPI_ABS: v = fabsf(v); break;
+            case T0_TEPI_NEG: v = -v; break;
+            case T0_TEPI_CLAMP: v = fminf(fmaxf(v, p.clamp_min), p.clamp_max); break;
+            default: break;
+        }
+    }
+    return v;
+}
+
+
+// CTA 0 stamps the SM cycle counter and the global nanosecond timer at entry and exit; the host turns
+// the two deltas into the SM clock the kernel actually ran at (power management moves it).
+struct ClockProbe {
+    long long c0 = 0;
+    unsigned long long t0 = 0;
+    __device__ __forceinline__ void begin(const KParams& p) {
+        if (p.probe && blockIdx.x == 0 && threadIdx.x == 0) { c0 = clock64(); t0 = ptx::globaltimer_ns(); }
+    }
+    __device__ __forceinline__ void end(const KParams& p) {
+        if (p.probe && blockIdx.x == 0 && threadIdx.x == 0) {
+            p.probe[0] = (unsigned long long)(clock64() - c0);
+            p.probe[1] = ptx::globaltimer_ns() - t0;
+        }
+    }
+};
+
+// One 32-column chunk of one accumulator row: epilogue, then the store (vectorised when the row
+// stride and base allow 16-byte accesses, element-wise with bounds checks otherwise).
+__device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r)[32], uint32_t row, bool row_ok, uint32_t col0,
+                                            uint32_t split, bool vec32, bool vec16) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (p.n_ops) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float bj = (p.bias && col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
+            v[j] = apply_chain(v[j], bj, p);
+        }
+    } else if (p.epilogue != T0_EPI_STORE_F32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float bj = (p.bias && col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
+            v[j] += bj;
+            if (p.epilogue == T0_EPI_BIAS_ADD_RELU_STORE_F32) v[j] = fmaxf(v[j], 0.0f);
+        }
+    }
+    if (!row_ok) return;
+    const size_t off = (size_t)split * p.plane_stride + (size_t)row * p.N + col0;
+    if (!p.out_bf16) {
+        float* dst = (float*)p.y + off;
+        if (vec32 && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ((float4*)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        } else {
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = v[j];
+        }
+    } else {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.y + off;
+        if (vec16 && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                uint4 q;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                q.x = *(uint32_t*)&h0; q.y = *(uint32_t*)&h1; q.z = *(uint32_t*)&h2; q.w = *(uint32_t*)&h3;
+                ((uint4*)dst)[j] = q;
+            }
+        } else {
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ launch (host)
+
+// Launch with programmatic stream serialisation so the prologue of this grid overlaps the tail of the
+// previous one (T0_NO_PDL=1 in the environment turns it off).
+template <typename Kernel>
+inline cudaError_t launch_pdl(Kernel kern, uint32_t grid, uint32_t block, uint32_t smem, cudaStream_t stream,
+                              const CUtensorMap& ma, const CUtensorMap& mb, const KParams& p) {
+    static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
+}
+
+// ------------------------------------------------------------------ tensor maps (host)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// 3-D view [split][rows][k_per_split] of a row-major [rows][ld] bf16 matrix (K contiguous, ld >= K).
+inline int make_map_kmajor(CUtensorMap* map, const void* base, uint32_t rows, uint32_t ld, uint32_t k_per_split, uint32_t split,
+                    uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {k_per_split, rows, split};
+    // with a single split the third dimension has extent 1; its stride only has to be a legal value
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, split > 1 ? (cuuint64_t)k_per_split * 2 : (cuuint64_t)ld * 2 * rows};
+    cuuint32_t box[3] = {BK, box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (K-major, rows=%u ld=%u) failed: %d", rows, ld, (int)r);
+    return T0_OK;
+}
+
+// 3-D view [split][k_per_split][N] of a row-major [K][ld] bf16 matrix (N contiguous, ld >= N).
+inline int make_map_nmajor(CUtensorMap* map, const void* base, uint32_t N, uint32_t ld, uint32_t k_per_split, uint32_t split) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {N, k_per_split, split};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)k_per_split * ld * 2};   // always a multiple of 16
+    cuuint32_t box[3] = {64, BK, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (N-major, N=%u) failed: %d", N, (int)r);
+    return T0_OK;
+}
+
+
+}  // namespace gemm
+}  // namespace t0

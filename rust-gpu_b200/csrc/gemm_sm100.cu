@@ -16,77 +16,17 @@
 // error word the host turns into an error (no trap, no unbounded spin).
 #include "kernels.h"
 #include "ptx_sm100.cuh"
+#include "gemm_common.cuh"
 
-#include <cuda_bf16.h>
-#include <mutex>
 
 namespace t0 {
 
 namespace {
 
-constexpr uint32_t BM = 128;
-constexpr uint32_t BK = 64;
+using namespace gemm;
 constexpr uint32_t kThreads = 192;
-constexpr uint32_t kAStageBytes = BM * BK * 2;   // 16 KiB
 
 __host__ __device__ constexpr uint32_t stages_for(uint32_t bn) { return bn == 256 ? 4 : bn == 128 ? 6 : 8; }
-
-struct KParams {
-    void* y;
-    const float* bias;
-    int* status;
-    uint64_t plane_stride;
-    uint32_t M, N, K;
-    uint32_t tiles_m, tiles_n, split_k;
-    uint32_t kb_per_split;
-    uint32_t swap_grid, raster_group;
-    uint32_t out_bf16, epilogue, n_ops;
-    float scale, clamp_min, clamp_max;
-    uint8_t ops[T0_TILE_MAX_EPILOGUE];
-};
-
-struct WorkItem { uint32_t m_blk, n_blk, split; };
-
-__device__ __forceinline__ WorkItem decode_work(uint32_t w, const KParams& p) {
-    WorkItem it;
-    it.split = w % p.split_k;
-    const uint32_t t = w / p.split_k;
-    const uint32_t tiles_fast = p.swap_grid ? p.tiles_n : p.tiles_m;
-    const uint32_t tiles_slow = p.swap_grid ? p.tiles_m : p.tiles_n;
-    const uint32_t group_size = p.raster_group * tiles_fast;
-    const uint32_t g = t / group_size;
-    const uint32_t first = g * p.raster_group;
-    const uint32_t gsz = min(p.raster_group, tiles_slow - first);
-    const uint32_t r = t - g * group_size;
-    const uint32_t slow = first + r % gsz;
-    const uint32_t fast = r / gsz;
-    it.m_blk = p.swap_grid ? slow : fast;
-    it.n_blk = p.swap_grid ? fast : slow;
-    return it;
-}
-
-__device__ __forceinline__ float sigmoid_seq(float x) {
-    // tile_ir.rs:3448-3477: negate, scale by log2(e), exp2, add one, reciprocal
-    const float e = exp2f((-x) * 1.44269504088896340736f);
-    return __frcp_rn(e + 1.0f);
-}
-
-__device__ __forceinline__ float apply_chain(float v, float bias, const KParams& p) {
-    for (uint32_t o = 0; o < p.n_ops; ++o) {
-        switch (p.ops[o]) {
-            case T0_TEPI_BIAS_ADD: v = v + bias; break;
-            case T0_TEPI_SCALE: v = v * p.scale; break;
-            case T0_TEPI_RELU: v = fmaxf(v, 0.0f); break;
-            case T0_TEPI_SILU: v = v * sigmoid_seq(v); break;
-            case T0_TEPI_GELU: v = v * sigmoid_seq(v * 1.702f); break;
-            case T0_TEPI_ABS: v = fabsf(v); break;
-            case T0_TEPI_NEG: v = -v; break;
-            case T0_TEPI_CLAMP: v = fminf(fmaxf(v, p.clamp_min), p.clamp_max); break;
-            default: break;
-        }
-    }
-    return v;
-}
 
 template <uint32_t BN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -137,6 +77,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    // everything above touched only shared and tensor memory; global memory comes after the previous grid is done
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+    ClockProbe probe;
+    probe.begin(p);
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -229,54 +174,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * BN + c * 32, r);
                 ptx::tmem_ld_wait();
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-                if (p.n_ops) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float bj = (p.bias && col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
-                        v[j] = apply_chain(v[j], bj, p);
-                    }
-                } else if (p.epilogue != T0_EPI_STORE_F32) {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const float bj = (p.bias && col0 + j < p.N) ? __ldg(p.bias + col0 + j) : 0.0f;
-                        v[j] += bj;
-                        if (p.epilogue == T0_EPI_BIAS_ADD_RELU_STORE_F32) v[j] = fmaxf(v[j], 0.0f);
-                    }
-                }
-                if (row_ok) {
-                    const size_t off = (size_t)wi.split * p.plane_stride + (size_t)row * p.N + col0;
-                    if (!p.out_bf16) {
-                        float* dst = (float*)p.y + off;
-                        if (vec32 && col0 + 32 <= p.N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                ((float4*)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                        } else {
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) dst[j] = v[j];
-                        }
-                    } else {
-                        __nv_bfloat16* dst = (__nv_bfloat16*)p.y + off;
-                        if (vec16 && col0 + 32 <= p.N) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 q;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                                q.x = *(uint32_t*)&h0; q.y = *(uint32_t*)&h1; q.z = *(uint32_t*)&h2; q.w = *(uint32_t*)&h3;
-                                ((uint4*)dst)[j] = q;
-                            }
-                        } else {
-                            for (int j = 0; j < 32; ++j)
-                                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    }
-                }
+                store_chunk(p, r, row, row_ok, col0, wi.split, vec32, vec16);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -286,6 +184,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
     // ---------------------------------------------------------------- common exit
     __syncwarp();
+    probe.end(p);
     if (*abort_flag) {
         // give copies and UMMAs already in flight time to land before shared and tensor memory go away
         for (int i = 0; i < 64; ++i) __nanosleep(1000);
@@ -300,54 +199,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 // ------------------------------------------------------------------ host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-// 3-D view [split][rows][k_per_split] of a row-major [rows][ld] bf16 matrix (K contiguous, ld >= K).
-int make_map_kmajor(CUtensorMap* map, const void* base, uint32_t rows, uint32_t ld, uint32_t k_per_split, uint32_t split,
-                    uint32_t box_rows) {
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[3] = {k_per_split, rows, split};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)k_per_split * 2};
-    cuuint32_t box[3] = {BK, box_rows, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (K-major, rows=%u ld=%u) failed: %d", rows, ld, (int)r);
-    return T0_OK;
-}
-
-// 3-D view [split][k_per_split][N] of a row-major [K][ld] bf16 matrix (N contiguous, ld >= N).
-int make_map_nmajor(CUtensorMap* map, const void* base, uint32_t N, uint32_t ld, uint32_t k_per_split, uint32_t split) {
-    EncodeTiledFn enc = get_encode_fn();
-    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[3] = {N, k_per_split, split};
-    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)k_per_split * ld * 2};
-    cuuint32_t box[3] = {64, BK, 1};
-    cuuint32_t estr[3] = {1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (N-major, N=%u) failed: %d", N, (int)r);
-    return T0_OK;
-}
-
 template <uint32_t BN, bool B_MN>
 int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& p, uint32_t grid, cudaStream_t stream) {
     auto kern = gemm_bf16_tcgen05_kernel<BN, B_MN>;
@@ -360,8 +211,7 @@ int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KParams&
         if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaFuncSetAttribute(smem=%u): %s", smem, cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    kern<<<grid, kThreads, smem, stream>>>(ma, mb, p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(kern, grid, kThreads, smem, stream, ma, mb, p);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
 }
@@ -392,7 +242,7 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
 
     KParams p;
     memset(&p, 0, sizeof p);
-    p.y = g.y; p.bias = g.bias; p.status = g.status; p.plane_stride = g.plane_stride;
+    p.y = g.y; p.bias = g.bias; p.status = g.status; p.probe = g.probe; p.plane_stride = g.plane_stride;
     p.M = g.m; p.N = g.n; p.K = g.k;
     p.tiles_m = ceil_div(g.m, BM); p.tiles_n = ceil_div(g.n, bn); p.split_k = split;
     p.kb_per_split = ceil_div(kps, BK);

@@ -74,6 +74,7 @@ static const std::vector<Preset>& presets() {
         {"b200_128x64_k64",    mk(128, 64, 64, 192, true, true, 1)},
         {"b200_128x128_k64",   mk(128, 128, 64, 192, true, true, 1)},
         {"b200_128x256_k64",   mk(128, 256, 64, 192, true, true, 1)},
+        {"b200_pair_256x256_k64", mk(256, 256, 64, 192, true, true, 1)},
     };
     return p;
 }
@@ -241,6 +242,7 @@ int t0_gemm_config_is_feasible(const t0_gemm_config* cfg) { return config_shape_
 
 uint32_t t0_gemm_config_lds_total(const t0_gemm_config* cfg) {
     if (!cfg) return 0;
+    if (cfg->wgp_mode && cfg->tile_m == 256 && cfg->tile_n == 256) return 6 * (128 * 64 * 2 + 128 * 64 * 2) + 1024;   // per CTA of the pair
     uint32_t bn = snap_tile_n(cfg->tile_n);
     uint32_t stage = 128 * 64 * 2 + bn * 64 * 2;
     uint32_t stages = bn == 256 ? 4 : bn == 128 ? 6 : 8;

@@ -27,12 +27,17 @@ struct GemmLaunch {
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
     float scale, clamp_min, clamp_max;
     int* status;          // device error word
+    unsigned long long* probe;   // optional device buffer of two words (cycles, ns) written by CTA 0
     uint32_t n_sms;
 };
 
 // Launches the tcgen05 GEMM. Requirements (checked): x and b 16-byte aligned, row strides and
 // K / split_k multiples of 8 elements, K % split_k == 0.  Returns a T0_* code.
 int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream);
+
+// The CTA-pair form (cta_group::2; 256 x 256 tiles, or 256 x 128 when tile_n <= 128), NT layout only.
+int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream);
+uint32_t gemm_pair_smem_bytes(uint32_t pair_n);
 
 // y[i] = sum_s planes[s][i] in split order, then the epilogue; K4.
 int launch_splitk_reduce(const float* planes, void* y, const float* bias, uint32_t m, uint32_t n, uint32_t split_k,

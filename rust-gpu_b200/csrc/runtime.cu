@@ -50,6 +50,7 @@ struct t0_runtime {
     std::atomic<size_t> slot{0};
     int* d_status = nullptr;     // device error word written by kernels whose bounded wait expired
     int* h_status = nullptr;     // pinned mirror
+    unsigned long long* d_probe = nullptr;   // {cycles, ns} of the last GEMM kernel's CTA 0
     Scratch scratch_a, scratch_b, scratch_planes;
 };
 
@@ -113,6 +114,7 @@ struct GemmRequest {
     uint32_t m, n, k;
     uint32_t tile_n, split_k;
     bool nn, out_bf16, planes, swap_grid;
+    int pair;                  // 0 = choose by shape, 1 = CTA-pair kernel, 2 = single-CTA kernel
     uint64_t plane_stride;     // elements; only when planes
     uint8_t epilogue, n_ops;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
@@ -156,10 +158,15 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q) {
     g.x = (const void*)q.x; g.b = (const void*)q.b;
     g.m = q.m; g.n = q.n; g.k = q.k;
     g.nn = q.nn; g.swap_grid = q.swap_grid;
-    g.status = rt->d_status; g.n_sms = (uint32_t)rt->sm_count;
+    g.status = rt->d_status; g.probe = rt->d_probe; g.n_sms = (uint32_t)rt->sm_count;
     g.split_k = split;
     g.tile_n = q.tile_n ? snap_tile_n(q.tile_n) : choose_tile_n(rt, q.m, q.n, q.k, split);
     if (q.nn && g.tile_n < 64) g.tile_n = 64;
+    // the CTA-pair kernel (256 x 256 tiles) pays off once there are enough tiles to fill the machine
+    const bool pair_fits = !q.nn && (uint64_t)ceil_div(q.m, 256) * ceil_div(q.n, 256) * split >= (uint64_t)rt->sm_count / 2;
+    const bool use_pair = q.pair == 1 ? !q.nn : (q.pair == 0 && pair_fits && (q.tile_n == 0 || q.tile_n >= 256));
+    if (use_pair) g.tile_n = q.tile_n;   // 0/256 -> 256-wide pair tiles, <= 128 -> 128-wide
+    auto launch = [&](const GemmLaunch& gl) { return use_pair ? launch_gemm_sm100_pair(gl, rt->stream) : launch_gemm_sm100(gl, rt->stream); };
 
     // --- staging for shapes the TMA path cannot address (row stride or base not 16-byte aligned)
     const uint32_t kps = q.k / split;
@@ -202,7 +209,7 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q) {
         if (rc != T0_OK) return rc;
         g.y = rt->scratch_planes.ptr; g.plane_stride = mn;
         g.out_bf16 = false; g.epilogue = T0_EPI_STORE_F32; g.n_ops = 0;
-        rc = launch_gemm_sm100(g, rt->stream);
+        rc = launch(g);
         if (rc != T0_OK) return rc;
         rt->launches.fetch_add(1);
         rc = launch_splitk_reduce((const float*)rt->scratch_planes.ptr, (void*)q.y, (const float*)q.bias, q.m, q.n, split,
@@ -217,7 +224,7 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q) {
     g.out_bf16 = q.out_bf16; g.epilogue = q.epilogue; g.n_ops = q.n_ops;
     memcpy(g.ops, q.ops, sizeof g.ops);
     g.scale = q.scale; g.clamp_min = q.clamp_min; g.clamp_max = q.clamp_max;
-    int rc = launch_gemm_sm100(g, rt->stream);
+    int rc = launch(g);
     if (rc != T0_OK) return rc;
     rt->launches.fetch_add(1);
     return T0_OK;
@@ -256,11 +263,14 @@ int decode_dispatch(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], 
         const t0_gemm_config& c = k->cfg;
         tile_m = c.tile_m; tile_n = c.tile_n; wg = c.wg_size; sk = split_of(&c); swap = c.swap_grid;
         q.nn = c.transpose == T0_NN; q.epilogue = c.epilogue;
+        // wgp_mode on a 256 x 256 tile is the CTA pair; every other config runs the single-CTA kernel
+        q.pair = (c.wgp_mode && c.tile_m == 256 && c.tile_n == 256) ? 1 : 2;
         if (c.epilogue != T0_EPI_STORE_F32) q.bias = rd_u64(ka + 40);
     } else {
         const t0_tile_gemm& s = k->spec;
         tile_m = s.tile_m; tile_n = s.tile_n; wg = t0_tile_gemm_wg_size(&s); sk = s.split_k ? s.split_k : 1; swap = s.swap_grid;
         q.nn = s.transpose == T0_NN;
+        q.pair = 2;
         q.m = rd_u32(ka + 40);
         q.n_ops = s.n_epilogue;
         memcpy(q.ops, s.epilogue, sizeof q.ops);
@@ -359,6 +369,8 @@ int t0_rt_new(int device, t0_runtime** out) {
     T0_CUDA(cudaEventCreate(&rt->ev_stop));
     T0_CUDA(cudaMalloc(&rt->d_status, sizeof(int)));
     T0_CUDA(cudaMemset(rt->d_status, 0, sizeof(int)));
+    T0_CUDA(cudaMalloc(&rt->d_probe, 2 * sizeof(unsigned long long)));
+    T0_CUDA(cudaMemset(rt->d_probe, 0, 2 * sizeof(unsigned long long)));
     T0_CUDA(cudaMallocHost(&rt->h_status, sizeof(int)));
     *rt->h_status = 0;
     *out = rt.release();
@@ -373,6 +385,7 @@ void t0_rt_free(t0_runtime* rt) {
     for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes})
         if (s->ptr) cudaFree(s->ptr);
     if (rt->d_status) cudaFree(rt->d_status);
+    if (rt->d_probe) cudaFree(rt->d_probe);
     if (rt->h_status) cudaFreeHost(rt->h_status);
     if (rt->ev_start) cudaEventDestroy(rt->ev_start);
     if (rt->ev_stop) cudaEventDestroy(rt->ev_stop);
@@ -399,6 +412,17 @@ void* t0_rt_stream(const t0_runtime* rt) { return rt ? (void*)rt->stream : nullp
 int t0_rt_device(const t0_runtime* rt) { return rt ? rt->device : -1; }
 int t0_rt_sm_count(const t0_runtime* rt) { return rt ? rt->sm_count : 0; }
 uint64_t t0_rt_launch_count(const t0_runtime* rt) { return rt ? rt->launches.load() : 0; }
+
+int t0_rt_last_kernel_clock(t0_runtime* rt, double* sm_mhz, double* kernel_us) {
+    if (!rt || !sm_mhz) return fail(T0_ERR_INVALID, "null argument");
+    DeviceGuard guard(rt->device);
+    unsigned long long w[2] = {0, 0};
+    T0_CUDA(cudaMemcpyAsync(w, rt->d_probe, sizeof w, cudaMemcpyDeviceToHost, rt->stream));
+    T0_CUDA(cudaStreamSynchronize(rt->stream));
+    *sm_mhz = w[1] ? (double)w[0] / (double)w[1] * 1e3 : 0.0;
+    if (kernel_us) *kernel_us = (double)w[1] * 1e-3;
+    return T0_OK;
+}
 
 int t0_rt_timer_start(t0_runtime* rt) {
     if (!rt) return fail(T0_ERR_INVALID, "null runtime");
@@ -640,6 +664,21 @@ int t0_rt_dispatch_bench(t0_runtime* rt, const t0_kernel* k, const uint32_t grid
     return dispatch_impl(rt, k, grid, kernargs, len, false, true);
 }
 
+int t0_rt_submit(t0_runtime* rt, const t0_kernel* k, const uint32_t grid[3], const uint8_t* kernargs, size_t len) {
+    return dispatch_impl(rt, k, grid, kernargs, len, false, false);
+}
+
+int t0_rt_flush(t0_runtime* rt) { return t0_rt_synchronize(rt); }
+
+int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count) {
+    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
+    for (size_t i = 0; i < count; ++i) {
+        int rc = t0_gemm_launch(rt, &args[i]);
+        if (rc != T0_OK) return rc;
+    }
+    return T0_OK;
+}
+
 int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* a) {
     int rc = check_rt(rt);
     if (rc != T0_OK) return rc;
@@ -656,6 +695,7 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* a) {
     q.tile_n = a->tile_n; q.split_k = sk;
     q.nn = a->transpose == T0_NN; q.out_bf16 = a->out_bf16; q.planes = a->planes && sk > 1; q.swap_grid = a->swap_grid;
     q.plane_stride = (uint64_t)a->m * a->n;
+    q.pair = a->pair_cta;
     q.epilogue = a->epilogue; q.n_ops = a->n_tile_epilogue;
     memcpy(q.ops, a->tile_epilogue, sizeof q.ops);
     q.scale = a->scale; q.clamp_min = a->clamp_min; q.clamp_max = a->clamp_max;
