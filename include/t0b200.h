@@ -262,6 +262,35 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 
+/* ------------------------------------------------------- INT4 weights (a14, a15) */
+/* build_dequant_int4_f32 / _bf16 (src/t0/quant_kernels.rs:53-171) in the reference wire format: packed = two codes per byte,
+ * low nibble first (:5-9); scales f32 and zero points i32 indexed by flat_element >> group_size_log2;
+ * out[e] = f32(code - zp) * scale, stored as f32 or as truncated bf16 (:167-168).  rows*cols elements. */
+int t0_dequant_int4(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zero_points, uint64_t out, uint32_t rows, uint32_t cols,
+                    uint32_t group_size_log2, int out_bf16);
+/* The same two kernels as dispatchable objects with the reference's 40-byte kernarg blob
+ * [packed, scales, zero_points, output: u64 x 4, rows, cols: u32 x 2] (quant_kernels.rs:45-47). */
+int t0_rt_ensure_dequant_kernel(t0_runtime* rt, uint32_t group_size_log2, int out_bf16, t0_kernel** out);
+/* B200 weight layout: codes packed eight per u32 along K (packed[K/8][N], code k%8 in bits 4*(k%8)), bf16 scales [K/G][N],
+ * uint4 zero points packed eight per u32 along N (zeros[K/G][ceil(N/8)], column n%8 in bits 4*(n%8)).
+ * w[k,n] = RNE_bf16(f32(q - z) * f32(s)) written as bf16 [K][N]. */
+int t0_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out_bf16, uint32_t K, uint32_t N, uint32_t group);
+/* Fused W4A16 GEMM (no counterpart kernel in the reference; nearest items GptqWeight and the dequant kernels above):
+ * y[M,N] f32 = a[M,K] bf16 * w[K,N], w dequantised in the main loop as above, fp32 accumulation.
+ * M <= 16 runs the HBM-bound fused kernel; other shapes dequantise once into scratch and run the bf16 GEMM. */
+int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
+                  uint32_t K, uint32_t group);
+/* GptqWeight::from_bytes (quant_kernels.rs:242-286): header rows, cols, group_size (u32 LE), packed codes, f32 scales,
+ * i32 zero points.  Fills the three section offsets; the asserts of the reference are error codes here. */
+int t0_gptq_parse(const uint8_t* raw, size_t len, uint32_t* rows, uint32_t* cols, uint32_t* group_size, size_t* packed_off,
+                  size_t* scales_off, size_t* zero_points_off);
+/* GptqWeight::gpu_buffer_size (quant_kernels.rs:289-293) */
+size_t t0_gptq_gpu_buffer_size(uint32_t rows, uint32_t cols, uint32_t group_size);
+/* Host-side repack of a GptqWeight (rows = output features N, cols = input features K) into the B200 layout above.
+ * Scales are rounded (RNE) to bf16; returns how many were not exactly representable, or -1 on error. */
+long t0_gptq_to_b200(const uint8_t* packed, const float* scales, const int32_t* zero_points, uint32_t rows, uint32_t cols,
+                     uint32_t group_size, uint32_t* packed_out, uint16_t* scales_out, uint32_t* zeros_out);
+
 /* ------------------------------------------------------- seeded inputs */
 /* Device-side generators for benchmark-sized inputs: element i of the stream (seed) gets the same bits as the
  * host generator of the test oracle, so any sub-range can be checked on the CPU without a full download. */

@@ -291,6 +291,39 @@ def bf16_to_f32(v: int) -> float:
     return float(lib().t0_bf16_to_f32(v))
 
 
+def gptq_parse(raw: bytes) -> dict:
+    """``GptqWeight::from_bytes`` (quant_kernels.rs:242-286)."""
+    buf = np.frombuffer(raw, dtype=np.uint8)
+    rows, cols, group = C.c_uint32(), C.c_uint32(), C.c_uint32()
+    po, so, zo = C.c_size_t(), C.c_size_t(), C.c_size_t()
+    _check(lib().t0_gptq_parse(buf.ctypes.data_as(C.c_void_p), len(raw), C.byref(rows), C.byref(cols), C.byref(group),
+                               C.byref(po), C.byref(so), C.byref(zo)))
+    r, c, g = rows.value, cols.value, group.value
+    n_params = (c // g) * r
+    return {"rows": r, "cols": c, "group_size": g, "n_groups": c // g,
+            "packed": buf[po.value:po.value + r * c // 2].copy(),
+            "scales": np.frombuffer(raw, dtype="<f4", count=n_params, offset=so.value).copy(),
+            "zero_points": np.frombuffer(raw, dtype="<i4", count=n_params, offset=zo.value).copy(),
+            "gpu_buffer_size": int(lib().t0_gptq_gpu_buffer_size(r, c, g))}
+
+
+def gptq_to_b200(packed, scales, zero_points, rows: int, cols: int, group_size: int):
+    """Repack a ``GptqWeight`` (rows = N, cols = K) into the B200 layout; returns (packed, scales, zeros, n_inexact_scales)."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    zero_points = np.ascontiguousarray(zero_points, dtype=np.int32)
+    N, K = rows, cols
+    p = np.zeros((K // 8, N), dtype=np.uint32)
+    s = np.zeros((K // group_size, N), dtype=np.uint16)
+    z = np.zeros((K // group_size, (N + 7) // 8), dtype=np.uint32)
+    vp = C.c_void_p
+    n = lib().t0_gptq_to_b200(packed.ctypes.data_as(vp), scales.ctypes.data_as(vp), zero_points.ctypes.data_as(vp), rows, cols,
+                              group_size, p.ctypes.data_as(vp), s.ctypes.data_as(vp), z.ctypes.data_as(vp))
+    if n < 0:
+        raise T0Error(1, lib().t0_last_error().decode())
+    return p, s, z, int(n)
+
+
 # --------------------------------------------------------------------------- runtime
 
 class GpuBuffer:
@@ -519,6 +552,22 @@ class GpuRuntime:
         a.scale, a.clamp_min, a.clamp_max = scale, clamp_min, clamp_max
         _check(lib().t0_gemm_launch(self._h, C.byref(a)))
 
+    def ensure_dequant_kernel(self, group_size_log2: int, out_bf16: bool) -> GpuKernel:
+        """``build_dequant_int4_f32/bf16(group_size_log2)`` (quant_kernels.rs:53,127) as a dispatchable kernel."""
+        h = C.c_void_p()
+        _check(lib().t0_rt_ensure_dequant_kernel(self._h, group_size_log2, int(out_bf16), C.byref(h)))
+        return GpuKernel(h)
+
+    def dequant_int4(self, packed: int, scales: int, zero_points: int, out: int, rows: int, cols: int, group_size_log2: int,
+                     out_bf16: bool = False) -> None:
+        _check(lib().t0_dequant_int4(self._h, packed, scales, zero_points, out, rows, cols, group_size_log2, int(out_bf16)))
+
+    def w4_dequant(self, packed: int, scales: int, zeros: int, out_bf16: int, K: int, N: int, group: int = 128) -> None:
+        _check(lib().t0_w4_dequant(self._h, packed, scales, zeros, out_bf16, K, N, group))
+
+    def w4a16_gemm(self, a: int, packed: int, scales: int, zeros: int, y: int, M: int, N: int, K: int, group: int = 128) -> None:
+        _check(lib().t0_w4a16_gemm(self._h, a, packed, scales, zeros, y, M, N, K, group))
+
     def fill_uniform_bf16(self, dst: int, n: int, seed: int, first_index: int = 0) -> None:
         _check(lib().t0_fill_uniform_bf16(self._h, dst, n, seed, first_index))
 
@@ -618,6 +667,13 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_gemm_launch_batch", i32, vp, C.POINTER(GemmArgs), sz)
     sig("t0_rt_submit", i32, vp, vp, u32p, u8p, sz)
     sig("t0_rt_flush", i32, vp)
+    sig("t0_dequant_int4", i32, vp, u64, u64, u64, u64, u32, u32, u32, i32)
+    sig("t0_rt_ensure_dequant_kernel", i32, vp, u32, i32, C.POINTER(vp))
+    sig("t0_w4_dequant", i32, vp, u64, u64, u64, u64, u32, u32, u32)
+    sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    sig("t0_gptq_parse", i32, vp, sz, u32p, u32p, u32p, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz))
+    sig("t0_gptq_gpu_buffer_size", sz, u32, u32, u32)
+    sig("t0_gptq_to_b200", C.c_long, vp, vp, vp, u32, u32, u32, vp, vp, vp)
     sig("t0_fill_uniform_bf16", i32, vp, u64, u64, u64, u64)
     sig("t0_fill_u32", i32, vp, u64, u64, u64, u64)
     sig("t0_fill_range_bf16", i32, vp, u64, u64, u64, u64, C.c_float, C.c_float)

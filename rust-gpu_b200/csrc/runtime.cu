@@ -3,111 +3,11 @@
 // one in-order stream stands in for the AQL queue, a size-keyed pool for BufferPool, a name-keyed
 // table of precompiled sm_100a kernels for the JIT kernel cache, and a poison flag with the same
 // fail-fast meaning.  The kernarg blobs the reference's builders produce are decoded here.
-#include "kernels.h"
-
-#include <algorithm>
-#include <atomic>
-#include <cstdlib>
-#include <map>
-#include <memory>
-#include <mutex>
-#include <string>
-#include <vector>
+#include "runtime_internal.h"
 
 using namespace t0;
 
-struct t0_buffer {
-    t0_runtime* rt;
-    void* dptr;
-    size_t size;       // pool size class (4 KiB multiple)
-};
-
-struct t0_kernel {
-    std::string name;
-    uint32_t kernarg_size;
-    int kind;          // 0 = gemm_gen config, 1 = TileIR spec
-    t0_gemm_config cfg;
-    t0_tile_gemm spec;
-};
-
-struct Scratch {
-    void* ptr = nullptr;
-    size_t size = 0;
-};
-
-struct t0_runtime {
-    int device = 0;
-    int sm_count = 148;
-    cudaStream_t stream = nullptr;
-    cudaEvent_t ev_start = nullptr, ev_stop = nullptr;
-    std::mutex mu;
-    std::map<size_t, std::vector<t0_buffer*>> pool;       // BufferPool.cache
-    size_t cached_bytes = 0;
-    std::map<uintptr_t, size_t> live;                      // device allocations handed out (for kernarg validation)
-    std::map<std::string, std::unique_ptr<t0_kernel>> kernels;
-    std::atomic<bool> poisoned{false};
-    std::atomic<uint64_t> launches{0};
-    std::atomic<size_t> slot{0};
-    int* d_status = nullptr;     // device error word written by kernels whose bounded wait expired
-    int* h_status = nullptr;     // pinned mirror
-    unsigned long long* d_probe = nullptr;   // {cycles, ns} of the last GEMM kernel's CTA 0
-    Scratch scratch_a, scratch_b, scratch_planes;
-};
-
 namespace {
-
-#define T0_CUDA(expr)                                                                                  \
-    do {                                                                                               \
-        cudaError_t _e = (expr);                                                                       \
-        if (_e != cudaSuccess) return fail(T0_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e));      \
-    } while (0)
-
-struct DeviceGuard {
-    int prev = -1;
-    explicit DeviceGuard(int dev) {
-        cudaGetDevice(&prev);
-        if (prev != dev) cudaSetDevice(dev);
-        else prev = -1;
-    }
-    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
-};
-
-int check_rt(const t0_runtime* rt) {
-    if (!rt) return fail(T0_ERR_INVALID, "null runtime");
-    if (rt->poisoned.load(std::memory_order_relaxed))
-        return fail(T0_ERR_POISONED, "runtime poisoned after a device failure - refusing dispatch");   // gpu_context.rs:311-313
-    return T0_OK;
-}
-
-// Grow-only scratch areas (staging copies, split-K planes). Growing waits for the stream first.
-int ensure_scratch(t0_runtime* rt, Scratch& s, size_t bytes) {
-    if (bytes <= s.size) return T0_OK;
-    T0_CUDA(cudaStreamSynchronize(rt->stream));
-    if (s.ptr) cudaFree(s.ptr);
-    s.ptr = nullptr; s.size = 0;
-    size_t want = (bytes + (1u << 20) - 1) & ~(size_t)((1u << 20) - 1);
-    T0_CUDA(cudaMalloc(&s.ptr, want));
-    s.size = want;
-    return T0_OK;
-}
-
-// After a synchronising call: read the device error word; a non-zero value poisons the runtime.
-int check_status_after_sync(t0_runtime* rt) {
-    cudaError_t e = cudaMemcpyAsync(rt->h_status, rt->d_status, sizeof(int), cudaMemcpyDeviceToHost, rt->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(rt->stream);
-    if (e != cudaSuccess) {
-        rt->poisoned.store(true);
-        return fail(T0_ERR_CUDA, "device failure while waiting: %s", cudaGetErrorString(e));
-    }
-    if (*rt->h_status != 0) {
-        int code = *rt->h_status;
-        rt->poisoned.store(true);
-        cudaMemsetAsync(rt->d_status, 0, sizeof(int), rt->stream);
-        return fail(T0_ERR_TIMEOUT, "a bounded device-side wait expired (status 0x%08x: role %d, work item %d)", code,
-                    (code >> 24) & 0xFF, code & 0xFFFFFF);
-    }
-    return T0_OK;
-}
 
 struct GemmRequest {
     uint64_t x, b, y, bias;
@@ -382,7 +282,7 @@ void t0_rt_free(t0_runtime* rt) {
     DeviceGuard guard(rt->device);
     cudaStreamSynchronize(rt->stream);
     t0_rt_pool_clear(rt);
-    for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes})
+    for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes, &rt->scratch_w4, &rt->scratch_w})
         if (s->ptr) cudaFree(s->ptr);
     if (rt->d_status) cudaFree(rt->d_status);
     if (rt->d_probe) cudaFree(rt->d_probe);
@@ -622,6 +522,28 @@ int t0_rt_ensure_tile_kernel(t0_runtime* rt, const t0_tile_gemm* spec, t0_kernel
     return T0_OK;
 }
 
+int t0_rt_ensure_dequant_kernel(t0_runtime* rt, uint32_t group_size_log2, int out_bf16, t0_kernel** out) {
+    if (!rt || !out) return fail(T0_ERR_INVALID, "null argument");
+    if (group_size_log2 > 31) return fail(T0_ERR_INVALID, "group_size_log2=%u out of range", group_size_log2);
+    // the reference names both kernels without the group size (quant_kernels.rs:54,128); the group is part of the key here
+    std::string name = std::string(out_bf16 ? "dequant_int4_bf16" : "dequant_int4_f32") + "_g" + std::to_string(group_size_log2);
+    std::lock_guard<std::mutex> g(rt->mu);
+    auto it = rt->kernels.find(name);
+    if (it == rt->kernels.end()) {
+        std::unique_ptr<t0_kernel> k(new t0_kernel());
+        k->name = name;
+        k->kind = 2;
+        memset(&k->cfg, 0, sizeof k->cfg);
+        memset(&k->spec, 0, sizeof k->spec);
+        k->group_log2 = group_size_log2;
+        k->out_bf16 = out_bf16 != 0;
+        k->kernarg_size = 40;
+        it = rt->kernels.emplace(name, std::move(k)).first;
+    }
+    *out = it->second.get();
+    return T0_OK;
+}
+
 uint32_t t0_kernel_kernarg_size(const t0_kernel* k) { return k ? k->kernarg_size : 0; }
 const char* t0_kernel_name(const t0_kernel* k) { return k ? k->name.c_str() : ""; }
 size_t t0_rt_kernel_cache_size(const t0_runtime* rt) {
@@ -638,6 +560,17 @@ static int dispatch_impl(t0_runtime* rt, const t0_kernel* k, const uint32_t grid
     if (rc != T0_OK) return rc;
     if (!k || !grid || !ka) return fail(T0_ERR_INVALID, "null argument");
     DeviceGuard guard(rt->device);
+    if (k->kind == 2) {
+        // dequant_int4_{f32,bf16}: [packed, scales, zero_points, output: u64 x 4, rows, cols: u32 x 2] (quant_kernels.rs:45-47);
+        // the grid is ceil(rows*cols/256)*256 threads there and is not needed here
+        if (len != k->kernarg_size)
+            return fail(T0_ERR_INVALID, "kernarg mismatch: builder produced %zuB, kernel declares %uB", len, k->kernarg_size);
+        rc = t0_dequant_int4(rt, rd_u64(ka), rd_u64(ka + 8), rd_u64(ka + 16), rd_u64(ka + 24), rd_u32(ka + 32), rd_u32(ka + 36),
+                             k->group_log2, k->out_bf16 ? 1 : 0);
+        if (rc != T0_OK) return rc;
+        rt->slot.fetch_add(1);
+        return wait ? check_status_after_sync(rt) : T0_OK;
+    }
     GemmRequest q;
     rc = decode_dispatch(rt, k, grid, ka, len, validate, &q);
     if (rc != T0_OK) return rc;

@@ -140,7 +140,12 @@ def test_auto_select_sizes(t0):
     # every selected tile is one the sm_100a kernel implements
     for (m, k, n) in [(4096, 4096, 4096), (2048, 2048, 2048), (64, 16384, 4096), (1, 4096, 11008)]:
         c = t0.auto_select(m, k, n)
-        assert c.tile_m == 128 and c.tile_n in (32, 64, 128, 256) and c.tile_k == 64
+        assert c.tile_k == 64
+        if c.tile_m == 256:      # the CTA pair: 256 x 256 over two SMs
+            assert c.wgp_mode and c.tile_n == 256
+        else:
+            assert c.tile_m == 128 and c.tile_n in (32, 64, 128, 256)
+    assert t0.auto_select(4096, 4096, 4096).name() == "t0_gemm_256x256_k64_ldsdb_wgp"
 
 
 def test_auto_select_legacy_preserved(t0):

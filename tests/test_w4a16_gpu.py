@@ -1,0 +1,232 @@
+"""GPU parity tests for the INT4 path: stand-alone dequantisation (bit-exact) and the fused W4A16 GEMM.
+
+Reference items: src/t0/quant_kernels.rs:53-171 (dequant kernels, kernarg ABI :45-47), :188-294 (GptqWeight),
+known answers :346-481.  The fused GEMM has no reference counterpart; it is checked against the oracle's
+dequant-then-GEMM with the GEMM tolerances (relative L2 <= 1e-3, |err| <= 5e-3*sqrt(K/256)), and its dequantised
+weights are extracted bit-exactly with one-hot activations.
+"""
+import struct
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def make_w4(oracle, K, N, G, seed=0):
+    packed = oracle.fill_u32((K // 8) * N, 1000 + seed)
+    scales = oracle.fill_range_bf16((K // G) * N, 2000 + seed, 0.001, 0.02)
+    zeros = oracle.fill_u32((K // G) * ((N + 7) // 8), 3000 + seed)
+    return packed, scales, zeros
+
+
+def run_w4a16(rt, a, packed, scales, zeros, M, N, K, G):
+    xa, xp, xs, xz = rt.upload(a), rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+    y = rt.alloc(M * N * 4 + 4096)
+    y.write(np.full(M * N + 1024, -9999.0, np.float32))
+    rt.w4a16_gemm(xa.gpu_addr(), xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), y.gpu_addr(), M, N, K, G)
+    rt.synchronize()
+    out = y.read(M * N * 4, np.float32).reshape(M, N)
+    tail = y.read_bytes(M * N * 4, 4096, np.float32)
+    assert np.all(tail == -9999.0), "wrote past the output"
+    for b in (xa, xp, xs, xz, y):
+        b.free()
+    return out
+
+
+def assert_close(got, ref, k):
+    err = np.abs(got.astype(np.float64) - ref)
+    rel = np.linalg.norm(got.astype(np.float64) - ref) / max(np.linalg.norm(ref.astype(np.float64)), 1e-30)
+    assert err.max() <= 5e-3 * np.sqrt(max(k, 256) / 256.0), err.max()
+    assert rel <= 1e-3, rel
+
+
+# ----------------------------------------------------------------------------- K3, reference wire format
+
+@pytest.mark.parametrize("rows,cols,glog2", [(16, 16, 4), (4, 256, 7), (33, 128, 7), (7, 50, 1), (64, 1024, 8)])
+@pytest.mark.parametrize("bf16", [False, True])
+def test_dequant_reference_format_bit_exact(t0, oracle, rt, rows, cols, glog2, bf16):
+    rng = np.random.default_rng(rows * cols + glog2)
+    total = rows * cols
+    packed = rng.integers(0, 256, size=(total + 1) // 2, dtype=np.uint8)
+    n_groups = ((total - 1) >> glog2) + 1
+    scales = rng.uniform(-2.0, 2.0, n_groups).astype(np.float32)
+    zps = rng.integers(-20, 20, n_groups).astype(np.int32)
+    want = oracle.dequant_int4_ref(packed, scales, zps, rows, cols, glog2, bf16=bf16)
+    xp, xs, xz = rt.upload(packed), rt.upload(scales), rt.upload(zps)
+    out = rt.alloc(total * 4)
+    rt.dequant_int4(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), out.gpu_addr(), rows, cols, glog2, out_bf16=bf16)
+    rt.synchronize()
+    got = out.read(total * (2 if bf16 else 4), np.uint16 if bf16 else np.float32).reshape(rows, cols)
+    assert np.array_equal(got.view(np.uint16 if bf16 else np.uint32), want.view(np.uint16 if bf16 else np.uint32))
+    # the same kernel through the reference's 40-byte kernarg blob (quant_kernels.rs:45-47) and its grid rule (:49-52)
+    kern = rt.ensure_dequant_kernel(glog2, bf16)
+    assert kern.kernarg_size == 40
+    out.zero()
+    ka = struct.pack("<QQQQII", xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), out.gpu_addr(), rows, cols)
+    rt.dispatch(kern, [-(-total // 256) * 256, 1, 1], ka)
+    got2 = out.read(total * (2 if bf16 else 4), np.uint16 if bf16 else np.float32).reshape(rows, cols)
+    assert np.array_equal(got2.view(np.uint16 if bf16 else np.uint32), want.view(np.uint16 if bf16 else np.uint32))
+
+
+def test_dequant_known_answers(t0, rt):
+    # quant_kernels.rs:347-354,365-372,441-448: 0xAB -> 11, 10; 0xD7 -> 7, 13; (12 - 8) * 0.5 = 2.0
+    xp = rt.upload(np.array([0xAB, 0xD7, 0x0C, 0x00], np.uint8))
+    xs = rt.upload(np.array([1.0, 0.5], np.float32))
+    xz = rt.upload(np.array([0, 8], np.int32))
+    out = rt.alloc(64)
+    rt.dequant_int4(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), out.gpu_addr(), 1, 8, 2)
+    rt.synchronize()
+    got = out.read(32, np.float32)
+    assert got[:4].tolist() == [11.0, 10.0, 7.0, 13.0]
+    assert got[4] == 2.0
+
+
+# ----------------------------------------------------------------------------- K3, B200 layout
+
+@pytest.mark.parametrize("K,N,G", [(128, 8, 128), (512, 264, 128), (256, 100, 64), (64, 1000, 32), (4096, 512, 128)])
+def test_dequant_b200_layout_bit_exact(t0, oracle, rt, K, N, G):
+    packed, scales, zeros = make_w4(oracle, K, N, G)
+    want = oracle.dequant_w4_b200(packed, scales, zeros, K, N, G)
+    xp, xs, xz = rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+    out = rt.alloc(K * N * 2)
+    rt.w4_dequant(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), out.gpu_addr(), K, N, G)
+    rt.synchronize()
+    assert np.array_equal(out.read(K * N * 2, np.uint16).reshape(K, N), want)
+
+
+def test_dequant_exhaustive_code_zero_scale(t0, oracle, rt):
+    # every (q, z, s): 16 codes down K in each group of 16, one (z, s) pair per (group, column):
+    # 65536 bf16 scale patterns x 16 zero points (non-finite scales excluded: NaN payloads are not a parity subject)
+    K, G, N = 4096, 16, 4096
+    k = np.arange(K)
+    codes = (k % 16).astype(np.uint32)
+    word_of_group = np.zeros(K // 8, np.uint32)
+    for kk in range(8):
+        word_of_group |= codes[kk::8] << np.uint32(4 * kk)
+    packed = np.repeat(word_of_group[:, None], N, axis=1).astype(np.uint32)
+    pair = np.arange((K // G) * N, dtype=np.uint32).reshape(K // G, N)
+    sbits = (pair & 0xFFFF).astype(np.uint16)
+    sbits = np.where((sbits & 0x7F80) == 0x7F80, np.uint16(0x3C00), sbits)
+    z = (pair >> 16).astype(np.uint32) & 0xF
+    zeros = np.zeros((K // G, N // 8), np.uint32)
+    for j in range(8):
+        zeros |= z[:, j::8] << np.uint32(4 * j)
+    want = oracle.dequant_w4_b200(packed, sbits, zeros, K, N, G)
+    xp, xs, xz = rt.upload(packed), rt.upload(sbits), rt.upload(zeros)
+    out = rt.alloc(K * N * 2)
+    rt.w4_dequant(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), out.gpu_addr(), K, N, G)
+    rt.synchronize()
+    assert np.array_equal(out.read(K * N * 2, np.uint16).reshape(K, N), want)
+    for b in (xp, xs, xz, out):
+        b.free()
+
+
+def test_gptq_container_to_b200(t0, oracle, rt):
+    # a GptqWeight blob (quant_kernels.rs:242-286) -> B200 layout -> same weights as the reference-format kernel, rounded once
+    rng = np.random.default_rng(11)
+    N, K, G = 48, 256, 128
+    q = rng.integers(0, 16, size=(N, K), dtype=np.uint8)
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8).ravel()
+    scales = oracle.bf16_to_f32(oracle.fill_range_bf16(N * (K // G), 1, 0.001, 0.02))
+    zps = rng.integers(0, 16, size=N * (K // G)).astype(np.int32)
+    raw = np.array([N, K, G], "<u4").tobytes() + packed.tobytes() + scales.astype("<f4").tobytes() + zps.astype("<i4").tobytes()
+    g = t0.gptq_parse(raw)
+    assert (g["rows"], g["cols"], g["group_size"], g["n_groups"]) == (N, K, G, K // G)
+    assert g["gpu_buffer_size"] == packed.size + scales.size * 4 + zps.size * 4
+    with pytest.raises(t0.T0Error):
+        t0.gptq_parse(raw[:-1])
+    p, s, z, inexact = t0.gptq_to_b200(g["packed"], g["scales"], g["zero_points"], N, K, G)
+    assert inexact == 0
+    po, so, zo, _ = oracle.gptq_to_b200(packed, scales, zps, N, K, G)
+    assert np.array_equal(p, po) and np.array_equal(s, so) and np.array_equal(z, zo)
+    ref = oracle.dequant_int4_ref(packed, scales, zps, N, K, 7)                       # [N, K] f32, reference formula
+    xp, xs, xz = rt.upload(p), rt.upload(s), rt.upload(z)
+    out = rt.alloc(K * N * 2)
+    rt.w4_dequant(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), out.gpu_addr(), K, N, G)
+    rt.synchronize()
+    w = oracle.bf16_to_f32(out.read(K * N * 2, np.uint16)).reshape(K, N)
+    assert np.array_equal(w, oracle.bf16_to_f32(oracle.f32_to_bf16_rne(ref)).reshape(N, K).T)
+    with pytest.raises(t0.T0Error):
+        t0.gptq_to_b200(packed, scales, np.full_like(zps, 16), N, K, G)              # a zero point that needs five bits
+
+
+# ----------------------------------------------------------------------------- K2, fused GEMM
+
+def test_fused_kernel_dequantises_bit_exactly(t0, oracle, rt):
+    # one-hot activations make row m of y equal to row k0+m of the dequantised weights, exactly:
+    # this reads the fused kernel's in-register dequant back without any rounding of its own
+    K, G, M = 32, 32, 16
+    N = 65536
+    codes = (np.arange(K) % 16).astype(np.uint32)
+    words = np.zeros(K // 8, np.uint32)
+    for kk in range(8):
+        words |= codes[kk::8] << np.uint32(4 * kk)
+    packed = np.repeat(words[:, None], N, axis=1).astype(np.uint32)
+    col = np.arange(N, dtype=np.uint32)
+    # positive and negative normal scales over four octaves around the benchmark's range, all 16 zero points
+    sbits = (0x3A00 + (col % 0x400)).astype(np.uint16) | ((col // 0x400 % 2) << 15).astype(np.uint16)
+    z = (col // 0x800) % 16
+    zeros = np.zeros((1, N // 8), np.uint32)
+    for j in range(8):
+        zeros[0] |= z[j::8].astype(np.uint32) << np.uint32(4 * j)
+    a = np.zeros((M, K), np.uint16)
+    for m in range(M):
+        a[m, m] = 0x3F80
+    want = oracle.bf16_to_f32(oracle.dequant_w4_b200(packed, sbits.reshape(1, N), zeros, K, N, G)).reshape(K, N)[:M]
+    got = run_w4a16(rt, a, packed, sbits.reshape(1, N), zeros, M, N, K, G)
+    assert np.array_equal(got.view(np.uint32) & 0x7FFFFFFF, want.view(np.uint32) & 0x7FFFFFFF)   # sign of zero aside
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16])
+@pytest.mark.parametrize("K,N,G", [(512, 264, 128), (32, 40, 32), (1024, 32, 64), (4096, 96, 128)])
+def test_fused_small_shapes(t0, oracle, rt, M, K, N, G):
+    a = oracle.fill_normal_bf16(M * K, 7 + M)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=M)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    got = run_w4a16(rt, a, packed, scales, zeros, M, N, K, G)
+    assert_close(got, ref, K)
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+@pytest.mark.parametrize("N", [11008, 14336])
+def test_baseline_config4_full_size(t0, oracle, rt, M, N):
+    # BASELINE config 4: K = 4096, group 128, activations N(0,1), codes uniform, scales U(0.001, 0.02), zero points uniform
+    K, G = 4096, 128
+    a = oracle.fill_normal_bf16(M * K, 7 + M)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=N)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    xa, xp, xs, xz = rt.upload(a), rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+    y = rt.alloc(M * N * 4)
+    outs = []
+    for _ in range(3):   # the scratch area (slab counters, straddling pieces) is reused: repeated calls must agree bit for bit
+        y.zero()
+        rt.w4a16_gemm(xa.gpu_addr(), xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), y.gpu_addr(), M, N, K, G)
+        rt.synchronize()
+        outs.append(y.read(M * N * 4, np.float32).reshape(M, N))
+    assert_close(outs[0], ref, K)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+    for b in (xa, xp, xs, xz, y):
+        b.free()
+
+
+def test_general_shapes_take_the_two_step_path(t0, oracle, rt):
+    # M > 16, or N / K / group the fused kernel does not take: dequantise into scratch, then the bf16 GEMM
+    for (M, K, N, G) in [(33, 256, 100, 64), (17, 512, 264, 128), (4, 64, 12, 8)]:
+        a = oracle.fill_normal_bf16(M * K, 3)
+        packed, scales, zeros = make_w4(oracle, K, N, G)
+        ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+        assert_close(run_w4a16(rt, a, packed, scales, zeros, M, N, K, G), ref, K)
+
+
+def test_argument_errors(t0, rt):
+    b = rt.alloc(4096)
+    with pytest.raises(t0.T0Error):
+        rt.w4a16_gemm(b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), 1, 8, 12, 4)    # K % 8
+    with pytest.raises(t0.T0Error):
+        rt.w4a16_gemm(b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), 1, 8, 64, 48)   # group does not divide K
+    with pytest.raises(t0.T0Error):
+        rt.w4a16_gemm(0, b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), 1, 8, 64, 32)
+    rt.w4a16_gemm(b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), 0, 8, 64, 32)        # M = 0: no-op
+    assert not rt.is_poisoned()
