@@ -262,6 +262,37 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 
+/* ------------------------------------------------------- autotuner (a10) */
+typedef struct t0_tuner t0_tuner;   /* GemmTuner  src/t0/auto_gemm.rs:46-55 */
+/* GemmTuner::new() / with_cache_dir(dir) (auto_gemm.rs:59-75).  Default directory: $T0_TUNE_DIR, else
+ * ~/.t0_autotune/b200_sm100a (the reference uses ~/.t0_autotune; the sub-directory keeps other hardware's results apart). */
+int t0_tuner_new(t0_tuner** out);
+int t0_tuner_with_cache_dir(const char* dir, t0_tuner** out);
+void t0_tuner_free(t0_tuner* t);
+/* the public fields max_candidates (8) and n_iters (5) (auto_gemm.rs:52-54); 0 leaves a field unchanged */
+int t0_tuner_configure(t0_tuner* t, size_t max_candidates, size_t n_iters);
+size_t t0_tuner_max_candidates(const t0_tuner* t);
+size_t t0_tuner_n_iters(const t0_tuner* t);
+size_t t0_tuner_cache_len(const t0_tuner* t);
+const char* t0_tuner_cache_dir(const t0_tuner* t);
+/* GemmTuner::tune(rt, m, n, k) -> GemmConfig (auto_gemm.rs:82-216): memory cache, disk cache gemm_{M}x{N}x{K}.json,
+ * else cost-model candidates -> 256^3 smoke test -> timed runs (median of n_iters) -> save.  Argument order (m, n, k). */
+int t0_tuner_tune(t0_tuner* t, t0_runtime* rt, uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* out);
+/* GemmTuneResult of a tuned size (auto_gemm.rs:30-41): best TFLOP/s, whether it came from disk, how many candidates were timed */
+int t0_tuner_result(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, double* best_tflops, int* from_cache, int* n_measured);
+/* save_cache / load_cache (auto_gemm.rs:439-501) and the JSON field reader (:603-625), exposed as the reference's tests use them */
+int t0_tuner_save_cache(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, const t0_gemm_config* best, double best_tflops);
+int t0_tuner_load_cache(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* best, double* best_tflops);
+int t0_parse_json_number(const char* json, const char* key, double* out);
+/* invalidate / clear / report (auto_gemm.rs:504-531) */
+void t0_tuner_invalidate(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k);
+void t0_tuner_clear(t0_tuner* t);
+void t0_tuner_report(const t0_tuner* t);
+/* global_tuner() (auto_gemm.rs:539) and the one-shot auto_gemm(rt, a, b, c, m, n, k) -> Result<f64> (auto_gemm.rs:555-590):
+ * tune or cache hit, then dispatch with the best config; returns the tuned TFLOP/s through `tflops`. */
+t0_tuner* t0_global_tuner(void);
+int t0_auto_gemm(t0_runtime* rt, t0_buffer* a, t0_buffer* b, t0_buffer* c, uint32_t m, uint32_t n, uint32_t k, double* tflops);
+
 /* ------------------------------------------------------- INT4 weights (a14, a15) */
 /* build_dequant_int4_f32 / _bf16 (src/t0/quant_kernels.rs:53-171) in the reference wire format: packed = two codes per byte,
  * low nibble first (:5-9); scales f32 and zero points i32 indexed by flat_element >> group_size_log2;
@@ -280,6 +311,13 @@ int t0_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zer
  * M <= 16 runs the HBM-bound fused kernel; other shapes dequantise once into scratch and run the bf16 GEMM. */
 int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
                   uint32_t K, uint32_t group);
+/* The same call with its arguments in a record, and `count` of them submitted back to back from native code
+ * (decode loops call one projection after another; cf. prefill_dispatch.rs:61-206). */
+typedef struct t0_w4a16_args {
+    uint64_t a, packed, scales, zeros, y;
+    uint32_t m, n, k, group;
+} t0_w4a16_args;
+int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
 /* GptqWeight::from_bytes (quant_kernels.rs:242-286): header rows, cols, group_size (u32 LE), packed codes, f32 scales,
  * i32 zero points.  Fills the three section offsets; the asserts of the reference are error codes here. */
 int t0_gptq_parse(const uint8_t* raw, size_t len, uint32_t* rows, uint32_t* cols, uint32_t* group_size, size_t* packed_off,

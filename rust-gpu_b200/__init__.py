@@ -183,6 +183,12 @@ class GemmArgs(C.Structure):
                 ("scale", C.c_float), ("clamp_min", C.c_float), ("clamp_max", C.c_float)]
 
 
+class W4A16Args(C.Structure):
+    """``t0_w4a16_args``."""
+    _fields_ = [("a", C.c_uint64), ("packed", C.c_uint64), ("scales", C.c_uint64), ("zeros", C.c_uint64), ("y", C.c_uint64),
+                ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32), ("group", C.c_uint32)]
+
+
 # --------------------------------------------------------------------------- selection / grids / kernargs
 
 def auto_select(m: int, k: int, n: int) -> GemmConfig:
@@ -568,6 +574,10 @@ class GpuRuntime:
     def w4a16_gemm(self, a: int, packed: int, scales: int, zeros: int, y: int, M: int, N: int, K: int, group: int = 128) -> None:
         _check(lib().t0_w4a16_gemm(self._h, a, packed, scales, zeros, y, M, N, K, group))
 
+    def w4a16_gemm_batch(self, calls: list[W4A16Args]) -> None:
+        arr = (W4A16Args * len(calls))(*calls)
+        _check(lib().t0_w4a16_gemm_batch(self._h, arr, len(calls)))
+
     def fill_uniform_bf16(self, dst: int, n: int, seed: int, first_index: int = 0) -> None:
         _check(lib().t0_fill_uniform_bf16(self._h, dst, n, seed, first_index))
 
@@ -576,6 +586,91 @@ class GpuRuntime:
 
     def fill_range_bf16(self, dst: int, n: int, seed: int, lo: float, hi: float, first_index: int = 0) -> None:
         _check(lib().t0_fill_range_bf16(self._h, dst, n, seed, first_index, lo, hi))
+
+
+class GemmTuner:
+    """``GemmTuner`` (src/t0/auto_gemm.rs:46-216)."""
+
+    def __init__(self, cache_dir: str | None = None, _handle=None):
+        if _handle is not None:
+            self._h, self._owned = _handle, False
+            return
+        h = C.c_void_p()
+        if cache_dir is None:
+            _check(lib().t0_tuner_new(C.byref(h)))
+        else:
+            _check(lib().t0_tuner_with_cache_dir(cache_dir.encode(), C.byref(h)))
+        self._h, self._owned = h, True
+
+    @classmethod
+    def with_cache_dir(cls, d: str) -> "GemmTuner":
+        return cls(d)
+
+    @property
+    def max_candidates(self) -> int:
+        return int(lib().t0_tuner_max_candidates(self._h))
+
+    @property
+    def n_iters(self) -> int:
+        return int(lib().t0_tuner_n_iters(self._h))
+
+    def configure(self, max_candidates: int = 0, n_iters: int = 0) -> None:
+        _check(lib().t0_tuner_configure(self._h, max_candidates, n_iters))
+
+    @property
+    def cache_dir(self) -> str:
+        return lib().t0_tuner_cache_dir(self._h).decode()
+
+    def cache_len(self) -> int:
+        return int(lib().t0_tuner_cache_len(self._h))
+
+    def tune(self, rt: "GpuRuntime", m: int, n: int, k: int) -> GemmConfig:
+        c = GemmConfig()
+        _check(lib().t0_tuner_tune(self._h, rt._h, m, n, k, C.byref(c)))
+        return c
+
+    def result(self, m: int, n: int, k: int) -> dict:
+        tf, fc, nm = C.c_double(), C.c_int(), C.c_int()
+        _check(lib().t0_tuner_result(self._h, m, n, k, C.byref(tf), C.byref(fc), C.byref(nm)))
+        return {"best_tflops": tf.value, "from_cache": bool(fc.value), "n_measured": nm.value}
+
+    def save_cache(self, m: int, n: int, k: int, best: GemmConfig, tflops: float) -> None:
+        _check(lib().t0_tuner_save_cache(self._h, m, n, k, C.byref(best), tflops))
+
+    def load_cache(self, m: int, n: int, k: int) -> tuple[GemmConfig, float]:
+        c, tf = GemmConfig(), C.c_double()
+        _check(lib().t0_tuner_load_cache(self._h, m, n, k, C.byref(c), C.byref(tf)))
+        return c, tf.value
+
+    def invalidate(self, m: int, n: int, k: int) -> None:
+        lib().t0_tuner_invalidate(self._h, m, n, k)
+
+    def clear(self) -> None:
+        lib().t0_tuner_clear(self._h)
+
+    def report(self) -> None:
+        lib().t0_tuner_report(self._h)
+
+    def free(self) -> None:
+        if self._owned and self._h:
+            lib().t0_tuner_free(self._h)
+            self._h = None
+
+
+def global_tuner() -> GemmTuner:
+    return GemmTuner(_handle=C.c_void_p(lib().t0_global_tuner()))
+
+
+def auto_gemm(rt: "GpuRuntime", a: "GpuBuffer", b: "GpuBuffer", c: "GpuBuffer", m: int, n: int, k: int) -> float:
+    """``auto_gemm(rt, a, b, c, m, n, k) -> Result<f64>`` (auto_gemm.rs:555-590); note the (m, n, k) order."""
+    tf = C.c_double()
+    _check(lib().t0_auto_gemm(rt._h, a._h, b._h, c._h, m, n, k, C.byref(tf)))
+    return tf.value
+
+
+def parse_json_number(json: str, key: str) -> float | None:
+    out = C.c_double()
+    return out.value if lib().t0_parse_json_number(json.encode(), key.encode(), C.byref(out)) == 0 else None
 
 
 # --------------------------------------------------------------------------- ctypes signatures
@@ -667,10 +762,29 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_gemm_launch_batch", i32, vp, C.POINTER(GemmArgs), sz)
     sig("t0_rt_submit", i32, vp, vp, u32p, u8p, sz)
     sig("t0_rt_flush", i32, vp)
+    sig("t0_tuner_new", i32, C.POINTER(vp))
+    sig("t0_tuner_with_cache_dir", i32, C.c_char_p, C.POINTER(vp))
+    sig("t0_tuner_free", None, vp)
+    sig("t0_tuner_configure", i32, vp, sz, sz)
+    sig("t0_tuner_max_candidates", sz, vp)
+    sig("t0_tuner_n_iters", sz, vp)
+    sig("t0_tuner_cache_len", sz, vp)
+    sig("t0_tuner_cache_dir", C.c_char_p, vp)
+    sig("t0_tuner_tune", i32, vp, vp, u32, u32, u32, cfgp)
+    sig("t0_tuner_result", i32, vp, u32, u32, u32, C.POINTER(C.c_double), C.POINTER(i32), C.POINTER(i32))
+    sig("t0_tuner_save_cache", i32, vp, u32, u32, u32, cfgp, C.c_double)
+    sig("t0_tuner_load_cache", i32, vp, u32, u32, u32, cfgp, C.POINTER(C.c_double))
+    sig("t0_parse_json_number", i32, C.c_char_p, C.c_char_p, C.POINTER(C.c_double))
+    sig("t0_tuner_invalidate", None, vp, u32, u32, u32)
+    sig("t0_tuner_clear", None, vp)
+    sig("t0_tuner_report", None, vp)
+    sig("t0_global_tuner", vp)
+    sig("t0_auto_gemm", i32, vp, vp, vp, vp, u32, u32, u32, C.POINTER(C.c_double))
     sig("t0_dequant_int4", i32, vp, u64, u64, u64, u64, u32, u32, u32, i32)
     sig("t0_rt_ensure_dequant_kernel", i32, vp, u32, i32, C.POINTER(vp))
     sig("t0_w4_dequant", i32, vp, u64, u64, u64, u64, u32, u32, u32)
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_gptq_parse", i32, vp, sz, u32p, u32p, u32p, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz))
     sig("t0_gptq_gpu_buffer_size", sz, u32, u32, u32)
     sig("t0_gptq_to_b200", C.c_long, vp, vp, vp, u32, u32, u32, vp, vp, vp)

@@ -1,0 +1,390 @@
+// Runtime autotuner for the GEMM: the reference's auto_gemm.rs (GemmTuner :46-216, smoke_test_256 :223-272,
+// benchmark_one :279-348, JSON cache :435-501, global_tuner :539, auto_gemm :555-590) over the C ABI.
+//
+// Pipeline, as in the reference: in-memory cache -> disk cache -> candidates from the cost model ->
+// 256^3 smoke test against a CPU dot product on sampled outputs -> timed runs (one warm-up, n_iters
+// synchronous dispatches, median) -> best config, saved as gemm_{M}x{N}x{K}.json.
+// Built only on the public entry points of this library (alloc, kernargs, grid, dispatch).
+#include "common.h"
+
+#include <algorithm>
+#include <cerrno>
+#include <chrono>
+#include <cmath>
+#include <cstdlib>
+#include <dirent.h>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <sys/stat.h>
+#include <tuple>
+#include <unistd.h>
+#include <vector>
+
+using namespace t0;
+
+namespace {
+
+struct TuneResult {
+    t0_gemm_config best;
+    double best_tflops = 0.0;
+    std::vector<std::pair<std::string, double>> all;
+    bool from_cache = false;
+};
+
+}  // namespace
+
+struct t0_tuner {
+    std::map<std::tuple<uint32_t, uint32_t, uint32_t>, TuneResult> cache;   // (M, N, K) -> result
+    std::string cache_dir;
+    size_t max_candidates = 8;   // auto_gemm.rs:63
+    size_t n_iters = 5;          // auto_gemm.rs:64
+};
+
+namespace {
+
+std::string default_cache_dir() {
+    // auto_gemm.rs:594-600 uses ~/.t0_autotune; a T0_TUNE_DIR override and a per-architecture sub-directory are added
+    // so that results tuned on other hardware are never read back here
+    if (const char* d = getenv("T0_TUNE_DIR")) return d;
+    const char* home = getenv("HOME");
+    return std::string(home ? home : "/tmp") + "/.t0_autotune/b200_sm100a";
+}
+
+void mkdir_p(const std::string& dir) {
+    std::string cur;
+    for (size_t i = 0; i <= dir.size(); ++i) {
+        if (i == dir.size() || dir[i] == '/') {
+            if (!cur.empty()) mkdir(cur.c_str(), 0755);
+        }
+        if (i < dir.size()) cur += dir[i];
+    }
+}
+
+std::string cache_path(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k) {
+    return t->cache_dir + "/gemm_" + std::to_string(m) + "x" + std::to_string(n) + "x" + std::to_string(k) + ".json";   // auto_gemm.rs:435-437
+}
+
+// auto_gemm.rs:603-625: minimal JSON field readers ("key":number)
+bool parse_number(const std::string& json, const char* key, double* out) {
+    const std::string pat = std::string("\"") + key + "\":";
+    size_t pos = json.find(pat);
+    if (pos == std::string::npos) return false;
+    pos += pat.size();
+    while (pos < json.size() && json[pos] == ' ') ++pos;
+    char* end = nullptr;
+    errno = 0;
+    double v = strtod(json.c_str() + pos, &end);
+    if (end == json.c_str() + pos || errno) return false;
+    *out = v;
+    return true;
+}
+
+bool load_cache(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, TuneResult* out) {
+    FILE* f = fopen(cache_path(t, m, n, k).c_str(), "rb");
+    if (!f) return false;
+    std::string content;
+    char buf[4096];
+    size_t got;
+    while ((got = fread(buf, 1, sizeof buf, f)) > 0) content.append(buf, got);
+    fclose(f);
+    double tile_m, tile_n, tile_k, wg, tflops, v;
+    if (!parse_number(content, "tile_m", &tile_m) || !parse_number(content, "tile_n", &tile_n) || !parse_number(content, "tile_k", &tile_k) ||
+        !parse_number(content, "wg_size", &wg) || !parse_number(content, "tflops", &tflops))
+        return false;
+    t0_gemm_config c;
+    memset(&c, 0, sizeof c);
+    c.tile_m = (uint32_t)tile_m; c.tile_n = (uint32_t)tile_n; c.tile_k = (uint32_t)tile_k; c.wg_size = (uint32_t)wg;
+    c.use_lds = 1; c.double_buffer = 1;
+    c.split_k = parse_number(content, "split_k", &v) && v > 1 ? (uint32_t)v : 0;
+    c.lds_pad = parse_number(content, "lds_pad", &v) ? (uint32_t)v : 0;
+    c.n_col_passes = parse_number(content, "n_col_passes", &v) ? (uint32_t)v : 1;
+    c.wgp_mode = content.find("\"wgp\":true") != std::string::npos;
+    c.swap_grid = content.find("\"swap\":true") != std::string::npos;
+    c.transpose = T0_NT; c.epilogue = T0_EPI_STORE_F32;
+    if (!t0_gemm_config_is_feasible(&c)) return false;
+    out->best = c; out->best_tflops = tflops; out->all.clear(); out->from_cache = true;
+    return true;
+}
+
+void save_cache(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, const TuneResult& r) {
+    mkdir_p(t->cache_dir);
+    const t0_gemm_config& c = r.best;
+    std::string all;
+    char tmp[256];
+    for (size_t i = 0; i < r.all.size(); ++i) {
+        snprintf(tmp, sizeof tmp, "%s[\"%s\",%.2f]", i ? "," : "", r.all[i].first.c_str(), r.all[i].second);
+        all += tmp;
+    }
+    char head[512];
+    // auto_gemm.rs:484-496: the same keys in the same order
+    snprintf(head, sizeof head,
+             "{\"tile_m\":%u,\"tile_n\":%u,\"tile_k\":%u,\"wg_size\":%u,\"split_k\":%u,\"lds_pad\":%u,\"n_col_passes\":%u,"
+             "\"wgp\":%s,\"swap\":%s,\"tflops\":%.2f,\"all\":[",
+             c.tile_m, c.tile_n, c.tile_k, c.wg_size, split_of(&c), c.lds_pad, c.n_col_passes, c.wgp_mode ? "true" : "false",
+             c.swap_grid ? "true" : "false", r.best_tflops);
+    const std::string path = cache_path(t, m, n, k);
+    FILE* f = fopen(path.c_str(), "wb");
+    if (!f) { fprintf(stderr, "[autotune] Cache write failed: %s\n", path.c_str()); return; }
+    fputs(head, f); fputs(all.c_str(), f); fputs("]}", f);
+    fclose(f);
+}
+
+uint16_t bf16_trunc(float v) { uint32_t b; memcpy(&b, &v, 4); return (uint16_t)(b >> 16); }
+
+struct Buffers {
+    t0_runtime* rt;
+    std::vector<t0_buffer*> bufs;
+    ~Buffers() { for (t0_buffer* b : bufs) t0_rt_recycle(rt, b); }
+    t0_buffer* alloc(size_t n) { t0_buffer* b = nullptr; if (t0_rt_alloc(rt, n, &b) != T0_OK) return nullptr; bufs.push_back(b); return b; }
+};
+
+int dispatch_cfg(t0_runtime* rt, const t0_gemm_config* cfg, t0_buffer* a, t0_buffer* b, t0_buffer* c, uint32_t m, uint32_t n, uint32_t k) {
+    t0_kernel* kern = nullptr;
+    int rc = t0_rt_ensure_gemm_kernel(rt, cfg, &kern);
+    if (rc != T0_OK) return rc;
+    uint8_t ka[40];
+    t0_build_kernargs(t0_buf_gpu_addr(a), t0_buf_gpu_addr(b), t0_buf_gpu_addr(c), k, n, m, cfg, ka);
+    uint32_t grid[3] = {0, 0, 1};
+    rc = t0_compute_grid_auto(cfg, m, n, &grid[0], &grid[1]);
+    if (rc != T0_OK) return rc;
+    return t0_rt_dispatch(rt, kern, grid, ka, sizeof ka);
+}
+
+// auto_gemm.rs:223-272: one 256^3 dispatch with a = i%7-3, b = j%5-2, 72 sampled outputs within 0.05 of the CPU dot product
+int smoke_test_256(t0_runtime* rt, const t0_gemm_config* cfg, bool* ok) {
+    const uint32_t S = 256;
+    t0_gemm_config c = *cfg;
+    std::vector<float> af(S * S), bf(S * S);
+    std::vector<uint16_t> ab(S * S), bb(S * S);
+    for (uint32_t i = 0; i < S * S; ++i) { af[i] = (float)(i % 7) - 3.0f; bf[i] = (float)(i % 5) - 2.0f; ab[i] = bf16_trunc(af[i]); bb[i] = bf16_trunc(bf[i]); }
+    Buffers B{rt, {}};
+    const uint32_t sk = split_of(&c);
+    t0_buffer *a = B.alloc(S * S * 2), *b = B.alloc(S * S * 2), *y = B.alloc((size_t)S * S * 4 * sk);
+    if (!a || !b || !y) return T0_ERR_CUDA;
+    int rc = t0_buf_write(a, ab.data(), ab.size() * 2);
+    if (rc == T0_OK) rc = t0_buf_write(b, bb.data(), bb.size() * 2);
+    if (rc == T0_OK) rc = t0_buf_zero(y);
+    if (rc == T0_OK) rc = dispatch_cfg(rt, &c, a, b, y, S, S, S);
+    if (rc != T0_OK) return rc;
+    std::vector<float> out((size_t)S * S * sk);
+    rc = t0_rt_read_f32(rt, y, out.size(), out.data());
+    if (rc != T0_OK) return rc;
+    std::vector<size_t> idx;
+    for (size_t i = 0; i < 16; ++i) idx.push_back(i * S + i);
+    for (size_t i = 0; i < 56; ++i) idx.push_back(i * 331 + 97);
+    *ok = true;
+    for (size_t i : idx) {
+        if (i >= (size_t)S * S) continue;
+        const size_t r = i / S, col = i % S;
+        float ref = 0.0f;
+        for (uint32_t kk = 0; kk < S; ++kk) ref += af[r * S + kk] * bf[col * S + kk];
+        float got = 0.0f;
+        for (uint32_t s = 0; s < sk; ++s) got += out[(size_t)s * S * S + i];   // split-K planes are summed by the host
+        if (std::fabs(got - ref) > 0.05f) { *ok = false; break; }
+    }
+    return T0_OK;
+}
+
+// auto_gemm.rs:279-348: zeroed buffers, one warm-up, n_iters synchronous dispatches, median -> TFLOP/s
+int benchmark_one(t0_runtime* rt, const t0_gemm_config* cfg, uint32_t m, uint32_t n, uint32_t k, size_t n_iters, double* tflops) {
+    Buffers B{rt, {}};
+    const uint32_t sk = split_of(cfg);
+    t0_buffer* a = B.alloc(std::max<size_t>((size_t)m * k * 2, 4096));
+    t0_buffer* b = B.alloc(std::max<size_t>((size_t)n * k * 2, 4096));
+    t0_buffer* c = B.alloc(std::max<size_t>((size_t)m * n * 4 * sk, 4096));
+    if (!a || !b || !c) return T0_ERR_CUDA;
+    t0_buf_zero(a); t0_buf_zero(b); t0_buf_zero(c);
+    int rc = dispatch_cfg(rt, cfg, a, b, c, m, n, k);
+    if (rc != T0_OK) return rc;
+    std::vector<double> times;
+    for (size_t i = 0; i < std::max<size_t>(n_iters, 1); ++i) {
+        // the reference times the synchronous dispatch with the host clock (:325-331); the device stopwatch on the same
+        // stream removes the host launch jitter from the comparison between candidates
+        float ms = 0.0f;
+        rc = t0_rt_timer_start(rt);
+        if (rc == T0_OK) rc = dispatch_cfg(rt, cfg, a, b, c, m, n, k);
+        if (rc == T0_OK) rc = t0_rt_timer_stop(rt, &ms);
+        if (rc != T0_OK) return rc;
+        times.push_back(ms);
+    }
+    std::sort(times.begin(), times.end());
+    const double median_ms = times[times.size() / 2];
+    *tflops = median_ms > 0 ? 2.0 * m * (double)n * k / (median_ms * 1e-3) / 1e12 : 0.0;
+    return T0_OK;
+}
+
+std::mutex g_global_mu;
+std::unique_ptr<t0_tuner> g_global;
+
+}  // namespace
+
+extern "C" {
+
+int t0_tuner_new(t0_tuner** out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    *out = new t0_tuner();
+    (*out)->cache_dir = default_cache_dir();
+    return T0_OK;
+}
+
+int t0_tuner_with_cache_dir(const char* dir, t0_tuner** out) {
+    if (!out || !dir) return fail(T0_ERR_INVALID, "null argument");
+    *out = new t0_tuner();
+    (*out)->cache_dir = dir;
+    return T0_OK;
+}
+
+void t0_tuner_free(t0_tuner* t) { delete t; }
+
+int t0_tuner_configure(t0_tuner* t, size_t max_candidates, size_t n_iters) {
+    if (!t) return fail(T0_ERR_INVALID, "null tuner");
+    if (max_candidates) t->max_candidates = max_candidates;
+    if (n_iters) t->n_iters = n_iters;
+    return T0_OK;
+}
+
+size_t t0_tuner_max_candidates(const t0_tuner* t) { return t ? t->max_candidates : 0; }
+size_t t0_tuner_n_iters(const t0_tuner* t) { return t ? t->n_iters : 0; }
+size_t t0_tuner_cache_len(const t0_tuner* t) { return t ? t->cache.size() : 0; }
+const char* t0_tuner_cache_dir(const t0_tuner* t) { return t ? t->cache_dir.c_str() : ""; }
+
+int t0_tuner_tune(t0_tuner* t, t0_runtime* rt, uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* out) {
+    if (!t || !rt || !out) return fail(T0_ERR_INVALID, "null argument");
+    if (m == 0 || n == 0 || k == 0) return fail(T0_ERR_INVALID, "tune needs positive dimensions");
+    const auto key = std::make_tuple(m, n, k);
+    auto it = t->cache.find(key);
+    if (it != t->cache.end()) { *out = it->second.best; return T0_OK; }            // 1. in-memory cache
+    TuneResult cached;
+    if (load_cache(t, m, n, k, &cached)) {                                         // 2. disk cache
+        fprintf(stderr, "[autotune] Cache hit: %ux%ux%u -> %s (%.1f TF)\n", m, n, k, gemm_config_name(cached.best).c_str(), cached.best_tflops);
+        *out = cached.best;
+        t->cache[key] = cached;
+        return T0_OK;
+    }
+    // 3. candidates from the cost model (argument order (m, n, k) there), best predicted first, distinct kernels only
+    std::vector<t0_gemm_config> cand(64);
+    std::vector<double> pred(64);
+    const int n_cand = t0_auto_schedule_gemm(m, n, k, cand.data(), pred.data(), 64);
+    std::vector<t0_gemm_config> pick;
+    std::vector<std::string> seen;
+    for (int i = 0; i < n_cand && pick.size() < t->max_candidates; ++i) {
+        const std::string nm = gemm_config_name(cand[i]);
+        if (std::find(seen.begin(), seen.end(), nm) != seen.end()) continue;
+        seen.push_back(nm);
+        pick.push_back(cand[i]);
+    }
+    if (pick.empty()) return fail(T0_ERR_UNSUPPORTED, "[autotune] no candidate configuration for %ux%ux%u", m, n, k);
+    // 4. safety screen, then timing
+    TuneResult res;
+    for (const t0_gemm_config& c : pick) {
+        bool ok = false;
+        int rc = smoke_test_256(rt, &c, &ok);
+        if (rc != T0_OK) return rc;                 // a dispatch failure poisons the runtime: stop (auto_gemm.rs:151-163)
+        const std::string nm = gemm_config_name(c);
+        if (!ok) { fprintf(stderr, "[autotune] %s failed the 256^3 check - skipped\n", nm.c_str()); continue; }
+        double tf = 0.0;
+        rc = benchmark_one(rt, &c, m, n, k, t->n_iters, &tf);
+        if (rc != T0_OK) return rc;
+        fprintf(stderr, "[autotune] %s: %.1f TF\n", nm.c_str(), tf);
+        res.all.emplace_back(nm, tf);
+        if (tf > res.best_tflops || res.all.size() == 1) { res.best_tflops = tf; res.best = c; }
+    }
+    if (res.all.empty()) return fail(T0_ERR_UNSUPPORTED, "[autotune] every candidate failed the correctness screen");
+    std::stable_sort(res.all.begin(), res.all.end(), [](const std::pair<std::string, double>& a, const std::pair<std::string, double>& b) { return a.second > b.second; });
+    res.from_cache = false;
+    save_cache(t, m, n, k, res);
+    t->cache[key] = res;
+    *out = res.best;
+    return T0_OK;
+}
+
+int t0_tuner_result(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, double* best_tflops, int* from_cache, int* n_measured) {
+    if (!t) return fail(T0_ERR_INVALID, "null tuner");
+    auto it = t->cache.find(std::make_tuple(m, n, k));
+    if (it == t->cache.end()) return fail(T0_ERR_INVALID, "no tuning result for %ux%ux%u", m, n, k);
+    if (best_tflops) *best_tflops = it->second.best_tflops;
+    if (from_cache) *from_cache = it->second.from_cache ? 1 : 0;
+    if (n_measured) *n_measured = (int)it->second.all.size();
+    return T0_OK;
+}
+
+// test hooks for the cache file format (auto_gemm.rs:751-780 round-trips save_cache/load_cache the same way)
+int t0_tuner_save_cache(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, const t0_gemm_config* best, double best_tflops) {
+    if (!t || !best) return fail(T0_ERR_INVALID, "null argument");
+    TuneResult r;
+    r.best = *best; r.best_tflops = best_tflops;
+    r.all.emplace_back(gemm_config_name(*best), best_tflops);
+    save_cache(t, m, n, k, r);
+    return T0_OK;
+}
+
+int t0_tuner_load_cache(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* best, double* best_tflops) {
+    if (!t || !best) return fail(T0_ERR_INVALID, "null argument");
+    TuneResult r;
+    if (!load_cache(t, m, n, k, &r)) return fail(T0_ERR_IO, "no readable cache file %s", cache_path(t, m, n, k).c_str());
+    *best = r.best;
+    if (best_tflops) *best_tflops = r.best_tflops;
+    return T0_OK;
+}
+
+int t0_parse_json_number(const char* json, const char* key, double* out) {
+    if (!json || !key || !out) return fail(T0_ERR_INVALID, "null argument");
+    return parse_number(json, key, out) ? T0_OK : fail(T0_ERR_IO, "key '%s' not found", key);
+}
+
+void t0_tuner_invalidate(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k) {
+    if (!t) return;
+    t->cache.erase(std::make_tuple(m, n, k));
+    unlink(cache_path(t, m, n, k).c_str());
+}
+
+void t0_tuner_clear(t0_tuner* t) {
+    if (!t) return;
+    t->cache.clear();
+    // auto_gemm.rs:513-516 removes the whole directory; only this tuner's own gemm_*.json files are removed here
+    if (DIR* d = opendir(t->cache_dir.c_str())) {
+        while (dirent* e = readdir(d)) {
+            const std::string nm = e->d_name;
+            if (nm.rfind("gemm_", 0) == 0 && nm.size() > 5 && nm.substr(nm.size() - 5) == ".json") unlink((t->cache_dir + "/" + nm).c_str());
+        }
+        closedir(d);
+        rmdir(t->cache_dir.c_str());
+    }
+}
+
+void t0_tuner_report(const t0_tuner* t) {
+    if (!t) return;
+    fprintf(stderr, "GEMM Autotune Cache (%zu entries)\n", t->cache.size());
+    for (const auto& kv : t->cache)
+        fprintf(stderr, "  %ux%ux%u -> %s (%.1f TF) %s\n", std::get<0>(kv.first), std::get<1>(kv.first), std::get<2>(kv.first),
+                gemm_config_name(kv.second.best).c_str(), kv.second.best_tflops, kv.second.from_cache ? "[cached]" : "[measured]");
+}
+
+t0_tuner* t0_global_tuner(void) {
+    std::lock_guard<std::mutex> g(g_global_mu);
+    if (!g_global) { g_global.reset(new t0_tuner()); g_global->cache_dir = default_cache_dir(); }
+    return g_global.get();
+}
+
+int t0_auto_gemm(t0_runtime* rt, t0_buffer* a, t0_buffer* b, t0_buffer* c, uint32_t m, uint32_t n, uint32_t k, double* tflops) {
+    if (!rt || !a || !b || !c) return fail(T0_ERR_INVALID, "null argument");
+    t0_gemm_config cfg;
+    t0_tuner* tuner = t0_global_tuner();
+    {
+        std::lock_guard<std::mutex> g(g_global_mu);
+        int rc = t0_tuner_tune(tuner, rt, m, n, k, &cfg);          // 1. tune (or cache hit)
+        if (rc != T0_OK) return rc;
+    }
+    if (split_of(&cfg) > 1 && t0_buf_size(c) < (size_t)m * n * 4 * split_of(&cfg)) cfg.split_k = 0;   // c holds one plane only
+    int rc = dispatch_cfg(rt, &cfg, a, b, c, m, n, k);             // 2-3. kernel (cached by name), kernargs, grid, dispatch
+    if (rc != T0_OK) return rc;
+    if (tflops) {                                                   // 4. the tuned figure
+        std::lock_guard<std::mutex> g(g_global_mu);
+        auto it = tuner->cache.find(std::make_tuple(m, n, k));
+        *tflops = it != tuner->cache.end() ? it->second.best_tflops : 0.0;
+    }
+    return T0_OK;
+}
+
+}  // extern "C"

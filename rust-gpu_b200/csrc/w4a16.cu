@@ -9,17 +9,19 @@
 //
 // K2 is HBM-bound for M <= 16 (the int4 weights are ~97% of the bytes), so it is organised around the
 // weight stream:
-//   * 148 persistent CTAs of 16 warps; the flattened space (32-column slab) x (512-deep k step) is cut
-//     into equal contiguous ranges, one per CTA (a slab may straddle two CTAs);
-//   * per k step every lane issues ONE 16-byte load (4 columns x 8 codes) so a warp reads four full
-//     128-byte rows; loads for the next steps are already in flight (register queue);
+//   * 148 persistent CTAs of 16 warps = 8 column slabs side by side x 2 k slices: one step of a CTA reads
+//     eight packed rows of 1 KiB each (a DRAM page is used whole while it is open; 128-byte pieces 44 KiB
+//     apart measured 11% of the copy bandwidth); the flattened space (256-column band) x (64-deep k step)
+//     is cut into equal contiguous ranges, one per CTA (a band straddles several CTAs);
+//   * per step every lane issues ONE 16-byte load (4 columns x 8 codes); loads for the next steps are
+//     already in flight (register queue);
 //   * codes become bf16 with one logic op (0x4300 | q is the bf16 128+q), minus (128+z), times s: two
 //     bf16x2 ops per pair, bit-identical to the oracle's fp32 formula because (q-z)*s is exact in fp32;
 //   * mma.sync m16n8k16 (bf16 in, fp32 out) does the dot products: the activations are the 16-row
 //     operand, read from shared memory where they sit pre-permuted to match the code order in a word;
-//   * the 16 warps' k slices are summed through shared memory in a fixed order; a slab finished by one
-//     CTA is stored directly, a straddling slab goes through a small scratch area and the CTA that
-//     arrives last adds the pieces in k order (no CTA ever waits for another).
+//   * the k slices of a slab are summed through shared memory in a fixed order; a band finished by one
+//     CTA is stored directly, otherwise each CTA leaves its M x 256 piece in a scratch area and the CTA
+//     that arrives last adds the pieces in k order (no CTA ever waits for another).
 #include "runtime_internal.h"
 
 #include <cuda_bf16.h>
@@ -30,11 +32,15 @@ namespace {
 
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
-constexpr int kSlabCols = 32;
-constexpr int kUnitK = kWarps * 32;      // k depth of one step of the CTA: 32 per warp
-constexpr int kDepth = 4;                // steps kept in flight per lane
-constexpr int kPieceFloats = 16 * kSlabCols;
-constexpr size_t kCounterRegion = 64 * 1024;   // arrival counters: up to 16384 slabs (N <= 524288)
+constexpr int kSlabCols = 32;            // columns one warp owns
+constexpr int kBandSlabs = 8;            // slabs side by side in a CTA: 256 columns = 1 KiB of every packed row
+constexpr int kBandCols = kSlabCols * kBandSlabs;
+constexpr int kSlices = kWarps / kBandSlabs;   // k slices of 64 per step
+constexpr int kUnitK = kSlices * 64;     // k depth of one step of the CTA: one quantisation group of 128
+constexpr int kDepth = 3;                // steps kept in flight per lane (two 16-byte loads each)
+constexpr int kARecord = 288;            // bytes per 8-k activation record (256 + 32: conflict-free quad reads)
+constexpr int kPieceFloats = 16 * kBandCols;
+constexpr size_t kCounterRegion = 16 * 1024;   // arrival counters: up to 4096 bands (N <= 1048576)
 
 struct W4Params {
     const uint16_t* a;
@@ -42,19 +48,20 @@ struct W4Params {
     const uint16_t* scales;
     const uint32_t* zeros;
     float* y;
-    float* partials;     // [grid][2][16*32]
-    int* counters;       // [n_slabs], zero between calls
+    float* partials;     // [grid][2][16*256]
+    int* counters;       // [n_bands], zero between calls
     uint32_t M, N, K, group;
+    uint32_t units_per_group;   // group / 64: steps that share one row of scales and zero points
     uint32_t nz;         // u32 words per row of `zeros`
-    uint32_t n_slabs, ksteps, total_units;
-    uint32_t a_stride;   // bytes between activation rows in shared memory
+    uint32_t n_bands, ksteps, total_units;
     uint32_t rows;       // activation rows staged: 8 or 16
+    unsigned long long* stamps;   // optional trace: 4 nanosecond stamps per CTA (entry, staged, loop done, exit)
 };
 
 struct UnitRegs {
-    uint4 w;     // 4 columns x 8 codes
+    uint4 w0, w1;   // 4 columns x 8 codes, packed rows r and r+4 of the lane's slice
     uint2 s;     // 4 bf16 scales
-    uint32_t z;  // 4 zero points in the low 16 bits
+    uint32_t z;  // the word holding this lane's 4 zero points (low or high half)
 };
 
 __device__ __forceinline__ uint32_t owner_of(uint32_t unit, uint32_t grid, uint32_t total) {
@@ -62,24 +69,6 @@ __device__ __forceinline__ uint32_t owner_of(uint32_t unit, uint32_t grid, uint3
 }
 __device__ __forceinline__ uint32_t range_begin(uint32_t cta, uint32_t grid, uint32_t total) {
     return (uint32_t)((uint64_t)cta * total / grid);
-}
-
-__device__ __forceinline__ UnitRegs load_unit(const W4Params& p, uint32_t unit, uint32_t warp, uint32_t g, uint32_t t) {
-    UnitRegs r;
-    r.w = make_uint4(0, 0, 0, 0);
-    r.s = make_uint2(0, 0);
-    r.z = 0;
-    const uint32_t slab = unit / p.ksteps, ks = unit - slab * p.ksteps;
-    const uint32_t kbase = ks * kUnitK + warp * 32;
-    const uint32_t col = slab * kSlabCols + 4 * g;
-    if (kbase < p.K && col < p.N) {
-        const uint32_t kg = (kbase >> 3) + t;
-        r.w = __ldcs((const uint4*)(p.packed + (size_t)kg * p.N + col));
-        const uint32_t grp = kbase / p.group;
-        r.s = __ldg((const uint2*)(p.scales + (size_t)grp * p.N + col));
-        r.z = __ldg(p.zeros + (size_t)grp * p.nz + (col >> 3)) >> ((col & 4) * 4);
-    }
-    return r;
 }
 
 __device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
@@ -98,80 +87,172 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// One lane's position in the weight stream: pointers advance by constant strides inside a band and are
+// rebuilt only when the stream crosses into the next band.
+struct Stream {
+    const uint4* w;        // 4 columns x 8 codes of this lane's first packed row of the step (the second is 4 rows down)
+    const uint2* s;        // 4 scales
+    const uint32_t* z;     // word holding the 4 zero points
+    uint32_t band, ks, gcnt;
+
+    __device__ __forceinline__ void set(const W4Params& p, uint32_t band_, uint32_t ks_, uint32_t lane_col, uint32_t row_in_unit) {
+        band = band_; ks = ks_;
+        const uint32_t col = band * kBandCols + lane_col;
+        const uint32_t grp = ks / p.units_per_group;
+        gcnt = ks - grp * p.units_per_group;
+        const uint32_t c = col < p.N ? col : band * kBandCols;
+        w = (const uint4*)(p.packed + (size_t)(ks * (kUnitK / 8) + row_in_unit) * p.N + c);
+        s = (const uint2*)(p.scales + (size_t)grp * p.N + c);
+        z = p.zeros + (size_t)grp * p.nz + (c >> 3);
+    }
+    __device__ __forceinline__ void step(const W4Params& p, uint32_t lane_col, uint32_t row_in_unit) {
+        if (++ks == p.ksteps) { set(p, band + 1, 0, lane_col, row_in_unit); return; }
+        w += (size_t)(kUnitK / 8) * (p.N / 4);
+        if (++gcnt == p.units_per_group) { gcnt = 0; s += p.N / 4; z += p.nz; }
+    }
+    // Nothing here may consume a loaded value: a warp issues in order, so the first use of a load result
+    // is where it waits for memory.  The zero-point word is shifted at the point of use instead.
+    // A lane whose columns lie beyond N reads the band's first columns instead: what it computes is never stored.
+    __device__ __forceinline__ UnitRegs load(uint32_t row_stride_u4) const {
+        UnitRegs r;
+        r.w0 = __ldcs(w);
+        r.w1 = __ldcs(w + 4 * (size_t)row_stride_u4);
+        r.s = __ldg(s);
+        r.z = __ldg(z);
+        return r;
+    }
+};
+
+// (x & mask) | magic in one LOP3; mask and magic must sit in registers (the instruction takes one immediate at most)
+__device__ __forceinline__ uint32_t and_or(uint32_t x, uint32_t mask, uint32_t magic) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(x), "r"(mask), "r"(magic));
+    return r;
+}
+
+// 32 k of one lane: 4 columns x 8 codes against the matching activation quads
+__device__ __forceinline__ void consume_word4(float (&acc)[4][4], const uint4& wq, const uint32_t (&zz)[4], const uint32_t (&ss)[4],
+                                              const uint4& qa0, const uint4& qa1, uint32_t mask, uint32_t magic) {
+    const uint32_t words[4] = {wq.x, wq.y, wq.z, wq.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t wv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t v = and_or(words[c] >> (4 * i), mask, magic);   // bf16x2 (128+q_i, 128+q_{i+4})
+            wv[i] = bf16x2_mul(bf16x2_sub(v, zz[c]), ss[c]);
+        }
+        mma_bf16_16816(acc[c], qa0.x, qa0.y, qa0.z, qa0.w, wv[0], wv[1]);
+        mma_bf16_16816(acc[c], qa1.x, qa1.y, qa1.z, qa1.w, wv[2], wv[3]);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params p) {
     extern __shared__ uint8_t smem[];
-    uint8_t* a_smem = smem;                                            // [rows][a_stride]
-    float* red = (float*)(smem + (size_t)p.rows * p.a_stride);        // [kWarps][16][33]
+    float* red = (float*)smem;                                        // [kWarps][16][33]
+    // activations of this CTA's k range, one 288-byte record per group of eight k: eight 16-byte quads
+    // {row g, row g+8} x {k0 k4 | k1 k5} then eight quads for {k2 k6 | k3 k7}: each quad is the A fragment of one MMA
+    uint8_t* a_smem = smem + (size_t)kWarps * 16 * 33 * sizeof(float);
     __shared__ int s_last;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t slab = warp & (kBandSlabs - 1), slice = warp / kBandSlabs;
     const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t lane_col = slab * kSlabCols + 4 * g;       // first of this lane's 4 columns, within a band
+    const uint32_t row_in_unit = slice * 8 + t;               // first packed row of this lane within a 128-deep step
+    const uint32_t zshift = (g & 1) * 16;
+    const uint32_t row_stride_u4 = p.N / 4;
     const uint32_t u0 = range_begin(blockIdx.x, gridDim.x, p.total_units);
     const uint32_t u1 = range_begin(blockIdx.x + 1, gridDim.x, p.total_units);
+    if (u0 >= u1) return;
+    auto stamp = [&](int i) {
+        if (p.stamps && tid == 0) { unsigned long long t_ns; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns)); p.stamps[blockIdx.x * 4 + i] = t_ns; }
+    };
+    stamp(0);
+    const uint32_t band_first = u0 / p.ksteps, band_last = (u1 - 1) / p.ksteps;
+    const uint32_t ks_first = u0 - band_first * p.ksteps;
 
     // weights first: they are the long pole
+    Stream pre;
+    pre.set(p, band_first, ks_first, lane_col, row_in_unit);
     UnitRegs q[kDepth];
 #pragma unroll
     for (int d = 0; d < kDepth; ++d)
-        if (u0 + d < u1) q[d] = load_unit(p, u0 + d, warp, g, t);
+        if (u0 + d < u1) { q[d] = pre.load(row_stride_u4); pre.step(p, lane_col, row_in_unit); }
 
+    // the k range this CTA touches: one stretch of a band, or everything when its range crosses into the next band
+    uint32_t k_lo = 0, k_hi = p.K;
+    if (band_first == band_last) {
+        k_lo = ks_first * kUnitK;
+        k_hi = (u1 - band_first * p.ksteps) * kUnitK;
+    }
     // stage the activations: within every group of eight k the order becomes 0,4,1,5,2,6,3,7 so that the
-    // pair (code i, code i+4) a single mask pulls out of a word lines up with consecutive bf16 in a row
-    const uint32_t k8 = p.K >> 3;
-    for (uint32_t i = tid; i < p.rows * k8; i += kThreads) {
-        const uint32_t r = i / k8, c = i - r * k8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < p.M) v = __ldg((const uint4*)(p.a + (size_t)r * p.K + (size_t)c * 8));
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410);   // k0, k4
-        o.y = __byte_perm(v.x, v.z, 0x7632);   // k1, k5
-        o.z = __byte_perm(v.y, v.w, 0x5410);   // k2, k6
-        o.w = __byte_perm(v.y, v.w, 0x7632);   // k3, k7
-        *(uint4*)(a_smem + (size_t)r * p.a_stride + (size_t)c * 16) = o;
+    // pair (code i, code i+4) a single mask pulls out of a word lines up with the two bf16 of one register
+    const uint32_t n_kg = (k_hi - k_lo) >> 3;
+    for (uint32_t i0 = tid; i0 < n_kg * 8; i0 += 4 * kThreads) {
+        // four records per thread per round: all loads are issued before the first is used
+        uint4 lo[4], hi[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t i = i0 + j * kThreads, kg = i >> 3, r = i & 7;
+            lo[j] = make_uint4(0, 0, 0, 0); hi[j] = make_uint4(0, 0, 0, 0);
+            if (i < n_kg * 8 && r < p.M) lo[j] = __ldg((const uint4*)(p.a + (size_t)r * p.K + k_lo + (size_t)kg * 8));
+            if (i < n_kg * 8 && r + 8 < p.M) hi[j] = __ldg((const uint4*)(p.a + (size_t)(r + 8) * p.K + k_lo + (size_t)kg * 8));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t i = i0 + j * kThreads, kg = i >> 3, r = i & 7;
+            if (i >= n_kg * 8) break;
+            uint4 q0, q1;
+            q0.x = __byte_perm(lo[j].x, lo[j].z, 0x5410); q0.y = __byte_perm(hi[j].x, hi[j].z, 0x5410);   // k0 k4: rows r, r+8
+            q0.z = __byte_perm(lo[j].x, lo[j].z, 0x7632); q0.w = __byte_perm(hi[j].x, hi[j].z, 0x7632);   // k1 k5
+            q1.x = __byte_perm(lo[j].y, lo[j].w, 0x5410); q1.y = __byte_perm(hi[j].y, hi[j].w, 0x5410);   // k2 k6
+            q1.z = __byte_perm(lo[j].y, lo[j].w, 0x7632); q1.w = __byte_perm(hi[j].y, hi[j].w, 0x7632);   // k3 k7
+            *(uint4*)(a_smem + (size_t)kg * kARecord + r * 16) = q0;
+            *(uint4*)(a_smem + (size_t)kg * kARecord + 128 + r * 16) = q1;
+        }
     }
     __syncthreads();
+    stamp(1);
 
     float acc[4][4];
 #pragma unroll
     for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[c][j] = 0.0f;
+    // constants the compiler must keep in registers (see and_or)
+    uint32_t mask, magic;
+    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
+    asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
 
-    for (uint32_t u = u0; u < u1; ++u) {
-        // take the oldest entry of the queue, refill it with the step kDepth ahead
-        const UnitRegs cur = q[0];
+    uint32_t band = band_first, ks = ks_first;
+    // this lane's activation records of the current step: record (k/8) for its first word, 4 records on for the second
+    const uint8_t* arec = a_smem + (size_t)((ks_first * kUnitK - k_lo) / 8 + row_in_unit) * kARecord + g * 16;
+
+    for (uint32_t ub = u0; ub < u1; ub += kDepth) {
 #pragma unroll
-        for (int d = 0; d < kDepth - 1; ++d) q[d] = q[d + 1];
-        if (u + kDepth < u1) q[kDepth - 1] = load_unit(p, u + kDepth, warp, g, t);
-
-        const uint32_t slab = u / p.ksteps, ks = u - slab * p.ksteps;
-        const uint32_t kbase = ks * kUnitK + warp * 32;
-        if (kbase < p.K) {
-            const uint8_t* arow = a_smem + (size_t)g * p.a_stride + (size_t)(kbase + 8 * t) * 2;
-            const uint4 alo = *(const uint4*)arow;
-            uint4 ahi = make_uint4(0, 0, 0, 0);
-            if (p.rows > 8) ahi = *(const uint4*)(arow + 8 * (size_t)p.a_stride);
-            const uint32_t words[4] = {cur.w.x, cur.w.y, cur.w.z, cur.w.w};
+      for (int d = 0; d < kDepth; ++d) {
+        const uint32_t u = ub + d;
+        if (u >= u1) break;
+        {
+            uint32_t zz[4], ss[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const uint32_t z = (cur.z >> (4 * c)) & 0xFu;
-                const uint32_t zz = 0x43004300u | z | (z << 16);                         // bf16x2 (128+z, 128+z)
-                const uint32_t sbits = (c & 1) ? ((c & 2 ? cur.s.y : cur.s.x) >> 16) : ((c & 2 ? cur.s.y : cur.s.x) & 0xFFFFu);
-                const uint32_t ss = sbits | (sbits << 16);
-                uint32_t wv[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const uint32_t v = ((words[c] >> (4 * i)) & 0x000F000Fu) | 0x43004300u;   // bf16x2 (128+q_i, 128+q_{i+4})
-                    wv[i] = bf16x2_mul(bf16x2_sub(v, zz), ss);
-                }
-                mma_bf16_16816(acc[c], alo.x, ahi.x, alo.y, ahi.y, wv[0], wv[1]);
-                mma_bf16_16816(acc[c], alo.z, ahi.z, alo.w, ahi.w, wv[2], wv[3]);
+                const uint32_t z = (q[d].z >> (zshift + 4 * c)) & 0xFu;
+                zz[c] = z * 0x00010001u + 0x43004300u;                                   // bf16x2 (128+z, 128+z)
+                ss[c] = __byte_perm((c & 2) ? q[d].s.y : q[d].s.x, 0, (c & 1) ? 0x3232 : 0x1010);   // (s, s)
             }
+            consume_word4(acc, q[d].w0, zz, ss, *(const uint4*)arec, *(const uint4*)(arec + 128), mask, magic);
+            consume_word4(acc, q[d].w1, zz, ss, *(const uint4*)(arec + 4 * kARecord), *(const uint4*)(arec + 4 * kARecord + 128), mask, magic);
         }
+        // slot d of the ring is consumed: refill it with the step kDepth ahead
+        if (u + kDepth < u1) { q[d] = pre.load(row_stride_u4); pre.step(p, lane_col, row_in_unit); }
+        arec += (kUnitK / 8) * kARecord;
 
-        const bool slab_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
-        if (slab_ends) {
-            // fixed-order sum of the 16 warps' k slices
+        const bool band_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
+        if (u + 1 == u1) stamp(2);
+        if (band_ends) {
+            // every warp parks its 16 x 32 partial; the k slices of a slab are then added in slice order
             float* mine = red + (size_t)warp * 16 * 33;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -183,39 +264,71 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
                 for (int j = 0; j < 4; ++j) acc[c][j] = 0.0f;
             }
             __syncthreads();
-            const uint32_t row = tid >> 5, col = tid & 31;
-            float sum = 0.0f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) sum += red[(size_t)w * 16 * 33 + row * 33 + col];
-
-            const uint32_t first_unit = slab * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
-            const uint32_t ncol = slab * kSlabCols + col;
+            const uint32_t first_unit = band * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
             const bool whole = first_unit >= u0 && last_unit <= u1;
-            if (whole) {
-                if (row < p.M && ncol < p.N) p.y[(size_t)row * p.N + ncol] = sum;
-            } else {
-                const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
-                const uint32_t c_last = owner_of(last_unit - 1, gridDim.x, p.total_units);
-                const uint32_t slot = (first_unit <= u0) ? 0u : 1u;   // the piece of the slab holding this CTA's first unit is slot 0
-                p.partials[((size_t)blockIdx.x * 2 + slot) * kPieceFloats + tid] = sum;
-                __threadfence();
-                __syncthreads();
-                if (tid == 0) s_last = (atomicAdd(&p.counters[slab], 1) == (int)(c_last - c_first)) ? 1 : 0;
+            const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
+            const uint32_t c_last = owner_of(last_unit - 1, gridDim.x, p.total_units);
+            const uint32_t slot = (first_unit <= u0) ? 0u : 1u;   // the piece of the band holding this CTA's first unit is slot 0
+            float* piece = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPieceFloats;
+            for (uint32_t idx = tid; idx < p.M * kBandCols; idx += kThreads) {
+                const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
+                const uint32_t sl = col / kSlabCols, c32 = col - sl * kSlabCols;
+                float sum = 0.0f;
+#pragma unroll
+                for (int s = 0; s < kSlices; ++s) sum += red[(size_t)(s * kBandSlabs + sl) * 16 * 33 + row * 33 + c32];
+                const uint32_t ncol = band * kBandCols + col;
+                if (whole) { if (ncol < p.N) p.y[(size_t)row * p.N + ncol] = sum; }
+                else piece[idx] = sum;
+            }
+            if (!whole) {
+                __syncthreads();                       // every thread's part of the piece is written ...
+                if (tid == 0) {
+                    __threadfence();                   // ... and made visible before this CTA is counted
+                    s_last = (atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first)) ? 1 : 0;
+                    if (s_last) __threadfence();
+                }
                 __syncthreads();
                 if (s_last) {
-                    __threadfence();
-                    float total = 0.0f;
+                    // last to arrive: add the pieces in k order (CTA order) and store; nobody waits for anybody.
+                    // Only the first contributor can hold this band in slot 1 (its range began in the band before).
+                    const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
+                    constexpr int kPer = kPieceFloats / kThreads;   // 8 outputs per thread when M = 16
+                    float total[kPer];
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
                     for (uint32_t c = c_first; c <= c_last; ++c) {
-                        const uint32_t cs = (first_unit <= range_begin(c, gridDim.x, p.total_units)) ? 0u : 1u;
-                        total += __ldcg(p.partials + ((size_t)c * 2 + cs) * kPieceFloats + tid);
+                        const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
+                        float v[kPer];
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j) {
+                            const uint32_t idx = tid + j * kThreads;
+                            v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j) total[j] += v[j];
                     }
-                    if (row < p.M && ncol < p.N) p.y[(size_t)row * p.N + ncol] = total;
-                    if (tid == 0) p.counters[slab] = 0;   // ready for the next call
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) {
+                        const uint32_t idx = tid + j * kThreads;
+                        if (idx < p.M * kBandCols) {
+                            const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
+                            const uint32_t ncol = band * kBandCols + col;
+                            if (ncol < p.N) p.y[(size_t)row * p.N + ncol] = total[j];
+                        }
+                    }
+                    if (tid == 0) p.counters[band] = 0;   // ready for the next call
                 }
             }
             __syncthreads();
         }
+        if (++ks == p.ksteps) {
+            // next band: k starts over (a CTA that crosses bands staged the whole K range, k_lo = 0)
+            ks = 0; ++band;
+            arec = a_smem + (size_t)row_in_unit * kARecord + g * 16;
+        }
+      }
     }
+    stamp(3);
 }
 
 // ------------------------------------------------------------------ K3: stand-alone dequantisation
@@ -333,10 +446,9 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     DeviceGuard guard(rt->device);
 
     const uint32_t rows = M <= 8 ? 8 : 16;
-    const uint32_t a_stride = K * 2 + 64;   // +64 B: the eight rows a quarter-warp reads land in distinct banks
-    const size_t smem = (size_t)rows * a_stride + (size_t)kWarps * 16 * 33 * sizeof(float);
-    const bool fused = M <= 16 && (N % 8 == 0) && (K % 32 == 0) && (group % 32 == 0) && smem <= 200 * 1024 &&
-                       ceil_div(N, kSlabCols) * sizeof(int) <= kCounterRegion &&
+    const size_t smem = (size_t)(K / 8) * kARecord + (size_t)kWarps * 16 * 33 * sizeof(float);
+    const bool fused = M <= 16 && (N % 8 == 0) && (K % kUnitK == 0) && (group % kUnitK == 0) && smem <= 200 * 1024 &&
+                       ceil_div(N, kBandCols) * sizeof(int) <= kCounterRegion &&
                        ((a | packed | scales) & 15) == 0 && (zeros & 3) == 0 && (y & 3) == 0;
     if (!fused) {
         // general shapes: dequantise once into scratch, then the tcgen05 GEMM on B[K,N]
@@ -351,12 +463,11 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         return t0_gemm_launch(rt, &ga);
     }
 
-    const uint32_t n_slabs = ceil_div(N, kSlabCols), ksteps = ceil_div(K, kUnitK);
-    const uint64_t total = (uint64_t)n_slabs * ksteps;
+    const uint32_t n_bands = ceil_div(N, kBandCols), ksteps = ceil_div(K, kUnitK);
+    const uint64_t total = (uint64_t)n_bands * ksteps;
     if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "problem too large");
     const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
-    // scratch: one arrival counter per slab (zero between calls) in a fixed 64 KiB region, then two straddling
-    // pieces per CTA
+    // scratch: one arrival counter per band (zero between calls) in a fixed region, then two M x 256 pieces per CTA
     const size_t piece_bytes = (size_t)grid * 2 * kPieceFloats * sizeof(float);
     const size_t need = kCounterRegion + piece_bytes;
     if (need > rt->scratch_w4.size) {
@@ -371,18 +482,51 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     p.counters = (int*)rt->scratch_w4.ptr;
     p.partials = (float*)((uint8_t*)rt->scratch_w4.ptr + kCounterRegion);
     p.M = M; p.N = N; p.K = K; p.group = group; p.nz = (N + 7) / 8;
-    p.n_slabs = n_slabs; p.ksteps = ksteps; p.total_units = (uint32_t)total;
-    p.a_stride = a_stride; p.rows = rows;
+    p.units_per_group = group / kUnitK;
+    p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
+    p.rows = rows;
 
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
         T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_set[rt->device] = true;
     }
+    // T0_W4_TRACE=1: per-CTA stage stamps, summarised on stderr after a blocking wait (a debugging aid, off by default)
+    static const bool trace = getenv("T0_W4_TRACE") != nullptr;
+    unsigned long long* d_stamps = nullptr;
+    if (trace) {
+        T0_CUDA(cudaMalloc(&d_stamps, (size_t)grid * 4 * sizeof(unsigned long long)));
+        T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 4 * sizeof(unsigned long long)));
+        p.stamps = d_stamps;
+    }
     w4a16_gemm_kernel<<<grid, kThreads, smem, rt->stream>>>(p);
+    if (trace) {
+        std::vector<unsigned long long> h((size_t)grid * 4);
+        T0_CUDA(cudaStreamSynchronize(rt->stream));
+        T0_CUDA(cudaMemcpy(h.data(), d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        cudaFree(d_stamps);
+        unsigned long long t_min = ~0ull, t_max = 0;
+        double stage = 0, loop = 0, tail = 0;
+        for (uint32_t c = 0; c < grid; ++c) {
+            t_min = std::min(t_min, h[c * 4]); t_max = std::max(t_max, h[c * 4 + 3]);
+            stage += (double)(h[c * 4 + 1] - h[c * 4]); loop += (double)(h[c * 4 + 2] - h[c * 4 + 1]); tail += (double)(h[c * 4 + 3] - h[c * 4 + 2]);
+        }
+        fprintf(stderr, "[w4a16 trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: staging %.2f us, main loop %.2f us, flush+exit %.2f us\n",
+                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3);
+    }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(e));
     rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count) {
+    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
+    for (size_t i = 0; i < count; ++i) {
+        const t0_w4a16_args& a = args[i];
+        int rc = t0_w4a16_gemm(rt, a.a, a.packed, a.scales, a.zeros, a.y, a.m, a.n, a.k, a.group);
+        if (rc != T0_OK) return rc;
+    }
     return T0_OK;
 }
 

@@ -156,7 +156,7 @@ def test_gptq_container_to_b200(t0, oracle, rt):
 def test_fused_kernel_dequantises_bit_exactly(t0, oracle, rt):
     # one-hot activations make row m of y equal to row k0+m of the dequantised weights, exactly:
     # this reads the fused kernel's in-register dequant back without any rounding of its own
-    K, G, M = 32, 32, 16
+    K, G, M = 128, 128, 16
     N = 65536
     codes = (np.arange(K) % 16).astype(np.uint32)
     words = np.zeros(K // 8, np.uint32)
