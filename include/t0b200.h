@@ -329,6 +329,27 @@ size_t t0_gptq_gpu_buffer_size(uint32_t rows, uint32_t cols, uint32_t group_size
 long t0_gptq_to_b200(const uint8_t* packed, const float* scales, const int32_t* zero_points, uint32_t rows, uint32_t cols,
                      uint32_t group_size, uint32_t* packed_out, uint16_t* scales_out, uint32_t* zeros_out);
 
+/* ------------------------------------------------------- multi-GPU sharding */
+/* The reference is single-GPU (its MultiGpuManager bounces through host memory, src/universal/runtime/multi_gpu.rs:64-159);
+ * this section has no Rust counterpart to bind.  A large GEMM shards by N-column blocks: GPU r computes
+ * C[:, r*N/g:(r+1)*N/g] from the replicated A and its rows [r*N/g, (r+1)*N/g) of WT[N,K].  No exchange in the computation. */
+typedef struct t0_mg t0_mg;
+/* the partition rule, for callers that run one process per GPU */
+int t0_shard_columns(uint32_t n, uint32_t n_gpus, uint32_t rank, uint32_t* first_col, uint32_t* n_cols);
+/* one process driving n_gpus devices: one runtime (stream, pool) per device */
+int t0_mg_new(int n_gpus, t0_mg** out);
+void t0_mg_free(t0_mg* mg);
+int t0_mg_size(const t0_mg* mg);
+t0_runtime* t0_mg_runtime(t0_mg* mg, int rank);
+int t0_mg_synchronize(t0_mg* mg);
+/* launches rank r's block on GPU r for every r, without waiting: x[r] = A on GPU r ([M,K] bf16), b_slice[r] = its N/g rows of
+ * WT, y_slice[r] = where its [M, N/g] f32 block goes (slot r of the gather buffer when a gathered C is wanted). */
+int t0_mg_gemm_sharded(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, const uint64_t* y_slice, uint32_t m, uint32_t n, uint32_t k,
+                       uint32_t tile_n, int pair_cta);
+/* optional: every GPU ends up with all of C in the rank-major layout C_g[g][M][N/g]; c_gathered[r] is that buffer on GPU r,
+ * whose slot r the GEMM already filled.  One in-place ncclAllGather over NVLink (NCCL is loaded at run time). */
+int t0_mg_all_gather_c(t0_mg* mg, const uint64_t* c_gathered, uint32_t m, uint32_t n);
+
 /* ------------------------------------------------------- seeded inputs */
 /* Device-side generators for benchmark-sized inputs: element i of the stream (seed) gets the same bits as the
  * host generator of the test oracle, so any sub-range can be checked on the CPU without a full download. */

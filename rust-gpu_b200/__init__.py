@@ -588,6 +588,44 @@ class GpuRuntime:
         _check(lib().t0_fill_range_bf16(self._h, dst, n, seed, first_index, lo, hi))
 
 
+def shard_columns(n: int, n_gpus: int, rank: int) -> tuple[int, int]:
+    """(first column, number of columns) of rank's block of C: ``t0_shard_columns``."""
+    a, b = C.c_uint32(), C.c_uint32()
+    _check(lib().t0_shard_columns(n, n_gpus, rank, C.byref(a), C.byref(b)))
+    return a.value, b.value
+
+
+class MultiGpu:
+    """One process driving several GPUs (``t0_mg``): N-column sharded GEMM, optional gathered C."""
+
+    def __init__(self, n_gpus: int):
+        h = C.c_void_p()
+        _check(lib().t0_mg_new(n_gpus, C.byref(h)))
+        self._h = h
+        self.n = n_gpus
+
+    def runtime(self, rank: int) -> "GpuRuntime":
+        rt = GpuRuntime.__new__(GpuRuntime)
+        rt._h = C.c_void_p(lib().t0_mg_runtime(self._h, rank))
+        return rt
+
+    def gemm_sharded(self, x: list[int], b_slice: list[int], y_slice: list[int], m: int, n: int, k: int, tile_n: int = 0,
+                     pair_cta: int = 0) -> None:
+        arr = lambda v: (C.c_uint64 * len(v))(*v)
+        _check(lib().t0_mg_gemm_sharded(self._h, arr(x), arr(b_slice), arr(y_slice), m, n, k, tile_n, pair_cta))
+
+    def all_gather_c(self, c_gathered: list[int], m: int, n: int) -> None:
+        _check(lib().t0_mg_all_gather_c(self._h, (C.c_uint64 * len(c_gathered))(*c_gathered), m, n))
+
+    def synchronize(self) -> None:
+        _check(lib().t0_mg_synchronize(self._h))
+
+    def free(self) -> None:
+        if self._h:
+            lib().t0_mg_free(self._h)
+            self._h = None
+
+
 class GemmTuner:
     """``GemmTuner`` (src/t0/auto_gemm.rs:46-216)."""
 
@@ -762,6 +800,14 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_gemm_launch_batch", i32, vp, C.POINTER(GemmArgs), sz)
     sig("t0_rt_submit", i32, vp, vp, u32p, u8p, sz)
     sig("t0_rt_flush", i32, vp)
+    sig("t0_shard_columns", i32, u32, u32, u32, u32p, u32p)
+    sig("t0_mg_new", i32, i32, C.POINTER(vp))
+    sig("t0_mg_free", None, vp)
+    sig("t0_mg_size", i32, vp)
+    sig("t0_mg_runtime", vp, vp, i32)
+    sig("t0_mg_synchronize", i32, vp)
+    sig("t0_mg_gemm_sharded", i32, vp, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64), u32, u32, u32, u32, i32)
+    sig("t0_mg_all_gather_c", i32, vp, C.POINTER(u64), u32, u32)
     sig("t0_tuner_new", i32, C.POINTER(vp))
     sig("t0_tuner_with_cache_dir", i32, C.c_char_p, C.POINTER(vp))
     sig("t0_tuner_free", None, vp)

@@ -1,0 +1,156 @@
+// N-column sharding of a large GEMM over the GPUs of one node.
+//
+// The reference is single-GPU; its only multi-device code moves data through host memory
+// (src/universal/runtime/multi_gpu.rs:64-159).  Here the GEMM shards naturally: GPU r computes
+// C[:, r*N/g : (r+1)*N/g] = A * B[:, slice] with A replicated and its slice of B local (in the NT layout the
+// slice is rows [r*N/g, (r+1)*N/g) of WT[N,K], contiguous).  No exchange is needed in the computation.
+// When the caller wants every GPU to hold all of C, each rank's kernel stores straight into slot `rank` of a
+// rank-major buffer C_g[g][M][N/g] and one in-place ncclAllGather over NVLink completes it.
+// NCCL is loaded at run time (dlopen) so the core library has no link-time dependency on it.
+#include "runtime_internal.h"
+
+#include <dlfcn.h>
+
+using namespace t0;
+
+namespace {
+
+typedef struct ncclComm* ncclComm_t;
+typedef int ncclResult_t;
+typedef int ncclDataType_t;
+constexpr ncclDataType_t kNcclFloat32 = 7;
+
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*CommInitAll)(ncclComm_t*, int, const int*) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+NcclApi* nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        for (const char* name : {"libnccl.so.2", "libnccl.so"}) {
+            api.handle = dlopen(name, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (!api.handle) return;
+        api.CommInitAll = (decltype(api.CommInitAll))dlsym(api.handle, "ncclCommInitAll");
+        api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
+        api.AllGather = (decltype(api.AllGather))dlsym(api.handle, "ncclAllGather");
+        api.GroupStart = (decltype(api.GroupStart))dlsym(api.handle, "ncclGroupStart");
+        api.GroupEnd = (decltype(api.GroupEnd))dlsym(api.handle, "ncclGroupEnd");
+        api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
+    });
+    return (api.handle && api.CommInitAll && api.AllGather && api.GroupStart && api.GroupEnd) ? &api : nullptr;
+}
+
+}  // namespace
+
+struct t0_mg {
+    std::vector<t0_runtime*> rts;
+    std::vector<ncclComm_t> comms;   // created on first gather
+};
+
+extern "C" {
+
+int t0_shard_columns(uint32_t n, uint32_t n_gpus, uint32_t rank, uint32_t* first_col, uint32_t* n_cols) {
+    if (!first_col || !n_cols) return fail(T0_ERR_INVALID, "null output");
+    if (n_gpus == 0 || rank >= n_gpus) return fail(T0_ERR_INVALID, "rank %u of %u", rank, n_gpus);
+    // equal blocks keep every rank's slice a whole number of 256-column tiles at the benchmark sizes and make the
+    // gathered layout C_g[g][M][N/g] regular; a ragged N is refused rather than silently unbalanced
+    if (n % n_gpus) return fail(T0_ERR_INVALID, "N=%u is not divisible by the number of GPUs %u", n, n_gpus);
+    *n_cols = n / n_gpus;
+    *first_col = rank * (n / n_gpus);
+    return T0_OK;
+}
+
+int t0_mg_new(int n_gpus, t0_mg** out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    *out = nullptr;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) return fail(T0_ERR_CUDA, "no CUDA device available; this library has no CPU fallback");
+    if (n_gpus <= 0 || n_gpus > n_dev) return fail(T0_ERR_INVALID, "%d GPUs requested, %d present", n_gpus, n_dev);
+    std::unique_ptr<t0_mg> mg(new t0_mg());
+    for (int d = 0; d < n_gpus; ++d) {
+        t0_runtime* rt = nullptr;
+        int rc = t0_rt_new(d, &rt);
+        if (rc != T0_OK) { for (t0_runtime* r : mg->rts) t0_rt_free(r); return rc; }
+        mg->rts.push_back(rt);
+    }
+    *out = mg.release();
+    return T0_OK;
+}
+
+void t0_mg_free(t0_mg* mg) {
+    if (!mg) return;
+    NcclApi* api = nccl();
+    for (ncclComm_t c : mg->comms) if (api && api->CommDestroy) api->CommDestroy(c);
+    for (t0_runtime* r : mg->rts) t0_rt_free(r);
+    delete mg;
+}
+
+int t0_mg_size(const t0_mg* mg) { return mg ? (int)mg->rts.size() : 0; }
+t0_runtime* t0_mg_runtime(t0_mg* mg, int rank) { return (mg && rank >= 0 && rank < (int)mg->rts.size()) ? mg->rts[rank] : nullptr; }
+
+int t0_mg_synchronize(t0_mg* mg) {
+    if (!mg) return fail(T0_ERR_INVALID, "null handle");
+    int first = T0_OK;
+    for (t0_runtime* r : mg->rts) { int rc = t0_rt_synchronize(r); if (rc != T0_OK && first == T0_OK) first = rc; }
+    return first;
+}
+
+int t0_mg_gemm_sharded(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, const uint64_t* y_slice, uint32_t m, uint32_t n, uint32_t k,
+                       uint32_t tile_n, int pair_cta) {
+    if (!mg || !x || !b_slice || !y_slice) return fail(T0_ERR_INVALID, "null argument");
+    const uint32_t g = (uint32_t)mg->rts.size();
+    uint32_t first = 0, n_local = 0;
+    int rc = t0_shard_columns(n, g, 0, &first, &n_local);
+    if (rc != T0_OK) return rc;
+    // launch on every GPU before waiting on any
+    for (uint32_t r = 0; r < g; ++r) {
+        t0_gemm_args a;
+        memset(&a, 0, sizeof a);
+        a.x = x[r]; a.b = b_slice[r]; a.y = y_slice[r];
+        a.m = m; a.n = n_local; a.k = k; a.tile_n = tile_n; a.transpose = T0_NT; a.swap_grid = 1; a.pair_cta = (uint8_t)pair_cta;
+        rc = t0_gemm_launch(mg->rts[r], &a);
+        if (rc != T0_OK) return rc;
+    }
+    return T0_OK;
+}
+
+int t0_mg_all_gather_c(t0_mg* mg, const uint64_t* c_gathered, uint32_t m, uint32_t n) {
+    if (!mg || !c_gathered) return fail(T0_ERR_INVALID, "null argument");
+    const int g = (int)mg->rts.size();
+    if (n % (uint32_t)g) return fail(T0_ERR_INVALID, "N=%u is not divisible by the number of GPUs %d", n, g);
+    if (g == 1) return T0_OK;
+    NcclApi* api = nccl();
+    if (!api) return fail(T0_ERR_UNSUPPORTED, "libnccl.so.2 could not be loaded: the gathered C needs NCCL");
+    if (mg->comms.empty()) {
+        std::vector<int> devs(g);
+        for (int r = 0; r < g; ++r) devs[r] = mg->rts[r]->device;
+        mg->comms.resize(g);
+        ncclResult_t e = api->CommInitAll(mg->comms.data(), g, devs.data());
+        if (e != 0) { mg->comms.clear(); return fail(T0_ERR_CUDA, "ncclCommInitAll: %s", api->GetErrorString ? api->GetErrorString(e) : "error"); }
+    }
+    const size_t count = (size_t)m * (n / g);   // floats per rank
+    api->GroupStart();
+    ncclResult_t first_err = 0;
+    for (int r = 0; r < g; ++r) {
+        DeviceGuard guard(mg->rts[r]->device);
+        float* recv = (float*)c_gathered[r];
+        // in place: this rank's block already sits in slot r (the GEMM stored it there)
+        ncclResult_t e = api->AllGather(recv + (size_t)r * count, recv, count, kNcclFloat32, mg->comms[r], mg->rts[r]->stream);
+        if (e != 0 && first_err == 0) first_err = e;
+    }
+    ncclResult_t e = api->GroupEnd();
+    if (first_err == 0) first_err = e;
+    if (first_err != 0) return fail(T0_ERR_CUDA, "ncclAllGather: %s", api->GetErrorString ? api->GetErrorString(first_err) : "error");
+    return T0_OK;
+}
+
+}  // extern "C"

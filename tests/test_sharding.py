@@ -1,0 +1,107 @@
+"""N-column sharding: the partition rule and the gathered layout, with world_size-2 gloo ranks on CPU; the
+multi-device path on GPUs when more than one is present."""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_columns_rule(t0):
+    assert t0.shard_columns(16384, 8, 0) == (0, 2048)
+    assert t0.shard_columns(16384, 8, 7) == (14336, 2048)
+    assert t0.shard_columns(4096, 1, 0) == (0, 4096)
+    covered = []
+    for r in range(4):
+        first, cnt = t0.shard_columns(1024, 4, r)
+        covered += list(range(first, first + cnt))
+    assert covered == list(range(1024))
+    with pytest.raises(t0.T0Error):
+        t0.shard_columns(1000, 3, 0)       # ragged N is refused
+    with pytest.raises(t0.T0Error):
+        t0.shard_columns(1024, 4, 4)
+
+
+_WORKER = textwrap.dedent("""
+    import importlib, os, sys
+    import numpy as np, torch, torch.distributed as dist
+    sys.path.insert(0, {root!r})
+    t0 = importlib.import_module("rust-gpu_b200")
+    import oracle
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    M, N, K = 24, 64, 96
+    a = oracle.fill_uniform_bf16(M * K, 42 + M)                       # A is replicated: every rank regenerates it
+    first, cnt = t0.shard_columns(N, world, rank)
+    # rank r owns rows [first, first+cnt) of WT[N,K]: the same stream, offset by its first element (as bench.py does)
+    b_slice = oracle.fill_uniform_bf16(cnt * K, 137 + N, first * K)
+    y_slice = oracle.gemm_nt(a, b_slice, M, K, cnt)                   # stand-in for the rank's GPU kernel on CPU ranks
+    blocks = [torch.empty(M, cnt) for _ in range(world)]              # rank-major C_g[g][M][N/g]
+    dist.all_gather(blocks, torch.from_numpy(y_slice))
+    gathered = torch.stack(blocks)
+    full = oracle.gemm_nt(a, oracle.fill_uniform_bf16(N * K, 137 + N), M, K, N)
+    rebuilt = np.concatenate([gathered[r].numpy() for r in range(world)], axis=1)
+    assert np.array_equal(rebuilt, full), "gathered blocks do not reassemble to the full product"
+    # timing rule of the benchmark: the reported time is the max over ranks
+    t = torch.tensor([1.0 + rank], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    assert t.item() == float(world)
+    dist.destroy_process_group()
+    print("rank", rank, "ok")
+""")
+
+
+def test_two_rank_gloo_sharded_gemm_and_gather(t0, oracle, tmp_path):
+    script = tmp_path / "worker.py"
+    script.write_text(_WORKER.format(root=ROOT))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for rank in range(2):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), LOCAL_RANK=str(rank))
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for rank, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, out
+        assert f"rank {rank} ok" in out
+
+
+def test_bench_reference_arm_other_ranks_exit_quietly():
+    # under torchrun only rank 0 runs the CPU reference arm; the other ranks exit 0 without output
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1", "--warmup", "0"],
+                       env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip() == ""
+
+
+@pytest.mark.gpu
+def test_multi_device_sharded_gemm_and_gather(t0, oracle):
+    import torch
+    g = min(torch.cuda.device_count(), 4)
+    if g < 2:
+        pytest.skip("needs at least two GPUs")       # like the reference's multi-GPU tests (src/universal/multi_gpu_tests.rs:64-70)
+    M, N, K = 256, 512 * g, 256
+    mg = t0.MultiGpu(g)
+    a = oracle.fill_uniform_bf16(M * K, 42 + M)
+    b = oracle.fill_uniform_bf16(N * K, 137 + N)
+    xs, bs, cs = [], [], []
+    for r in range(g):
+        rt = mg.runtime(r)
+        first, cnt = t0.shard_columns(N, g, r)
+        xs.append(rt.upload(a)); bs.append(rt.upload(b.reshape(N, K)[first:first + cnt])); cs.append(rt.alloc_zero(M * N * 4))
+    cnt = N // g
+    mg.gemm_sharded([x.gpu_addr() for x in xs], [x.gpu_addr() for x in bs], [c.gpu_addr() + r * M * cnt * 4 for r, c in enumerate(cs)], M, N, K)
+    mg.all_gather_c([c.gpu_addr() for c in cs], M, N)
+    mg.synchronize()
+    full = oracle.gemm_nt(a, b, M, K, N)
+    for r in range(g):
+        blocks = cs[r].read(M * N * 4, np.float32).reshape(g, M, cnt)
+        rebuilt = np.concatenate(list(blocks), axis=1)
+        assert np.abs(rebuilt - full).max() <= 5e-3 and np.linalg.norm(rebuilt - full) / np.linalg.norm(full) <= 1e-3
+    mg.free()
