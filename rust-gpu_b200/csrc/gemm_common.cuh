@@ -200,6 +200,22 @@ inline int make_map_kmajor(CUtensorMap* map, const void* base, uint32_t rows, ui
     return T0_OK;
 }
 
+// Plain 2-D row-major view [rows][cols] of 16- or 32-bit elements, no swizzle, box = box_cols x box_rows.
+inline int make_map_2d_plain(CUtensorMap* map, const void* base, uint32_t elem_bytes, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                             uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * elem_bytes};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (plain 2-D, %llu x %llu) failed: %d", (unsigned long long)rows, (unsigned long long)cols, (int)r);
+    return T0_OK;
+}
+
 // 3-D view [split][k_per_split][N] of a row-major [K][ld] bf16 matrix (N contiguous, ld >= N).
 inline int make_map_nmajor(CUtensorMap* map, const void* base, uint32_t N, uint32_t ld, uint32_t k_per_split, uint32_t split) {
     EncodeTiledFn enc = get_encode_fn();

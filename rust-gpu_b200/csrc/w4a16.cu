@@ -23,6 +23,7 @@
 //     CTA is stored directly, otherwise each CTA leaves its M x 256 piece in a scratch area and the CTA
 //     that arrives last adds the pieces in k order (no CTA ever waits for another).
 #include "runtime_internal.h"
+#include "gemm_common.cuh"
 
 #include <cuda_bf16.h>
 
@@ -30,38 +31,36 @@ using namespace t0;
 
 namespace {
 
-constexpr int kWarps = 16;
-constexpr int kThreads = kWarps * 32;
+constexpr int kWarps = 16;               // consumer warps; one more warp feeds them through TMA
+constexpr int kThreads = (kWarps + 1) * 32;
 constexpr int kSlabCols = 32;            // columns one warp owns
 constexpr int kBandSlabs = 8;            // slabs side by side in a CTA: 256 columns = 1 KiB of every packed row
 constexpr int kBandCols = kSlabCols * kBandSlabs;
 constexpr int kSlices = kWarps / kBandSlabs;   // k slices of 64 per step
-constexpr int kUnitK = kSlices * 64;     // k depth of one step of the CTA: one quantisation group of 128
-constexpr int kDepth = 3;                // steps kept in flight per lane (two 16-byte loads each)
+constexpr int kUnitK = kSlices * 64;     // k depth of one step of the CTA: 128
+constexpr int kStages = 8;               // steps in flight per CTA (TMA ring)
 constexpr int kARecord = 288;            // bytes per 8-k activation record (256 + 32: conflict-free quad reads)
+constexpr int kWeightBytes = (kUnitK / 8) * kBandCols * 4;   // 16 packed rows x 1 KiB
+constexpr int kScaleBytes = kBandCols * 2;
+constexpr int kZeroBytes = (kBandCols / 8) * 4;
+constexpr int kStageBytes = kWeightBytes + kScaleBytes + kZeroBytes + 128;   // 17152, keeps every stage 128-byte aligned
+constexpr int kRedBytes = kWarps * 16 * 33 * 4;
 constexpr int kPieceFloats = 16 * kBandCols;
+constexpr int kMaxAUnits = 12;           // steps of activations staged at a time (54 KiB)
+constexpr size_t kMaxSmem = 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)kMaxAUnits * (kUnitK / 8) * kARecord;
 constexpr size_t kCounterRegion = 16 * 1024;   // arrival counters: up to 4096 bands (N <= 1048576)
 
 struct W4Params {
     const uint16_t* a;
-    const uint32_t* packed;
-    const uint16_t* scales;
-    const uint32_t* zeros;
     float* y;
     float* partials;     // [grid][2][16*256]
     int* counters;       // [n_bands], zero between calls
-    uint32_t M, N, K, group;
-    uint32_t units_per_group;   // group / 64: steps that share one row of scales and zero points
-    uint32_t nz;         // u32 words per row of `zeros`
+    int* status;         // error word of the runtime (bounded waits)
+    uint32_t M, N, K;
+    uint32_t units_per_group;   // group / 128: steps that share one row of scales and zero points
     uint32_t n_bands, ksteps, total_units;
-    uint32_t rows;       // activation rows staged: 8 or 16
+    uint32_t a_units;    // steps of activations the shared-memory area holds (max steps of one CTA)
     unsigned long long* stamps;   // optional trace: 4 nanosecond stamps per CTA (entry, staged, loop done, exit)
-};
-
-struct UnitRegs {
-    uint4 w0, w1;   // 4 columns x 8 codes, packed rows r and r+4 of the lane's slice
-    uint2 s;     // 4 bf16 scales
-    uint32_t z;  // the word holding this lane's 4 zero points (low or high half)
 };
 
 __device__ __forceinline__ uint32_t owner_of(uint32_t unit, uint32_t grid, uint32_t total) {
@@ -87,42 +86,6 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One lane's position in the weight stream: pointers advance by constant strides inside a band and are
-// rebuilt only when the stream crosses into the next band.
-struct Stream {
-    const uint4* w;        // 4 columns x 8 codes of this lane's first packed row of the step (the second is 4 rows down)
-    const uint2* s;        // 4 scales
-    const uint32_t* z;     // word holding the 4 zero points
-    uint32_t band, ks, gcnt;
-
-    __device__ __forceinline__ void set(const W4Params& p, uint32_t band_, uint32_t ks_, uint32_t lane_col, uint32_t row_in_unit) {
-        band = band_; ks = ks_;
-        const uint32_t col = band * kBandCols + lane_col;
-        const uint32_t grp = ks / p.units_per_group;
-        gcnt = ks - grp * p.units_per_group;
-        const uint32_t c = col < p.N ? col : band * kBandCols;
-        w = (const uint4*)(p.packed + (size_t)(ks * (kUnitK / 8) + row_in_unit) * p.N + c);
-        s = (const uint2*)(p.scales + (size_t)grp * p.N + c);
-        z = p.zeros + (size_t)grp * p.nz + (c >> 3);
-    }
-    __device__ __forceinline__ void step(const W4Params& p, uint32_t lane_col, uint32_t row_in_unit) {
-        if (++ks == p.ksteps) { set(p, band + 1, 0, lane_col, row_in_unit); return; }
-        w += (size_t)(kUnitK / 8) * (p.N / 4);
-        if (++gcnt == p.units_per_group) { gcnt = 0; s += p.N / 4; z += p.nz; }
-    }
-    // Nothing here may consume a loaded value: a warp issues in order, so the first use of a load result
-    // is where it waits for memory.  The zero-point word is shifted at the point of use instead.
-    // A lane whose columns lie beyond N reads the band's first columns instead: what it computes is never stored.
-    __device__ __forceinline__ UnitRegs load(uint32_t row_stride_u4) const {
-        UnitRegs r;
-        r.w0 = __ldcs(w);
-        r.w1 = __ldcs(w + 4 * (size_t)row_stride_u4);
-        r.s = __ldg(s);
-        r.z = __ldg(z);
-        return r;
-    }
-};
-
 // (x & mask) | magic in one LOP3; mask and magic must sit in registers (the instruction takes one immediate at most)
 __device__ __forceinline__ uint32_t and_or(uint32_t x, uint32_t mask, uint32_t magic) {
     uint32_t r;
@@ -147,73 +110,109 @@ __device__ __forceinline__ void consume_word4(float (&acc)[4][4], const uint4& w
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params p) {
-    extern __shared__ uint8_t smem[];
-    float* red = (float*)smem;                                        // [kWarps][16][33]
-    // activations of this CTA's k range, one 288-byte record per group of eight k: eight 16-byte quads
-    // {row g, row g+8} x {k0 k4 | k1 k5} then eight quads for {k2 k6 | k3 k7}: each quad is the A fragment of one MMA
-    uint8_t* a_smem = smem + (size_t)kWarps * 16 * 33 * sizeof(float);
-    __shared__ int s_last;
+constexpr int kConsumers = kWarps * 32;
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers) : "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+                  const __grid_constant__ CUtensorMap map_z, const W4Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    uint8_t* ring = smem;                                             // kStages x {16 KiB codes, 512 B scales, 128 B zero points}
+    float* red = (float*)(smem + kStages * kStageBytes);              // [kWarps][16][33]
+    uint64_t* full_bar = (uint64_t*)(smem + kStages * kStageBytes + kRedBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    volatile int* abort_flag = (volatile int*)(empty_bar + kStages);
+    int* s_last = (int*)(abort_flag + 1);
+    // activations of this CTA's steps, in the order it walks them: one 288-byte record per group of eight k, eight
+    // 16-byte quads {row g, row g+8} x {k0 k4 | k1 k5} then eight for {k2 k6 | k3 k7}: each quad is the A fragment of one MMA
+    uint8_t* a_smem = smem + kStages * kStageBytes + kRedBytes + 256;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t slab = warp & (kBandSlabs - 1), slice = warp / kBandSlabs;
-    const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t lane_col = slab * kSlabCols + 4 * g;       // first of this lane's 4 columns, within a band
-    const uint32_t row_in_unit = slice * 8 + t;               // first packed row of this lane within a 128-deep step
-    const uint32_t zshift = (g & 1) * 16;
-    const uint32_t row_stride_u4 = p.N / 4;
     const uint32_t u0 = range_begin(blockIdx.x, gridDim.x, p.total_units);
     const uint32_t u1 = range_begin(blockIdx.x + 1, gridDim.x, p.total_units);
     if (u0 >= u1) return;
     auto stamp = [&](int i) {
         if (p.stamps && tid == 0) { unsigned long long t_ns; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns)); p.stamps[blockIdx.x * 4 + i] = t_ns; }
     };
-    stamp(0);
-    const uint32_t band_first = u0 / p.ksteps, band_last = (u1 - 1) / p.ksteps;
-    const uint32_t ks_first = u0 - band_first * p.ksteps;
-
-    // weights first: they are the long pole
-    Stream pre;
-    pre.set(p, band_first, ks_first, lane_col, row_in_unit);
-    UnitRegs q[kDepth];
-#pragma unroll
-    for (int d = 0; d < kDepth; ++d)
-        if (u0 + d < u1) { q[d] = pre.load(row_stride_u4); pre.step(p, lane_col, row_in_unit); }
-
-    // the k range this CTA touches: one stretch of a band, or everything when its range crosses into the next band
-    uint32_t k_lo = 0, k_hi = p.K;
-    if (band_first == band_last) {
-        k_lo = ks_first * kUnitK;
-        k_hi = (u1 - band_first * p.ksteps) * kUnitK;
-    }
-    // stage the activations: within every group of eight k the order becomes 0,4,1,5,2,6,3,7 so that the
-    // pair (code i, code i+4) a single mask pulls out of a word lines up with the two bf16 of one register
-    const uint32_t n_kg = (k_hi - k_lo) >> 3;
-    for (uint32_t i0 = tid; i0 < n_kg * 8; i0 += 4 * kThreads) {
-        // four records per thread per round: all loads are issued before the first is used
-        uint4 lo[4], hi[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t i = i0 + j * kThreads, kg = i >> 3, r = i & 7;
-            lo[j] = make_uint4(0, 0, 0, 0); hi[j] = make_uint4(0, 0, 0, 0);
-            if (i < n_kg * 8 && r < p.M) lo[j] = __ldg((const uint4*)(p.a + (size_t)r * p.K + k_lo + (size_t)kg * 8));
-            if (i < n_kg * 8 && r + 8 < p.M) hi[j] = __ldg((const uint4*)(p.a + (size_t)(r + 8) * p.K + k_lo + (size_t)kg * 8));
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), kWarps);
         }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t i = i0 + j * kThreads, kg = i >> 3, r = i & 7;
-            if (i >= n_kg * 8) break;
-            uint4 q0, q1;
-            q0.x = __byte_perm(lo[j].x, lo[j].z, 0x5410); q0.y = __byte_perm(hi[j].x, hi[j].z, 0x5410);   // k0 k4: rows r, r+8
-            q0.z = __byte_perm(lo[j].x, lo[j].z, 0x7632); q0.w = __byte_perm(hi[j].x, hi[j].z, 0x7632);   // k1 k5
-            q1.x = __byte_perm(lo[j].y, lo[j].w, 0x5410); q1.y = __byte_perm(hi[j].y, hi[j].w, 0x5410);   // k2 k6
-            q1.z = __byte_perm(lo[j].y, lo[j].w, 0x7632); q1.w = __byte_perm(hi[j].y, hi[j].w, 0x7632);   // k3 k7
-            *(uint4*)(a_smem + (size_t)kg * kARecord + r * 16) = q0;
-            *(uint4*)(a_smem + (size_t)kg * kARecord + 128 + r * 16) = q1;
-        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_s);
+        ptx::tma_prefetch_desc(&map_z);
     }
     __syncthreads();
-    stamp(1);
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();      // global memory is touched only after the previous grid in the stream is done
+    stamp(0);
+    const uint32_t band_first = u0 / p.ksteps;
+    const uint32_t ks_first = u0 - band_first * p.ksteps;
+
+    if (warp == kWarps) {
+        // ------------------------------------------------------------ producer: one elected lane streams the steps in
+        if (lane == 0) {
+            uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
+            for (uint32_t u = u0; u < u1; ++u) {
+                if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                    atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(u & 0xFFFFFF));
+                    break;
+                }
+                const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+                uint8_t* dst = ring + stage * kStageBytes;
+                const uint32_t grp = ks / p.units_per_group;
+                ptx::mbar_arrive_expect_tx(fb, kWeightBytes + kScaleBytes + kZeroBytes);
+                ptx::tma_load_2d(ptx::smem_u32(dst), &map_w, fb, (int32_t)(band * kBandCols), (int32_t)(ks * (kUnitK / 8)));
+                ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes), &map_s, fb, (int32_t)(band * kBandCols), (int32_t)grp);
+                ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes + kScaleBytes), &map_z, fb, (int32_t)(band * (kBandCols / 8)), (int32_t)grp);
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+                if (++ks == p.ksteps) { ks = 0; ++band; }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers (16 warps)
+    const uint32_t slab = warp & (kBandSlabs - 1), slice = warp / kBandSlabs;
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t row_in_unit = slice * 8 + t;               // first packed row of this lane within a 128-deep step
+    const uint32_t zshift = (g & 1) * 16;
+
+    // Activations are staged for a_units steps at a time (all of this CTA's steps when they fit).  Within every group
+    // of eight k the order becomes 0,4,1,5,2,6,3,7 so that the pair (code i, code i+4) a single mask pulls out of a
+    // word lines up with the two bf16 of one register.  While the consumers restage, the ring keeps filling.
+    auto stage_activations = [&](uint32_t ks_at, uint32_t count) {
+        const uint32_t n_items = count * (kUnitK / 8) * 8;      // (record, row pair)
+        for (uint32_t i0 = tid; i0 < n_items; i0 += 4 * kConsumers) {
+            uint4 lo[4], hi[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t i = i0 + j * kConsumers, rec = i >> 3, r = i & 7;
+                const uint32_t unit = rec / (kUnitK / 8), kks = (ks_at + unit) % p.ksteps;
+                const uint32_t kk = kks * kUnitK + (rec - unit * (kUnitK / 8)) * 8;
+                lo[j] = make_uint4(0, 0, 0, 0); hi[j] = make_uint4(0, 0, 0, 0);
+                if (i < n_items && r < p.M) lo[j] = __ldg((const uint4*)(p.a + (size_t)r * p.K + kk));
+                if (i < n_items && r + 8 < p.M) hi[j] = __ldg((const uint4*)(p.a + (size_t)(r + 8) * p.K + kk));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t i = i0 + j * kConsumers, rec = i >> 3, r = i & 7;
+                if (i >= n_items) break;
+                uint4 q0, q1;
+                q0.x = __byte_perm(lo[j].x, lo[j].z, 0x5410); q0.y = __byte_perm(hi[j].x, hi[j].z, 0x5410);   // k0 k4: rows r, r+8
+                q0.z = __byte_perm(lo[j].x, lo[j].z, 0x7632); q0.w = __byte_perm(hi[j].x, hi[j].z, 0x7632);   // k1 k5
+                q1.x = __byte_perm(lo[j].y, lo[j].w, 0x5410); q1.y = __byte_perm(hi[j].y, hi[j].w, 0x5410);   // k2 k6
+                q1.z = __byte_perm(lo[j].y, lo[j].w, 0x7632); q1.w = __byte_perm(hi[j].y, hi[j].w, 0x7632);   // k3 k7
+                *(uint4*)(a_smem + (size_t)rec * kARecord + r * 16) = q0;
+                *(uint4*)(a_smem + (size_t)rec * kARecord + 128 + r * 16) = q1;
+            }
+        }
+    };
 
     float acc[4][4];
 #pragma unroll
@@ -225,28 +224,50 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
     asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
     asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
 
-    uint32_t band = band_first, ks = ks_first;
-    // this lane's activation records of the current step: record (k/8) for its first word, 4 records on for the second
-    const uint8_t* arec = a_smem + (size_t)((ks_first * kUnitK - k_lo) / 8 + row_in_unit) * kARecord + g * 16;
+    uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
+    bool ok = true;    // false after a wait expired: the warp keeps walking (barriers stay matched) but does no work
+    const uint8_t* const arec0 = a_smem + (size_t)row_in_unit * kARecord + g * 16;
+    const uint8_t* arec = arec0;
+    // this lane's places inside a stage
+    const uint32_t w_off = row_in_unit * (kBandCols * 4) + slab * (kSlabCols * 4) + g * 16;
+    const uint32_t s_off = kWeightBytes + (slab * kSlabCols + 4 * g) * 2;
+    const uint32_t z_off = kWeightBytes + kScaleBytes + (slab * (kSlabCols / 8) + (g >> 1)) * 4;
 
-    for (uint32_t ub = u0; ub < u1; ub += kDepth) {
-#pragma unroll
-      for (int d = 0; d < kDepth; ++d) {
-        const uint32_t u = ub + d;
-        if (u >= u1) break;
-        {
+    for (uint32_t u = u0; u < u1; ++u) {
+        if ((u - u0) % p.a_units == 0) {
+            if (u != u0) consumer_sync();          // everyone is done reading the previous batch
+            stage_activations(ks, min(p.a_units, u1 - u));
+            consumer_sync();
+            if (u == u0) stamp(1);
+            arec = arec0;
+        }
+        if (ok && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            if (lane == 0) atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(u & 0xFFFFFF));
+            ok = false;
+        }
+        if (ok) {
+            const uint8_t* st = ring + stage * kStageBytes;
+            const uint4 w0 = *(const uint4*)(st + w_off);
+            const uint4 w1 = *(const uint4*)(st + w_off + 4 * (kBandCols * 4));
+            const uint2 sc = *(const uint2*)(st + s_off);
+            const uint32_t zw = *(const uint32_t*)(st + z_off) >> zshift;
             uint32_t zz[4], ss[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const uint32_t z = (q[d].z >> (zshift + 4 * c)) & 0xFu;
+                const uint32_t z = (zw >> (4 * c)) & 0xFu;
                 zz[c] = z * 0x00010001u + 0x43004300u;                                   // bf16x2 (128+z, 128+z)
-                ss[c] = __byte_perm((c & 2) ? q[d].s.y : q[d].s.x, 0, (c & 1) ? 0x3232 : 0x1010);   // (s, s)
+                ss[c] = __byte_perm((c & 2) ? sc.y : sc.x, 0, (c & 1) ? 0x3232 : 0x1010);   // (s, s)
             }
-            consume_word4(acc, q[d].w0, zz, ss, *(const uint4*)arec, *(const uint4*)(arec + 128), mask, magic);
-            consume_word4(acc, q[d].w1, zz, ss, *(const uint4*)(arec + 4 * kARecord), *(const uint4*)(arec + 4 * kARecord + 128), mask, magic);
+            consume_word4(acc, w0, zz, ss, *(const uint4*)arec, *(const uint4*)(arec + 128), mask, magic);
+            consume_word4(acc, w1, zz, ss, *(const uint4*)(arec + 4 * kARecord), *(const uint4*)(arec + 4 * kARecord + 128), mask, magic);
+            // The stage was read through the generic proxy and TMA (async proxy) will overwrite it: the reads are fenced
+            // against the async proxy before the producer is told the stage is free.  Without the fence, launches that
+            // ran with cold TLBs were seen consuming 32-byte sectors of the step loaded into the same stage eight steps later.
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&empty_bar[stage]));          // this warp is done with the stage
         }
-        // slot d of the ring is consumed: refill it with the step kDepth ahead
-        if (u + kDepth < u1) { q[d] = pre.load(row_stride_u4); pre.step(p, lane_col, row_in_unit); }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
         arec += (kUnitK / 8) * kARecord;
 
         const bool band_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
@@ -263,14 +284,14 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[c][j] = 0.0f;
             }
-            __syncthreads();
+            consumer_sync();
             const uint32_t first_unit = band * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
             const bool whole = first_unit >= u0 && last_unit <= u1;
             const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
             const uint32_t c_last = owner_of(last_unit - 1, gridDim.x, p.total_units);
             const uint32_t slot = (first_unit <= u0) ? 0u : 1u;   // the piece of the band holding this CTA's first unit is slot 0
             float* piece = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPieceFloats;
-            for (uint32_t idx = tid; idx < p.M * kBandCols; idx += kThreads) {
+            for (uint32_t idx = tid; idx < p.M * kBandCols; idx += kConsumers) {
                 const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
                 const uint32_t sl = col / kSlabCols, c32 = col - sl * kSlabCols;
                 float sum = 0.0f;
@@ -281,18 +302,18 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
                 else piece[idx] = sum;
             }
             if (!whole) {
-                __syncthreads();                       // every thread's part of the piece is written ...
+                consumer_sync();                       // every thread's part of the piece is written ...
                 if (tid == 0) {
                     __threadfence();                   // ... and made visible before this CTA is counted
-                    s_last = (atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first)) ? 1 : 0;
-                    if (s_last) __threadfence();
+                    *s_last = (atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first)) ? 1 : 0;
+                    if (*s_last) __threadfence();
                 }
-                __syncthreads();
-                if (s_last) {
+                consumer_sync();
+                if (*s_last) {
                     // last to arrive: add the pieces in k order (CTA order) and store; nobody waits for anybody.
                     // Only the first contributor can hold this band in slot 1 (its range began in the band before).
                     const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
-                    constexpr int kPer = kPieceFloats / kThreads;   // 8 outputs per thread when M = 16
+                    constexpr int kPer = kPieceFloats / kConsumers;   // 8 outputs per thread when M = 16
                     float total[kPer];
 #pragma unroll
                     for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
@@ -301,7 +322,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
                         float v[kPer];
 #pragma unroll
                         for (int j = 0; j < kPer; ++j) {
-                            const uint32_t idx = tid + j * kThreads;
+                            const uint32_t idx = tid + j * kConsumers;
                             v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
                         }
 #pragma unroll
@@ -309,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
                     }
 #pragma unroll
                     for (int j = 0; j < kPer; ++j) {
-                        const uint32_t idx = tid + j * kThreads;
+                        const uint32_t idx = tid + j * kConsumers;
                         if (idx < p.M * kBandCols) {
                             const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
                             const uint32_t ncol = band * kBandCols + col;
@@ -319,14 +340,9 @@ __global__ void __launch_bounds__(kThreads, 1) w4a16_gemm_kernel(const W4Params 
                     if (tid == 0) p.counters[band] = 0;   // ready for the next call
                 }
             }
-            __syncthreads();
+            consumer_sync();
         }
-        if (++ks == p.ksteps) {
-            // next band: k starts over (a CTA that crosses bands staged the whole K range, k_lo = 0)
-            ks = 0; ++band;
-            arec = a_smem + (size_t)row_in_unit * kARecord + g * 16;
-        }
-      }
+        if (++ks == p.ksteps) { ks = 0; ++band; }
     }
     stamp(3);
 }
@@ -445,11 +461,13 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     if (group == 0 || group % 8 || K % group) return fail(T0_ERR_INVALID, "group size %u must divide K=%u and be a multiple of 8", group, K);
     DeviceGuard guard(rt->device);
 
-    const uint32_t rows = M <= 8 ? 8 : 16;
-    const size_t smem = (size_t)(K / 8) * kARecord + (size_t)kWarps * 16 * 33 * sizeof(float);
-    const bool fused = M <= 16 && (N % 8 == 0) && (K % kUnitK == 0) && (group % kUnitK == 0) && smem <= 200 * 1024 &&
-                       ceil_div(N, kBandCols) * sizeof(int) <= kCounterRegion &&
-                       ((a | packed | scales) & 15) == 0 && (zeros & 3) == 0 && (y & 3) == 0;
+    const uint32_t n_bands = ceil_div(N, kBandCols), ksteps = ceil_div(K, kUnitK);
+    const uint64_t total = (uint64_t)n_bands * ksteps;
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(std::max<uint64_t>(total, 1), (uint64_t)rt->sm_count);
+    // the TMA views need 16-byte row pitches: N % 32 for the zero points (N/8 words per row)
+    const bool fused = M <= 16 && (N % 32 == 0) && (K % kUnitK == 0) && (group % kUnitK == 0) && total <= 0x7FFFFFFFull &&
+                       n_bands * sizeof(int) <= kCounterRegion &&
+                       ((a | packed | scales | zeros) & 15) == 0 && (y & 3) == 0;
     if (!fused) {
         // general shapes: dequantise once into scratch, then the tcgen05 GEMM on B[K,N]
         rc = ensure_scratch(rt, rt->scratch_w, (size_t)K * N * 2);
@@ -463,10 +481,6 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         return t0_gemm_launch(rt, &ga);
     }
 
-    const uint32_t n_bands = ceil_div(N, kBandCols), ksteps = ceil_div(K, kUnitK);
-    const uint64_t total = (uint64_t)n_bands * ksteps;
-    if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "problem too large");
-    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
     // scratch: one arrival counter per band (zero between calls) in a fixed region, then two M x 256 pieces per CTA
     const size_t piece_bytes = (size_t)grid * 2 * kPieceFloats * sizeof(float);
     const size_t need = kCounterRegion + piece_bytes;
@@ -477,18 +491,28 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     }
     W4Params p;
     memset(&p, 0, sizeof p);
-    p.a = (const uint16_t*)a; p.packed = (const uint32_t*)packed; p.scales = (const uint16_t*)scales; p.zeros = (const uint32_t*)zeros;
+    p.a = (const uint16_t*)a;
     p.y = (float*)y;
     p.counters = (int*)rt->scratch_w4.ptr;
     p.partials = (float*)((uint8_t*)rt->scratch_w4.ptr + kCounterRegion);
-    p.M = M; p.N = N; p.K = K; p.group = group; p.nz = (N + 7) / 8;
+    p.status = rt->d_status;
+    p.M = M; p.N = N; p.K = K;
     p.units_per_group = group / kUnitK;
     p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
-    p.rows = rows;
+    p.a_units = std::min<uint32_t>((uint32_t)ceil_div((uint32_t)total, grid), kMaxAUnits);
+    const size_t smem = 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
+
+    CUtensorMap map_w, map_s, map_z;
+    rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kBandCols, kUnitK / 8);
+    if (rc != T0_OK) return rc;
+    rc = gemm::make_map_2d_plain(&map_s, (const void*)scales, 2, K / group, N, kBandCols, 1);
+    if (rc != T0_OK) return rc;
+    rc = gemm::make_map_2d_plain(&map_z, (const void*)zeros, 4, K / group, N / 8, kBandCols / 8, 1);
+    if (rc != T0_OK) return rc;
 
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
-        T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
         attr_set[rt->device] = true;
     }
     // T0_W4_TRACE=1: per-CTA stage stamps, summarised on stderr after a blocking wait (a debugging aid, off by default)
@@ -499,7 +523,23 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 4 * sizeof(unsigned long long)));
         p.stamps = d_stamps;
     }
-    w4a16_gemm_kernel<<<grid, kThreads, smem, rt->stream>>>(p);
+    {
+        // programmatic dependent launch: the next kernel's launch and barrier set-up overlap this one's tail; the
+        // kernel touches global memory only after griddepcontrol.wait
+        static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid, 1, 1);
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = rt->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = use_pdl ? 1 : 0;
+        cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
+        if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
+    }
     if (trace) {
         std::vector<unsigned long long> h((size_t)grid * 4);
         T0_CUDA(cudaStreamSynchronize(rt->stream));
