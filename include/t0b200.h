@@ -289,7 +289,9 @@ void t0_tuner_invalidate(t0_tuner* t, uint32_t m, uint32_t n, uint32_t k);
 void t0_tuner_clear(t0_tuner* t);
 void t0_tuner_report(const t0_tuner* t);
 /* global_tuner() (auto_gemm.rs:539) and the one-shot auto_gemm(rt, a, b, c, m, n, k) -> Result<f64> (auto_gemm.rs:555-590):
- * tune or cache hit, then dispatch with the best config; returns the tuned TFLOP/s through `tflops`. */
+ * tune or cache hit, then dispatch with the best config; returns the tuned TFLOP/s through `tflops`.
+ * c always receives the complete product in its first m*n floats: a split-K winner is launched with the
+ * device-side reduction instead of leaving partial planes for the host to add. */
 t0_tuner* t0_global_tuner(void);
 int t0_auto_gemm(t0_runtime* rt, t0_buffer* a, t0_buffer* b, t0_buffer* c, uint32_t m, uint32_t n, uint32_t k, double* tflops);
 

@@ -376,8 +376,22 @@ int t0_auto_gemm(t0_runtime* rt, t0_buffer* a, t0_buffer* b, t0_buffer* c, uint3
         int rc = t0_tuner_tune(tuner, rt, m, n, k, &cfg);          // 1. tune (or cache hit)
         if (rc != T0_OK) return rc;
     }
-    if (split_of(&cfg) > 1 && t0_buf_size(c) < (size_t)m * n * 4 * split_of(&cfg)) cfg.split_k = 0;   // c holds one plane only
-    int rc = dispatch_cfg(rt, &cfg, a, b, c, m, n, k);             // 2-3. kernel (cached by name), kernargs, grid, dispatch
+    int rc;
+    if (split_of(&cfg) > 1) {
+        // A split-K winner: the dispatch contract would leave split_k partial planes in c for the host to add
+        // (gemm_gen.rs:447-448).  The one-shot call promises C = A * B in c[0 .. m*n), so the same kernel is launched
+        // with the device-side reduction (partials in the runtime's scratch, added in split order).
+        if (t0_buf_size(c) < (size_t)m * n * 4) return fail(T0_ERR_BOUNDS, "c holds %zu bytes, %zu needed", t0_buf_size(c), (size_t)m * n * 4);
+        t0_gemm_args ga;
+        memset(&ga, 0, sizeof ga);
+        ga.x = t0_buf_gpu_addr(a); ga.b = t0_buf_gpu_addr(b); ga.y = t0_buf_gpu_addr(c);
+        ga.m = m; ga.n = n; ga.k = k; ga.tile_n = cfg.tile_n; ga.split_k = split_of(&cfg);
+        ga.transpose = T0_NT; ga.epilogue = (uint8_t)cfg.epilogue; ga.swap_grid = (uint8_t)cfg.swap_grid;
+        ga.pair_cta = (cfg.wgp_mode && cfg.tile_m == 256 && cfg.tile_n == 256) ? 1 : 2;
+        rc = t0_gemm_launch(rt, &ga);
+    } else {
+        rc = dispatch_cfg(rt, &cfg, a, b, c, m, n, k);             // 2-3. kernel (cached by name), kernargs, grid, dispatch
+    }
     if (rc != T0_OK) return rc;
     if (tflops) {                                                   // 4. the tuned figure
         std::lock_guard<std::mutex> g(g_global_mu);
