@@ -34,10 +34,143 @@ WORKLOADS = {
     "gemm_bf16_2048": dict(m=2048, n=2048, k=2048),
     "gemm_bf16_8192": dict(m=8192, n=8192, k=8192),
     "gemm_bf16_16384_sharded": dict(m=16384, n=16384, k=16384),
+    # HBM-bound secondary workloads (BASELINE configs 3 and 4); metric: algorithmic GB/s
+    "gemm_bf16_skinny_128x4096x4096": dict(m=128, n=4096, k=4096, hbm=True),
+    "gemm_bf16_skinny_64x4096x16384_sk4": dict(m=64, n=4096, k=16384, split_k=4, hbm=True),
+    "w4a16_m1_n11008": dict(m=1, n=11008, k=4096, w4=True, hbm=True),
+    "w4a16_m16_n11008": dict(m=16, n=11008, k=4096, w4=True, hbm=True),
+    "w4a16_m1_n14336": dict(m=1, n=14336, k=4096, w4=True, hbm=True),
+    "w4a16_m16_n14336": dict(m=16, n=14336, k=4096, w4=True, hbm=True),
+    "w4a16_m128_n11008": dict(m=128, n=11008, k=4096, w4=True, hbm=True),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from the ncu capture summarised
 # in profiles/ (bytes); None until a capture of that workload exists.
 NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": None}
+W4_GROUP = 128
+
+
+def run_hbm_workload(args, name):
+    """Secondary single-GPU workloads that are HBM-bound: the skinny GEMMs and the W4A16 GEMM.  One JSON line with the
+    same keys as the headline; `value` is algorithmic bytes / second (the bytes formula is in `config.bytes`)."""
+    import torch
+    t0 = importlib.import_module("rust-gpu_b200")
+    t0.lib()
+    import oracle
+    oracle.build()
+    w = WORKLOADS[name]
+    M, N, K = w["m"], w["n"], w["k"]
+    w4 = bool(w.get("w4"))
+    G = W4_GROUP
+    steps = args.steps if args.steps is not None else 200
+    warmup = max(3, args.warmup if args.warmup is not None else 10)
+    torch.cuda.set_device(0)
+    rt = t0.GpuRuntime(0)
+    if w4:
+        alg_bytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2 + M * K * 2 + M * N * 4
+        set_bytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2
+    else:
+        alg_bytes = M * K * 2 + N * K * 2 + M * N * 4
+        set_bytes = N * K * 2
+    n_sets = max(2, -(-3 * 126 * 2 ** 20 // set_bytes))      # rotating weight sets: together three times the L2
+    a_host = oracle.fill_normal_bf16(M * K, 7 + M) if w4 else oracle.fill_uniform_bf16(M * K, 42 + M)
+    xa = rt.upload(a_host)
+    y = rt.alloc(M * N * 4)
+    sets = []
+    for s in range(n_sets):
+        if w4:
+            xp, xs, xz = rt.alloc((K // 8) * N * 4), rt.alloc((K // G) * N * 2), rt.alloc((K // G) * (N // 8) * 4)
+            rt.fill_u32(xp.gpu_addr(), (K // 8) * N, 1000 + s)
+            rt.fill_range_bf16(xs.gpu_addr(), (K // G) * N, 2000 + s, 0.001, 0.02)
+            rt.fill_u32(xz.gpu_addr(), (K // G) * (N // 8), 3000 + s)
+            sets.append((xp, xs, xz))
+        else:
+            xb = rt.alloc(N * K * 2)
+            rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N + 1000 * s)
+            sets.append((xb,))
+    if w4:
+        calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), y.gpu_addr(), M, N, K, G) for i in range(steps)]
+        submit = rt.w4a16_gemm_batch
+        kernel = "w4a16_gemm_kernel" if M <= 16 else "dequant_w4_b200_kernel + gemm"
+    else:
+        cfg = t0.auto_select(M, K, N)
+        sk = w.get("split_k", cfg.split())
+        kw = dict(tile_n=cfg.tile_n, split_k=sk, swap_grid=bool(cfg.swap_grid), pair_cta=2)
+        calls = [rt.gemm_args(xa.gpu_addr(), sets[i % n_sets][0].gpu_addr(), y.gpu_addr(), M, N, K, **kw) for i in range(steps)]
+        submit = rt.gemm_batch
+        kernel = cfg.copy(split_k=sk).name()
+    submit(calls[:warmup])
+    rt.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    before = rt.launch_count()
+    best = float("inf")
+    for _ in range(3):
+        rt.timer_start()
+        submit(calls)
+        best = min(best, rt.timer_stop())
+    clocks = sampler.stop()
+    launches = (rt.launch_count() - before) // 3
+    per_launch_s = best * 1e-3 / steps
+    gbs = alg_bytes / per_launch_s / 1e9
+
+    # parity of the last step against the oracle (full result: these shapes are small)
+    s_idx = (steps - 1) % n_sets
+    got = y.read(M * N * 4, np.float32).reshape(M, N)
+    if w4:
+        ref = oracle.w4a16_gemm(a_host, oracle.fill_u32((K // 8) * N, 1000 + s_idx), oracle.fill_range_bf16((K // G) * N, 2000 + s_idx, 0.001, 0.02),
+                                oracle.fill_u32((K // G) * (N // 8), 3000 + s_idx), M, N, K, G)
+    else:
+        ref = oracle.gemm_nt(a_host, oracle.fill_uniform_bf16(N * K, 137 + N + 1000 * s_idx), M, K, N)
+    err = float(np.abs(got - ref).max())
+    tol = 5e-3 * (K / 256) ** 0.5
+    if not err <= tol:
+        print(json.dumps({"error": "parity check failed", "max_abs_err": err, "tol": tol}), flush=True)
+        sys.exit(1)
+
+    # end to end: the step's activations go up from pinned host memory, the result comes back; weights stay resident
+    a_pin = torch.from_numpy(a_host.view(np.int16).copy()).pin_memory().numpy()
+    y_pin = torch.empty(M * N, dtype=torch.float32).pin_memory().numpy()
+    C = __import__("ctypes")
+    e2e_steps = min(steps, 50)
+    t_start = time.perf_counter()
+    for i in range(e2e_steps):
+        xa.write(a_pin)
+        submit([calls[i]])
+        t0._check(t0.lib().t0_rt_read_f32(rt._h, y._h, M * N, y_pin.ctypes.data_as(C.c_void_p)))
+    e2e_s = (time.perf_counter() - t_start) / e2e_steps
+
+    # CPU baseline on a bounded sample: all rows, the first n_cpu columns
+    n_cpu = min(N, 2048)
+    t_cpu = float("inf")
+    if w4:
+        pk = oracle.fill_u32((K // 8) * N, 1000).reshape(K // 8, N)[:, :n_cpu].copy().reshape(-1)
+        sc = oracle.fill_range_bf16((K // G) * N, 2000, 0.001, 0.02).reshape(K // G, N)[:, :n_cpu].copy().reshape(-1)
+        zp = oracle.fill_u32((K // G) * (n_cpu // 8), 3000)
+        for _ in range(3):
+            t = time.perf_counter(); oracle.w4a16_gemm(a_host, pk, sc, zp, M, n_cpu, K, G); t_cpu = min(t_cpu, time.perf_counter() - t)
+    else:
+        bh = oracle.fill_uniform_bf16(n_cpu * K, 137 + N)
+        for _ in range(3):
+            t = time.perf_counter(); oracle.gemm_nt(a_host, bh, M, K, n_cpu); t_cpu = min(t_cpu, time.perf_counter() - t)
+    cpu_gbs = alg_bytes * (n_cpu / N) / t_cpu / 1e9
+
+    peaks = measured_peaks()
+    line = {"metric": "w4a16_hbm_gbs" if w4 else "skinny_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": per_launch_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int4 x bf16 -> f32" if w4 else "bf16", "data": "synthetic",
+            "config": {"workload": name, "m": M, "n": N, "k": K, "group": G if w4 else None, "kernel": kernel, "bytes": alg_bytes,
+                       "tflops": 2.0 * M * N * K / per_launch_s / 1e12, "input_sets": n_sets,
+                       "l2": f"{n_sets} resident weight sets of {set_bytes >> 20} MiB rotate (> 126 MB L2)",
+                       "pct_of_nominal_hbm": round(100.0 * gbs / 8000.0, 1)},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                         "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peaks['source']} (copy bandwidth)"},
+            "clocks": clocks, "gpu_launches": int(launches), "parity": {"max_abs_err": err, "tol": tol},
+            "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 4,
+                    "steps": e2e_steps, "note": "weights resident; the step's activations and result cross PCIe"},
+            "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": oracle.host_threads(), "kind": "port",
+                             "sample": f"all {M} rows, the first {n_cpu} of {N} columns, best of 3, {t_cpu:.3f} s per pass"}}
+    print(json.dumps(line), flush=True)
+    rt.close()
 
 
 def measured_peaks():
@@ -178,6 +311,12 @@ def main():
     t0.lib()   # raises if the CUDA library is missing: there is no fallback path
 
     name = args.workload or ("gemm_bf16_4096" if world == 1 else "gemm_bf16_16384_sharded")
+    if WORKLOADS[name].get("hbm"):
+        if world != 1:
+            print(f"workload {name} is single-GPU (replicas only)", file=sys.stderr)
+            sys.exit(2)
+        run_hbm_workload(args, name)
+        return
     sharded = name.endswith("_sharded")
     w = WORKLOADS[name]
     M, N_total, K = w["m"], w["n"], w["k"]
