@@ -320,6 +320,16 @@ typedef struct t0_w4a16_args {
     uint32_t m, n, k, group;
 } t0_w4a16_args;
 int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
+/* The fused W4A16 GEMM for callers that may not allocate device memory (no counterpart in the reference, which has no
+ * fused INT4 GEMM).  Same arguments and result as t0_w4a16_gemm, bit for bit, but the scratch the kernel needs lives in a
+ * fixed array inside the library (t0_w4a16_gemm_static_scratch_bytes() bytes per device), so the call never allocates or
+ * frees.  Limits: M <= 16, K % 128 == 0, group % 128 == 0, N % 32 == 0, N <= 1048576, at most 160 SMs; anything else
+ * returns T0_ERR_UNSUPPORTED (there is no two-step fallback here).  The first call on a device looks up the array's
+ * address: make it before starting a stream capture.  All calls on one device share the array: calls that overlap in
+ * time (different runtimes or streams) race; calls on one runtime are ordered by its stream. */
+int t0_w4a16_gemm_static(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
+                         uint32_t K, uint32_t group);
+size_t t0_w4a16_gemm_static_scratch_bytes(void);
 /* GptqWeight::from_bytes (quant_kernels.rs:242-286): header rows, cols, group_size (u32 LE), packed codes, f32 scales,
  * i32 zero points.  Fills the three section offsets; the asserts of the reference are error codes here. */
 int t0_gptq_parse(const uint8_t* raw, size_t len, uint32_t* rows, uint32_t* cols, uint32_t* group_size, size_t* packed_off,

@@ -574,6 +574,10 @@ class GpuRuntime:
     def w4a16_gemm(self, a: int, packed: int, scales: int, zeros: int, y: int, M: int, N: int, K: int, group: int = 128) -> None:
         _check(lib().t0_w4a16_gemm(self._h, a, packed, scales, zeros, y, M, N, K, group))
 
+    def w4a16_gemm_static(self, a: int, packed: int, scales: int, zeros: int, y: int, M: int, N: int, K: int, group: int = 128) -> None:
+        """``t0_w4a16_gemm_static``: the fused kernel on the library's fixed scratch array; never allocates."""
+        _check(lib().t0_w4a16_gemm_static(self._h, a, packed, scales, zeros, y, M, N, K, group))
+
     def w4a16_gemm_batch(self, calls: list[W4A16Args]) -> None:
         arr = (W4A16Args * len(calls))(*calls)
         _check(lib().t0_w4a16_gemm_batch(self._h, arr, len(calls)))
@@ -831,6 +835,8 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4_dequant", i32, vp, u64, u64, u64, u64, u32, u32, u32)
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
+    sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    sig("t0_w4a16_gemm_static_scratch_bytes", sz)
     sig("t0_gptq_parse", i32, vp, sz, u32p, u32p, u32p, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz))
     sig("t0_gptq_gpu_buffer_size", sz, u32, u32, u32)
     sig("t0_gptq_to_b200", C.c_long, vp, vp, vp, u32, u32, u32, vp, vp, vp)

@@ -424,6 +424,67 @@ int launch_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t
 
 }  // namespace
 
+namespace t0 {
+
+// Bytes of caller-provided scratch the fused kernel needs for a grid of `ctas` CTAs: the arrival counters, then two
+// 16 x 256 pieces per CTA.
+size_t w4a16_fixed_scratch_bytes(uint32_t ctas) { return kCounterRegion + (size_t)ctas * 2 * kPieceFloats * sizeof(float); }
+
+// The fused kernel on scratch memory the caller owns (first kCounterRegion bytes: counters, zero before the first use;
+// the kernel leaves them zero).  Takes only the shapes the fused kernel handles and never allocates: there is no
+// two-step fallback here.
+int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
+                             uint32_t K, uint32_t group, void* scratch, size_t scratch_bytes) {
+    if (M == 0 || N == 0) return T0_OK;
+    if (!a || !packed || !scales || !zeros || !y || !scratch) return fail(T0_ERR_INVALID, "null device pointer");
+    if (M > 16) return fail(T0_ERR_UNSUPPORTED, "M=%u: this entry takes M <= 16 only (larger M needs a K x N scratch matrix)", M);
+    if (K == 0 || K % kUnitK || group == 0 || group % kUnitK || K % group || N % 32)
+        return fail(T0_ERR_UNSUPPORTED, "shape K=%u N=%u group=%u: this entry needs K %% 128 == 0, group %% 128 == 0, group | K, N %% 32 == 0", K, N, group);
+    if (((a | packed | scales | zeros) & 15) != 0 || (y & 3) != 0) return fail(T0_ERR_INVALID, "operands must be 16-byte aligned (y: 4-byte)");
+    const uint32_t n_bands = ceil_div(N, kBandCols), ksteps = K / kUnitK;
+    const uint64_t total = (uint64_t)n_bands * ksteps;
+    if (total > 0x7FFFFFFFull || n_bands * sizeof(int) > kCounterRegion)
+        return fail(T0_ERR_UNSUPPORTED, "N=%u is beyond the fixed scratch: at most %zu bands of 256 columns", N, kCounterRegion / sizeof(int));
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
+    if (w4a16_fixed_scratch_bytes(grid) > scratch_bytes)
+        return fail(T0_ERR_UNSUPPORTED, "a grid of %u CTAs needs %zu bytes of scratch, the fixed area holds %zu", grid, w4a16_fixed_scratch_bytes(grid), scratch_bytes);
+    W4Params p;
+    memset(&p, 0, sizeof p);
+    p.a = (const uint16_t*)a;
+    p.y = (float*)y;
+    p.counters = (int*)scratch;
+    p.partials = (float*)((uint8_t*)scratch + kCounterRegion);
+    p.status = rt->d_status;
+    p.M = M; p.N = N; p.K = K;
+    p.units_per_group = group / kUnitK;
+    p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
+    p.a_units = std::min<uint32_t>((uint32_t)ceil_div((uint32_t)total, grid), kMaxAUnits);
+    const size_t smem = 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
+    CUtensorMap map_w, map_s, map_z;
+    int rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kBandCols, kUnitK / 8);
+    if (rc != T0_OK) return rc;
+    rc = gemm::make_map_2d_plain(&map_s, (const void*)scales, 2, K / group, N, kBandCols, 1);
+    if (rc != T0_OK) return rc;
+    rc = gemm::make_map_2d_plain(&map_z, (const void*)zeros, 4, K / group, N / 8, kBandCols / 8, 1);
+    if (rc != T0_OK) return rc;
+    static bool attr_set[64] = {};
+    if (rt->device < 64 && !attr_set[rt->device]) {
+        T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+        attr_set[rt->device] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = rt->stream;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
+    if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
+    rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+}  // namespace t0
+
 extern "C" {
 
 int t0_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out_bf16, uint32_t K, uint32_t N, uint32_t group) {
