@@ -45,7 +45,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from the ncu capture summarised
 # in profiles/ (bytes); None until a capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": None}
+NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": 127.5e6}
 W4_GROUP = 128
 
 
