@@ -26,6 +26,7 @@ struct KParams {
     uint32_t tiles_m, tiles_n, split_k;
     uint32_t kb_per_split;
     uint32_t swap_grid, raster_group;
+    uint32_t tail_start;         // pair kernel: work items from here on are half-width tiles (two per output tile); = total when unused
     uint32_t out_bf16, epilogue, n_ops;
     float scale, clamp_min, clamp_max;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
@@ -147,9 +148,8 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
 
 // Launch with programmatic stream serialisation so the prologue of this grid overlaps the tail of the
 // previous one (T0_NO_PDL=1 in the environment turns it off).
-template <typename Kernel>
-inline cudaError_t launch_pdl(Kernel kern, uint32_t grid, uint32_t block, uint32_t smem, cudaStream_t stream,
-                              const CUtensorMap& ma, const CUtensorMap& mb, const KParams& p) {
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_pdl(Kernel kern, uint32_t grid, uint32_t block, uint32_t smem, cudaStream_t stream, const Args&... args) {
     static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -161,7 +161,7 @@ inline cudaError_t launch_pdl(Kernel kern, uint32_t grid, uint32_t block, uint32
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
+    return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
 // ------------------------------------------------------------------ tensor maps (host)

@@ -29,13 +29,20 @@ __host__ __device__ constexpr uint32_t pair_stages(uint32_t pair_n) { return pai
 // kPairN = output columns per pair (256, or 128 when 256-wide tiles would quantise badly over the SMs)
 template <uint32_t kPairN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                              const __grid_constant__ CUtensorMap map_b_half, const KParams p) {
     constexpr uint32_t kBHalfRows = kPairN / 2;                    // rows of B each CTA loads
     constexpr uint32_t kBStageBytes = kBHalfRows * BK * 2;
     constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;  // per CTA
     constexpr uint32_t kStages = pair_stages(kPairN);
     constexpr uint32_t kTmemCols = 2 * kPairN;                     // two accumulator buffers
     constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(kPairM, kPairN, 0u);
+    // Tail of the tile list: when the last wave would leave more than half of the pairs idle, its tiles are cut into two
+    // half-width tiles (work items >= p.tail_start; item tail_start + 2i + h is half h of tile tail_start + i), so the wave
+    // costs a half-width tile instead of a full one.  B then comes through a tensor map with a box half as tall.
+    constexpr uint32_t kHalfN = kPairN / 2;
+    constexpr uint32_t kIdescHalf = ptx::make_idesc_bf16_f32(kPairM, kHalfN, 0u);
+    constexpr uint32_t kBHalfStageBytes = (kHalfN / 2) * BK * 2;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -54,7 +61,9 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     const uint32_t cta_rank = ptx::cluster_ctarank();   // 0 = even CTA (issues the UMMAs), 1 = odd
     const uint32_t pair_id = blockIdx.x >> 1;
     const uint32_t n_pairs = gridDim.x >> 1;
-    const uint32_t total_work = p.tiles_m * p.tiles_n * p.split_k;
+    const uint32_t n_tiles = p.tiles_m * p.tiles_n * p.split_k;
+    const uint32_t tail_start = min(p.tail_start, n_tiles);
+    const uint32_t total_work = tail_start + 2 * (n_tiles - tail_start);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -92,7 +101,9 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t w = pair_id; ok && w < total_work; w += n_pairs) {
-                const WorkItem wi = decode_work(w, p);
+                const bool tail = w >= tail_start;
+                const uint32_t half = tail ? ((w - tail_start) & 1u) : 0u;
+                const WorkItem wi = decode_work(tail ? tail_start + ((w - tail_start) >> 1) : w, p);
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
                         atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(w & 0xFFFFFF));
@@ -100,12 +111,16 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                         break;
                     }
                     const uint32_t fb_local = ptx::smem_u32(&full_bar[stage]);
-                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(fb_local, 2 * kStageBytes);   // bytes of both CTAs
+                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(fb_local, 2 * (kAStageBytes + (tail ? kBHalfStageBytes : kBStageBytes)));   // bytes of both CTAs
                     const uint32_t fb = ptx::mapa(fb_local, 0);   // the even CTA's barrier, from either CTA
                     ptx::tma_load_3d_pair(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
                                           (int32_t)(kb * BK), (int32_t)(wi.m_blk * kPairM + cta_rank * BM), (int32_t)wi.split);
-                    ptx::tma_load_3d_pair(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b, fb,
-                                          (int32_t)(kb * BK), (int32_t)(wi.n_blk * kPairN + cta_rank * kBHalfRows), (int32_t)wi.split);
+                    if (!tail)
+                        ptx::tma_load_3d_pair(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b, fb,
+                                              (int32_t)(kb * BK), (int32_t)(wi.n_blk * kPairN + cta_rank * kBHalfRows), (int32_t)wi.split);
+                    else
+                        ptx::tma_load_3d_pair(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b_half, fb,
+                                              (int32_t)(kb * BK), (int32_t)(wi.n_blk * kPairN + half * kHalfN + cta_rank * (kHalfN / 2)), (int32_t)wi.split);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -123,6 +138,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + buf * kPairN;
+                const uint32_t idesc = w >= tail_start ? kIdescHalf : kIdesc;
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
                         atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000 | (int)(w & 0x7FFFFF));
@@ -136,7 +152,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                     for (uint32_t k4 = 0; k4 < BK / 16; ++k4) {
                         const uint64_t da = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024);
                         const uint64_t db = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024);
-                        ptx::umma_bf16_ss_pair(tmem_d, da, db, kIdesc, (kb | k4) != 0 ? 1u : 0u);
+                        ptx::umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
                     }
                     // the stage is free in both CTAs once these UMMAs have read it
                     const uint32_t eb = ptx::smem_u32(&empty_bar[stage]);
@@ -158,7 +174,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
         uint32_t iter = 0;
         for (uint32_t w = pair_id; w < total_work; w += n_pairs, ++iter) {
-            const WorkItem wi = decode_work(w, p);
+            const bool tail = w >= tail_start;
+            const uint32_t half = tail ? ((w - tail_start) & 1u) : 0u;
+            const WorkItem wi = decode_work(tail ? tail_start + ((w - tail_start) >> 1) : w, p);
+            const uint32_t n_chunks = tail ? kHalfN / 32 : kPairN / 32;
             const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
             if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(w & 0xFFFFFF));
@@ -168,8 +187,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
             const uint32_t row = wi.m_blk * kPairM + cta_rank * BM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
 #pragma unroll 1
-            for (uint32_t c = 0; c < kPairN / 32; ++c) {
-                const uint32_t col0 = wi.n_blk * kPairN + c * 32;
+            for (uint32_t c = 0; c < n_chunks; ++c) {
+                const uint32_t col0 = wi.n_blk * kPairN + half * kHalfN + c * 32;
                 if (col0 >= p.N) break;
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * kPairN + c * 32, r);
@@ -210,7 +229,7 @@ uint32_t gemm_pair_smem_bytes(uint32_t pair_n) {
 namespace {
 
 template <uint32_t kPairN>
-int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& p, uint64_t total, uint32_t n_sms,
+int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_half, KParams p, uint64_t total, uint32_t n_sms,
                          cudaStream_t stream) {
     auto kern = gemm_bf16_tcgen05_pair_kernel<kPairN>;
     const uint32_t smem = gemm_pair_smem_bytes(kPairN);
@@ -234,7 +253,12 @@ int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KPa
         attr_set[dev] = true;
     }
     const uint32_t pairs = (uint32_t)std::min<uint64_t>(total, (uint64_t)max_pairs[dev]);
-    cudaError_t e = launch_pdl(kern, 2 * pairs, kThreads, smem, stream, ma, mb, p);
+    // last wave: `rest` tiles for `pairs` pairs; cut them in two when both halves still fit in one wave
+    const uint32_t rest = (uint32_t)(total % pairs);
+    static const bool no_tail = getenv("T0_NO_TAIL_SPLIT") != nullptr;
+    p.tail_start = (uint32_t)total;
+    if (!no_tail && p.split_k == 1 && total > pairs && rest != 0 && 2 * rest <= pairs) p.tail_start = (uint32_t)total - rest;
+    cudaError_t e = launch_pdl(kern, 2 * pairs, kThreads, smem, stream, ma, mb, mb_half, p);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "pair GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
 }
@@ -272,11 +296,14 @@ int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
     if (rc != T0_OK) return rc;
     rc = make_map_kmajor(&mb, g.b, g.n, ldb, kps, split, pair_n / 2);
     if (rc != T0_OK) return rc;
+    CUtensorMap mb_half;
+    rc = make_map_kmajor(&mb_half, g.b, g.n, ldb, kps, split, pair_n / 4);
+    if (rc != T0_OK) return rc;
     const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * split;
     if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
     const uint32_t n_sms = g.n_sms ? g.n_sms : 148;
-    return pair_n == 256 ? launch_pair_instance<256>(ma, mb, p, total, n_sms, stream)
-                         : launch_pair_instance<128>(ma, mb, p, total, n_sms, stream);
+    return pair_n == 256 ? launch_pair_instance<256>(ma, mb, mb_half, p, total, n_sms, stream)
+                         : launch_pair_instance<128>(ma, mb, mb_half, p, total, n_sms, stream);
 }
 
 }  // namespace t0

@@ -492,3 +492,23 @@ def test_skinny_configs_full_size(t0, oracle, rt, m, n, k, sk):
         assert_gemm_close(rt.read_f32(y, m * n).reshape(m, n), oracle.gemm_nt(a, b, m, k, n), k)
     for buf in (xa, xb, y):
         buf.free()
+
+
+@pytest.mark.parametrize("m,n,k,tile_n", [(2304, 2304, 128, 256),    # 81 tiles over 74 pairs: 7 tail tiles cut in halves
+                                          (2500, 2400, 200, 256),    # 100 tiles, ragged edges inside tail tiles
+                                          (2304, 1152, 192, 128),    # the 256 x 128 instance, 81 tiles
+                                          (3072, 2560, 64, 256)])    # 120 tiles: the last wave is too full to be cut
+def test_pair_kernel_tail_tiles_full_compare(t0, oracle, rt, m, n, k, tile_n):
+    # the CTA-pair kernel cuts the tiles of a thin last wave into two half-width tiles: every element is compared
+    a = oracle.fill_uniform_bf16(m * k, 42 + m)
+    b = oracle.fill_uniform_bf16(n * k, 137 + n)
+    xa, xb = rt.upload(a), rt.upload(b)
+    y = rt.alloc(m * n * 4 + 4096)
+    y.write(np.full(m * n + 1024, -9999.0, np.float32))
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, tile_n=tile_n, pair_cta=1)
+    rt.synchronize()
+    got = y.read(m * n * 4, np.float32).reshape(m, n)
+    assert_gemm_close(got, oracle.gemm_nt(a, b, m, k, n), k)
+    assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == -9999.0)
+    for buf in (xa, xb, y):
+        buf.free()
