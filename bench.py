@@ -87,10 +87,20 @@ def run_hbm_workload(args, name):
             xb = rt.alloc(N * K * 2)
             rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N + 1000 * s)
             sets.append((xb,))
-    if w4:
+    if w4 and M <= 16 and not args.row_layout:
+        # weights go to the streaming layout once, outside the timed region (a weight-load-time conversion)
+        pre = [rt.w4_prepack(*(b.gpu_addr() for b in st), K, N, G) for st in sets]
+        rt.synchronize()
+        for st in sets:
+            for b in st:
+                b.free()
+        calls = [t0.W4A16Args(xa.gpu_addr(), pre[i % n_sets].gpu_addr(), 0, 0, y.gpu_addr(), M, N, K, G) for i in range(steps)]
+        submit = rt.w4a16_gemm_prepacked_batch
+        kernel = "w4a16_tc_kernel<true> (streaming layout)"
+    elif w4:
         calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), y.gpu_addr(), M, N, K, G) for i in range(steps)]
         submit = rt.w4a16_gemm_batch
-        kernel = "w4a16_gemm_kernel" if M <= 16 else "dequant_w4_b200_kernel + gemm"
+        kernel = "w4a16_tc_kernel<false> (row layout)" if M <= 16 else "dequant_w4_b200_kernel + gemm"
     else:
         cfg = t0.auto_select(M, K, N)
         sk = w.get("split_k", cfg.split())
@@ -290,6 +300,7 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--row-layout", action="store_true", help="W4A16 workloads: weights in the row layout instead of the streaming layout")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -320,6 +320,18 @@ typedef struct t0_w4a16_args {
     uint32_t m, n, k, group;
 } t0_w4a16_args;
 int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
+/* Streaming weight layout for the fused kernel (no counterpart in the reference).  The row layout above puts the 16 KiB
+ * a CTA needs per step in sixteen 1 KiB pieces 4N bytes apart, which HBM serves at about a quarter of its copy bandwidth;
+ * t0_w4_prepack rewrites the three arrays once (weight-load time) into one buffer of t0_w4_prepacked_bytes(K, N, group):
+ *   tiles[N/256][K/128][16][256] u32, the eight codes of a word in the order k0 k2 k4 k6 k1 k3 k5 k7,
+ *   then scales[N/256][K/group][256] bf16, then zero points [N/256][K/group][32] u32 (columns past N are zero).
+ * t0_w4a16_gemm_prepacked computes the same y as t0_w4a16_gemm from that buffer (M <= 16, K % 128 == 0, group % 128 == 0,
+ * N % 8 == 0, K*N small enough for one wave: at most 20 steps of 128 x 256 per SM); the batch form reads
+ * t0_w4a16_args.packed as the prepacked buffer and ignores .scales / .zeros. */
+size_t t0_w4_prepacked_bytes(uint32_t K, uint32_t N, uint32_t group);
+int t0_w4_prepack(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group);
+int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group);
+int t0_w4a16_gemm_prepacked_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
 /* The fused W4A16 GEMM for callers that may not allocate device memory (no counterpart in the reference, which has no
  * fused INT4 GEMM).  Same arguments and result as t0_w4a16_gemm, bit for bit, but the scratch the kernel needs lives in a
  * fixed array inside the library (t0_w4a16_gemm_static_scratch_bytes() bytes per device), so the call never allocates or

@@ -215,6 +215,23 @@ def w4a16_gemm(a: np.ndarray, packed: np.ndarray, scales: np.ndarray, zeros: np.
     return y
 
 
+def w4_prepack(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, K: int, N: int, group: int = 128) -> np.ndarray:
+    """Tile-major streaming layout of the B200 W4A16 kernel (one uint8 buffer)."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.uint16)
+    zeros = np.ascontiguousarray(zeros, dtype=np.uint32)
+    off = (C.c_size_t * 3)()
+    L = lib()
+    L.oracle_w4_prepacked_layout.restype = C.c_size_t
+    L.oracle_w4_prepacked_layout.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_size_t)]
+    L.oracle_w4_prepack.restype = None
+    L.oracle_w4_prepack.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]
+    total = L.oracle_w4_prepacked_layout(K, N, group, off)
+    out = np.zeros(total, dtype=np.uint8)
+    L.oracle_w4_prepack(_p(packed), _p(scales), _p(zeros), _p(out), K, N, group)
+    return out
+
+
 def gptq_parse(raw: bytes):
     """GptqWeight::from_bytes wire format (quant_kernels.rs:242-286) -> dict of arrays."""
     buf = np.frombuffer(raw, dtype=np.uint8)

@@ -352,6 +352,46 @@ void oracle_w4a16_gemm(const uint16_t* a, const uint32_t* packed, const uint16_t
     free(w);
 }
 
+/* The streaming layout of the B200 W4A16 kernel (this build's own format; no reference counterpart).
+ * One buffer: tiles[band][kstep][16][256] u32, then scales_t[band][K/G][256] bf16, then
+ * zeros_t[band][K/G][32] u32; band = 256 columns (zero-padded past N), kstep = 128 k.  Inside a word
+ * the eight codes of a column sit in the order k0 k2 k4 k6 k1 k3 k5 k7 (nibble i and nibble i+4 are
+ * consecutive k).  Offsets of the three parts are returned through off[3]; the result is the size. */
+size_t oracle_w4_prepacked_layout(uint32_t K, uint32_t N, uint32_t group, size_t off[3]) {
+    size_t bands = (N + 255) / 256, ksteps = K / 128, groups = K / group;
+    off[0] = 0;
+    off[1] = bands * ksteps * 16 * 256 * 4;
+    off[2] = off[1] + bands * groups * 256 * 2;
+    return off[2] + bands * groups * 32 * 4;
+}
+
+void oracle_w4_prepack(const uint32_t* packed, const uint16_t* scales, const uint32_t* zeros,
+                       uint8_t* out, uint32_t K, uint32_t N, uint32_t group) {
+    size_t off[3];
+    size_t total = oracle_w4_prepacked_layout(K, N, group, off);
+    uint32_t bands = (N + 255) / 256, ksteps = K / 128, groups = K / group, nz = (N + 7) / 8;
+    static const int order[8] = {0, 2, 4, 6, 1, 3, 5, 7};   /* nibble i of the new word holds code order[i] */
+    memset(out, 0, total);
+    uint32_t* tiles = (uint32_t*)(out + off[0]);
+    uint16_t* st = (uint16_t*)(out + off[1]);
+    uint32_t* zt = (uint32_t*)(out + off[2]);
+    for (uint32_t b = 0; b < bands; ++b)
+        for (uint32_t c = 0; c < 256; ++c) {
+            uint32_t n = b * 256 + c;
+            if (n >= N) continue;
+            for (uint32_t r = 0; r < K / 8; ++r) {
+                uint32_t w = packed[(size_t)r * N + n], v = 0;
+                for (int i = 0; i < 8; ++i) v |= ((w >> (4 * order[i])) & 0xFu) << (4 * i);
+                tiles[(((size_t)b * ksteps + r / 16) * 16 + r % 16) * 256 + c] = v;
+            }
+            for (uint32_t g = 0; g < groups; ++g) {
+                st[((size_t)b * groups + g) * 256 + c] = scales[(size_t)g * N + n];
+                uint32_t z = (zeros[(size_t)g * nz + (n >> 3)] >> (4 * (n & 7))) & 0xFu;
+                zt[((size_t)b * groups + g) * 32 + (c >> 3)] |= z << (4 * (c & 7));
+            }
+        }
+}
+
 static uint32_t rd_u32le(const uint8_t* p) {
     return (uint32_t)p[0] | ((uint32_t)p[1] << 8) | ((uint32_t)p[2] << 16) | ((uint32_t)p[3] << 24);
 }

@@ -94,6 +94,10 @@ void oracle_dequant_int4_ref_bf16(const uint8_t* packed, const float* scales, co
  * w[k,n] = RNE_bf16( f32(q - z) * f32(s) ). */
 void oracle_dequant_w4_b200(const uint32_t* packed, const uint16_t* scales, const uint32_t* zeros,
                             uint16_t* w_out, uint32_t K, uint32_t N, uint32_t group);
+/* Streaming (tile-major) layout of the B200 W4A16 kernel: sizes/offsets and the repack itself. */
+size_t oracle_w4_prepacked_layout(uint32_t K, uint32_t N, uint32_t group, size_t off[3]);
+void oracle_w4_prepack(const uint32_t* packed, const uint16_t* scales, const uint32_t* zeros,
+                       uint8_t* out, uint32_t K, uint32_t N, uint32_t group);
 /* y[m,n] = sum_k f32(a[m,k]) * f32(w[k,n]) with w from oracle_dequant_w4_b200,
  * fp32 sequential accumulation, k ascending */
 void oracle_w4a16_gemm(const uint16_t* a, const uint32_t* packed, const uint16_t* scales,

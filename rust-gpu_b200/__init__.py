@@ -578,6 +578,22 @@ class GpuRuntime:
         """``t0_w4a16_gemm_static``: the fused kernel on the library's fixed scratch array; never allocates."""
         _check(lib().t0_w4a16_gemm_static(self._h, a, packed, scales, zeros, y, M, N, K, group))
 
+    def w4_prepack(self, packed: int, scales: int, zeros: int, K: int, N: int, group: int = 128) -> "GpuBuffer":
+        """``t0_w4_prepack``: row layout -> streaming layout, into a new buffer."""
+        n = lib().t0_w4_prepacked_bytes(K, N, group)
+        if n == 0:
+            raise T0Error(6, f"no streaming layout for K={K} N={N} group={group}")
+        out = self.alloc(n)
+        _check(lib().t0_w4_prepack(self._h, packed, scales, zeros, out.gpu_addr(), K, N, group))
+        return out
+
+    def w4a16_gemm_prepacked(self, a: int, prepacked: int, y: int, M: int, N: int, K: int, group: int = 128) -> None:
+        _check(lib().t0_w4a16_gemm_prepacked(self._h, a, prepacked, y, M, N, K, group))
+
+    def w4a16_gemm_prepacked_batch(self, calls: list[W4A16Args]) -> None:
+        arr = (W4A16Args * len(calls))(*calls)
+        _check(lib().t0_w4a16_gemm_prepacked_batch(self._h, arr, len(calls)))
+
     def w4a16_gemm_batch(self, calls: list[W4A16Args]) -> None:
         arr = (W4A16Args * len(calls))(*calls)
         _check(lib().t0_w4a16_gemm_batch(self._h, arr, len(calls)))
@@ -836,6 +852,10 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    sig("t0_w4_prepacked_bytes", sz, u32, u32, u32)
+    sig("t0_w4_prepack", i32, vp, u64, u64, u64, u64, u32, u32, u32)
+    sig("t0_w4a16_gemm_prepacked", i32, vp, u64, u64, u64, u32, u32, u32, u32)
+    sig("t0_w4a16_gemm_prepacked_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_static_scratch_bytes", sz)
     sig("t0_gptq_parse", i32, vp, sz, u32p, u32p, u32p, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz))
     sig("t0_gptq_gpu_buffer_size", sz, u32, u32, u32)

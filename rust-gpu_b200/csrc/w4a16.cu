@@ -60,6 +60,10 @@ struct W4Params {
     uint32_t units_per_group;   // group / 128: steps that share one row of scales and zero points
     uint32_t n_bands, ksteps, total_units;
     uint32_t a_units;    // steps of activations the shared-memory area holds (max steps of one CTA)
+    const uint8_t* tiles;      // streaming layout only: [band][kstep][16][256] u32
+    const uint8_t* scales_t;   //   [band][K/G][256] bf16
+    const uint8_t* zeros_t;    //   [band][K/G][32] u32
+    uint32_t groups;           //   K / G
     unsigned long long* stamps;   // optional trace: 4 nanosecond stamps per CTA (entry, staged, loop done, exit)
 };
 
@@ -347,6 +351,412 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     stamp(3);
 }
 
+// ------------------------------------------------------------------ K2, tensor-memory form
+//
+// Same work split, ring and band fix-up as the kernel above, but the dot products run on tcgen05: the dequantised
+// weights are the 128-row A operand and live in tensor memory (each of 16 dequant warps writes the rows of its lane
+// quadrant with tcgen05.st), the activations are the 16-column B operand in shared memory (128-byte swizzle, K-major,
+// pre-permuted to the order a single mask pulls codes out of a word), accumulators are 128 lanes x 16 columns per
+// 128-column half band.  One UMMA (M 128, N 16, K 16) replaces 32 mma.sync; the k halves of a step accumulate into
+// the same tensor-memory tile, so no cross-warp reduction is left.
+constexpr int kTcWarps = 16;                         // dequant + epilogue warps
+constexpr int kTcIssuers = 4;                        // UMMA issuer warps: issuing one UMMA costs a thread ~120 cycles whatever its size,
+                                                     // so the 16 small UMMAs of a step are spread over four threads
+constexpr int kTcThreads = (kTcWarps + 1 + kTcIssuers) * 32;   // + TMA producer warp + UMMA issuer warps
+constexpr int kTcBUnitBytes = 2 * 16 * 128;          // activations of one step: two 64-deep atoms of 16 rows x 128 B
+constexpr int kTcMaxUnits = 20;                      // steps of one CTA whose activations fit beside the ring
+constexpr uint32_t kTcTmemCols = 512;
+constexpr uint32_t kTcACols = 128;                   // A columns per step: 2 half bands x 8 k steps x 8 columns
+constexpr uint32_t kTcABufs = 3;                     // A buffers: the dequant warps may run two steps ahead of the UMMAs
+constexpr uint32_t kTcDBase = kTcABufs * kTcACols;   // then the accumulators: 2 half bands x 4 partial sums x 16 columns
+constexpr uint32_t kTcDParts = 4;                    // k step j accumulates into partial sum j % 4: an UMMA this small is bound by the
+                                                     // latency of its accumulate dependency, so consecutive ones must not share a tile
+constexpr uint32_t kTcIdesc = ptx::make_idesc_bf16_f32(128, 16, 0u);
+__device__ __forceinline__ void tc_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTcWarps * 32) : "memory"); }
+
+// kStream = false: weights in the row layout packed[K/8][N], fetched with 2-D TMA boxes, activations staged by the dequant
+//   warps in the permuted order.
+// kStream = true: weights in the streaming layout (t0_w4_prepack): one 16 KiB bulk copy per step (1 KiB rows 43 KiB apart
+//   reach a quarter of the copy bandwidth, 16 KiB runs most of it), codes already in natural pair order, so the
+//   activations come straight from the caller's matrix through a swizzling tensor map (`map_w` is that map here);
+//   scales and zero points of all the CTA's steps arrive up front in a few bulk copies.
+template <bool kStream>
+__global__ void __launch_bounds__(kTcThreads, 1)
+w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+                const __grid_constant__ CUtensorMap map_z, const W4Params p) {
+    constexpr uint32_t kRingStage = kStream ? kWeightBytes : kStageBytes;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* b_area = smem;                                            // [a_units][2 atoms][16 rows][128 B], swizzled
+    uint8_t* ring = smem + (size_t)p.a_units * kTcBUnitBytes;          // kStages x {16 KiB codes, 512 B scales, 128 B zero points}
+    uint8_t* s_area = ring + kStages * kRingStage;                     // streaming layout: [a_units][256] bf16 scales ...
+    uint8_t* z_area = s_area + (kStream ? (size_t)p.a_units * kScaleBytes : 0);   // ... and [a_units][32] u32 zero points
+    uint64_t* full_bar = (uint64_t*)(z_area + (kStream ? (size_t)p.a_units * kZeroBytes : 0));
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* a_ready_bar = empty_bar + kStages;       // [kTcABufs] all 16 warps wrote their part of an A buffer
+    uint64_t* a_free_bar = a_ready_bar + kTcABufs;     // [kTcABufs] the UMMAs that read an A buffer are done
+    uint64_t* acc_full_bar = a_free_bar + kTcABufs;    // [2] a band piece is accumulated
+    uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2] all 16 warps have read an accumulator buffer
+    uint64_t* b_full_bar = acc_empty_bar + 2;          // streaming layout: activations of all steps have landed
+    uint64_t* sz_full_bar = b_full_bar + 1;            // streaming layout: scales and zero points have landed
+    uint32_t* tmem_holder = (uint32_t*)(sz_full_bar + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
+    int* s_last = (int*)(tmem_holder + 2);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t u0 = range_begin(blockIdx.x, gridDim.x, p.total_units);
+    const uint32_t u1 = range_begin(blockIdx.x + 1, gridDim.x, p.total_units);
+    if (u0 >= u1) return;
+    auto stamp = [&](int i) {
+        if (p.stamps && tid == 0) { unsigned long long t_ns; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns)); p.stamps[blockIdx.x * 4 + i] = t_ns; }
+    };
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), kTcWarps);
+        }
+        for (uint32_t b = 0; b < kTcABufs; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&a_ready_bar[b]), kTcWarps);
+            ptx::mbar_init(ptx::smem_u32(&a_free_bar[b]), kTcIssuers);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&acc_full_bar[b]), kTcIssuers);
+            ptx::mbar_init(ptx::smem_u32(&acc_empty_bar[b]), kTcWarps);
+        }
+        ptx::mbar_init(ptx::smem_u32(b_full_bar), 1);
+        ptx::mbar_init(ptx::smem_u32(sz_full_bar), 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::tma_prefetch_desc(&map_w);
+        if (!kStream) {
+            ptx::tma_prefetch_desc(&map_s);
+            ptx::tma_prefetch_desc(&map_z);
+        }
+    }
+    if (warp == kTcWarps + 1) {
+        ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTcTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();      // global memory is touched only after the previous grid in the stream is done
+    stamp(0);
+    const uint32_t band_first = u0 / p.ksteps;
+    const uint32_t ks_first = u0 - band_first * p.ksteps;
+
+    if (warp == kTcWarps) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
+            if (kStream) {
+                // scales and zero points of every (band, group) the CTA's steps touch: one copy of each per band piece,
+                // into consecutive slots; the barrier's byte count is posted after the copies (it cannot complete before
+                // this thread's arrival)
+                uint32_t left = u1 - u0, slot = 0, bytes = 0, b2 = band, k2 = ks;
+                const uint32_t sb = ptx::smem_u32(sz_full_bar);
+                while (left) {
+                    const uint32_t n_here = min(left, p.ksteps - k2);
+                    const uint32_t g_lo = k2 / p.units_per_group, ng = (k2 + n_here - 1) / p.units_per_group - g_lo + 1;
+                    const size_t row = (size_t)b2 * p.groups + g_lo;
+                    ptx::bulk_load(ptx::smem_u32(s_area + slot * kScaleBytes), p.scales_t + row * kScaleBytes, ng * kScaleBytes, sb);
+                    ptx::bulk_load(ptx::smem_u32(z_area + slot * kZeroBytes), p.zeros_t + row * kZeroBytes, ng * kZeroBytes, sb);
+                    bytes += ng * (kScaleBytes + kZeroBytes);
+                    slot += ng; left -= n_here; k2 = 0; ++b2;
+                }
+                ptx::mbar_arrive_expect_tx(sb, bytes);
+            }
+            for (uint32_t u = u0; u < u1; ++u) {
+                if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                    atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(u & 0xFFFFFF));
+                    break;
+                }
+                const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+                uint8_t* dst = ring + stage * kRingStage;
+                if (kStream) {
+                    ptx::mbar_arrive_expect_tx(fb, kWeightBytes);
+                    ptx::bulk_load(ptx::smem_u32(dst), p.tiles + ((size_t)band * p.ksteps + ks) * kWeightBytes, kWeightBytes, fb);
+                } else {
+                    const uint32_t grp = ks / p.units_per_group;
+                    ptx::mbar_arrive_expect_tx(fb, kWeightBytes + kScaleBytes + kZeroBytes);
+                    ptx::tma_load_2d(ptx::smem_u32(dst), &map_w, fb, (int32_t)(band * kBandCols), (int32_t)(ks * (kUnitK / 8)));
+                    ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes), &map_s, fb, (int32_t)(band * kBandCols), (int32_t)grp);
+                    ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes + kScaleBytes), &map_z, fb, (int32_t)(band * (kBandCols / 8)), (int32_t)grp);
+                }
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+                if (++ks == p.ksteps) { ks = 0; ++band; }
+            }
+        }
+    } else if (warp > kTcWarps) {
+        // ------------------------------------------------------------ UMMA issuers: issuer w owns k steps w and w + 4 of
+        // every step and partial accumulator w of both half bands
+        const uint32_t issuer = warp - kTcWarps - 1;
+        if (lane == 0) {
+            uint32_t ks = ks_first, piece = 0;
+            bool piece_start = true;
+            if (kStream) {
+                // activations of every step, as they lie in the caller's [M][K] matrix: two 64-deep swizzled atoms of 16
+                // rows per step (rows >= M are out of bounds and read as zero)
+                const uint32_t bb = ptx::smem_u32(b_full_bar);
+                if (issuer == 0) {
+                    for (uint32_t i = 0; i < u1 - u0; ++i) {
+                        const uint32_t kks = (ks_first + i) % p.ksteps;
+                        for (uint32_t atom = 0; atom < 2; ++atom)
+                            ptx::tma_load_3d(ptx::smem_u32(b_area + (size_t)i * kTcBUnitBytes + atom * 2048), &map_w, bb,
+                                             (int32_t)(kks * kUnitK + atom * 64), 0, 0);
+                    }
+                    ptx::mbar_arrive_expect_tx(bb, (u1 - u0) * kTcBUnitBytes);
+                }
+                if (!ptx::mbar_wait(bb, 0, abort_flag)) atomicCAS(p.status, 0, kStatusMmaTimeout | 0xC00000);
+            }
+            for (uint32_t u = u0; u < u1; ++u) {
+                const uint32_t i = u - u0, ab = i % kTcABufs, a_round = i / kTcABufs;
+                if (piece_start) {
+                    // the accumulators have been read by everyone (previous piece)
+                    if (!ptx::mbar_wait(ptx::smem_u32(&acc_empty_bar[0]), (piece & 1) ^ 1, abort_flag)) {
+                        atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000 | (int)(u & 0x7FFFFF));
+                        break;
+                    }
+                }
+                const long long t_w = p.stamps ? clock64() : 0;
+                if (!ptx::mbar_wait(ptx::smem_u32(&a_ready_bar[ab]), a_round & 1, abort_flag)) {
+                    atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(u & 0xFFFFFF));
+                    break;
+                }
+                if (p.stamps && issuer == 0) p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 3] += (unsigned long long)(clock64() - t_w);   // trace: idle time of issuer 0
+                ptx::tc_fence_after_sync();
+                const uint32_t b_addr = ptx::smem_u32(b_area + (size_t)i * kTcBUnitBytes);
+#pragma unroll
+                for (uint32_t jh = 0; jh < 2; ++jh) {
+                    const uint32_t j = issuer + jh * kTcDParts;
+                    const uint64_t db = ptx::make_smem_desc(b_addr + jh * 2048 + issuer * 32, 16, 1024);
+#pragma unroll
+                    for (uint32_t t = 0; t < 2; ++t)
+                        ptx::umma_bf16_ts(tmem_base + kTcDBase + (t * kTcDParts + issuer) * 16, tmem_base + ab * kTcACols + t * 64 + j * 8, db, kTcIdesc,
+                                          (piece_start && jh == 0) ? 0u : 1u);
+                }
+                ptx::umma_commit(ptx::smem_u32(&a_free_bar[ab]));
+                const bool band_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
+                piece_start = false;
+                if (band_ends) {
+                    ptx::umma_commit(ptx::smem_u32(&acc_full_bar[0]));
+                    ++piece;
+                    piece_start = true;
+                }
+                if (++ks == p.ksteps) ks = 0;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ dequant + epilogue warps (16)
+        const uint32_t q = warp & 3, t = (warp >> 2) & 1, h = warp >> 3;   // lane quadrant, half band, k half of a step
+        const uint32_t n_local = t * 128 + q * 32 + lane;                   // this thread's column within the band
+        const uint32_t lane_base = (q * 32) << 16;
+        const uint32_t n_units = u1 - u0;
+
+        // Activations -> shared memory as the B operand: 16 rows (m) x 64 k per 128-byte-swizzled atom.  Within every
+        // group of eight k the order becomes 0,4,1,5,2,6,3,7: the pair (code i, code i+4) one mask pulls out of a
+        // packed word is then one 32-bit column of the A tile.
+        for (uint32_t i = tid; !kStream && i < n_units * 256; i += kTcWarps * 32) {
+            const uint32_t unit = i >> 8, m = (i >> 4) & 15, g8 = i & 15;
+            const uint32_t kks = (ks_first + unit) % p.ksteps;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (m < p.M) v = __ldg((const uint4*)(p.a + (size_t)m * p.K + kks * kUnitK + g8 * 8));
+            uint4 o;
+            o.x = __byte_perm(v.x, v.z, 0x5410);   // k0 k4
+            o.y = __byte_perm(v.x, v.z, 0x7632);   // k1 k5
+            o.z = __byte_perm(v.y, v.w, 0x5410);   // k2 k6
+            o.w = __byte_perm(v.y, v.w, 0x7632);   // k3 k7
+            *(uint4*)(b_area + (size_t)unit * kTcBUnitBytes + (g8 >> 3) * 2048 + m * 128 + (((g8 & 7) ^ (m & 7)) << 4)) = o;
+        }
+        if (!kStream) {
+            ptx::fence_proxy_async_smem();        // the UMMAs read these bytes through the async proxy
+            tc_consumer_sync();
+        }
+        stamp(1);
+
+        uint32_t mask, magic;
+        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
+        asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
+        uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0, piece_idx = 0;
+        long long w_full = 0, w_afree = 0, w_acc = 0, t_mark = 0;   // trace only: cycles this warp waited on each barrier
+        const bool tracing = p.stamps != nullptr;
+        bool ok = true;    // false after a wait expired: the warp keeps walking (barriers stay matched) but does no work
+        uint32_t sz_slot = 0, in_group = ks_first % p.units_per_group;   // streaming layout: slot of the current (band, group)
+        if (kStream && !ptx::mbar_wait(ptx::smem_u32(sz_full_bar), 0, abort_flag)) {
+            if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xC00000);
+            ok = false;
+        }
+        const uint32_t w_off = (h * 8) * (kBandCols * 4) + n_local * 4;
+        const uint32_t s_off = kWeightBytes + n_local * 2;
+        const uint32_t z_off = kWeightBytes + kScaleBytes + (n_local >> 3) * 4;
+        const uint32_t z_shift = (n_local & 7) * 4;
+
+        for (uint32_t u = u0; u < u1; ++u) {
+            const uint32_t i = u - u0, ab = i % kTcABufs, a_round = i / kTcABufs;
+            if (tracing) t_mark = clock64();
+            if (ok && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(u & 0xFFFFFF));
+                ok = false;
+            }
+            if (tracing) { const long long now = clock64(); w_full += now - t_mark; t_mark = now; }
+            uint32_t words[8];
+            uint32_t zz = 0, ss = 0;
+            if (ok) {
+                const uint8_t* st = ring + stage * kRingStage;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) words[r] = *(const uint32_t*)(st + w_off + r * (kBandCols * 4));
+                uint32_t s, z;
+                if (kStream) {
+                    s = *(const uint16_t*)(s_area + sz_slot * kScaleBytes + n_local * 2);
+                    z = (*(const uint32_t*)(z_area + sz_slot * kZeroBytes + (n_local >> 3) * 4) >> z_shift) & 0xFu;
+                } else {
+                    s = *(const uint16_t*)(st + s_off);
+                    z = (*(const uint32_t*)(st + z_off) >> z_shift) & 0xFu;
+                }
+                zz = z * 0x00010001u + 0x43004300u;     // bf16x2 (128+z, 128+z)
+                ss = s * 0x00010001u;                    // (s, s)
+            }
+            // the A buffer is free once the UMMAs of two steps ago have read it
+            if (tracing) t_mark = clock64();
+            if (ok && !ptx::mbar_wait(ptx::smem_u32(&a_free_bar[ab]), (a_round & 1) ^ 1, abort_flag)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x400000 | (int)(u & 0x3FFFFF));
+                ok = false;
+            }
+            if (tracing) w_afree += clock64() - t_mark;
+            if (ok) {
+                ptx::tc_fence_after_sync();
+#pragma unroll
+                for (uint32_t jj = 0; jj < 4; ++jj) {
+                    uint32_t r8[8];
+#pragma unroll
+                    for (uint32_t half = 0; half < 2; ++half) {
+                        const uint32_t wd = words[2 * jj + half];
+#pragma unroll
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            const uint32_t v = and_or(wd >> (4 * c), mask, magic);          // bf16x2 (128 + nibble c, 128 + nibble c+4)
+                            r8[half * 4 + c] = bf16x2_mul(bf16x2_sub(v, zz), ss);
+                        }
+                    }
+                    ptx::tmem_st_32x32b_x8(tmem_base + lane_base + ab * kTcACols + t * 64 + (h * 4 + jj) * 8, r8);
+                }
+                // the stage was read through the generic proxy and TMA (async proxy) will overwrite it
+                ptx::fence_proxy_async_smem();
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(ptx::smem_u32(&empty_bar[stage]));
+                    ptx::mbar_arrive(ptx::smem_u32(&a_ready_bar[ab]));
+                }
+            }
+            if (++stage == kStages) { stage = 0; phase ^= 1; }
+
+            const bool band_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
+            if (u + 1 == u1) stamp(2);
+            if (band_ends) {
+                if (tracing) t_mark = clock64();
+                if (ok && !ptx::mbar_wait(ptx::smem_u32(&acc_full_bar[0]), piece_idx & 1, abort_flag)) {
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x800000 | (int)(u & 0x3FFFFF));
+                    ok = false;
+                }
+                if (tracing) w_acc += clock64() - t_mark;
+                uint32_t d[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) d[j] = 0;
+                if (ok) {
+                    ptx::tc_fence_after_sync();
+                    // rows m = 8h .. 8h+7 of column n_local: the four partial sums, added in k order
+                    uint32_t part[kTcDParts][8];
+#pragma unroll
+                    for (uint32_t jq = 0; jq < kTcDParts; ++jq)
+                        ptx::tmem_ld_32x32b_x8(tmem_base + lane_base + kTcDBase + (t * kTcDParts + jq) * 16 + h * 8, part[jq]);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        d[j] = __float_as_uint((__uint_as_float(part[0][j]) + __uint_as_float(part[1][j])) +
+                                               (__uint_as_float(part[2][j]) + __uint_as_float(part[3][j])));
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&acc_empty_bar[0]));
+                }
+                ++piece_idx;
+                const uint32_t first_unit = band * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
+                const bool whole = first_unit >= u0 && last_unit <= u1;
+                const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
+                const uint32_t c_last = owner_of(last_unit - 1, gridDim.x, p.total_units);
+                const uint32_t slot = (first_unit <= u0) ? 0u : 1u;   // the piece of the band holding this CTA's first unit is slot 0
+                float* piece = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPieceFloats;
+                const uint32_t ncol = band * kBandCols + n_local;
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j) {
+                    const uint32_t m = h * 8 + j;
+                    if (m < p.M) {
+                        if (!whole) piece[m * kBandCols + n_local] = __uint_as_float(d[j]);
+                        else if (ncol < p.N) p.y[(size_t)m * p.N + ncol] = __uint_as_float(d[j]);
+                    }
+                }
+                if (!whole) {
+                    tc_consumer_sync();                    // every thread's part of the piece is written ...
+                    if (tid == 0) {
+                        __threadfence();                   // ... and made visible before this CTA is counted
+                        *s_last = (atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first)) ? 1 : 0;
+                        if (*s_last) __threadfence();
+                    }
+                    tc_consumer_sync();
+                    if (*s_last) {
+                        // last to arrive: add the pieces in k order (CTA order) and store; nobody waits for anybody.
+                        // Only the first contributor can hold this band in slot 1 (its range began in the band before).
+                        const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
+                        constexpr int kPer = kPieceFloats / (kTcWarps * 32);   // 8 outputs per thread when M = 16
+                        float total[kPer];
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
+                        for (uint32_t c = c_first; c <= c_last; ++c) {
+                            const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
+                            float v[kPer];
+#pragma unroll
+                            for (int j = 0; j < kPer; ++j) {
+                                const uint32_t idx = tid + j * (kTcWarps * 32);
+                                v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
+                            }
+#pragma unroll
+                            for (int j = 0; j < kPer; ++j) total[j] += v[j];
+                        }
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j) {
+                            const uint32_t idx = tid + j * (kTcWarps * 32);
+                            if (idx < p.M * kBandCols) {
+                                const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
+                                const uint32_t nc = band * kBandCols + col;
+                                if (nc < p.N) p.y[(size_t)row * p.N + nc] = total[j];
+                            }
+                        }
+                        if (tid == 0) p.counters[band] = 0;   // ready for the next call
+                    }
+                    tc_consumer_sync();
+                }
+            }
+            // next step: a new slot when the group changes or the band ends
+            if (++in_group == p.units_per_group || ks + 1 == p.ksteps) { in_group = 0; ++sz_slot; }
+            if (++ks == p.ksteps) { ks = 0; ++band; }
+        }
+        if (tracing && tid == 0) { p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 0] = w_full; p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 1] = w_afree; p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 2] = w_acc; }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    __syncwarp();
+    stamp(3);
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kTcWarps + 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTcTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------ K3: stand-alone dequantisation
 
 // Reference wire format (quant_kernels.rs:53-171): one thread per 32 consecutive elements.
@@ -458,8 +868,13 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
     p.M = M; p.N = N; p.K = K;
     p.units_per_group = group / kUnitK;
     p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
-    p.a_units = std::min<uint32_t>((uint32_t)ceil_div((uint32_t)total, grid), kMaxAUnits);
-    const size_t smem = 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
+    // the same kernel choice as t0_w4a16_gemm, so both entries give the same bits
+    static const bool legacy = getenv("T0_W4_LEGACY") != nullptr;
+    const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
+    const bool use_tc = !legacy && units_per_cta <= (uint32_t)kTcMaxUnits;
+    p.a_units = use_tc ? units_per_cta : std::min<uint32_t>(units_per_cta, kMaxAUnits);
+    const size_t smem = use_tc ? 1024 + (size_t)p.a_units * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256
+                               : 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
     CUtensorMap map_w, map_s, map_z;
     int rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kBandCols, kUnitK / 8);
     if (rc != T0_OK) return rc;
@@ -470,14 +885,17 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
         T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(1024 + (size_t)kTcMaxUnits * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256)));
         attr_set[rt->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(use_tc ? kTcThreads : kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = rt->stream;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
+    cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<false>, map_w, map_s, map_z, p)
+                            : cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
     if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     rt->launches.fetch_add(1);
     return T0_OK;
@@ -560,8 +978,13 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     p.M = M; p.N = N; p.K = K;
     p.units_per_group = group / kUnitK;
     p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
-    p.a_units = std::min<uint32_t>((uint32_t)ceil_div((uint32_t)total, grid), kMaxAUnits);
-    const size_t smem = 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
+    // the tensor-memory kernel needs the activations of all of a CTA's steps resident beside the ring
+    static const bool legacy = getenv("T0_W4_LEGACY") != nullptr;
+    const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
+    const bool use_tc = !legacy && units_per_cta <= (uint32_t)kTcMaxUnits;
+    p.a_units = use_tc ? units_per_cta : std::min<uint32_t>(units_per_cta, kMaxAUnits);
+    const size_t smem = use_tc ? 1024 + (size_t)p.a_units * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256
+                               : 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
 
     CUtensorMap map_w, map_s, map_z;
     rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kBandCols, kUnitK / 8);
@@ -574,14 +997,16 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
         T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
+        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(1024 + (size_t)kTcMaxUnits * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256)));
         attr_set[rt->device] = true;
     }
     // T0_W4_TRACE=1: per-CTA stage stamps, summarised on stderr after a blocking wait (a debugging aid, off by default)
     static const bool trace = getenv("T0_W4_TRACE") != nullptr;
     unsigned long long* d_stamps = nullptr;
     if (trace) {
-        T0_CUDA(cudaMalloc(&d_stamps, (size_t)grid * 4 * sizeof(unsigned long long)));
-        T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 4 * sizeof(unsigned long long)));
+        T0_CUDA(cudaMalloc(&d_stamps, (size_t)grid * 8 * sizeof(unsigned long long)));
+        T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 8 * sizeof(unsigned long long)));
         p.stamps = d_stamps;
     }
     {
@@ -590,7 +1015,7 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid, 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.blockDim = dim3(use_tc ? kTcThreads : kThreads, 1, 1);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = rt->stream;
         cudaLaunchAttribute attr[1];
@@ -598,11 +1023,12 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = use_pdl ? 1 : 0;
-        cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
+        cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<false>, map_w, map_s, map_z, p)
+                                : cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
         if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     }
     if (trace) {
-        std::vector<unsigned long long> h((size_t)grid * 4);
+        std::vector<unsigned long long> h((size_t)grid * 8);
         T0_CUDA(cudaStreamSynchronize(rt->stream));
         T0_CUDA(cudaMemcpy(h.data(), d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
         cudaFree(d_stamps);
@@ -684,6 +1110,191 @@ long t0_gptq_to_b200(const uint8_t* packed, const float* scales, const int32_t* 
         }
     }
     return inexact;
+}
+
+}  // extern "C"
+// ------------------------------------------------------------------ streaming (tile-major) weight layout
+
+namespace {
+
+struct PrepackLayout { size_t off_tiles, off_scales, off_zeros, total; uint32_t bands, ksteps, groups; };
+
+PrepackLayout prepack_layout(uint32_t K, uint32_t N, uint32_t group) {
+    PrepackLayout L;
+    L.bands = ceil_div(N, kBandCols); L.ksteps = K / kUnitK; L.groups = K / group;
+    L.off_tiles = 0;
+    L.off_scales = (size_t)L.bands * L.ksteps * kWeightBytes;
+    L.off_zeros = L.off_scales + (size_t)L.bands * L.groups * kScaleBytes;
+    L.total = L.off_zeros + (size_t)L.bands * L.groups * kZeroBytes;
+    return L;
+}
+
+// Row layout -> streaming layout.  One thread per output element: a tile word (codes re-ordered k0 k2 k4 k6 k1 k3 k5 k7),
+// a scale, or a word of eight zero points.  Columns past N are written as zero.
+__global__ void w4_prepack_kernel(const uint32_t* __restrict__ packed, const uint16_t* __restrict__ scales, const uint32_t* __restrict__ zeros,
+                                  uint8_t* __restrict__ out, uint32_t K, uint32_t N, uint32_t nz, PrepackLayout L) {
+    const uint64_t n_words = (uint64_t)L.bands * L.ksteps * 16 * kBandCols;
+    const uint64_t n_scales = (uint64_t)L.bands * L.groups * kBandCols;
+    const uint64_t n_zwords = (uint64_t)L.bands * L.groups * (kBandCols / 8);
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words + n_scales + n_zwords; i += stride) {
+        if (i < n_words) {
+            const uint32_t c = (uint32_t)(i % kBandCols), r = (uint32_t)((i / kBandCols) % 16);
+            const uint64_t tile = i / (16 * kBandCols);
+            const uint32_t ks = (uint32_t)(tile % L.ksteps), band = (uint32_t)(tile / L.ksteps);
+            const uint32_t n = band * kBandCols + c;
+            uint32_t v = 0;
+            if (n < N) {
+                const uint32_t w = packed[(size_t)(ks * 16 + r) * N + n];
+                // nibble i of the new word: code 2i for i < 4, code 2(i-4)+1 above
+                v = (w & 0xFu) | ((w >> 4) & 0xF0u) | ((w >> 8) & 0xF00u) | ((w >> 12) & 0xF000u) |
+                    ((w << 12) & 0xF0000u) | ((w << 8) & 0xF00000u) | ((w << 4) & 0xF000000u) | (w & 0xF0000000u);
+            }
+            ((uint32_t*)(out + L.off_tiles))[i] = v;
+        } else if (i < n_words + n_scales) {
+            const uint64_t j = i - n_words;
+            const uint32_t c = (uint32_t)(j % kBandCols);
+            const uint64_t row = j / kBandCols;
+            const uint32_t g = (uint32_t)(row % L.groups), band = (uint32_t)(row / L.groups);
+            const uint32_t n = band * kBandCols + c;
+            ((uint16_t*)(out + L.off_scales))[j] = n < N ? scales[(size_t)g * N + n] : (uint16_t)0;
+        } else {
+            const uint64_t j = i - n_words - n_scales;
+            const uint32_t wz = (uint32_t)(j % (kBandCols / 8));
+            const uint64_t row = j / (kBandCols / 8);
+            const uint32_t g = (uint32_t)(row % L.groups), band = (uint32_t)(row / L.groups);
+            const uint32_t n0 = band * kBandCols + wz * 8;     // eight columns, aligned to a source word
+            ((uint32_t*)(out + L.off_zeros))[j] = n0 < N ? zeros[(size_t)g * nz + (n0 >> 3)] : 0u;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t t0_w4_prepacked_bytes(uint32_t K, uint32_t N, uint32_t group) {
+    if (K == 0 || N == 0 || group == 0 || K % kUnitK || group % kUnitK || K % group) return 0;
+    return prepack_layout(K, N, group).total;
+}
+
+int t0_w4_prepack(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!packed || !scales || !zeros || !out) return fail(T0_ERR_INVALID, "null device pointer");
+    if (K == 0 || N == 0 || group == 0 || K % kUnitK || group % kUnitK || K % group)
+        return fail(T0_ERR_UNSUPPORTED, "the streaming layout needs K %% 128 == 0 and group %% 128 == 0 with group | K (K=%u, group=%u)", K, group);
+    if (N % 8) return fail(T0_ERR_UNSUPPORTED, "N=%u must be a multiple of 8 (eight zero points per word)", N);
+    if (out & 127) return fail(T0_ERR_INVALID, "the output buffer must be 128-byte aligned");
+    DeviceGuard guard(rt->device);
+    const PrepackLayout L = prepack_layout(K, N, group);
+    const uint64_t n = L.total / 2;
+    w4_prepack_kernel<<<grid_for(n, 256), 256, 0, rt->stream>>>((const uint32_t*)packed, (const uint16_t*)scales, (const uint32_t*)zeros,
+                                                               (uint8_t*)out, K, N, (N + 7) / 8, L);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "prepack launch failed: %s", cudaGetErrorString(e));
+    rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (M == 0 || N == 0) return T0_OK;
+    if (!a || !prepacked || !y) return fail(T0_ERR_INVALID, "null device pointer");
+    if (M > 16) return fail(T0_ERR_UNSUPPORTED, "M=%u: the streaming-layout kernel takes M <= 16; use t0_w4a16_gemm on the row layout for larger M", M);
+    if (K == 0 || K % kUnitK || group == 0 || group % kUnitK || K % group || N % 8)
+        return fail(T0_ERR_UNSUPPORTED, "shape K=%u N=%u group=%u: needs K %% 128 == 0, group %% 128 == 0, group | K, N %% 8 == 0", K, N, group);
+    if ((a & 15) || (prepacked & 127) || (y & 3)) return fail(T0_ERR_INVALID, "a must be 16-byte, the weights 128-byte and y 4-byte aligned");
+    DeviceGuard guard(rt->device);
+    const PrepackLayout L = prepack_layout(K, N, group);
+    const uint64_t total = (uint64_t)L.bands * L.ksteps;
+    if (total > 0x7FFFFFFFull || L.bands * sizeof(int) > kCounterRegion) return fail(T0_ERR_UNSUPPORTED, "problem too large");
+    // enough CTAs that the activations of one CTA's steps fit in shared memory, at most one per SM
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
+    const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
+    if (units_per_cta > (uint32_t)kTcMaxUnits)
+        return fail(T0_ERR_UNSUPPORTED, "K*N too large for one wave: %u steps per CTA, at most %d", units_per_cta, kTcMaxUnits);
+    const size_t need = kCounterRegion + (size_t)grid * 2 * kPieceFloats * sizeof(float);
+    if (need > rt->scratch_w4.size) {
+        rc = ensure_scratch(rt, rt->scratch_w4, need);
+        if (rc != T0_OK) return rc;
+        T0_CUDA(cudaMemsetAsync(rt->scratch_w4.ptr, 0, kCounterRegion, rt->stream));
+    }
+    W4Params p;
+    memset(&p, 0, sizeof p);
+    p.a = (const uint16_t*)a;
+    p.y = (float*)y;
+    p.counters = (int*)rt->scratch_w4.ptr;
+    p.partials = (float*)((uint8_t*)rt->scratch_w4.ptr + kCounterRegion);
+    p.status = rt->d_status;
+    p.M = M; p.N = N; p.K = K;
+    p.units_per_group = group / kUnitK;
+    p.n_bands = L.bands; p.ksteps = L.ksteps; p.total_units = (uint32_t)total;
+    p.a_units = units_per_cta;
+    p.tiles = (const uint8_t*)prepacked + L.off_tiles;
+    p.scales_t = (const uint8_t*)prepacked + L.off_scales;
+    p.zeros_t = (const uint8_t*)prepacked + L.off_zeros;
+    p.groups = L.groups;
+    const size_t smem = 1024 + (size_t)units_per_cta * (kTcBUnitBytes + kScaleBytes + kZeroBytes) + (size_t)kStages * kWeightBytes + 256;
+    CUtensorMap map_a;
+    rc = gemm::make_map_kmajor(&map_a, (const void*)a, M, K, K, 1, 16);
+    if (rc != T0_OK) return rc;
+    static bool attr_set[64] = {};
+    if (rt->device < 64 && !attr_set[rt->device]) {
+        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(1024 + (size_t)kTcMaxUnits * (kTcBUnitBytes + kScaleBytes + kZeroBytes) + (size_t)kStages * kWeightBytes + 256)));
+        attr_set[rt->device] = true;
+    }
+    static const bool trace = getenv("T0_W4_TRACE") != nullptr;
+    unsigned long long* d_stamps = nullptr;
+    if (trace) {
+        T0_CUDA(cudaMalloc(&d_stamps, (size_t)grid * 8 * sizeof(unsigned long long)));
+        T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 8 * sizeof(unsigned long long)));
+        p.stamps = d_stamps;
+    }
+    static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kTcThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = rt->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<true>, map_a, map_a, map_a, p);
+    if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
+    if (trace) {
+        std::vector<unsigned long long> h((size_t)grid * 8);
+        T0_CUDA(cudaStreamSynchronize(rt->stream));
+        T0_CUDA(cudaMemcpy(h.data(), d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+        cudaFree(d_stamps);
+        unsigned long long t_min = ~0ull, t_max = 0;
+        double stage = 0, loop = 0, tail = 0;
+        for (uint32_t c = 0; c < grid; ++c) {
+            t_min = std::min(t_min, h[c * 4]); t_max = std::max(t_max, h[c * 4 + 3]);
+            stage += (double)(h[c * 4 + 1] - h[c * 4]); loop += (double)(h[c * 4 + 2] - h[c * 4 + 1]); tail += (double)(h[c * 4 + 3] - h[c * 4 + 2]);
+        }
+        double wf = 0, wa = 0, wc = 0, wm = 0;
+        for (uint32_t c = 0; c < grid; ++c) { wf += (double)h[grid * 4 + c * 4]; wa += (double)h[grid * 4 + c * 4 + 1]; wc += (double)h[grid * 4 + c * 4 + 2]; wm += (double)h[grid * 4 + c * 4 + 3]; }
+        fprintf(stderr, "[w4a16 stream trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: set-up %.2f us, main loop %.2f us, flush+exit %.2f us; "
+                "warp 0 waited (cycles): weights %.0f, A buffer %.0f, accumulator %.0f; UMMA issuer idle %.0f\n",
+                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3, wf / grid, wa / grid, wc / grid, wm / grid);
+    }
+    rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+int t0_w4a16_gemm_prepacked_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count) {
+    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
+    for (size_t i = 0; i < count; ++i) {
+        const t0_w4a16_args& a = args[i];
+        int rc = t0_w4a16_gemm_prepacked(rt, a.a, a.packed, a.y, a.m, a.n, a.k, a.group);
+        if (rc != T0_OK) return rc;
+    }
+    return T0_OK;
 }
 
 }  // extern "C"

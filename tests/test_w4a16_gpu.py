@@ -230,3 +230,87 @@ def test_argument_errors(t0, rt):
         rt.w4a16_gemm(0, b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), 1, 8, 64, 32)
     rt.w4a16_gemm(b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), b.gpu_addr(), 0, 8, 64, 32)        # M = 0: no-op
     assert not rt.is_poisoned()
+
+
+# ----------------------------------------------------------------------------- K2 on the streaming (tile-major) layout
+
+def run_w4a16_prepacked(rt, a, packed, scales, zeros, M, N, K, G, repeats=1):
+    xa, xp, xs, xz = rt.upload(a), rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+    pre = rt.w4_prepack(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G)
+    y = rt.alloc(M * N * 4 + 4096)
+    outs = []
+    for _ in range(repeats):
+        y.write(np.full(M * N + 1024, -9999.0, np.float32))
+        rt.w4a16_gemm_prepacked(xa.gpu_addr(), pre.gpu_addr(), y.gpu_addr(), M, N, K, G)
+        rt.synchronize()
+        outs.append(y.read(M * N * 4, np.float32).reshape(M, N))
+        assert np.all(y.read_bytes(M * N * 4, 4096, np.float32) == -9999.0), "wrote past the output"
+    for b in (xa, xp, xs, xz, pre, y):
+        b.free()
+    return outs if repeats > 1 else outs[0]
+
+
+@pytest.mark.parametrize("K,N,G", [(128, 8, 128), (256, 264, 128), (512, 1000, 256), (4096, 11008, 128), (1024, 256, 1024)])
+def test_prepack_matches_the_oracle_bit_for_bit(t0, oracle, rt, K, N, G):
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=K + N)
+    want = oracle.w4_prepack(packed, scales, zeros, K, N, G)
+    assert t0.lib().t0_w4_prepacked_bytes(K, N, G) == want.size
+    xp, xs, xz = rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+    pre = rt.w4_prepack(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G)
+    rt.synchronize()
+    assert np.array_equal(pre.read(want.size, np.uint8), want)
+    for b in (xp, xs, xz, pre):
+        b.free()
+
+
+def test_prepacked_kernel_dequantises_bit_exactly(t0, oracle, rt):
+    # one-hot activations, sixteen k at a time, read all 128 rows of the dequantised weights of a step back exactly
+    K, G, M = 256, 128, 16
+    N = 16384
+    rng = np.random.default_rng(5)
+    packed = rng.integers(0, 2 ** 32, size=(K // 8, N), dtype=np.uint64).astype(np.uint32)
+    col = np.arange(N, dtype=np.uint32)
+    sbits = np.stack([(0x3A00 + (col % 0x400)).astype(np.uint16) | ((col // 0x400 % 2) << 15).astype(np.uint16),
+                      (0x3B80 + (col % 0x300)).astype(np.uint16)])
+    zeros = rng.integers(0, 2 ** 32, size=(K // G, N // 8), dtype=np.uint64).astype(np.uint32)
+    want = oracle.bf16_to_f32(oracle.dequant_w4_b200(packed, sbits, zeros, K, N, G)).reshape(K, N)
+    for base in range(0, K, 16):
+        a = np.zeros((M, K), np.uint16)
+        for m in range(M):
+            a[m, base + m] = 0x3F80
+        got = run_w4a16_prepacked(rt, a, packed, sbits, zeros, M, N, K, G)
+        assert np.array_equal(got.view(np.uint32) & 0x7FFFFFFF, want[base:base + 16].view(np.uint32) & 0x7FFFFFFF), base
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("K,N,G", [(512, 264, 128), (4096, 96, 128), (1024, 1024, 256), (256, 8, 128), (2048, 3000, 512)])
+def test_prepacked_small_shapes(t0, oracle, rt, M, K, N, G):
+    a = oracle.fill_normal_bf16(M * K, 7 + M)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=M)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    assert_close(run_w4a16_prepacked(rt, a, packed, scales, zeros, M, N, K, G), ref, K)
+
+
+@pytest.mark.parametrize("M", [1, 16])
+@pytest.mark.parametrize("N", [11008, 14336])
+def test_prepacked_baseline_config4_full_size(t0, oracle, rt, M, N):
+    K, G = 4096, 128
+    a = oracle.fill_normal_bf16(M * K, 7 + M)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=N)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    outs = run_w4a16_prepacked(rt, a, packed, scales, zeros, M, N, K, G, repeats=3)   # the first call runs on cold buffers
+    assert_close(outs[0], ref, K)
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+
+
+def test_prepacked_argument_errors(t0, rt):
+    buf = rt.alloc(1 << 20)
+    p = buf.gpu_addr()
+    lib = t0.lib()
+    assert lib.t0_w4_prepacked_bytes(100, 64, 128) == 0
+    assert lib.t0_w4a16_gemm_prepacked(rt._h, p, p, p, 17, 256, 128, 128) == 6        # M beyond the fused kernel
+    assert lib.t0_w4a16_gemm_prepacked(rt._h, p, p, p, 4, 256, 192, 64) == 6          # K, group not multiples of 128
+    assert lib.t0_w4a16_gemm_prepacked(rt._h, p, p, p, 1, 28672, 8192, 128) == 6      # more than one wave of steps
+    assert lib.t0_w4a16_gemm_prepacked(rt._h, p, 0, p, 1, 256, 128, 128) == 1         # null pointer
+    assert not rt.is_poisoned()
+    buf.free()
