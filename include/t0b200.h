@@ -262,6 +262,25 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 
+/* ------------------------------------------------------- f32 framework entries */
+/* Ignis matmul(x[M,K] f32, w[K,N] f32) -> y[M,N] f32 (src/ignis/ops/bf16_matmul.rs:33-59,162-207): operands rounded to
+ * bf16 (nearest even, :371-372) on the device, fp32 accumulate.  Device pointers; no padding, transposing or host round
+ * trips (the reference does all three on the CPU, :356-423).  Argument order (m, k, n) as the reference's helpers. */
+int t0_matmul_f32(t0_runtime* rt, uint64_t x, uint64_t w, uint64_t y, uint32_t m, uint32_t k, uint32_t n);
+/* matmul_with_wt_bf16 (:93-133): the weight already transposed to [N,K] and in bf16 */
+int t0_matmul_f32_with_wt_bf16(t0_runtime* rt, uint64_t x, uint64_t wt_bf16, uint64_t y, uint32_t m, uint32_t k, uint32_t n);
+/* gemm_backward_data (:216-262): dX[M,K] = dY[M,N] * W[K,N]^T;  gemm_backward_weight (:264-312): dW[K,N] = X[M,K]^T * dY[M,N] */
+int t0_matmul_f32_backward_data(t0_runtime* rt, uint64_t dy, uint64_t w, uint64_t dx, uint32_t m, uint32_t k, uint32_t n);
+int t0_matmul_f32_backward_weight(t0_runtime* rt, uint64_t x, uint64_t dy, uint64_t dw, uint32_t m, uint32_t k, uint32_t n);
+/* BlasLib::gemm / gemv for DType::F32 (src/universal/math/mod.rs:24-47; CPU body math/blas.rs:18-100):
+ * C[m,n] = alpha * A[m,k] * B[k,n] + beta * C, row-major with leading dimensions; y = alpha * A[m,n] * x + beta * y.
+ * gemm multiplies on the bf16 tensor path (inputs rounded to bf16, fp32 accumulate: the GEMM tolerance applies, where the
+ * reference's CPU body is exact f32); gemv is f32 throughout.  beta == 0 does not read C / y. */
+int t0_blas_gemm_f32(t0_runtime* rt, uint32_t m, uint32_t n, uint32_t k, float alpha, uint64_t a, uint32_t lda, uint64_t b, uint32_t ldb,
+                     float beta, uint64_t c, uint32_t ldc);
+int t0_blas_gemv_f32(t0_runtime* rt, uint32_t m, uint32_t n, float alpha, uint64_t a, uint32_t lda, uint64_t x, uint32_t incx, float beta,
+                     uint64_t y, uint32_t incy);
+
 /* ------------------------------------------------------- autotuner (a10) */
 typedef struct t0_tuner t0_tuner;   /* GemmTuner  src/t0/auto_gemm.rs:46-55 */
 /* GemmTuner::new() / with_cache_dir(dir) (auto_gemm.rs:59-75).  Default directory: $T0_TUNE_DIR, else

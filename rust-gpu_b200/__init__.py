@@ -578,6 +578,26 @@ class GpuRuntime:
         """``t0_w4a16_gemm_static``: the fused kernel on the library's fixed scratch array; never allocates."""
         _check(lib().t0_w4a16_gemm_static(self._h, a, packed, scales, zeros, y, M, N, K, group))
 
+    def matmul_f32(self, x: int, w: int, y: int, m: int, k: int, n: int) -> None:
+        """Ignis ``matmul`` (src/ignis/ops/bf16_matmul.rs:33-59): y[M,N] = bf16(x[M,K]) * bf16(w[K,N]), f32 in and out."""
+        _check(lib().t0_matmul_f32(self._h, x, w, y, m, k, n))
+
+    def matmul_f32_with_wt_bf16(self, x: int, wt_bf16: int, y: int, m: int, k: int, n: int) -> None:
+        _check(lib().t0_matmul_f32_with_wt_bf16(self._h, x, wt_bf16, y, m, k, n))
+
+    def matmul_f32_backward_data(self, dy: int, w: int, dx: int, m: int, k: int, n: int) -> None:
+        _check(lib().t0_matmul_f32_backward_data(self._h, dy, w, dx, m, k, n))
+
+    def matmul_f32_backward_weight(self, x: int, dy: int, dw: int, m: int, k: int, n: int) -> None:
+        _check(lib().t0_matmul_f32_backward_weight(self._h, x, dy, dw, m, k, n))
+
+    def blas_gemm_f32(self, m: int, n: int, k: int, alpha: float, a: int, lda: int, b: int, ldb: int, beta: float, c: int, ldc: int) -> None:
+        """``BlasLib::gemm`` (src/universal/math/mod.rs:24-35) for f32 operands."""
+        _check(lib().t0_blas_gemm_f32(self._h, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc))
+
+    def blas_gemv_f32(self, m: int, n: int, alpha: float, a: int, lda: int, x: int, incx: int, beta: float, y: int, incy: int) -> None:
+        _check(lib().t0_blas_gemv_f32(self._h, m, n, alpha, a, lda, x, incx, beta, y, incy))
+
     def w4_prepack(self, packed: int, scales: int, zeros: int, K: int, N: int, group: int = 128) -> "GpuBuffer":
         """``t0_w4_prepack``: row layout -> streaming layout, into a new buffer."""
         n = lib().t0_w4_prepacked_bytes(K, N, group)
@@ -852,6 +872,13 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    f32 = C.c_float
+    sig("t0_matmul_f32", i32, vp, u64, u64, u64, u32, u32, u32)
+    sig("t0_matmul_f32_with_wt_bf16", i32, vp, u64, u64, u64, u32, u32, u32)
+    sig("t0_matmul_f32_backward_data", i32, vp, u64, u64, u64, u32, u32, u32)
+    sig("t0_matmul_f32_backward_weight", i32, vp, u64, u64, u64, u32, u32, u32)
+    sig("t0_blas_gemm_f32", i32, vp, u32, u32, u32, f32, u64, u32, u64, u32, f32, u64, u32)
+    sig("t0_blas_gemv_f32", i32, vp, u32, u32, f32, u64, u32, u64, u32, f32, u64, u32)
     sig("t0_w4_prepacked_bytes", sz, u32, u32, u32)
     sig("t0_w4_prepack", i32, vp, u64, u64, u64, u64, u32, u32, u32)
     sig("t0_w4a16_gemm_prepacked", i32, vp, u64, u64, u64, u32, u32, u32, u32)

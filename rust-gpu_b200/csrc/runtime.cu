@@ -282,7 +282,7 @@ void t0_rt_free(t0_runtime* rt) {
     DeviceGuard guard(rt->device);
     cudaStreamSynchronize(rt->stream);
     t0_rt_pool_clear(rt);
-    for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes, &rt->scratch_w4, &rt->scratch_w})
+    for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes, &rt->scratch_w4, &rt->scratch_w, &rt->scratch_cvt_a, &rt->scratch_cvt_b, &rt->scratch_cvt_c})
         if (s->ptr) cudaFree(s->ptr);
     if (rt->d_status) cudaFree(rt->d_status);
     if (rt->d_probe) cudaFree(rt->d_probe);

@@ -52,6 +52,7 @@ struct t0_runtime {
     Scratch scratch_a, scratch_b, scratch_planes;
     Scratch scratch_w4;          // W4A16: slab arrival counters + straddling pieces
     Scratch scratch_w;           // W4A16 general path: dequantised weights
+    Scratch scratch_cvt_a, scratch_cvt_b, scratch_cvt_c;   // f32 entries: bf16 copies of the operands, f32 product before alpha/beta
 };
 
 namespace t0 {
