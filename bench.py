@@ -300,6 +300,7 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--gather", action="store_true", help="sharded workload: also time GEMM + in-place NCCL all-gather of C (reported under \"gather\")")
     ap.add_argument("--row-layout", action="store_true", help="W4A16 workloads: weights in the row layout instead of the streaming layout")
     args = ap.parse_args()
 
@@ -389,6 +390,40 @@ def main():
     flops_per_step = 2.0 * M * N_total * K
     value = flops_per_step * steps / (ms_max * 1e-3) / 1e12
 
+    # optional: the gathered C.  Every rank's GEMM stores straight into slot `rank` of C_g[g][M][N/g]; one in-place
+    # all-gather over NVLink completes it.  NCCL is issued on the runtime's own stream, so the device timer covers both.
+    gather = None
+    if args.gather and sharded and world > 1:
+        c_g = torch.empty((world, M, N), dtype=torch.float32, device="cuda")
+        ext = torch.cuda.ExternalStream(rt.stream())
+        xa, xb, _ = sets[0]
+        slot_ptr = c_g.data_ptr() + rank * M * N * 4
+        g_args = [rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), slot_ptr, M, N, K, **gemm_kw)]
+
+        def gather_step():
+            rt.gemm_batch(g_args)
+            with torch.cuda.stream(ext):
+                dist.all_gather_into_tensor(c_g.view(-1), c_g[rank].reshape(-1))
+
+        for _ in range(warmup):
+            gather_step()
+        barrier()
+        rt.timer_start()
+        for _ in range(steps):
+            gather_step()
+        g_ms = rt.timer_stop()
+        barrier()
+        tg = torch.tensor([g_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tg, op=dist.ReduceOp.MAX)
+        g_ms = float(tg.item())
+        # every rank must now hold every block: compare a sample of a remote block with the owner's copy
+        probe = c_g[(rank + 1) % world, 0, :8].clone()
+        owner = [torch.empty_like(probe) for _ in range(world)]
+        dist.all_gather(owner, c_g[rank, 0, :8].clone())
+        ok = bool(torch.equal(probe, owner[(rank + 1) % world]))
+        gather = {"ms_per_step": g_ms / steps, "value": 2.0 * M * N_total * K * steps / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                  "gathered_bytes_per_rank": M * N * 4 * (world - 1), "layout": "C_g[g][M][N/g]", "remote_block_matches": ok}
+
     # parity spot check on rank 0 (the full parity suite is tests/ -m gpu)
     parity = None
     if rank == 0:
@@ -462,6 +497,8 @@ def main():
                 "clocks": clocks, "gpu_launches": int(launches), "parity": parity}
         if e2e:
             line["e2e"] = e2e
+        if gather:
+            line["gather"] = gather
         if not args.no_cpu and world == 1:
             import oracle
             rows = max(32, min(M, int(M * (2.0 * 4096 ** 3) / (2.0 * M * N_total * K))))
