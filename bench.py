@@ -96,11 +96,11 @@ def run_hbm_workload(args, name):
                 b.free()
         calls = [t0.W4A16Args(xa.gpu_addr(), pre[i % n_sets].gpu_addr(), 0, 0, y.gpu_addr(), M, N, K, G) for i in range(steps)]
         submit = rt.w4a16_gemm_prepacked_batch
-        kernel = "w4a16_tc_kernel<true> (streaming layout)"
+        kernel = "w4a16_frag_kernel (streaming layout, mma.sync fragment order)"
     elif w4:
         calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), y.gpu_addr(), M, N, K, G) for i in range(steps)]
         submit = rt.w4a16_gemm_batch
-        kernel = "w4a16_tc_kernel<false> (row layout)" if M <= 16 else "dequant_w4_b200_kernel + gemm"
+        kernel = "w4a16_tc_kernel (row layout, tcgen05)" if M <= 16 else "dequant_w4_b200_kernel + gemm"
     else:
         cfg = t0.auto_select(M, K, N)
         sk = w.get("split_k", cfg.split())

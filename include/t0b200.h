@@ -340,9 +340,13 @@ typedef struct t0_w4a16_args {
 } t0_w4a16_args;
 int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
 /* Streaming weight layout for the fused kernel (no counterpart in the reference).  The row layout above puts the 16 KiB
- * a CTA needs per step in sixteen 1 KiB pieces 4N bytes apart, which HBM serves at about a quarter of its copy bandwidth;
- * t0_w4_prepack rewrites the three arrays once (weight-load time) into one buffer of t0_w4_prepacked_bytes(K, N, group):
- *   tiles[N/256][K/128][16][256] u32, the eight codes of a word in the order k0 k2 k4 k6 k1 k3 k5 k7,
+ * a CTA needs per step in sixteen 1 KiB pieces 4N bytes apart, which HBM serves at about a quarter of its copy bandwidth,
+ * and leaves the codes in an order no MMA fragment has.  t0_w4_prepack rewrites the three arrays once (weight-load time)
+ * into one buffer of t0_w4_prepacked_bytes(K, N, group) bytes:
+ *   tiles[N/256][K/128][4096] u32: one contiguous 16 KiB tile per (256-column band, 128-deep k step) in mma.sync fragment
+ *     order: word ((w*2 + j)*32 + lane)*4 + e holds, for column tile w (16 columns), k step s = 4j + e (16 k) and lane
+ *     (g = lane/4, t = lane%4), in nibbles c and c+4 (c = 0..3) the codes (k, k+1) of column 16w + g + 8(c&1) at
+ *     k = 16s + 2t + 8(c>>1);
  *   then scales[N/256][K/group][256] bf16, then zero points [N/256][K/group][32] u32 (columns past N are zero).
  * t0_w4a16_gemm_prepacked computes the same y as t0_w4a16_gemm from that buffer (M <= 16, K % 128 == 0, group % 128 == 0,
  * N % 8 == 0, K*N small enough for one wave: at most 20 steps of 128 x 256 per SM); the batch form reads

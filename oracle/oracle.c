@@ -353,10 +353,12 @@ void oracle_w4a16_gemm(const uint16_t* a, const uint32_t* packed, const uint16_t
 }
 
 /* The streaming layout of the B200 W4A16 kernel (this build's own format; no reference counterpart).
- * One buffer: tiles[band][kstep][16][256] u32, then scales_t[band][K/G][256] bf16, then
- * zeros_t[band][K/G][32] u32; band = 256 columns (zero-padded past N), kstep = 128 k.  Inside a word
- * the eight codes of a column sit in the order k0 k2 k4 k6 k1 k3 k5 k7 (nibble i and nibble i+4 are
- * consecutive k).  Offsets of the three parts are returned through off[3]; the result is the size. */
+ * One buffer: tiles[band][kstep][4096] u32, then scales_t[band][K/G][256] bf16, then
+ * zeros_t[band][K/G][32] u32; band = 256 columns (zero-padded past N), kstep = 128 k.  A tile is in
+ * mma.sync fragment order: word index ((w*2 + j)*32 + lane)*4 + e holds, for column tile w (16 columns),
+ * k step s = 4j + e (16 k) and lane (g = lane/4, t = lane%4), in nibbles c and c+4 (c = 0..3) the codes
+ * (k, k+1) of column 16w + g + 8(c&1) at k = 16s + 2t + 8(c>>1).  Offsets of the three parts are
+ * returned through off[3]; the result is the size. */
 size_t oracle_w4_prepacked_layout(uint32_t K, uint32_t N, uint32_t group, size_t off[3]) {
     size_t bands = (N + 255) / 256, ksteps = K / 128, groups = K / group;
     off[0] = 0;
@@ -365,31 +367,46 @@ size_t oracle_w4_prepacked_layout(uint32_t K, uint32_t N, uint32_t group, size_t
     return off[2] + bands * groups * 32 * 4;
 }
 
+static uint32_t w4_code(const uint32_t* packed, uint32_t N, uint32_t k, uint32_t n) {
+    return (packed[(size_t)(k >> 3) * N + n] >> (4 * (k & 7))) & 0xFu;
+}
+
 void oracle_w4_prepack(const uint32_t* packed, const uint16_t* scales, const uint32_t* zeros,
                        uint8_t* out, uint32_t K, uint32_t N, uint32_t group) {
     size_t off[3];
     size_t total = oracle_w4_prepacked_layout(K, N, group, off);
     uint32_t bands = (N + 255) / 256, ksteps = K / 128, groups = K / group, nz = (N + 7) / 8;
-    static const int order[8] = {0, 2, 4, 6, 1, 3, 5, 7};   /* nibble i of the new word holds code order[i] */
     memset(out, 0, total);
     uint32_t* tiles = (uint32_t*)(out + off[0]);
     uint16_t* st = (uint16_t*)(out + off[1]);
     uint32_t* zt = (uint32_t*)(out + off[2]);
-    for (uint32_t b = 0; b < bands; ++b)
+    for (uint32_t b = 0; b < bands; ++b) {
+        for (uint32_t ks = 0; ks < ksteps; ++ks) {
+            uint32_t* tile = tiles + ((size_t)b * ksteps + ks) * 4096;
+            for (uint32_t w = 0; w < 16; ++w)
+                for (uint32_t s = 0; s < 8; ++s)
+                    for (uint32_t lane = 0; lane < 32; ++lane) {
+                        uint32_t g = lane >> 2, t = lane & 3, v = 0;
+                        for (uint32_t c = 0; c < 4; ++c) {
+                            uint32_t n = b * 256 + w * 16 + g + 8 * (c & 1);
+                            uint32_t k = ks * 128 + s * 16 + 2 * t + 8 * (c >> 1);
+                            if (n >= N) continue;
+                            v |= w4_code(packed, N, k, n) << (4 * c);
+                            v |= w4_code(packed, N, k + 1, n) << (4 * (c + 4));
+                        }
+                        tile[((w * 2 + (s >> 2)) * 32 + lane) * 4 + (s & 3)] = v;
+                    }
+        }
         for (uint32_t c = 0; c < 256; ++c) {
             uint32_t n = b * 256 + c;
             if (n >= N) continue;
-            for (uint32_t r = 0; r < K / 8; ++r) {
-                uint32_t w = packed[(size_t)r * N + n], v = 0;
-                for (int i = 0; i < 8; ++i) v |= ((w >> (4 * order[i])) & 0xFu) << (4 * i);
-                tiles[(((size_t)b * ksteps + r / 16) * 16 + r % 16) * 256 + c] = v;
-            }
             for (uint32_t g = 0; g < groups; ++g) {
                 st[((size_t)b * groups + g) * 256 + c] = scales[(size_t)g * N + n];
                 uint32_t z = (zeros[(size_t)g * nz + (n >> 3)] >> (4 * (n & 7))) & 0xFu;
                 zt[((size_t)b * groups + g) * 32 + (c >> 3)] |= z << (4 * (c & 7));
             }
         }
+    }
 }
 
 static uint32_t rd_u32le(const uint8_t* p) {

@@ -360,8 +360,9 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 // 128-column half band.  One UMMA (M 128, N 16, K 16) replaces 32 mma.sync; the k halves of a step accumulate into
 // the same tensor-memory tile, so no cross-warp reduction is left.
 constexpr int kTcWarps = 16;                         // dequant + epilogue warps
-constexpr int kTcIssuers = 4;                        // UMMA issuer warps: issuing one UMMA costs a thread ~120 cycles whatever its size,
-                                                     // so the 16 small UMMAs of a step are spread over four threads
+constexpr int kTcIssuers = 4;                        // UMMA issuer warps.  A 128 x 16 x 16 UMMA with its A tile in tensor memory costs about
+                                                     // 100 cycles whatever its N and however many threads issue (measured); four issuers
+                                                     // shorten the tail of a band a little, no more
 constexpr int kTcThreads = (kTcWarps + 1 + kTcIssuers) * 32;   // + TMA producer warp + UMMA issuer warps
 constexpr int kTcBUnitBytes = 2 * 16 * 128;          // activations of one step: two 64-deep atoms of 16 rows x 128 B
 constexpr int kTcMaxUnits = 20;                      // steps of one CTA whose activations fit beside the ring
@@ -369,37 +370,27 @@ constexpr uint32_t kTcTmemCols = 512;
 constexpr uint32_t kTcACols = 128;                   // A columns per step: 2 half bands x 8 k steps x 8 columns
 constexpr uint32_t kTcABufs = 3;                     // A buffers: the dequant warps may run two steps ahead of the UMMAs
 constexpr uint32_t kTcDBase = kTcABufs * kTcACols;   // then the accumulators: 2 half bands x 4 partial sums x 16 columns
-constexpr uint32_t kTcDParts = 4;                    // k step j accumulates into partial sum j % 4: an UMMA this small is bound by the
-                                                     // latency of its accumulate dependency, so consecutive ones must not share a tile
+constexpr uint32_t kTcDParts = 4;                    // k step j accumulates into partial sum j % 4, so every issuer owns its accumulators
 constexpr uint32_t kTcIdesc = ptx::make_idesc_bf16_f32(128, 16, 0u);
 __device__ __forceinline__ void tc_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kTcWarps * 32) : "memory"); }
 
-// kStream = false: weights in the row layout packed[K/8][N], fetched with 2-D TMA boxes, activations staged by the dequant
-//   warps in the permuted order.
-// kStream = true: weights in the streaming layout (t0_w4_prepack): one 16 KiB bulk copy per step (1 KiB rows 43 KiB apart
-//   reach a quarter of the copy bandwidth, 16 KiB runs most of it), codes already in natural pair order, so the
-//   activations come straight from the caller's matrix through a swizzling tensor map (`map_w` is that map here);
-//   scales and zero points of all the CTA's steps arrive up front in a few bulk copies.
-template <bool kStream>
+// Weights in the row layout packed[K/8][N], fetched with 2-D TMA boxes; activations staged by the dequant warps in the
+// permuted order.
 __global__ void __launch_bounds__(kTcThreads, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
                 const __grid_constant__ CUtensorMap map_z, const W4Params p) {
-    constexpr uint32_t kRingStage = kStream ? kWeightBytes : kStageBytes;
+    constexpr uint32_t kRingStage = kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* b_area = smem;                                            // [a_units][2 atoms][16 rows][128 B], swizzled
     uint8_t* ring = smem + (size_t)p.a_units * kTcBUnitBytes;          // kStages x {16 KiB codes, 512 B scales, 128 B zero points}
-    uint8_t* s_area = ring + kStages * kRingStage;                     // streaming layout: [a_units][256] bf16 scales ...
-    uint8_t* z_area = s_area + (kStream ? (size_t)p.a_units * kScaleBytes : 0);   // ... and [a_units][32] u32 zero points
-    uint64_t* full_bar = (uint64_t*)(z_area + (kStream ? (size_t)p.a_units * kZeroBytes : 0));
+    uint64_t* full_bar = (uint64_t*)(ring + kStages * kRingStage);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* a_ready_bar = empty_bar + kStages;       // [kTcABufs] all 16 warps wrote their part of an A buffer
     uint64_t* a_free_bar = a_ready_bar + kTcABufs;     // [kTcABufs] the UMMAs that read an A buffer are done
     uint64_t* acc_full_bar = a_free_bar + kTcABufs;    // [2] a band piece is accumulated
     uint64_t* acc_empty_bar = acc_full_bar + 2;        // [2] all 16 warps have read an accumulator buffer
-    uint64_t* b_full_bar = acc_empty_bar + 2;          // streaming layout: activations of all steps have landed
-    uint64_t* sz_full_bar = b_full_bar + 1;            // streaming layout: scales and zero points have landed
-    uint32_t* tmem_holder = (uint32_t*)(sz_full_bar + 1);
+    uint32_t* tmem_holder = (uint32_t*)(acc_empty_bar + 2);
     volatile int* abort_flag = (volatile int*)(tmem_holder + 1);
     int* s_last = (int*)(tmem_holder + 2);
 
@@ -423,16 +414,12 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             ptx::mbar_init(ptx::smem_u32(&acc_full_bar[b]), kTcIssuers);
             ptx::mbar_init(ptx::smem_u32(&acc_empty_bar[b]), kTcWarps);
         }
-        ptx::mbar_init(ptx::smem_u32(b_full_bar), 1);
-        ptx::mbar_init(ptx::smem_u32(sz_full_bar), 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
         ptx::tma_prefetch_desc(&map_w);
-        if (!kStream) {
-            ptx::tma_prefetch_desc(&map_s);
-            ptx::tma_prefetch_desc(&map_z);
-        }
+        ptx::tma_prefetch_desc(&map_s);
+        ptx::tma_prefetch_desc(&map_z);
     }
     if (warp == kTcWarps + 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTcTmemCols);
@@ -452,23 +439,6 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
-            if (kStream) {
-                // scales and zero points of every (band, group) the CTA's steps touch: one copy of each per band piece,
-                // into consecutive slots; the barrier's byte count is posted after the copies (it cannot complete before
-                // this thread's arrival)
-                uint32_t left = u1 - u0, slot = 0, bytes = 0, b2 = band, k2 = ks;
-                const uint32_t sb = ptx::smem_u32(sz_full_bar);
-                while (left) {
-                    const uint32_t n_here = min(left, p.ksteps - k2);
-                    const uint32_t g_lo = k2 / p.units_per_group, ng = (k2 + n_here - 1) / p.units_per_group - g_lo + 1;
-                    const size_t row = (size_t)b2 * p.groups + g_lo;
-                    ptx::bulk_load(ptx::smem_u32(s_area + slot * kScaleBytes), p.scales_t + row * kScaleBytes, ng * kScaleBytes, sb);
-                    ptx::bulk_load(ptx::smem_u32(z_area + slot * kZeroBytes), p.zeros_t + row * kZeroBytes, ng * kZeroBytes, sb);
-                    bytes += ng * (kScaleBytes + kZeroBytes);
-                    slot += ng; left -= n_here; k2 = 0; ++b2;
-                }
-                ptx::mbar_arrive_expect_tx(sb, bytes);
-            }
             for (uint32_t u = u0; u < u1; ++u) {
                 if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
                     atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(u & 0xFFFFFF));
@@ -476,16 +446,12 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 }
                 const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
                 uint8_t* dst = ring + stage * kRingStage;
-                if (kStream) {
-                    ptx::mbar_arrive_expect_tx(fb, kWeightBytes);
-                    ptx::bulk_load(ptx::smem_u32(dst), p.tiles + ((size_t)band * p.ksteps + ks) * kWeightBytes, kWeightBytes, fb);
-                } else {
-                    const uint32_t grp = ks / p.units_per_group;
-                    ptx::mbar_arrive_expect_tx(fb, kWeightBytes + kScaleBytes + kZeroBytes);
-                    ptx::tma_load_2d(ptx::smem_u32(dst), &map_w, fb, (int32_t)(band * kBandCols), (int32_t)(ks * (kUnitK / 8)));
-                    ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes), &map_s, fb, (int32_t)(band * kBandCols), (int32_t)grp);
-                    ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes + kScaleBytes), &map_z, fb, (int32_t)(band * (kBandCols / 8)), (int32_t)grp);
-                }
+                const uint32_t grp = ks / p.units_per_group;
+                ptx::mbar_arrive_expect_tx(fb, kWeightBytes + kScaleBytes + kZeroBytes);
+                ptx::tma_load_2d(ptx::smem_u32(dst), &map_w, fb, (int32_t)(band * kBandCols), (int32_t)(ks * (kUnitK / 8)));
+                ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes), &map_s, fb, (int32_t)(band * kBandCols), (int32_t)grp);
+                ptx::tma_load_2d(ptx::smem_u32(dst + kWeightBytes + kScaleBytes), &map_z, fb, (int32_t)(band * (kBandCols / 8)), (int32_t)grp);
+            
                 if (++stage == kStages) { stage = 0; phase ^= 1; }
                 if (++ks == p.ksteps) { ks = 0; ++band; }
             }
@@ -497,21 +463,6 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (lane == 0) {
             uint32_t ks = ks_first, piece = 0;
             bool piece_start = true;
-            if (kStream) {
-                // activations of every step, as they lie in the caller's [M][K] matrix: two 64-deep swizzled atoms of 16
-                // rows per step (rows >= M are out of bounds and read as zero)
-                const uint32_t bb = ptx::smem_u32(b_full_bar);
-                if (issuer == 0) {
-                    for (uint32_t i = 0; i < u1 - u0; ++i) {
-                        const uint32_t kks = (ks_first + i) % p.ksteps;
-                        for (uint32_t atom = 0; atom < 2; ++atom)
-                            ptx::tma_load_3d(ptx::smem_u32(b_area + (size_t)i * kTcBUnitBytes + atom * 2048), &map_w, bb,
-                                             (int32_t)(kks * kUnitK + atom * 64), 0, 0);
-                    }
-                    ptx::mbar_arrive_expect_tx(bb, (u1 - u0) * kTcBUnitBytes);
-                }
-                if (!ptx::mbar_wait(bb, 0, abort_flag)) atomicCAS(p.status, 0, kStatusMmaTimeout | 0xC00000);
-            }
             for (uint32_t u = u0; u < u1; ++u) {
                 const uint32_t i = u - u0, ab = i % kTcABufs, a_round = i / kTcABufs;
                 if (piece_start) {
@@ -559,7 +510,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         // Activations -> shared memory as the B operand: 16 rows (m) x 64 k per 128-byte-swizzled atom.  Within every
         // group of eight k the order becomes 0,4,1,5,2,6,3,7: the pair (code i, code i+4) one mask pulls out of a
         // packed word is then one 32-bit column of the A tile.
-        for (uint32_t i = tid; !kStream && i < n_units * 256; i += kTcWarps * 32) {
+        for (uint32_t i = tid; i < n_units * 256; i += kTcWarps * 32) {
             const uint32_t unit = i >> 8, m = (i >> 4) & 15, g8 = i & 15;
             const uint32_t kks = (ks_first + unit) % p.ksteps;
             uint4 v = make_uint4(0, 0, 0, 0);
@@ -571,10 +522,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             o.w = __byte_perm(v.y, v.w, 0x7632);   // k3 k7
             *(uint4*)(b_area + (size_t)unit * kTcBUnitBytes + (g8 >> 3) * 2048 + m * 128 + (((g8 & 7) ^ (m & 7)) << 4)) = o;
         }
-        if (!kStream) {
-            ptx::fence_proxy_async_smem();        // the UMMAs read these bytes through the async proxy
-            tc_consumer_sync();
-        }
+        ptx::fence_proxy_async_smem();            // the UMMAs read these bytes through the async proxy
+        tc_consumer_sync();
         stamp(1);
 
         uint32_t mask, magic;
@@ -584,11 +533,6 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         long long w_full = 0, w_afree = 0, w_acc = 0, t_mark = 0;   // trace only: cycles this warp waited on each barrier
         const bool tracing = p.stamps != nullptr;
         bool ok = true;    // false after a wait expired: the warp keeps walking (barriers stay matched) but does no work
-        uint32_t sz_slot = 0, in_group = ks_first % p.units_per_group;   // streaming layout: slot of the current (band, group)
-        if (kStream && !ptx::mbar_wait(ptx::smem_u32(sz_full_bar), 0, abort_flag)) {
-            if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xC00000);
-            ok = false;
-        }
         const uint32_t w_off = (h * 8) * (kBandCols * 4) + n_local * 4;
         const uint32_t s_off = kWeightBytes + n_local * 2;
         const uint32_t z_off = kWeightBytes + kScaleBytes + (n_local >> 3) * 4;
@@ -609,13 +553,9 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                 for (int r = 0; r < 8; ++r) words[r] = *(const uint32_t*)(st + w_off + r * (kBandCols * 4));
                 uint32_t s, z;
-                if (kStream) {
-                    s = *(const uint16_t*)(s_area + sz_slot * kScaleBytes + n_local * 2);
-                    z = (*(const uint32_t*)(z_area + sz_slot * kZeroBytes + (n_local >> 3) * 4) >> z_shift) & 0xFu;
-                } else {
-                    s = *(const uint16_t*)(st + s_off);
-                    z = (*(const uint32_t*)(st + z_off) >> z_shift) & 0xFu;
-                }
+                s = *(const uint16_t*)(st + s_off);
+                z = (*(const uint32_t*)(st + z_off) >> z_shift) & 0xFu;
+            
                 zz = z * 0x00010001u + 0x43004300u;     // bf16x2 (128+z, 128+z)
                 ss = s * 0x00010001u;                    // (s, s)
             }
@@ -739,8 +679,6 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     tc_consumer_sync();
                 }
             }
-            // next step: a new slot when the group changes or the band ends
-            if (++in_group == p.units_per_group || ks + 1 == p.ksteps) { in_group = 0; ++sz_slot; }
             if (++ks == p.ksteps) { ks = 0; ++band; }
         }
         if (tracing && tid == 0) { p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 0] = w_full; p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 1] = w_afree; p.stamps[gridDim.x * 4 + blockIdx.x * 4 + 2] = w_acc; }
@@ -755,6 +693,263 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTcTmemCols);
     }
+}
+
+// ------------------------------------------------------------------ K2, fragment-ordered streaming form
+//
+// The kernel `bench.py` measures.  Weights come in the streaming layout of t0_w4_prepack: per (256-column band, 128-deep
+// k step) one contiguous 16 KiB tile whose words are already in mma.sync fragment order, so a lane reads its eight words
+// of a step with two LDS.128 and each word IS the A fragment (16 weight columns x 16 k) of one m16n8k16 after dequantising
+// (nibble c / c+4 of a word -> register a_c).  The activations are the 8-column B operand (two column groups when M > 8).
+// A stand-alone probe of this inner loop (7 integer + 8 bf16x2 operations + 1 MMA per word) runs at 477 cycles per step
+// per SM, under the 700 cycles HBM needs to deliver a step, which neither the tensor-memory form (about 100 cycles per
+// small UMMA, 16 per step) nor the first form (activations as the 16-row operand: twice the MMAs) can do.
+constexpr int kFrWarps = 16;                         // consumer warps: warp w owns columns 16w .. 16w+15 of the band, all k
+constexpr int kFrThreads = (kFrWarps + 1) * 32;      // + the TMA producer warp
+constexpr int kFrMaxUnits = 20;                      // steps of one CTA whose activations fit beside the ring
+constexpr int kFrAUnitBytes = 2048;                  // activations of one step and one group of eight rows, in fragment order
+__device__ __forceinline__ void fr_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kFrWarps * 32) : "memory"); }
+
+template <int kMGroups>    // 1: M <= 8, 2: M <= 16
+__global__ void __launch_bounds__(kFrThreads, 1)
+w4a16_frag_kernel(const W4Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+    uint8_t* ring = smem;                                              // kStages x 16 KiB tiles
+    uint8_t* s_area = ring + kStages * kWeightBytes;                   // [a_units][256] bf16 scales ...
+    uint8_t* z_area = s_area + (size_t)p.a_units * kScaleBytes;        // ... and [a_units][32] u32 zero points
+    uint8_t* a_area = z_area + (size_t)p.a_units * kZeroBytes;         // [a_units][kMGroups][2][2][32] uint4 B fragments
+    uint64_t* full_bar = (uint64_t*)(a_area + (size_t)p.a_units * kMGroups * kFrAUnitBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* sz_full_bar = empty_bar + kStages;
+    volatile int* abort_flag = (volatile int*)(sz_full_bar + 1);
+    int* s_last = (int*)(abort_flag + 1);
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t u0 = range_begin(blockIdx.x, gridDim.x, p.total_units);
+    const uint32_t u1 = range_begin(blockIdx.x + 1, gridDim.x, p.total_units);
+    if (u0 >= u1) return;
+    auto stamp = [&](int i) {
+        if (p.stamps && tid == 0) { unsigned long long t_ns; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns)); p.stamps[blockIdx.x * 4 + i] = t_ns; }
+    };
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), kFrWarps);
+        }
+        ptx::mbar_init(ptx::smem_u32(sz_full_bar), 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    __syncthreads();
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();      // global memory is touched only after the previous grid in the stream is done
+    stamp(0);
+    const uint32_t band_first = u0 / p.ksteps;
+    const uint32_t ks_first = u0 - band_first * p.ksteps;
+
+    if (warp == kFrWarps) {
+        // ------------------------------------------------------------ producer: bulk copies
+        if (lane == 0) {
+            uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
+            {
+                // scales and zero points of every (band, group) the CTA's steps touch, into consecutive slots
+                uint32_t left = u1 - u0, slot = 0, bytes = 0, b2 = band, k2 = ks;
+                const uint32_t sb = ptx::smem_u32(sz_full_bar);
+                while (left) {
+                    const uint32_t n_here = min(left, p.ksteps - k2);
+                    const uint32_t g_lo = k2 / p.units_per_group, ng = (k2 + n_here - 1) / p.units_per_group - g_lo + 1;
+                    const size_t row = (size_t)b2 * p.groups + g_lo;
+                    ptx::bulk_load(ptx::smem_u32(s_area + slot * kScaleBytes), p.scales_t + row * kScaleBytes, ng * kScaleBytes, sb);
+                    ptx::bulk_load(ptx::smem_u32(z_area + slot * kZeroBytes), p.zeros_t + row * kZeroBytes, ng * kZeroBytes, sb);
+                    bytes += ng * (kScaleBytes + kZeroBytes);
+                    slot += ng; left -= n_here; k2 = 0; ++b2;
+                }
+                ptx::mbar_arrive_expect_tx(sb, bytes);
+            }
+            for (uint32_t u = u0; u < u1; ++u) {
+                if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                    atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(u & 0xFFFFFF));
+                    break;
+                }
+                // The consumers read the stage through the generic proxy (their reads are ordered before this point by
+                // their release-arrive and the acquire-wait above); the copy overwrites it through the async proxy, and
+                // this fence orders the two.  Without a proxy fence, launches with cold TLBs consumed sectors of the
+                // step loaded into the same stage eight steps later.  One fence here instead of one per consumer
+                // thread: the per-thread fence cost more than the dequantisation itself.
+                ptx::fence_proxy_async_smem();
+                const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+                ptx::mbar_arrive_expect_tx(fb, kWeightBytes);
+                ptx::bulk_load(ptx::smem_u32(ring + stage * kWeightBytes), p.tiles + ((size_t)band * p.ksteps + ks) * kWeightBytes, kWeightBytes, fb);
+                if (++stage == kStages) { stage = 0; phase ^= 1; }
+                if (++ks == p.ksteps) { ks = 0; ++band; }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------- consumers (16 warps)
+    const uint32_t g = lane >> 2, t = lane & 3;
+    const uint32_t n_units = u1 - u0;
+
+    // Activations -> B fragments: for step u, row group mg, half j, pair pr, lane (g, t) one uint4
+    // {b0(s), b1(s), b0(s+1), b1(s+1)}, s = 4j + 2pr, b0(s) = a[m][k0 + 16s + 2t .. +1], b1(s) = a[m][k0 + 16s + 2t + 8 .. +9], m = 8mg + g.
+    for (uint32_t i = tid; i < n_units * kMGroups * 128; i += kFrWarps * 32) {
+        const uint32_t ln = i & 31, pr = (i >> 5) & 1, j = (i >> 6) & 1, mg = kMGroups == 2 ? (i >> 7) & 1 : 0, unit = i / (128 * kMGroups);
+        const uint32_t m = mg * 8 + (ln >> 2), tt = ln & 3;
+        const uint32_t kks = (ks_first + unit) % p.ksteps;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (m < p.M) {
+            const uint32_t* row = (const uint32_t*)(p.a + (size_t)m * p.K + kks * kUnitK + (4 * j + 2 * pr) * 16 + 2 * tt);   // 4-byte aligned
+            v.x = __ldg(row); v.y = __ldg(row + 4); v.z = __ldg(row + 8); v.w = __ldg(row + 12);
+        }
+        *(uint4*)(a_area + ((((size_t)unit * kMGroups + mg) * 2 + j) * 2 + pr) * 512 + ln * 16) = v;
+    }
+    fr_consumer_sync();
+    stamp(1);
+
+    // four accumulator sets, one per k step modulo 4: consecutive MMAs must not wait for each other's result
+    constexpr int kAccSets = 4;
+    float acc[kMGroups][kAccSets][4];
+#pragma unroll
+    for (int mg = 0; mg < kMGroups; ++mg)
+#pragma unroll
+        for (int a = 0; a < kAccSets; ++a)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[mg][a][j] = 0.0f;
+    uint32_t mask, magic;
+    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
+    asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
+    uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
+    uint32_t sz_slot = 0, in_group = ks_first % p.units_per_group;
+    bool ok = true;    // false after a wait expired: the warp keeps walking (barriers stay matched) but does no work
+    if (!ptx::mbar_wait(ptx::smem_u32(sz_full_bar), 0, abort_flag)) {
+        if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xC00000);
+        ok = false;
+    }
+    const uint32_t col0 = warp * 16 + g;                     // this lane's two columns within the band: col0 and col0 + 8
+    const uint32_t w_off = warp * 1024 + lane * 16;           // [w][j][lane] uint4
+    const uint8_t* a_frag = a_area + lane * 16;
+
+    long long w_full = 0;      // trace only: cycles this warp waited for weights
+    for (uint32_t u = u0; u < u1; ++u) {
+        const long long t_mark = p.stamps ? clock64() : 0;
+        if (ok && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+            if (lane == 0) atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(u & 0xFFFFFF));
+            ok = false;
+        }
+        if (p.stamps) w_full += clock64() - t_mark;
+        if (ok) {
+            const uint8_t* st = ring + stage * kWeightBytes;
+            const uint4 q0 = *(const uint4*)(st + w_off);
+            const uint4 q1 = *(const uint4*)(st + w_off + 512);
+            // scale and zero point of the lane's two columns for this step's group
+            const uint32_t s0 = *(const uint16_t*)(s_area + sz_slot * kScaleBytes + col0 * 2);
+            const uint32_t s1 = *(const uint16_t*)(s_area + sz_slot * kScaleBytes + (col0 + 8) * 2);
+            const uint32_t zw = *(const uint32_t*)(z_area + sz_slot * kZeroBytes + (col0 >> 3) * 4);          // columns 8(col0/8) .. +7
+            const uint32_t zw8 = *(const uint32_t*)(z_area + sz_slot * kZeroBytes + ((col0 >> 3) + 1) * 4);
+            const uint32_t zsh = (col0 & 7) * 4;
+            const uint32_t zz0 = ((zw >> zsh) & 0xFu) * 0x00010001u + 0x43004300u, zz1 = ((zw8 >> zsh) & 0xFu) * 0x00010001u + 0x43004300u;
+            const uint32_t ss0 = s0 * 0x00010001u, ss1 = s1 * 0x00010001u;
+            const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            const uint8_t* af = a_frag + (size_t)(u - u0) * kMGroups * kFrAUnitBytes;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+#pragma unroll
+                for (int pr = 0; pr < 2; ++pr) {
+                    uint4 bf[kMGroups];
+#pragma unroll
+                    for (int mg = 0; mg < kMGroups; ++mg) bf[mg] = *(const uint4*)(af + ((mg * 2 + j) * 2 + pr) * 512);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const uint32_t wd = words[j * 4 + pr * 2 + e];
+                        const uint32_t a0 = bf16x2_mul(bf16x2_sub(and_or(wd, mask, magic), zz0), ss0);
+                        const uint32_t a1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz1), ss1);
+                        const uint32_t a2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz0), ss0);
+                        const uint32_t a3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz1), ss1);
+#pragma unroll
+                        for (int mg = 0; mg < kMGroups; ++mg)
+                            mma_bf16_16816(acc[mg][pr * 2 + e], a0, a1, a2, a3, e ? bf[mg].z : bf[mg].x, e ? bf[mg].w : bf[mg].y);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&empty_bar[stage]));          // this warp has read the stage
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+
+        const bool band_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
+        if (u + 1 == u1) stamp(2);
+        if (band_ends) {
+            const uint32_t first_unit = band * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
+            const bool whole = first_unit >= u0 && last_unit <= u1;
+            const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
+            const uint32_t c_last = owner_of(last_unit - 1, gridDim.x, p.total_units);
+            const uint32_t slot = (first_unit <= u0) ? 0u : 1u;   // the piece of the band holding this CTA's first unit is slot 0
+            float* piece = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPieceFloats;
+            // accumulator fragment: c0,c1 = (column col0, rows 2t, 2t+1), c2,c3 = (column col0 + 8, same rows)
+#pragma unroll
+            for (int mg = 0; mg < kMGroups; ++mg) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t m = mg * 8 + 2 * t + (j & 1), col = col0 + (j >> 1) * 8;
+                    const uint32_t ncol = band * kBandCols + col;
+                    const float v = (acc[mg][0][j] + acc[mg][1][j]) + (acc[mg][2][j] + acc[mg][3][j]);
+                    if (m < p.M) {
+                        if (!whole) piece[m * kBandCols + col] = v;
+                        else if (ncol < p.N) p.y[(size_t)m * p.N + ncol] = v;
+                    }
+#pragma unroll
+                    for (int a = 0; a < kAccSets; ++a) acc[mg][a][j] = 0.0f;
+                }
+            }
+            if (!whole) {
+                fr_consumer_sync();                    // every thread's part of the piece is written ...
+                if (tid == 0) {
+                    __threadfence();                   // ... and made visible before this CTA is counted
+                    *s_last = (atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first)) ? 1 : 0;
+                    if (*s_last) __threadfence();
+                }
+                fr_consumer_sync();
+                if (*s_last) {
+                    // last to arrive: add the pieces in k order (CTA order) and store; nobody waits for anybody.
+                    // Only the first contributor can hold this band in slot 1 (its range began in the band before).
+                    const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
+                    constexpr int kPer = kPieceFloats / (kFrWarps * 32);   // 8 outputs per thread when M = 16
+                    float total[kPer];
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
+                    for (uint32_t c = c_first; c <= c_last; ++c) {
+                        const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
+                        float v[kPer];
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j) {
+                            const uint32_t idx = tid + j * (kFrWarps * 32);
+                            v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < kPer; ++j) total[j] += v[j];
+                    }
+#pragma unroll
+                    for (int j = 0; j < kPer; ++j) {
+                        const uint32_t idx = tid + j * (kFrWarps * 32);
+                        if (idx < p.M * kBandCols) {
+                            const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
+                            const uint32_t nc = band * kBandCols + col;
+                            if (nc < p.N) p.y[(size_t)row * p.N + nc] = total[j];
+                        }
+                    }
+                    if (tid == 0) p.counters[band] = 0;   // ready for the next call
+                }
+                fr_consumer_sync();
+            }
+        }
+        if (++in_group == p.units_per_group || ks + 1 == p.ksteps) { in_group = 0; ++sz_slot; }
+        if (++ks == p.ksteps) { ks = 0; ++band; }
+    }
+    if (p.stamps && tid == 0) p.stamps[gridDim.x * 4 + blockIdx.x * 4] = (unsigned long long)w_full;
+    stamp(3);
 }
 
 // ------------------------------------------------------------------ K3: stand-alone dequantisation
@@ -885,7 +1080,7 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
         T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)(1024 + (size_t)kTcMaxUnits * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256)));
         attr_set[rt->device] = true;
     }
@@ -894,7 +1089,7 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
     cfg.blockDim = dim3(use_tc ? kTcThreads : kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = rt->stream;
-    cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<false>, map_w, map_s, map_z, p)
+    cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel, map_w, map_s, map_z, p)
                             : cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
     if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     rt->launches.fetch_add(1);
@@ -997,7 +1192,7 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
         T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)(1024 + (size_t)kTcMaxUnits * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256)));
         attr_set[rt->device] = true;
     }
@@ -1023,7 +1218,7 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = use_pdl ? 1 : 0;
-        cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<false>, map_w, map_s, map_z, p)
+        cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel, map_w, map_s, map_z, p)
                                 : cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
         if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     }
@@ -1129,7 +1324,7 @@ PrepackLayout prepack_layout(uint32_t K, uint32_t N, uint32_t group) {
     return L;
 }
 
-// Row layout -> streaming layout.  One thread per output element: a tile word (codes re-ordered k0 k2 k4 k6 k1 k3 k5 k7),
+// Row layout -> streaming layout.  One thread per output element: a tile word (eight codes in mma.sync fragment order),
 // a scale, or a word of eight zero points.  Columns past N are written as zero.
 __global__ void w4_prepack_kernel(const uint32_t* __restrict__ packed, const uint16_t* __restrict__ scales, const uint32_t* __restrict__ zeros,
                                   uint8_t* __restrict__ out, uint32_t K, uint32_t N, uint32_t nz, PrepackLayout L) {
@@ -1139,16 +1334,22 @@ __global__ void w4_prepack_kernel(const uint32_t* __restrict__ packed, const uin
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words + n_scales + n_zwords; i += stride) {
         if (i < n_words) {
-            const uint32_t c = (uint32_t)(i % kBandCols), r = (uint32_t)((i / kBandCols) % 16);
-            const uint64_t tile = i / (16 * kBandCols);
+            // word (tile, w, j, lane, e) of the fragment order: k step s = 4j + e of column tile w, lane (g, t);
+            // nibble c / c+4 = codes (k, k+1) of column n = 16w + g + 8(c & 1) at k = 16s + 2t + 8(c >> 1)
+            const uint32_t e = (uint32_t)(i & 3), ln = (uint32_t)((i >> 2) & 31), j = (uint32_t)((i >> 7) & 1), w = (uint32_t)((i >> 8) & 15);
+            const uint64_t tile = i >> 12;
             const uint32_t ks = (uint32_t)(tile % L.ksteps), band = (uint32_t)(tile / L.ksteps);
-            const uint32_t n = band * kBandCols + c;
+            const uint32_t g = ln >> 2, t = ln & 3, sstep = 4 * j + e;
             uint32_t v = 0;
-            if (n < N) {
-                const uint32_t w = packed[(size_t)(ks * 16 + r) * N + n];
-                // nibble i of the new word: code 2i for i < 4, code 2(i-4)+1 above
-                v = (w & 0xFu) | ((w >> 4) & 0xF0u) | ((w >> 8) & 0xF00u) | ((w >> 12) & 0xF000u) |
-                    ((w << 12) & 0xF0000u) | ((w << 8) & 0xF00000u) | ((w << 4) & 0xF000000u) | (w & 0xF0000000u);
+#pragma unroll
+            for (uint32_t c = 0; c < 4; ++c) {
+                const uint32_t n = band * kBandCols + w * 16 + g + 8 * (c & 1);
+                const uint32_t k = ks * kUnitK + sstep * 16 + 2 * t + 8 * (c >> 1);
+                if (n < N) {
+                    const uint32_t src = packed[(size_t)(k >> 3) * N + n] >> (4 * (k & 7));
+                    v |= (src & 0xFu) << (4 * c);
+                    v |= ((src >> 4) & 0xFu) << (4 * (c + 4));
+                }
             }
             ((uint32_t*)(out + L.off_tiles))[i] = v;
         } else if (i < n_words + n_scales) {
@@ -1213,8 +1414,8 @@ int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint
     // enough CTAs that the activations of one CTA's steps fit in shared memory, at most one per SM
     const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
     const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
-    if (units_per_cta > (uint32_t)kTcMaxUnits)
-        return fail(T0_ERR_UNSUPPORTED, "K*N too large for one wave: %u steps per CTA, at most %d", units_per_cta, kTcMaxUnits);
+    if (units_per_cta > (uint32_t)kFrMaxUnits)
+        return fail(T0_ERR_UNSUPPORTED, "K*N too large for one wave: %u steps per CTA, at most %d", units_per_cta, kFrMaxUnits);
     const size_t need = kCounterRegion + (size_t)grid * 2 * kPieceFloats * sizeof(float);
     if (need > rt->scratch_w4.size) {
         rc = ensure_scratch(rt, rt->scratch_w4, need);
@@ -1236,14 +1437,15 @@ int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint
     p.scales_t = (const uint8_t*)prepacked + L.off_scales;
     p.zeros_t = (const uint8_t*)prepacked + L.off_zeros;
     p.groups = L.groups;
-    const size_t smem = 1024 + (size_t)units_per_cta * (kTcBUnitBytes + kScaleBytes + kZeroBytes) + (size_t)kStages * kWeightBytes + 256;
-    CUtensorMap map_a;
-    rc = gemm::make_map_kmajor(&map_a, (const void*)a, M, K, K, 1, 16);
-    if (rc != T0_OK) return rc;
+    const uint32_t m_groups = M <= 8 ? 1 : 2;
+    auto smem_for = [](uint32_t units, uint32_t mg) {
+        return (size_t)128 + (size_t)kStages * kWeightBytes + (size_t)units * (kScaleBytes + kZeroBytes + mg * kFrAUnitBytes) + 256;
+    };
+    const size_t smem = smem_for(units_per_cta, m_groups);
     static bool attr_set[64] = {};
     if (rt->device < 64 && !attr_set[rt->device]) {
-        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)(1024 + (size_t)kTcMaxUnits * (kTcBUnitBytes + kScaleBytes + kZeroBytes) + (size_t)kStages * kWeightBytes + 256)));
+        T0_CUDA(cudaFuncSetAttribute(w4a16_frag_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_for(kFrMaxUnits, 1)));
+        T0_CUDA(cudaFuncSetAttribute(w4a16_frag_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_for(kFrMaxUnits, 2)));
         attr_set[rt->device] = true;
     }
     static const bool trace = getenv("T0_W4_TRACE") != nullptr;
@@ -1256,7 +1458,7 @@ int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint
     static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kTcThreads, 1, 1);
+    cfg.blockDim = dim3(kFrThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = rt->stream;
     cudaLaunchAttribute attr[1];
@@ -1264,7 +1466,7 @@ int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = use_pdl ? 1 : 0;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<true>, map_a, map_a, map_a, p);
+    cudaError_t le = m_groups == 1 ? cudaLaunchKernelEx(&cfg, w4a16_frag_kernel<1>, p) : cudaLaunchKernelEx(&cfg, w4a16_frag_kernel<2>, p);
     if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     if (trace) {
         std::vector<unsigned long long> h((size_t)grid * 8);
