@@ -53,7 +53,9 @@ static double predict_us(const B200Limits& hw, uint32_t m, uint32_t n, uint32_t 
     // a partially filled machine cannot pull full bandwidth: scale by the fraction of SMs busy
     const double fill = std::min(1.0, tiles * (pair ? 2.0 : 1.0) / hw.n_sms);
     // split-K runs a second, serialised kernel: it reads sk planes and writes y
-    const double reduce_us = sk > 1 ? hw.launch_us + (sk + 1.0) * 4.0 * (double)m * n / (hw.hbm_gbs * 1e3) : 0.0;
+    // (a kernel that follows another in the same stream costs about 3 us of launch gap, measured; hw.launch_us is the
+    // cost of the first)
+    const double reduce_us = sk > 1 ? 3.0 + (sk + 1.0) * 4.0 * (double)m * n / (hw.hbm_gbs * 1e3) : 0.0;
     return std::max(tensor_us, mem_us / std::max(fill, 0.05)) + hw.launch_us + reduce_us;
 }
 

@@ -136,7 +136,9 @@ def test_auto_select_sizes(t0):
     assert c.tile_m >= 64 and c.tile_n >= 128
     c = t0.auto_select(128, 4096, 4096)
     assert 128 % c.tile_m == 0
-    assert c.tile_n <= 64            # a skinny, bandwidth-bound shape wants many CTAs
+    # a skinny, bandwidth-bound shape wants many CTAs: narrow tiles or, as measured best on B200 (18.8 us against 23.1),
+    # 128-wide tiles with the contraction split four ways
+    assert c.tile_n <= 64 or c.split() >= 2
     # every selected tile is one the sm_100a kernel implements
     for (m, k, n) in [(4096, 4096, 4096), (2048, 2048, 2048), (64, 16384, 4096), (1, 4096, 11008)]:
         c = t0.auto_select(m, k, n)
