@@ -830,16 +830,17 @@ w4a16_frag_kernel(const W4Params p) {
     }
     const uint32_t col0 = warp * 16 + g;                     // this lane's two columns within the band: col0 and col0 + 8
     const uint32_t w_off = warp * 1024 + lane * 16;           // [w][j][lane] uint4
-    const uint8_t* a_frag = a_area + lane * 16;
 
-    long long w_full = 0;      // trace only: cycles this warp waited for weights
-    for (uint32_t u = u0; u < u1; ++u) {
-        const long long t_mark = p.stamps ? clock64() : 0;
+    // walked piece by piece (the steps of one band this CTA owns), so the inner loop carries no band logic
+    const uint8_t* af = a_area + lane * 16;                  // B fragments of the current step
+    uint32_t u = u0;
+    while (u < u1) {
+      const uint32_t piece_end = min(u1, u + (p.ksteps - ks));
+      for (; u < piece_end; ++u) {
         if (ok && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
             if (lane == 0) atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(u & 0xFFFFFF));
             ok = false;
         }
-        if (p.stamps) w_full += clock64() - t_mark;
         if (ok) {
             const uint8_t* st = ring + stage * kWeightBytes;
             const uint4 q0 = *(const uint4*)(st + w_off);
@@ -853,7 +854,6 @@ w4a16_frag_kernel(const W4Params p) {
             const uint32_t zz0 = ((zw >> zsh) & 0xFu) * 0x00010001u + 0x43004300u, zz1 = ((zw8 >> zsh) & 0xFu) * 0x00010001u + 0x43004300u;
             const uint32_t ss0 = s0 * 0x00010001u, ss1 = s1 * 0x00010001u;
             const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-            const uint8_t* af = a_frag + (size_t)(u - u0) * kMGroups * kFrAUnitBytes;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
 #pragma unroll
@@ -878,10 +878,11 @@ w4a16_frag_kernel(const W4Params p) {
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&empty_bar[stage]));          // this warp has read the stage
         }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
-
-        const bool band_ends = (ks + 1 == p.ksteps) || (u + 1 == u1);
-        if (u + 1 == u1) stamp(2);
-        if (band_ends) {
+        af += kMGroups * kFrAUnitBytes;
+        if (++in_group == p.units_per_group) { in_group = 0; ++sz_slot; }
+      }
+      if (u == u1) stamp(2);
+      {
             const uint32_t first_unit = band * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
             const bool whole = first_unit >= u0 && last_unit <= u1;
             const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
@@ -945,10 +946,9 @@ w4a16_frag_kernel(const W4Params p) {
                 fr_consumer_sync();
             }
         }
-        if (++in_group == p.units_per_group || ks + 1 == p.ksteps) { in_group = 0; ++sz_slot; }
-        if (++ks == p.ksteps) { ks = 0; ++band; }
+      ks = 0;          // a further piece starts a new band
+      ++band;
     }
-    if (p.stamps && tid == 0) p.stamps[gridDim.x * 4 + blockIdx.x * 4] = (unsigned long long)w_full;
     stamp(3);
 }
 
@@ -981,27 +981,61 @@ __global__ void dequant_int4_ref_kernel(const uint8_t* __restrict__ packed, cons
     }
 }
 
-// B200 layout -> bf16 [K][N]: one thread per (k group of 8, 4 columns); writes 8 rows of 8 bytes.
+// B200 layout -> bf16 [K][N]: one thread per (k group of 8, 8 columns): reads eight packed words (32 bytes), writes eight
+// rows of 16 bytes, so a warp stores 512 contiguous bytes per row.  Ragged N (not a multiple of 8) takes the scalar tail.
 __global__ void dequant_w4_b200_kernel(const uint32_t* __restrict__ packed, const uint16_t* __restrict__ scales,
                                        const uint32_t* __restrict__ zeros, uint16_t* __restrict__ out, uint32_t K, uint32_t N,
                                        uint32_t group, uint32_t nz) {
-    const uint32_t n4 = (N + 3) / 4;
-    const uint64_t total = (uint64_t)(K / 8) * n4;
+    const uint32_t n8 = (N + 7) / 8;
+    const uint64_t total = (uint64_t)(K / 8) * n8;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const bool vec = (N % 8 == 0) && (((uintptr_t)packed & 15) == 0) && (((uintptr_t)scales & 15) == 0) && (((uintptr_t)out & 15) == 0);
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const uint32_t kg = (uint32_t)(i / n4), col = (uint32_t)(i % n4) * 4;
+        const uint32_t kg = (uint32_t)(i / n8), col = (uint32_t)(i % n8) * 8;
         const uint32_t grp = (kg * 8) / group;
-        for (uint32_t c = 0; c < 4 && col + c < N; ++c) {
-            const uint32_t n = col + c;
-            const uint32_t word = packed[(size_t)kg * N + n];
-            const int32_t z = (int32_t)((zeros[(size_t)grp * nz + (n >> 3)] >> (4 * (n & 7))) & 0xFu);
-            const float s = __uint_as_float((uint32_t)scales[(size_t)grp * N + n] << 16);
+        const uint32_t zword = zeros[(size_t)grp * nz + (col >> 3)];        // the zero points of these eight columns
+        uint32_t words[8];
+        uint16_t sbits[8];
+        if (vec) {
+            const uint4 w0 = __ldcs((const uint4*)(packed + (size_t)kg * N + col)), w1 = __ldcs((const uint4*)(packed + (size_t)kg * N + col + 4));
+            words[0] = w0.x; words[1] = w0.y; words[2] = w0.z; words[3] = w0.w; words[4] = w1.x; words[5] = w1.y; words[6] = w1.z; words[7] = w1.w;
+            const uint4 sv = __ldg((const uint4*)(scales + (size_t)grp * N + col));
+            sbits[0] = (uint16_t)sv.x; sbits[1] = (uint16_t)(sv.x >> 16); sbits[2] = (uint16_t)sv.y; sbits[3] = (uint16_t)(sv.y >> 16);
+            sbits[4] = (uint16_t)sv.z; sbits[5] = (uint16_t)(sv.z >> 16); sbits[6] = (uint16_t)sv.w; sbits[7] = (uint16_t)(sv.w >> 16);
+        } else {
 #pragma unroll
-            for (uint32_t kk = 0; kk < 8; ++kk) {
-                const int32_t qv = (int32_t)((word >> (4 * kk)) & 0xFu);
-                const float v = __fmul_rn((float)(qv - z), s);
+            for (uint32_t c = 0; c < 8; ++c) {
+                const bool in = col + c < N;
+                words[c] = in ? packed[(size_t)kg * N + col + c] : 0u;
+                sbits[c] = in ? scales[(size_t)grp * N + col + c] : (uint16_t)0;
+            }
+        }
+        float s[8];
+        int32_t z[8];
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c) {
+            s[c] = __uint_as_float((uint32_t)sbits[c] << 16);
+            z[c] = (int32_t)((zword >> (4 * c)) & 0xFu);
+        }
+#pragma unroll
+        for (uint32_t kk = 0; kk < 8; ++kk) {
+            uint16_t o[8];
+#pragma unroll
+            for (uint32_t c = 0; c < 8; ++c) {
+                const int32_t qv = (int32_t)((words[c] >> (4 * kk)) & 0xFu);
+                const float v = __fmul_rn((float)(qv - z[c]), s[c]);
                 const uint32_t bits = __float_as_uint(v);
-                out[(size_t)(kg * 8 + kk) * N + n] = (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+                o[c] = (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+            }
+            uint16_t* dst = out + (size_t)(kg * 8 + kk) * N + col;
+            if (vec) {
+                uint4 q;
+                q.x = o[0] | ((uint32_t)o[1] << 16); q.y = o[2] | ((uint32_t)o[3] << 16); q.z = o[4] | ((uint32_t)o[5] << 16); q.w = o[6] | ((uint32_t)o[7] << 16);
+                __stcs((uint4*)dst, q);
+            } else {
+#pragma unroll
+                for (uint32_t c = 0; c < 8; ++c)
+                    if (col + c < N) dst[c] = o[c];
             }
         }
     }
@@ -1018,7 +1052,7 @@ int launch_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t
     if (K == 0 || N == 0) return T0_OK;
     if (K % 8) return fail(T0_ERR_INVALID, "K=%u must be a multiple of 8 (eight codes per word)", K);
     if (group == 0 || group % 8) return fail(T0_ERR_INVALID, "group size %u must be a positive multiple of 8", group);
-    const uint64_t total = (uint64_t)(K / 8) * ((N + 3) / 4);
+    const uint64_t total = (uint64_t)(K / 8) * ((N + 7) / 8);
     dequant_w4_b200_kernel<<<grid_for(total, 256), 256, 0, rt->stream>>>((const uint32_t*)packed, (const uint16_t*)scales,
                                                                         (const uint32_t*)zeros, (uint16_t*)out, K, N, group, (N + 7) / 8);
     cudaError_t e = cudaGetLastError();
@@ -1479,11 +1513,8 @@ int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint
             t_min = std::min(t_min, h[c * 4]); t_max = std::max(t_max, h[c * 4 + 3]);
             stage += (double)(h[c * 4 + 1] - h[c * 4]); loop += (double)(h[c * 4 + 2] - h[c * 4 + 1]); tail += (double)(h[c * 4 + 3] - h[c * 4 + 2]);
         }
-        double wf = 0, wa = 0, wc = 0, wm = 0;
-        for (uint32_t c = 0; c < grid; ++c) { wf += (double)h[grid * 4 + c * 4]; wa += (double)h[grid * 4 + c * 4 + 1]; wc += (double)h[grid * 4 + c * 4 + 2]; wm += (double)h[grid * 4 + c * 4 + 3]; }
-        fprintf(stderr, "[w4a16 stream trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: set-up %.2f us, main loop %.2f us, flush+exit %.2f us; "
-                "warp 0 waited (cycles): weights %.0f, A buffer %.0f, accumulator %.0f; UMMA issuer idle %.0f\n",
-                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3, wf / grid, wa / grid, wc / grid, wm / grid);
+        fprintf(stderr, "[w4a16 stream trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: set-up %.2f us, main loop %.2f us, flush+exit %.2f us\n",
+                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3);
     }
     rt->launches.fetch_add(1);
     return T0_OK;
