@@ -314,3 +314,17 @@ def test_prepacked_argument_errors(t0, rt):
     assert lib.t0_w4a16_gemm_prepacked(rt._h, p, 0, p, 1, 256, 128, 128) == 1         # null pointer
     assert not rt.is_poisoned()
     buf.free()
+
+
+def test_row_layout_more_than_one_wave_of_steps(t0, oracle, rt):
+    # K*N large enough that a CTA owns more than 20 steps: the row-layout entry then runs the first fused kernel, which
+    # restages its activations in batches of 12 steps; the streaming-layout entry refuses (covered above)
+    M, K, N, G = 4, 8192, 16384, 128
+    a = oracle.fill_normal_bf16(M * K, 5)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=3)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    outs = []
+    for _ in range(2):
+        outs.append(run_w4a16(rt, a, packed, scales, zeros, M, N, K, G))
+    assert_close(outs[0], ref, K)
+    assert np.array_equal(outs[0], outs[1])
