@@ -262,6 +262,26 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 
+/* ------------------------------------------------------- warp-layout planners */
+/* WarpLayout / WarpOrientation and the planners (src/t0/tile_ir.rs:8365-8545): pure host arithmetic over a tile shape,
+ * kept for callers that size their own kernels with it.  The reference's asserts become T0_ERR_INVALID. */
+enum { T0_WARP_ROW_DOMINANT = 0, T0_WARP_COL_DOMINANT = 1, T0_WARP_SQUARE = 2 };
+typedef struct t0_warp_layout {
+    uint32_t n_warps, rows_per_warp, cols_per_warp;
+    uint32_t orientation;     /* T0_WARP_* */
+} t0_warp_layout;
+int t0_warp_layout_row_dominant(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out);   /* :8390-8413 */
+int t0_warp_layout_col_dominant(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out);   /* :8418-8429 */
+int t0_warp_layout_square(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out);         /* :8434-8451 */
+uint32_t t0_warp_layout_wmma_row_blocks(const t0_warp_layout* l);      /* rows_per_warp / 16 */
+uint32_t t0_warp_layout_wmma_col_tiles(const t0_warp_layout* l);       /* cols_per_warp / 16 */
+uint32_t t0_warp_layout_wmma_ops_per_warp(const t0_warp_layout* l);
+uint32_t t0_warp_layout_acc_vgprs_per_warp(const t0_warp_layout* l);   /* 8 per 16 x 16 output block */
+uint32_t t0_warp_layout_wg_size(const t0_warp_layout* l);
+int t0_warp_layout_is_compatible(const t0_warp_layout* l, uint32_t tile_m, uint32_t tile_n);
+int t0_plan_flash_attention_warps(uint32_t n_warps, uint32_t m, uint32_t n, uint32_t d, t0_warp_layout* qk, t0_warp_layout* av);   /* :8487-8524 */
+int t0_plan_single_dot_warps(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out);                              /* :8529-8540 */
+
 /* ------------------------------------------------------- f32 framework entries */
 /* Ignis matmul(x[M,K] f32, w[K,N] f32) -> y[M,N] f32 (src/ignis/ops/bf16_matmul.rs:33-59,162-207): operands rounded to
  * bf16 (nearest even, :371-372) on the device, fp32 accumulate.  Device pointers; no padding, transposing or host round

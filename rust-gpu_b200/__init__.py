@@ -183,6 +183,49 @@ class GemmArgs(C.Structure):
                 ("scale", C.c_float), ("clamp_min", C.c_float), ("clamp_max", C.c_float)]
 
 
+class WarpLayout(C.Structure):
+    """``WarpLayout`` (src/t0/tile_ir.rs:8365-8475)."""
+    _fields_ = [("n_warps", C.c_uint32), ("rows_per_warp", C.c_uint32), ("cols_per_warp", C.c_uint32), ("orientation", C.c_uint32)]
+    ROW_DOMINANT, COL_DOMINANT, SQUARE = 0, 1, 2
+
+    @staticmethod
+    def _make(fn: str, n_warps: int, tile_m: int, tile_n: int) -> "WarpLayout":
+        out = WarpLayout()
+        _check(getattr(lib(), fn)(n_warps, tile_m, tile_n, C.byref(out)))
+        return out
+
+    @staticmethod
+    def row_dominant(n_warps: int, tile_m: int, tile_n: int) -> "WarpLayout":
+        return WarpLayout._make("t0_warp_layout_row_dominant", n_warps, tile_m, tile_n)
+
+    @staticmethod
+    def col_dominant(n_warps: int, tile_m: int, tile_n: int) -> "WarpLayout":
+        return WarpLayout._make("t0_warp_layout_col_dominant", n_warps, tile_m, tile_n)
+
+    @staticmethod
+    def square(n_warps: int, tile_m: int, tile_n: int) -> "WarpLayout":
+        return WarpLayout._make("t0_warp_layout_square", n_warps, tile_m, tile_n)
+
+    def wmma_row_blocks(self) -> int: return lib().t0_warp_layout_wmma_row_blocks(C.byref(self))
+    def wmma_col_tiles(self) -> int: return lib().t0_warp_layout_wmma_col_tiles(C.byref(self))
+    def wmma_ops_per_warp(self) -> int: return lib().t0_warp_layout_wmma_ops_per_warp(C.byref(self))
+    def acc_vgprs_per_warp(self) -> int: return lib().t0_warp_layout_acc_vgprs_per_warp(C.byref(self))
+    def wg_size(self) -> int: return lib().t0_warp_layout_wg_size(C.byref(self))
+    def is_compatible(self, tile_m: int, tile_n: int) -> bool: return bool(lib().t0_warp_layout_is_compatible(C.byref(self), tile_m, tile_n))
+
+
+def plan_flash_attention_warps(n_warps: int, m: int, n: int, d: int):
+    """``plan_flash_attention_warps`` (tile_ir.rs:8487-8524) -> (qk_layout, av_layout)."""
+    qk, av = WarpLayout(), WarpLayout()
+    _check(lib().t0_plan_flash_attention_warps(n_warps, m, n, d, C.byref(qk), C.byref(av)))
+    return qk, av
+
+
+def plan_single_dot_warps(n_warps: int, tile_m: int, tile_n: int) -> WarpLayout:
+    """``plan_single_dot_warps`` (tile_ir.rs:8529-8540)."""
+    return WarpLayout._make("t0_plan_single_dot_warps", n_warps, tile_m, tile_n)
+
+
 class W4A16Args(C.Structure):
     """``t0_w4a16_args``."""
     _fields_ = [("a", C.c_uint64), ("packed", C.c_uint64), ("scales", C.c_uint64), ("zeros", C.c_uint64), ("y", C.c_uint64),
@@ -872,6 +915,14 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    wlp = C.POINTER(WarpLayout)
+    for fn in ("t0_warp_layout_row_dominant", "t0_warp_layout_col_dominant", "t0_warp_layout_square", "t0_plan_single_dot_warps"):
+        sig(fn, i32, u32, u32, u32, wlp)
+    for fn in ("t0_warp_layout_wmma_row_blocks", "t0_warp_layout_wmma_col_tiles", "t0_warp_layout_wmma_ops_per_warp",
+               "t0_warp_layout_acc_vgprs_per_warp", "t0_warp_layout_wg_size"):
+        sig(fn, u32, wlp)
+    sig("t0_warp_layout_is_compatible", i32, wlp, u32, u32)
+    sig("t0_plan_flash_attention_warps", i32, u32, u32, u32, u32, wlp, wlp)
     f32 = C.c_float
     sig("t0_matmul_f32", i32, vp, u64, u64, u64, u32, u32, u32)
     sig("t0_matmul_f32_with_wt_bf16", i32, vp, u64, u64, u64, u32, u32, u32)

@@ -433,4 +433,68 @@ int t0_tile_compute_grid(const t0_tile_gemm* s, uint32_t m, uint32_t n, uint32_t
 uint16_t t0_f32_to_bf16(float v) { uint32_t b; memcpy(&b, &v, 4); return (uint16_t)(b >> 16); }
 float t0_bf16_to_f32(uint16_t v) { uint32_t b = (uint32_t)v << 16; float f; memcpy(&f, &b, 4); return f; }
 
+
+// ------------------------------------------------------------------ warp-layout planners (tile_ir.rs:8365-8545)
+
+int t0_warp_layout_row_dominant(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    if (n_warps == 0 || n_warps > 8) return fail(T0_ERR_INVALID, "n_warps must be 1-8");
+    // small M (decode): fewer warps so that each still has 16 rows
+    const uint32_t eff = tile_m < n_warps * 16 ? tile_m / 16 : n_warps;
+    if (eff == 0) return fail(T0_ERR_INVALID, "tile_m=%u too small for any warp", tile_m);
+    if (tile_m % (eff * 16)) return fail(T0_ERR_INVALID, "tile_m=%u must be divisible by effective_warps*16=%u", tile_m, eff * 16);
+    *out = t0_warp_layout{eff, tile_m / eff, tile_n, T0_WARP_ROW_DOMINANT};
+    return T0_OK;
+}
+
+int t0_warp_layout_col_dominant(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    if (n_warps == 0 || n_warps > 8) return fail(T0_ERR_INVALID, "n_warps must be 1-8");
+    if (tile_n % (n_warps * 16)) return fail(T0_ERR_INVALID, "tile_n=%u must be divisible by n_warps*16=%u", tile_n, n_warps * 16);
+    *out = t0_warp_layout{n_warps, tile_m, tile_n / n_warps, T0_WARP_COL_DOMINANT};
+    return T0_OK;
+}
+
+int t0_warp_layout_square(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    if (n_warps != 4 && n_warps != 8) return fail(T0_ERR_INVALID, "square layout requires 4 or 8 warps, got %u", n_warps);
+    const uint32_t row_warps = n_warps == 4 ? 2 : 4, col_warps = 2;
+    if (tile_m % (row_warps * 16)) return fail(T0_ERR_INVALID, "tile_m=%u must be divisible by %u*16", tile_m, row_warps);
+    if (tile_n % (col_warps * 16)) return fail(T0_ERR_INVALID, "tile_n=%u must be divisible by %u*16", tile_n, col_warps);
+    *out = t0_warp_layout{n_warps, tile_m / row_warps, tile_n / col_warps, T0_WARP_SQUARE};
+    return T0_OK;
+}
+
+uint32_t t0_warp_layout_wmma_row_blocks(const t0_warp_layout* l) { return l ? l->rows_per_warp / 16 : 0; }
+uint32_t t0_warp_layout_wmma_col_tiles(const t0_warp_layout* l) { return l ? l->cols_per_warp / 16 : 0; }
+uint32_t t0_warp_layout_wmma_ops_per_warp(const t0_warp_layout* l) { return t0_warp_layout_wmma_row_blocks(l) * t0_warp_layout_wmma_col_tiles(l); }
+uint32_t t0_warp_layout_acc_vgprs_per_warp(const t0_warp_layout* l) { return t0_warp_layout_wmma_ops_per_warp(l) * 8; }
+uint32_t t0_warp_layout_wg_size(const t0_warp_layout* l) { return l ? l->n_warps * 32 : 0; }
+int t0_warp_layout_is_compatible(const t0_warp_layout* l, uint32_t tile_m, uint32_t tile_n) {
+    return l && l->rows_per_warp && l->cols_per_warp && tile_m % l->rows_per_warp == 0 && tile_n % l->cols_per_warp == 0;
+}
+
+int t0_plan_flash_attention_warps(uint32_t n_warps, uint32_t m, uint32_t n, uint32_t d, t0_warp_layout* qk, t0_warp_layout* av) {
+    if (!qk || !av) return fail(T0_ERR_INVALID, "null output");
+    // small M (decode): limit the warps so each gets at least 16 rows
+    const uint32_t eff = std::max<uint32_t>(1, std::min(n_warps, std::max<uint32_t>(m, 16) / 16));
+    int rc;
+    if (m <= 32) rc = t0_warp_layout_row_dominant(eff, std::max(m, eff * 16), n, qk);
+    else if (m >= 64 && n <= 128) rc = t0_warp_layout_row_dominant(n_warps, m, n, qk);
+    else if (n >= 128) rc = t0_warp_layout_row_dominant(n_warps, m, n, qk);
+    else rc = t0_warp_layout_square(n_warps, m, n, qk);
+    if (rc != T0_OK) return rc;
+    const uint32_t av_warps = qk->n_warps;    // the second product keeps the warp count of the first
+    if (qk->orientation == T0_WARP_ROW_DOMINANT) {
+        if (d % (av_warps * 16) == 0) return t0_warp_layout_col_dominant(av_warps, std::max(m, av_warps * 16), d, av);
+        return t0_warp_layout_square(av_warps, std::max(m, av_warps * 16), std::max<uint32_t>(d, 32), av);
+    }
+    return t0_warp_layout_row_dominant(av_warps, std::max(m, av_warps * 16), d, av);
+}
+
+int t0_plan_single_dot_warps(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out) {
+    if (tile_n >= tile_m * 2 && tile_m < tile_n * 2) return t0_warp_layout_col_dominant(n_warps, tile_m, tile_n, out);   // wide
+    return t0_warp_layout_row_dominant(n_warps, tile_m, tile_n, out);                                                      // tall or square-ish
+}
+
 }  // extern "C"

@@ -251,3 +251,32 @@ def test_no_gpu_means_loud_failure(t0):
     with pytest.raises(t0.T0Error) as e:
         t0.GpuRuntime(0)
     assert "no CPU fallback" in str(e.value)
+
+
+def test_warp_layout_planners(t0):
+    # the reference's own known answers: src/t0/tile_ir.rs:8552-8618
+    l = t0.WarpLayout.row_dominant(4, 128, 64)
+    assert (l.n_warps, l.rows_per_warp, l.cols_per_warp) == (4, 32, 64)
+    assert (l.wmma_row_blocks(), l.wmma_col_tiles(), l.wmma_ops_per_warp(), l.acc_vgprs_per_warp()) == (2, 4, 8, 64)
+    assert l.wg_size() == 128 and l.is_compatible(128, 64) and not l.is_compatible(48, 64)
+    l = t0.WarpLayout.col_dominant(4, 64, 128)
+    assert (l.rows_per_warp, l.cols_per_warp, l.wmma_ops_per_warp()) == (64, 32, 8)
+    l = t0.WarpLayout.square(4, 128, 128)
+    assert (l.rows_per_warp, l.cols_per_warp, l.wmma_ops_per_warp()) == (64, 64, 16)
+    qk, av = t0.plan_flash_attention_warps(4, 128, 64, 64)
+    assert qk.orientation == t0.WarpLayout.ROW_DOMINANT and av.orientation == t0.WarpLayout.COL_DOMINANT
+    qk, av = t0.plan_flash_attention_warps(4, 16, 64, 64)          # decode: one warp of 16 rows
+    assert qk.orientation == t0.WarpLayout.ROW_DOMINANT and qk.n_warps == 1 and qk.rows_per_warp == 16
+    l = t0.plan_single_dot_warps(4, 128, 64)
+    assert (l.rows_per_warp, l.cols_per_warp) == (32, 64)
+    l = t0.plan_single_dot_warps(4, 64, 128)
+    assert (l.rows_per_warp, l.cols_per_warp) == (64, 32)
+    l = t0.WarpLayout.row_dominant(4, 64, 64)
+    assert l.rows_per_warp == 16
+    l = t0.WarpLayout.row_dominant(4, 32, 64)                       # fewer warps than asked: each keeps 16 rows
+    assert (l.n_warps, l.rows_per_warp) == (2, 16)
+    # the reference's asserts become errors
+    for bad in (lambda: t0.WarpLayout.row_dominant(9, 128, 64), lambda: t0.WarpLayout.row_dominant(4, 8, 64),
+                lambda: t0.WarpLayout.col_dominant(4, 64, 100), lambda: t0.WarpLayout.square(3, 128, 128)):
+        with pytest.raises(t0.T0Error):
+            bad()
