@@ -262,6 +262,33 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 
+/* ------------------------------------------------------- cost-model records */
+/* TileConfig (src/t0/cost_model.rs:130-168) and TileCost (:171-190): the cost model's own candidate record and its
+ * estimate.  On B200 `waves_per_wg` counts the CTA's warps (6: producer, UMMA issuer, four epilogue warps),
+ * `vgprs` / `sgprs` / `occupancy` report registers per thread, 0 and resident CTAs per SM, `lds_bytes` the dynamic
+ * shared memory of the kernel instance, `score` the predicted TFLOP/s. */
+typedef struct t0_tile_config {
+    uint32_t tile_m, tile_n, tile_k, waves_per_wg;
+    uint8_t use_lds, wgp_mode, swap_grid, _pad;
+    uint32_t split_k;        /* 1 = no split */
+    uint32_t lds_pad;
+} t0_tile_config;
+typedef struct t0_tile_cost {
+    t0_tile_config config;
+    uint32_t vgprs, sgprs, lds_bytes, occupancy, n_wgs;
+    int feasible;
+    double score;
+    char bottleneck[24];
+} t0_tile_cost;
+/* auto_schedule_gemm(m, n, k, fmt) -> Vec<TileCost>, best first (cost_model.rs:464-534); returns how many were written */
+int t0_auto_schedule_tile_costs(uint32_t m, uint32_t n, uint32_t k, t0_tile_cost* out, int cap);
+/* TileConfig::name / to_gemm_config / to_tile_gemm / can_use_tile_ir (cost_model.rs:157-163,578-647).  to_gemm_config keeps
+ * the tile width (no 64-column passes: that was a register-file workaround of the reference's target). */
+int t0_tile_config_name(const t0_tile_config* c, char* buf, size_t buf_len);
+int t0_tile_config_to_gemm_config(const t0_tile_config* c, t0_gemm_config* out);
+int t0_tile_config_to_tile_gemm(const t0_tile_config* c, t0_tile_gemm* out);
+int t0_tile_config_can_use_tile_ir(const t0_tile_config* c);
+
 /* ------------------------------------------------------- warp-layout planners */
 /* WarpLayout / WarpOrientation and the planners (src/t0/tile_ir.rs:8365-8545): pure host arithmetic over a tile shape,
  * kept for callers that size their own kernels with it.  The reference's asserts become T0_ERR_INVALID. */

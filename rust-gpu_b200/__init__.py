@@ -183,6 +183,45 @@ class GemmArgs(C.Structure):
                 ("scale", C.c_float), ("clamp_min", C.c_float), ("clamp_max", C.c_float)]
 
 
+class TileConfig(C.Structure):
+    """``cost_model::TileConfig`` (src/t0/cost_model.rs:130-168)."""
+    _fields_ = [("tile_m", C.c_uint32), ("tile_n", C.c_uint32), ("tile_k", C.c_uint32), ("waves_per_wg", C.c_uint32),
+                ("use_lds", C.c_uint8), ("wgp_mode", C.c_uint8), ("swap_grid", C.c_uint8), ("_pad", C.c_uint8),
+                ("split_k", C.c_uint32), ("lds_pad", C.c_uint32)]
+
+    def name(self) -> str:
+        buf = C.create_string_buffer(96)
+        _check(lib().t0_tile_config_name(C.byref(self), buf, 96))
+        return buf.value.decode()
+
+    def to_gemm_config(self) -> "GemmConfig":
+        out = GemmConfig()
+        _check(lib().t0_tile_config_to_gemm_config(C.byref(self), C.byref(out)))
+        return out
+
+    def to_tile_gemm(self) -> "TileGemm":
+        out = TileGemm()
+        _check(lib().t0_tile_config_to_tile_gemm(C.byref(self), C.byref(out)))
+        return out
+
+    def can_use_tile_ir(self) -> bool:
+        return bool(lib().t0_tile_config_can_use_tile_ir(C.byref(self)))
+
+
+class TileCost(C.Structure):
+    """``cost_model::TileCost`` (src/t0/cost_model.rs:171-190)."""
+    _fields_ = [("config", TileConfig), ("vgprs", C.c_uint32), ("sgprs", C.c_uint32), ("lds_bytes", C.c_uint32),
+                ("occupancy", C.c_uint32), ("n_wgs", C.c_uint32), ("feasible", C.c_int), ("score", C.c_double),
+                ("bottleneck", C.c_char * 24)]
+
+
+def auto_schedule_gemm(m: int, n: int, k: int, cap: int = 64) -> list:
+    """``cost_model::auto_schedule_gemm`` (cost_model.rs:464-534): feasible candidates, best first."""
+    arr = (TileCost * cap)()
+    got = lib().t0_auto_schedule_tile_costs(m, n, k, arr, cap)
+    return [arr[i] for i in range(got)]
+
+
 class WarpLayout(C.Structure):
     """``WarpLayout`` (src/t0/tile_ir.rs:8365-8475)."""
     _fields_ = [("n_warps", C.c_uint32), ("rows_per_warp", C.c_uint32), ("cols_per_warp", C.c_uint32), ("orientation", C.c_uint32)]
@@ -266,7 +305,8 @@ def cache_size() -> int:
     return int(lib().t0_cache_size())
 
 
-def auto_schedule_gemm(m: int, n: int, k: int, cap: int = 64) -> list[tuple[GemmConfig, float]]:
+def auto_schedule_gemm_configs(m: int, n: int, k: int, cap: int = 64) -> list[tuple[GemmConfig, float]]:
+    """The same ranking as (GemmConfig, predicted TFLOP/s) pairs."""
     cfgs = (GemmConfig * cap)()
     tf = (C.c_double * cap)()
     cnt = lib().t0_auto_schedule_gemm(m, n, k, cfgs, tf, cap)
@@ -915,6 +955,12 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
+    tcp = C.POINTER(TileConfig)
+    sig("t0_auto_schedule_tile_costs", i32, u32, u32, u32, C.POINTER(TileCost), i32)
+    sig("t0_tile_config_name", i32, tcp, C.c_char_p, sz)
+    sig("t0_tile_config_to_gemm_config", i32, tcp, C.POINTER(GemmConfig))
+    sig("t0_tile_config_to_tile_gemm", i32, tcp, C.POINTER(TileGemm))
+    sig("t0_tile_config_can_use_tile_ir", i32, tcp)
     wlp = C.POINTER(WarpLayout)
     for fn in ("t0_warp_layout_row_dominant", "t0_warp_layout_col_dominant", "t0_warp_layout_square", "t0_plan_single_dot_warps"):
         sig(fn, i32, u32, u32, u32, wlp)

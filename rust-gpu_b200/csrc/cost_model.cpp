@@ -10,6 +10,11 @@
 // algorithmic bytes) + launch (+ the split-K reduction pass).
 #include "common.h"
 
+namespace t0 {
+uint32_t gemm_smem_bytes(uint32_t tile_n);        // gemm_sm100.cu
+uint32_t gemm_pair_smem_bytes(uint32_t pair_n);   // gemm_sm100_pair.cu
+}
+
 #include <algorithm>
 #include <cmath>
 #include <map>
@@ -145,6 +150,88 @@ int t0_auto_schedule_gemm(uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* ou
         if (pred_tflops) pred_tflops[w] = c[w].pred_tflops;
     }
     return w;
+}
+
+static t0_tile_config tile_config_of(const t0_gemm_config& g) {
+    t0_tile_config c;
+    memset(&c, 0, sizeof c);
+    c.tile_m = g.tile_m; c.tile_n = g.tile_n; c.tile_k = g.tile_k;
+    c.waves_per_wg = g.wg_size / 32;
+    c.use_lds = 1; c.wgp_mode = g.wgp_mode; c.swap_grid = g.swap_grid;
+    c.split_k = g.split_k > 1 ? g.split_k : 1;
+    c.lds_pad = 0;
+    return c;
+}
+
+int t0_auto_schedule_tile_costs(uint32_t m, uint32_t n, uint32_t k, t0_tile_cost* out, int cap) {
+    std::vector<Candidate> cands = schedule(m, n, k);
+    B200Limits hw;
+    int w = 0;
+    for (; w < (int)cands.size() && w < cap; ++w) {
+        if (!out) continue;
+        const t0_gemm_config& g = cands[w].cfg;
+        t0_tile_cost& tc = out[w];
+        memset(&tc, 0, sizeof tc);
+        tc.config = tile_config_of(g);
+        const bool pair = g.wgp_mode && g.tile_m == 256;
+        const uint32_t sk = tc.config.split_k;
+        tc.vgprs = pair ? 101 : 104;                              // registers per thread of the kernel instances (ptxas)
+        tc.sgprs = 0;
+        tc.lds_bytes = pair ? gemm_pair_smem_bytes(g.tile_n) : gemm_smem_bytes(g.tile_n);
+        tc.occupancy = 1;                                         // one persistent CTA per SM
+        tc.n_wgs = ceil_div(m, g.tile_m) * ceil_div(n, g.tile_n) * sk;
+        tc.feasible = 1;
+        tc.score = cands[w].pred_tflops;
+        const double tiles = (double)tc.n_wgs, slots = pair ? hw.n_sms / 2 : hw.n_sms;
+        const char* why = tiles < slots ? "parallelism" : (2.0 * m * (double)n * k / (2.0 * m * k + 2.0 * (double)n * k + 4.0 * (double)m * n) < 200.0 ? "memory" : "tensor");
+        snprintf(tc.bottleneck, sizeof tc.bottleneck, "%s", why);
+    }
+    return w;
+}
+
+int t0_tile_config_name(const t0_tile_config* c, char* buf, size_t buf_len) {
+    if (!c || !buf || buf_len == 0) return fail(T0_ERR_INVALID, "null argument");
+    // cost_model.rs:157-163
+    std::string nm = std::to_string(c->tile_m) + "x" + std::to_string(c->tile_n) + "_k" + std::to_string(c->tile_k);
+    if (c->split_k > 1) nm += "_sk" + std::to_string(c->split_k);
+    if (!c->swap_grid) nm += "_mg";
+    if (c->wgp_mode) nm += "_wgp";
+    if (c->lds_pad > 0) nm += "_pad" + std::to_string(c->lds_pad);
+    if (nm.size() + 1 > buf_len) return fail(T0_ERR_BOUNDS, "name buffer too small");
+    memcpy(buf, nm.c_str(), nm.size() + 1);
+    return T0_OK;
+}
+
+int t0_tile_config_to_gemm_config(const t0_tile_config* c, t0_gemm_config* out) {
+    if (!c || !out) return fail(T0_ERR_INVALID, "null argument");
+    memset(out, 0, sizeof *out);
+    out->tile_m = c->tile_m; out->tile_n = c->tile_n; out->tile_k = c->tile_k;
+    out->wg_size = c->waves_per_wg * 32;
+    out->use_lds = c->use_lds; out->double_buffer = c->use_lds;          // cost_model.rs:597: always double-buffer with LDS
+    out->split_k = c->split_k > 1 ? c->split_k : 0;
+    out->lds_pad = c->lds_pad; out->n_col_passes = 1;
+    out->swap_grid = c->swap_grid; out->wgp_mode = c->wgp_mode;
+    out->transpose = T0_NT; out->epilogue = T0_EPI_STORE_F32;
+    return T0_OK;
+}
+
+int t0_tile_config_to_tile_gemm(const t0_tile_config* c, t0_tile_gemm* out) {
+    if (!c || !out) return fail(T0_ERR_INVALID, "null argument");
+    memset(out, 0, sizeof *out);
+    out->tile_m = c->tile_m; out->tile_n = c->tile_n; out->tile_k = c->tile_k;
+    out->wgp_mode = c->wgp_mode; out->double_buffer = c->use_lds; out->triple_buffer = 0;
+    out->split_k = c->split_k;
+    out->swap_grid = 1;                                                   // cost_model.rs:618
+    out->transpose = T0_NT;
+    return T0_OK;
+}
+
+int t0_tile_config_can_use_tile_ir(const t0_tile_config* c) {
+    if (!c) return 0;
+    // cost_model.rs:639-647
+    const uint32_t tile_ir_waves = c->tile_m / 32;
+    const bool pow2 = c->tile_k && (c->tile_k & (c->tile_k - 1)) == 0;
+    return pow2 && c->tile_m >= 32 && c->tile_n >= 32 && c->waves_per_wg == tile_ir_waves && c->swap_grid && c->split_k <= 1;
 }
 
 int t0_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out) {

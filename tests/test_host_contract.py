@@ -280,3 +280,27 @@ def test_warp_layout_planners(t0):
                 lambda: t0.WarpLayout.col_dominant(4, 64, 100), lambda: t0.WarpLayout.square(3, 128, 128)):
         with pytest.raises(t0.T0Error):
             bad()
+
+
+def test_cost_model_records(t0):
+    # cost_model.rs:130-168,464-534,578-647: TileConfig / TileCost, the ranked schedule and the conversions
+    costs = t0.auto_schedule_gemm(4096, 4096, 4096)
+    assert len(costs) >= 4 and all(c.feasible for c in costs)
+    assert all(costs[i].score >= costs[i + 1].score - 1e-9 for i in range(len(costs) - 1))      # best first
+    best = costs[0]
+    assert best.config.to_gemm_config().name() == t0.auto_select(4096, 4096, 4096).name()
+    assert best.n_wgs == 16 * 16 and best.lds_bytes > 100 * 1024 and best.bottleneck.decode() == "tensor"
+    skinny = t0.auto_schedule_gemm(16, 4096, 4096)[0]
+    assert skinny.bottleneck.decode() in ("memory", "parallelism")
+    c = t0.TileConfig(tile_m=128, tile_n=64, tile_k=32, waves_per_wg=4, use_lds=1, wgp_mode=1, swap_grid=0, split_k=4, lds_pad=8)
+    assert c.name() == "128x64_k32_sk4_mg_wgp_pad8"                    # cost_model.rs:157-163
+    g = c.to_gemm_config()
+    assert (g.tile_m, g.tile_n, g.tile_k, g.wg_size, g.split_k, g.lds_pad, g.swap_grid, g.wgp_mode) == (128, 64, 32, 128, 4, 8, 0, 1)
+    assert g.use_lds and g.double_buffer
+    tg = c.to_tile_gemm()
+    assert (tg.tile_m, tg.tile_n, tg.tile_k, tg.split_k, tg.swap_grid, tg.double_buffer) == (128, 64, 32, 4, 1, 1)
+    assert not c.can_use_tile_ir()                                     # split_k > 1 and swap_grid false
+    ok = t0.TileConfig(tile_m=128, tile_n=64, tile_k=32, waves_per_wg=4, use_lds=1, wgp_mode=0, swap_grid=1, split_k=1, lds_pad=0)
+    assert ok.can_use_tile_ir()
+    assert not t0.TileConfig(tile_m=128, tile_n=64, tile_k=48, waves_per_wg=4, use_lds=1, swap_grid=1, split_k=1).can_use_tile_ir()   # tile_k not a power of two
+    assert not t0.TileConfig(tile_m=128, tile_n=64, tile_k=32, waves_per_wg=8, use_lds=1, swap_grid=1, split_k=1).can_use_tile_ir()   # waves != tile_m / 32
