@@ -344,6 +344,8 @@ const char* t0_tuner_cache_dir(const t0_tuner* t);
 /* GemmTuner::tune(rt, m, n, k) -> GemmConfig (auto_gemm.rs:82-216): memory cache, disk cache gemm_{M}x{N}x{K}.json,
  * else cost-model candidates -> 256^3 smoke test -> timed runs (median of n_iters) -> save.  Argument order (m, n, k). */
 int t0_tuner_tune(t0_tuner* t, t0_runtime* rt, uint32_t m, uint32_t n, uint32_t k, t0_gemm_config* out);
+/* GemmTuner::benchmark_tile_ir (auto_gemm.rs:352-431): times one TileGemm spec through the TileIR dispatch path */
+int t0_tuner_benchmark_tile_ir(t0_tuner* t, t0_runtime* rt, const t0_tile_gemm* spec, uint32_t m, uint32_t n, uint32_t k, double* tflops);
 /* GemmTuneResult of a tuned size (auto_gemm.rs:30-41): best TFLOP/s, whether it came from disk, how many candidates were timed */
 int t0_tuner_result(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, double* best_tflops, int* from_cache, int* n_measured);
 /* save_cache / load_cache (auto_gemm.rs:439-501) and the JSON field reader (:603-625), exposed as the reference's tests use them */

@@ -790,6 +790,12 @@ class GemmTuner:
         _check(lib().t0_tuner_tune(self._h, rt._h, m, n, k, C.byref(c)))
         return c
 
+    def benchmark_tile_ir(self, rt: "GpuRuntime", spec: "TileGemm", m: int, n: int, k: int) -> float:
+        """``GemmTuner::benchmark_tile_ir`` (auto_gemm.rs:352-431): median TFLOP/s of one TileGemm spec."""
+        tf = C.c_double()
+        _check(lib().t0_tuner_benchmark_tile_ir(self._h, rt._h, C.byref(spec), m, n, k, C.byref(tf)))
+        return tf.value
+
     def result(self, m: int, n: int, k: int) -> dict:
         tf, fc, nm = C.c_double(), C.c_int(), C.c_int()
         _check(lib().t0_tuner_result(self._h, m, n, k, C.byref(tf), C.byref(fc), C.byref(nm)))
@@ -947,6 +953,7 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_tuner_invalidate", None, vp, u32, u32, u32)
     sig("t0_tuner_clear", None, vp)
     sig("t0_tuner_report", None, vp)
+    sig("t0_tuner_benchmark_tile_ir", i32, vp, vp, C.POINTER(TileGemm), u32, u32, u32, C.POINTER(C.c_double))
     sig("t0_global_tuner", vp)
     sig("t0_auto_gemm", i32, vp, vp, vp, vp, u32, u32, u32, C.POINTER(C.c_double))
     sig("t0_dequant_int4", i32, vp, u64, u64, u64, u64, u32, u32, u32, i32)

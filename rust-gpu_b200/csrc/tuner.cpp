@@ -299,6 +299,44 @@ int t0_tuner_tune(t0_tuner* t, t0_runtime* rt, uint32_t m, uint32_t n, uint32_t 
     return T0_OK;
 }
 
+int t0_tuner_benchmark_tile_ir(t0_tuner* t, t0_runtime* rt, const t0_tile_gemm* spec, uint32_t m, uint32_t n, uint32_t k, double* tflops) {
+    // auto_gemm.rs:352-431: kernel from the TileGemm, zeroed buffers, tile_ir kernargs and grid, one warm-up, n_iters
+    // synchronous dispatches, median -> TFLOP/s.  (The reference's 64 KiB LDS guard does not apply to this hardware.)
+    if (!t || !rt || !spec || !tflops) return fail(T0_ERR_INVALID, "null argument");
+    t0_kernel* kern = nullptr;
+    int rc = t0_rt_ensure_tile_kernel(rt, spec, &kern);
+    if (rc != T0_OK) return rc;
+    Buffers B{rt, {}};
+    const uint32_t sk = spec->split_k > 1 ? spec->split_k : 1;
+    t0_buffer* a = B.alloc(std::max<size_t>((size_t)m * k * 2, 4096));
+    t0_buffer* b = B.alloc(std::max<size_t>((size_t)n * k * 2, 4096));
+    t0_buffer* c = B.alloc(std::max<size_t>((size_t)m * n * 4 * sk, 4096));
+    if (!a || !b || !c) return T0_ERR_CUDA;
+    t0_buf_zero(a); t0_buf_zero(b); t0_buf_zero(c);
+    uint8_t ka[64];
+    size_t ka_len = 0;
+    rc = t0_tile_build_kernargs_m(t0_buf_gpu_addr(a), t0_buf_gpu_addr(b), t0_buf_gpu_addr(c), k, n, m, spec, ka, sizeof ka, &ka_len);
+    if (rc != T0_OK) return rc;
+    uint32_t grid[3] = {0, 0, 1};
+    rc = t0_tile_compute_grid(spec, m, n, grid);
+    if (rc != T0_OK) return rc;
+    rc = t0_rt_dispatch(rt, kern, grid, ka, ka_len);
+    if (rc != T0_OK) return rc;
+    std::vector<double> times;
+    for (size_t i = 0; i < std::max<size_t>(t->n_iters, 1); ++i) {
+        float ms = 0.0f;
+        rc = t0_rt_timer_start(rt);
+        if (rc == T0_OK) rc = t0_rt_dispatch(rt, kern, grid, ka, ka_len);
+        if (rc == T0_OK) rc = t0_rt_timer_stop(rt, &ms);
+        if (rc != T0_OK) return rc;
+        times.push_back(ms);
+    }
+    std::sort(times.begin(), times.end());
+    const double median_ms = times[times.size() / 2];
+    *tflops = median_ms > 0 ? 2.0 * m * (double)n * k / (median_ms * 1e-3) / 1e12 : 0.0;
+    return T0_OK;
+}
+
 int t0_tuner_result(const t0_tuner* t, uint32_t m, uint32_t n, uint32_t k, double* best_tflops, int* from_cache, int* n_measured) {
     if (!t) return fail(T0_ERR_INVALID, "null tuner");
     auto it = t->cache.find(std::make_tuple(m, n, k));

@@ -91,3 +91,14 @@ def test_auto_gemm_one_shot(t0, oracle, rt, tmp_path, monkeypatch):
     assert np.array_equal(rt.read_f32(y, m * n).reshape(m, n), oracle.gemm_nt(a, b, m, k, n))
     assert t0.auto_gemm(rt, xa, xb, y, m, n, k) == tf          # cache hit: same tuned figure
     t0.global_tuner().invalidate(m, n, k)
+
+
+@pytest.mark.gpu
+def test_benchmark_tile_ir(t0, rt, tmp_path):
+    # auto_gemm.rs:352-431: one TileGemm spec timed through the TileIR kernargs / grid / dispatch path
+    t = t0.GemmTuner.with_cache_dir(str(tmp_path / "tune"))
+    spec = t0.tile_auto_select(1024, 1024, 1024)
+    tf = t.benchmark_tile_ir(rt, spec, 1024, 1024, 1024)
+    assert tf > 1.0
+    assert not rt.is_poisoned()
+    t.free()
