@@ -1513,8 +1513,13 @@ int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint
             t_min = std::min(t_min, h[c * 4]); t_max = std::max(t_max, h[c * 4 + 3]);
             stage += (double)(h[c * 4 + 1] - h[c * 4]); loop += (double)(h[c * 4 + 2] - h[c * 4 + 1]); tail += (double)(h[c * 4 + 3] - h[c * 4 + 2]);
         }
-        fprintf(stderr, "[w4a16 stream trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: set-up %.2f us, main loop %.2f us, flush+exit %.2f us\n",
-                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3);
+        uint32_t slow = 0;
+        for (uint32_t c = 1; c < grid; ++c)
+            if (h[c * 4 + 3] - h[c * 4] > h[slow * 4 + 3] - h[slow * 4]) slow = c;
+        fprintf(stderr, "[w4a16 stream trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: set-up %.2f us, main loop %.2f us, flush+exit %.2f us; "
+                "slowest CTA %u: entered %.2f us after the first, set-up %.2f, main loop %.2f, flush+exit %.2f\n",
+                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3, slow, (h[slow * 4] - t_min) * 1e-3,
+                (h[slow * 4 + 1] - h[slow * 4]) * 1e-3, (h[slow * 4 + 2] - h[slow * 4 + 1]) * 1e-3, (h[slow * 4 + 3] - h[slow * 4 + 2]) * 1e-3);
     }
     rt->launches.fetch_add(1);
     return T0_OK;
