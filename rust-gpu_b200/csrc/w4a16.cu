@@ -724,6 +724,7 @@ w4a16_frag_kernel(const W4Params p) {
     uint64_t* sz_full_bar = empty_bar + kStages;
     volatile int* abort_flag = (volatile int*)(sz_full_bar + 1);
     int* s_last = (int*)(abort_flag + 1);
+    int* s_head_last = s_last + 1;       // band + 1 when this CTA turned out to be the last contributor of its head band
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t u0 = range_begin(blockIdx.x, gridDim.x, p.total_units);
@@ -739,6 +740,7 @@ w4a16_frag_kernel(const W4Params p) {
         }
         ptx::mbar_init(ptx::smem_u32(sz_full_bar), 1);
         *abort_flag = 0;
+        *s_head_last = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
     }
@@ -831,6 +833,40 @@ w4a16_frag_kernel(const W4Params p) {
     const uint32_t col0 = warp * 16 + g;                     // this lane's two columns within the band: col0 and col0 + 8
     const uint32_t w_off = warp * 1024 + lane * 16;           // [w][j][lane] uint4
 
+    // The CTA that contributes last to a band adds the pieces in k order (CTA order) and stores; nobody waits for anybody.
+    // Only the first contributor can hold the band in slot 1 (its range began in the band before).
+    auto reduce_band = [&](uint32_t rb) {
+        const uint32_t first_unit = rb * p.ksteps;
+        const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
+        const uint32_t c_last = owner_of(first_unit + p.ksteps - 1, gridDim.x, p.total_units);
+        const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
+        constexpr int kPer = kPieceFloats / (kFrWarps * 32);   // 8 outputs per thread when M = 16
+        float total[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
+        for (uint32_t c = c_first; c <= c_last; ++c) {
+            const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
+            float v[kPer];
+#pragma unroll
+            for (int j = 0; j < kPer; ++j) {
+                const uint32_t idx = tid + j * (kFrWarps * 32);
+                v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < kPer; ++j) total[j] += v[j];
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) {
+            const uint32_t idx = tid + j * (kFrWarps * 32);
+            if (idx < p.M * kBandCols) {
+                const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
+                const uint32_t nc = rb * kBandCols + col;
+                if (nc < p.N) p.y[(size_t)row * p.N + nc] = total[j];
+            }
+        }
+        if (tid == 0) p.counters[rb] = 0;   // ready for the next call
+    };
+
     // walked piece by piece (the steps of one band this CTA owns), so the inner loop carries no band logic
     const uint8_t* af = a_area + lane * 16;                  // B fragments of the current step
     uint32_t u = u0;
@@ -907,48 +943,26 @@ w4a16_frag_kernel(const W4Params p) {
             }
             if (!whole) {
                 fr_consumer_sync();                    // every thread's part of the piece is written ...
+                const bool range_goes_on = u < u1;     // this was the head band of the range: more steps follow
                 if (tid == 0) {
                     __threadfence();                   // ... and made visible before this CTA is counted
-                    *s_last = (atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first)) ? 1 : 0;
-                    if (*s_last) __threadfence();
+                    const int last = atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first);
+                    if (last) __threadfence();
+                    if (range_goes_on) *s_head_last = last ? (int)band + 1 : 0;   // looked at when the range is done
+                    else *s_last = last;
                 }
-                fr_consumer_sync();
-                if (*s_last) {
-                    // last to arrive: add the pieces in k order (CTA order) and store; nobody waits for anybody.
-                    // Only the first contributor can hold this band in slot 1 (its range began in the band before).
-                    const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
-                    constexpr int kPer = kPieceFloats / (kFrWarps * 32);   // 8 outputs per thread when M = 16
-                    float total[kPer];
-#pragma unroll
-                    for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
-                    for (uint32_t c = c_first; c <= c_last; ++c) {
-                        const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
-                        float v[kPer];
-#pragma unroll
-                        for (int j = 0; j < kPer; ++j) {
-                            const uint32_t idx = tid + j * (kFrWarps * 32);
-                            v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
-                        }
-#pragma unroll
-                        for (int j = 0; j < kPer; ++j) total[j] += v[j];
-                    }
-#pragma unroll
-                    for (int j = 0; j < kPer; ++j) {
-                        const uint32_t idx = tid + j * (kFrWarps * 32);
-                        if (idx < p.M * kBandCols) {
-                            const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
-                            const uint32_t nc = band * kBandCols + col;
-                            if (nc < p.N) p.y[(size_t)row * p.N + nc] = total[j];
-                        }
-                    }
-                    if (tid == 0) p.counters[band] = 0;   // ready for the next call
+                if (!range_goes_on) {
+                    fr_consumer_sync();
+                    if (*s_last) reduce_band(band);
                 }
-                fr_consumer_sync();
+                // (head band: nobody waits for the counter's answer; thread 0 alone pays the round trip, the ring's slack absorbs it)
             }
         }
       ks = 0;          // a further piece starts a new band
       ++band;
     }
+    fr_consumer_sync();
+    if (*s_head_last) reduce_band((uint32_t)*s_head_last - 1);
     stamp(3);
 }
 
