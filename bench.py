@@ -301,6 +301,7 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn"], help="B as WT[N,K] (the reference's native layout) or as B[K,N]")
     ap.add_argument("--gather", action="store_true", help="sharded workload: also time GEMM + in-place NCCL all-gather of C (reported under \"gather\")")
     ap.add_argument("--row-layout", action="store_true", help="W4A16 workloads: weights in the row layout instead of the streaming layout")
     args = ap.parse_args()
@@ -356,7 +357,11 @@ def main():
     tile_n = args.tile_n or cfg.tile_n
     split_k = cfg.split()
     pair = 1 if (cfg.wgp_mode and cfg.tile_m == 256 and not args.tile_n) else 2
-    gemm_kw = dict(tile_n=tile_n, split_k=split_k, swap_grid=bool(cfg.swap_grid), pair_cta=pair)
+    nn = args.layout == "nn"
+    if nn and sharded:
+        print("--layout nn is for the single-GPU workloads (a column slice of B[K,N] is strided)", file=sys.stderr)
+        sys.exit(2)
+    gemm_kw = dict(tile_n=tile_n, split_k=split_k, swap_grid=bool(cfg.swap_grid), pair_cta=pair, transpose=t0.NN if nn else t0.NT)
     step_args = [rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K, **gemm_kw) for (xa, xb, y) in sets]
 
     def step(i):
@@ -437,7 +442,7 @@ def main():
         worst = 0.0
         for r in rows:
             a_row = oracle.fill_uniform_bf16(K, 42 + M + 1000 * s_idx, r * K)
-            ref = oracle.gemm_nt(a_row, b_host, 1, K, N)
+            ref = oracle.gemm_nn(a_row, b_host, 1, K, N) if nn else oracle.gemm_nt(a_row, b_host, 1, K, N)
             got = y.read_bytes(r * N * 4, N * 4, np.float32)
             worst = max(worst, float(np.abs(ref[0] - got).max()))
         parity = {"sampled_rows": rows, "max_abs_err": worst, "tol": 5e-3 * (K / 256) ** 0.5}
@@ -487,8 +492,9 @@ def main():
         line = {"metric": "bf16_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
                 "warmup": warmup, "ms_per_step": ms_max / steps, "higher_is_better": True,
                 "scaling": "strong" if sharded else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": name, "m": M, "n": N_total, "k": K, "layout": "NT", "out": "f32",
-                           "kernel": (cfg if not args.tile_n else cfg.copy(tile_m=128, tile_n=tile_n, wgp_mode=0)).name(), "per_rank_n": N, "input_sets": n_sets,
+                "config": {"workload": name, "m": M, "n": N_total, "k": K, "layout": "NN" if nn else "NT", "out": "f32",
+                           "kernel": (cfg if not args.tile_n else cfg.copy(tile_m=128, tile_n=tile_n, wgp_mode=0)).copy(transpose=t0.NN if nn else t0.NT).name(),
+                           "per_rank_n": N, "input_sets": n_sets,
                            "l2": f"{n_sets} resident operand sets of {set_bytes >> 20} MiB rotate (> 126 MB L2)" if n_sets > 1
                                  else f"operands {set_bytes >> 20} MiB per rank (> 126 MB L2)",
                            "pct_of_nominal_dense_peak": round(100.0 * value / world / 2250.0, 1)},

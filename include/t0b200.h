@@ -249,7 +249,7 @@ typedef struct t0_gemm_args {
     uint32_t split_k;       /* 0/1 = none */
     uint8_t transpose, epilogue, out_bf16, planes;
     uint8_t swap_grid;
-    uint8_t pair_cta;       /* 0 = choose by shape, 1 = two-CTA pair kernel (256 x 256 tiles, NT only), 2 = single-CTA kernel */
+    uint8_t pair_cta;       /* 0 = choose by shape, 1 = two-CTA pair kernel (256 x 256 tiles; 256 x 128 for NT with tile_n <= 128), 2 = single-CTA kernel */
     uint8_t _pad[2];
     /* TileIR epilogue chain (used when n_tile_epilogue > 0; epilogue above is then ignored) */
     uint8_t n_tile_epilogue;

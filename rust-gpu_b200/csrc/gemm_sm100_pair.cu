@@ -27,7 +27,10 @@ constexpr uint32_t kPairM = 256;         // output rows per pair
 __host__ __device__ constexpr uint32_t pair_stages(uint32_t pair_n) { return pair_n == 256 ? 6 : 8; }
 
 // kPairN = output columns per pair (256, or 128 when 256-wide tiles would quantise badly over the SMs)
-template <uint32_t kPairN>
+// B_MN = B is given as B[K,N] (N contiguous): each CTA then loads its half of the columns as 64(k) x 64(n) boxes and the
+// UMMA reads B through an MN-major descriptor, exactly as the single-CTA kernel does; `map_b_half` is unused (the boxes
+// are 64 columns wide whatever the tile).
+template <uint32_t kPairN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                               const __grid_constant__ CUtensorMap map_b_half, const KParams p) {
@@ -36,12 +39,12 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;  // per CTA
     constexpr uint32_t kStages = pair_stages(kPairN);
     constexpr uint32_t kTmemCols = 2 * kPairN;                     // two accumulator buffers
-    constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(kPairM, kPairN, 0u);
+    constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(kPairM, kPairN, B_MN ? 1u : 0u);
     // Tail of the tile list: when the last wave would leave more than half of the pairs idle, its tiles are cut into two
     // half-width tiles (work items >= p.tail_start; item tail_start + 2i + h is half h of tile tail_start + i), so the wave
     // costs a half-width tile instead of a full one.  B then comes through a tensor map with a box half as tall.
     constexpr uint32_t kHalfN = kPairN / 2;
-    constexpr uint32_t kIdescHalf = ptx::make_idesc_bf16_f32(kPairM, kHalfN, 0u);
+    constexpr uint32_t kIdescHalf = ptx::make_idesc_bf16_f32(kPairM, kHalfN, B_MN ? 1u : 0u);
     constexpr uint32_t kBHalfStageBytes = (kHalfN / 2) * BK * 2;
 
     extern __shared__ uint8_t smem_raw[];
@@ -115,12 +118,20 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                     const uint32_t fb = ptx::mapa(fb_local, 0);   // the even CTA's barrier, from either CTA
                     ptx::tma_load_3d_pair(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
                                           (int32_t)(kb * BK), (int32_t)(wi.m_blk * kPairM + cta_rank * BM), (int32_t)wi.split);
-                    if (!tail)
+                    if constexpr (B_MN) {
+                        // this CTA's columns of B[K,N]: one 64(k) x 64(n) box (a [k][128 B] block) per 64 columns
+                        const uint32_t cols = tail ? kHalfN / 2 : kBHalfRows;
+                        const uint32_t n0 = wi.n_blk * kPairN + (tail ? half * kHalfN : 0) + cta_rank * cols;
+                        for (uint32_t j = 0; j < cols / 64; ++j)
+                            ptx::tma_load_3d_pair(ptx::smem_u32(b_tiles + stage * kBStageBytes + j * (BK * 128)), &map_b, fb,
+                                                  (int32_t)(n0 + j * 64), (int32_t)(kb * BK), (int32_t)wi.split);
+                    } else if (!tail) {
                         ptx::tma_load_3d_pair(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b, fb,
                                               (int32_t)(kb * BK), (int32_t)(wi.n_blk * kPairN + cta_rank * kBHalfRows), (int32_t)wi.split);
-                    else
+                    } else {
                         ptx::tma_load_3d_pair(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b_half, fb,
                                               (int32_t)(kb * BK), (int32_t)(wi.n_blk * kPairN + half * kHalfN + cta_rank * (kHalfN / 2)), (int32_t)wi.split);
+                    }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -151,7 +162,9 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; ++k4) {
                         const uint64_t da = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024);
-                        const uint64_t db = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024);
+                        // N-major B: 64-column atoms 8 KiB apart, 8-row k groups 1024 B apart; a K step is two groups
+                        const uint64_t db = B_MN ? ptx::make_smem_desc(b_addr + k4 * 2048, BK * 128, 1024)
+                                                 : ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024);
                         ptx::umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb | k4) != 0 ? 1u : 0u);
                     }
                     // the stage is free in both CTAs once these UMMAs have read it
@@ -228,10 +241,10 @@ uint32_t gemm_pair_smem_bytes(uint32_t pair_n) {
 
 namespace {
 
-template <uint32_t kPairN>
+template <uint32_t kPairN, bool B_MN>
 int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_half, KParams p, uint64_t total, uint32_t n_sms,
                          cudaStream_t stream) {
-    auto kern = gemm_bf16_tcgen05_pair_kernel<kPairN>;
+    auto kern = gemm_bf16_tcgen05_pair_kernel<kPairN, B_MN>;
     const uint32_t smem = gemm_pair_smem_bytes(kPairN);
     static bool attr_set[64] = {};
     static int max_pairs[64] = {};
@@ -257,7 +270,8 @@ int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     const uint32_t rest = (uint32_t)(total % pairs);
     static const bool no_tail = getenv("T0_NO_TAIL_SPLIT") != nullptr;
     p.tail_start = (uint32_t)total;
-    if (!no_tail && p.split_k == 1 && total > pairs && rest != 0 && 2 * rest <= pairs) p.tail_start = (uint32_t)total - rest;
+    const bool tail_ok = !(B_MN && kPairN == 128);   // B[K,N] boxes are 64 columns wide: a quarter of a 128-wide tile is too narrow
+    if (!no_tail && tail_ok && p.split_k == 1 && total > pairs && rest != 0 && 2 * rest <= pairs) p.tail_start = (uint32_t)total - rest;
     cudaError_t e = launch_pdl(kern, 2 * pairs, kThreads, smem, stream, ma, mb, mb_half, p);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "pair GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
@@ -269,12 +283,11 @@ int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
 int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
     if (g.m == 0 || g.n == 0) return T0_OK;
     if (g.k == 0) return fail(T0_ERR_INVALID, "K must be positive");
-    if (g.nn) return fail(T0_ERR_UNSUPPORTED, "the CTA-pair kernel implements the NT layout only");
     const uint32_t split = g.split_k ? g.split_k : 1;
     if (g.k % split) return fail(T0_ERR_UNSUPPORTED, "K=%u not divisible by split_k=%u", g.k, split);
     const uint32_t kps = g.k / split;
     const uint32_t ldx = g.ldx ? g.ldx : g.k;
-    const uint32_t ldb = g.ldb ? g.ldb : g.k;
+    const uint32_t ldb = g.ldb ? g.ldb : (g.nn ? g.n : g.k);
     if ((ldx % 8) || (ldb % 8) || (split > 1 && (kps % 8)))
         return fail(T0_ERR_UNSUPPORTED, "row strides (%u, %u) and, with split-K, K per split (%u) must be multiples of 8 for the TMA path", ldx, ldb, kps);
     if (((uintptr_t)g.x & 15) || ((uintptr_t)g.b & 15)) return fail(T0_ERR_UNSUPPORTED, "operand pointers must be 16-byte aligned");
@@ -294,16 +307,24 @@ int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
     CUtensorMap ma, mb;
     int rc = make_map_kmajor(&ma, g.x, g.m, ldx, kps, split, BM);
     if (rc != T0_OK) return rc;
-    rc = make_map_kmajor(&mb, g.b, g.n, ldb, kps, split, pair_n / 2);
-    if (rc != T0_OK) return rc;
     CUtensorMap mb_half;
-    rc = make_map_kmajor(&mb_half, g.b, g.n, ldb, kps, split, pair_n / 4);
+    if (g.nn) {
+        rc = make_map_nmajor(&mb, g.b, g.n, ldb, kps, split);
+        mb_half = mb;
+    } else {
+        rc = make_map_kmajor(&mb, g.b, g.n, ldb, kps, split, pair_n / 2);
+        if (rc != T0_OK) return rc;
+        rc = make_map_kmajor(&mb_half, g.b, g.n, ldb, kps, split, pair_n / 4);
+    }
     if (rc != T0_OK) return rc;
     const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * split;
     if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
     const uint32_t n_sms = g.n_sms ? g.n_sms : 148;
-    return pair_n == 256 ? launch_pair_instance<256>(ma, mb, mb_half, p, total, n_sms, stream)
-                         : launch_pair_instance<128>(ma, mb, mb_half, p, total, n_sms, stream);
+    if (g.nn)
+        return pair_n == 256 ? launch_pair_instance<256, true>(ma, mb, mb_half, p, total, n_sms, stream)
+                             : launch_pair_instance<128, true>(ma, mb, mb_half, p, total, n_sms, stream);
+    return pair_n == 256 ? launch_pair_instance<256, false>(ma, mb, mb_half, p, total, n_sms, stream)
+                         : launch_pair_instance<128, false>(ma, mb, mb_half, p, total, n_sms, stream);
 }
 
 }  // namespace t0

@@ -63,8 +63,10 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q) {
     g.tile_n = q.tile_n ? snap_tile_n(q.tile_n) : choose_tile_n(rt, q.m, q.n, q.k, split);
     if (q.nn && g.tile_n < 64) g.tile_n = 64;
     // the CTA-pair kernel (256 x 256 tiles) pays off once there are enough tiles to fill the machine
-    const bool pair_fits = !q.nn && (uint64_t)ceil_div(q.m, 256) * ceil_div(q.n, 256) * split >= (uint64_t)rt->sm_count / 2;
-    const bool use_pair = q.pair == 1 ? !q.nn : (q.pair == 0 && pair_fits && (q.tile_n == 0 || q.tile_n >= 256));
+    const bool pair_fits = (uint64_t)ceil_div(q.m, 256) * ceil_div(q.n, 256) * split >= (uint64_t)rt->sm_count / 2;
+    // (with B[K,N] the half tiles of a 128-wide pair tile would be 32 columns per CTA, under the 64-column box: 256-wide only)
+    const bool pair_ok = !q.nn || q.tile_n == 0 || q.tile_n >= 256;
+    const bool use_pair = pair_ok && (q.pair == 1 || (q.pair == 0 && pair_fits && (q.tile_n == 0 || q.tile_n >= 256)));
     if (use_pair) g.tile_n = q.tile_n;   // 0/256 -> 256-wide pair tiles, <= 128 -> 128-wide
     auto launch = [&](const GemmLaunch& gl) { return use_pair ? launch_gemm_sm100_pair(gl, rt->stream) : launch_gemm_sm100(gl, rt->stream); };
 

@@ -512,3 +512,22 @@ def test_pair_kernel_tail_tiles_full_compare(t0, oracle, rt, m, n, k, tile_n):
     assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == -9999.0)
     for buf in (xa, xb, y):
         buf.free()
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 256),        # 4 tiles
+                                   (2304, 2304, 128),      # 81 tiles: 7 tail tiles cut in halves
+                                   (2500, 2400, 200),      # ragged edges, tail tiles
+                                   (3072, 2560, 64)])      # 120 tiles, no tail
+def test_pair_kernel_nn_layout_full_compare(t0, oracle, rt, m, n, k):
+    # B given as B[K,N]: the CTA-pair kernel reads it through N-major boxes and an MN-major UMMA descriptor
+    a = oracle.fill_uniform_bf16(m * k, 42 + m)
+    b = oracle.fill_uniform_bf16(k * n, 137 + n)
+    xa, xb = rt.upload(a), rt.upload(b)
+    y = rt.alloc(m * n * 4 + 4096)
+    y.write(np.full(m * n + 1024, -9999.0, np.float32))
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, transpose=t0.NN, pair_cta=1)
+    rt.synchronize()
+    assert_gemm_close(y.read(m * n * 4, np.float32).reshape(m, n), oracle.gemm_nn(a, b, m, k, n), k)
+    assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == -9999.0)
+    for buf in (xa, xb, y):
+        buf.free()
