@@ -35,7 +35,7 @@ struct GemmLaunch {
 // K / split_k multiples of 8 elements, K % split_k == 0.  Returns a T0_* code.
 int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream);
 
-// The CTA-pair form (cta_group::2; 256 x 256 tiles, or 256 x 128 when tile_n <= 128), NT layout only.
+// The CTA-pair form (cta_group::2; 256 x 256 tiles, or 256 x 128 when tile_n <= 128); NT, and NN with 256-wide tiles.
 int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream);
 uint32_t gemm_pair_smem_bytes(uint32_t pair_n);
 
