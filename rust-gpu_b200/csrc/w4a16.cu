@@ -651,19 +651,26 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                         // Only the first contributor can hold this band in slot 1 (its range began in the band before).
                         const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
                         constexpr int kPer = kPieceFloats / (kTcWarps * 32);   // 8 outputs per thread when M = 16
+                        constexpr int kCo = 2;                                  // contributors whose pieces are in flight together
                         float total[kPer];
 #pragma unroll
                         for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
-                        for (uint32_t c = c_first; c <= c_last; ++c) {
-                            const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
-                            float v[kPer];
+                        for (uint32_t c = c_first; c <= c_last; c += kCo) {
+                            float v[kCo][kPer];
 #pragma unroll
-                            for (int j = 0; j < kPer; ++j) {
-                                const uint32_t idx = tid + j * (kTcWarps * 32);
-                                v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
+                            for (int b = 0; b < kCo; ++b) {
+                                const uint32_t cc = c + b;
+                                const float* src = p.partials + ((size_t)cc * 2 + (cc == c_first ? first_slot : 0u)) * kPieceFloats;
+#pragma unroll
+                                for (int j = 0; j < kPer; ++j) {
+                                    const uint32_t idx = tid + j * (kTcWarps * 32);
+                                    v[b][j] = (cc <= c_last && idx < p.M * kBandCols) ? __ldcg(src + idx) : 0.0f;
+                                }
                             }
 #pragma unroll
-                            for (int j = 0; j < kPer; ++j) total[j] += v[j];
+                            for (int b = 0; b < kCo; ++b)       // still added in CTA order, one contributor after the other
+#pragma unroll
+                                for (int j = 0; j < kPer; ++j) total[j] += v[b][j];
                         }
 #pragma unroll
                         for (int j = 0; j < kPer; ++j) {
@@ -705,7 +712,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 // per SM, under the 700 cycles HBM needs to deliver a step, which neither the tensor-memory form (about 100 cycles per
 // small UMMA, 16 per step) nor the first form (activations as the 16-row operand: twice the MMAs) can do.
 constexpr int kFrWarps = 16;                         // consumer warps: warp w owns columns 16w .. 16w+15 of the band, all k
-constexpr int kFrThreads = (kFrWarps + 1) * 32;      // + the TMA producer warp
+constexpr int kFrThreads = (kFrWarps + 2) * 32;      // + the producer warp + the warp that counts a head piece in
 constexpr int kFrMaxUnits = 20;                      // steps of one CTA whose activations fit beside the ring
 constexpr int kFrAUnitBytes = 2048;                  // activations of one step and one group of eight rows, in fragment order
 __device__ __forceinline__ void fr_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kFrWarps * 32) : "memory"); }
@@ -722,7 +729,9 @@ w4a16_frag_kernel(const W4Params p) {
     uint64_t* full_bar = (uint64_t*)(a_area + (size_t)p.a_units * kMGroups * kFrAUnitBytes);
     uint64_t* empty_bar = full_bar + kStages;
     uint64_t* sz_full_bar = empty_bar + kStages;
-    volatile int* abort_flag = (volatile int*)(sz_full_bar + 1);
+    uint64_t* head_written_bar = sz_full_bar + 1;      // all 16 consumer warps have stored their part of the head piece
+    uint64_t* head_counted_bar = head_written_bar + 1; // the head piece is counted in and s_head_last is valid
+    volatile int* abort_flag = (volatile int*)(head_counted_bar + 1);
     int* s_last = (int*)(abort_flag + 1);
     int* s_head_last = s_last + 1;       // band + 1 when this CTA turned out to be the last contributor of its head band
 
@@ -739,6 +748,8 @@ w4a16_frag_kernel(const W4Params p) {
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), kFrWarps);
         }
         ptx::mbar_init(ptx::smem_u32(sz_full_bar), 1);
+        ptx::mbar_init(ptx::smem_u32(head_written_bar), kFrWarps);
+        ptx::mbar_init(ptx::smem_u32(head_counted_bar), 1);
         *abort_flag = 0;
         *s_head_last = 0;
         ptx::fence_barrier_init();
@@ -750,7 +761,30 @@ w4a16_frag_kernel(const W4Params p) {
     stamp(0);
     const uint32_t band_first = u0 / p.ksteps;
     const uint32_t ks_first = u0 - band_first * p.ksteps;
+    // A head piece: the range starts inside a band (or the band is longer than the range's part of it) and goes on into
+    // the next band.  Counting it in (fence, atomic round trip) is the helper warp's job, so no consumer warp falls
+    // behind the others while the range goes on.
+    const bool has_head = (band_first + 1) * p.ksteps < u1 && ks_first != 0;
 
+    if (warp == kFrWarps + 1) {
+        // ------------------------------------------------------------ helper: counts the head piece in
+        if (lane == 0 && has_head) {
+            int last = 0;
+            if (ptx::mbar_wait(ptx::smem_u32(head_written_bar), 0, abort_flag)) {
+                const uint32_t first_unit = band_first * p.ksteps;
+                const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
+                const uint32_t c_last = owner_of(first_unit + p.ksteps - 1, gridDim.x, p.total_units);
+                __threadfence();                   // the piece is visible before this CTA is counted
+                last = atomicAdd(&p.counters[band_first], 1) == (int)(c_last - c_first);
+                if (last) __threadfence();
+            } else {
+                atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xD00000);
+            }
+            *s_head_last = last ? (int)band_first + 1 : 0;   // looked at when the range is done
+            ptx::mbar_arrive(ptx::smem_u32(head_counted_bar));
+        }
+        return;
+    }
     if (warp == kFrWarps) {
         // ------------------------------------------------------------ producer: bulk copies
         if (lane == 0) {
@@ -797,16 +831,32 @@ w4a16_frag_kernel(const W4Params p) {
 
     // Activations -> B fragments: for step u, row group mg, half j, pair pr, lane (g, t) one uint4
     // {b0(s), b1(s), b0(s+1), b1(s+1)}, s = 4j + 2pr, b0(s) = a[m][k0 + 16s + 2t .. +1], b1(s) = a[m][k0 + 16s + 2t + 8 .. +9], m = 8mg + g.
-    for (uint32_t i = tid; i < n_units * kMGroups * 128; i += kFrWarps * 32) {
-        const uint32_t ln = i & 31, pr = (i >> 5) & 1, j = (i >> 6) & 1, mg = kMGroups == 2 ? (i >> 7) & 1 : 0, unit = i / (128 * kMGroups);
-        const uint32_t m = mg * 8 + (ln >> 2), tt = ln & 3;
-        const uint32_t kks = (ks_first + unit) % p.ksteps;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (m < p.M) {
-            const uint32_t* row = (const uint32_t*)(p.a + (size_t)m * p.K + kks * kUnitK + (4 * j + 2 * pr) * 16 + 2 * tt);   // 4-byte aligned
-            v.x = __ldg(row); v.y = __ldg(row + 4); v.z = __ldg(row + 8); v.w = __ldg(row + 12);
+    // Four items per thread and pass, all their loads issued before the first store: the set-up costs one memory round
+    // trip per pass instead of one per item.
+    {
+        constexpr uint32_t kBatch = 4;
+        const uint32_t items = n_units * kMGroups * 128;
+        for (uint32_t base = 0; base < items; base += kBatch * kFrWarps * 32) {
+            uint4 v[kBatch];
+#pragma unroll
+            for (uint32_t r = 0; r < kBatch; ++r) {
+                const uint32_t i = base + r * (kFrWarps * 32) + tid;
+                const uint32_t ln = i & 31, pr = (i >> 5) & 1, j = (i >> 6) & 1, mg = kMGroups == 2 ? (i >> 7) & 1 : 0, unit = i / (128 * kMGroups);
+                const uint32_t m = mg * 8 + (ln >> 2), tt = ln & 3;
+                v[r] = make_uint4(0, 0, 0, 0);
+                if (i < items && m < p.M) {
+                    const uint32_t kks = (ks_first + unit) % p.ksteps;
+                    const uint32_t* row = (const uint32_t*)(p.a + (size_t)m * p.K + kks * kUnitK + (4 * j + 2 * pr) * 16 + 2 * tt);   // 4-byte aligned
+                    v[r].x = __ldg(row); v[r].y = __ldg(row + 4); v[r].z = __ldg(row + 8); v[r].w = __ldg(row + 12);
+                }
+            }
+#pragma unroll
+            for (uint32_t r = 0; r < kBatch; ++r) {
+                const uint32_t i = base + r * (kFrWarps * 32) + tid;
+                const uint32_t ln = i & 31, pr = (i >> 5) & 1, j = (i >> 6) & 1, mg = kMGroups == 2 ? (i >> 7) & 1 : 0, unit = i / (128 * kMGroups);
+                if (i < items) *(uint4*)(a_area + ((((size_t)unit * kMGroups + mg) * 2 + j) * 2 + pr) * 512 + ln * 16) = v[r];
+            }
         }
-        *(uint4*)(a_area + ((((size_t)unit * kMGroups + mg) * 2 + j) * 2 + pr) * 512 + ln * 16) = v;
     }
     fr_consumer_sync();
     stamp(1);
@@ -840,20 +890,27 @@ w4a16_frag_kernel(const W4Params p) {
         const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
         const uint32_t c_last = owner_of(first_unit + p.ksteps - 1, gridDim.x, p.total_units);
         const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
-        constexpr int kPer = kPieceFloats / (kFrWarps * 32);   // 8 outputs per thread when M = 16
+        constexpr int kPer = kMGroups * 8 * kBandCols / (kFrWarps * 32);   // outputs per thread: 4 for M <= 8, 8 for M <= 16
+        constexpr int kCo = 4;                                              // contributors whose pieces are in flight together
         float total[kPer];
 #pragma unroll
         for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
-        for (uint32_t c = c_first; c <= c_last; ++c) {
-            const float* src = p.partials + ((size_t)c * 2 + (c == c_first ? first_slot : 0u)) * kPieceFloats;
-            float v[kPer];
+        for (uint32_t c = c_first; c <= c_last; c += kCo) {
+            float v[kCo][kPer];
 #pragma unroll
-            for (int j = 0; j < kPer; ++j) {
-                const uint32_t idx = tid + j * (kFrWarps * 32);
-                v[j] = idx < p.M * kBandCols ? __ldcg(src + idx) : 0.0f;
+            for (int b = 0; b < kCo; ++b) {
+                const uint32_t cc = c + b;
+                const float* src = p.partials + ((size_t)cc * 2 + (cc == c_first ? first_slot : 0u)) * kPieceFloats;
+#pragma unroll
+                for (int j = 0; j < kPer; ++j) {
+                    const uint32_t idx = tid + j * (kFrWarps * 32);
+                    v[b][j] = (cc <= c_last && idx < p.M * kBandCols) ? __ldcg(src + idx) : 0.0f;
+                }
             }
 #pragma unroll
-            for (int j = 0; j < kPer; ++j) total[j] += v[j];
+            for (int b = 0; b < kCo; ++b)       // still added in CTA order, one contributor after the other
+#pragma unroll
+                for (int j = 0; j < kPer; ++j) total[j] += v[b][j];
         }
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
@@ -942,27 +999,30 @@ w4a16_frag_kernel(const W4Params p) {
                 }
             }
             if (!whole) {
-                fr_consumer_sync();                    // every thread's part of the piece is written ...
-                const bool range_goes_on = u < u1;     // this was the head band of the range: more steps follow
-                if (tid == 0) {
-                    __threadfence();                   // ... and made visible before this CTA is counted
-                    const int last = atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first);
-                    if (last) __threadfence();
-                    if (range_goes_on) *s_head_last = last ? (int)band + 1 : 0;   // looked at when the range is done
-                    else *s_last = last;
-                }
-                if (!range_goes_on) {
+                if (u < u1) {
+                    // head piece, more steps follow: hand it to the helper warp and go on
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(head_written_bar));
+                } else {
+                    fr_consumer_sync();                    // every thread's part of the piece is written ...
+                    if (tid == 0) {
+                        __threadfence();                   // ... and made visible before this CTA is counted
+                        *s_last = atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first);
+                        if (*s_last) __threadfence();
+                    }
                     fr_consumer_sync();
                     if (*s_last) reduce_band(band);
                 }
-                // (head band: nobody waits for the counter's answer; thread 0 alone pays the round trip, the ring's slack absorbs it)
             }
         }
       ks = 0;          // a further piece starts a new band
       ++band;
     }
-    fr_consumer_sync();
-    if (*s_head_last) reduce_band((uint32_t)*s_head_last - 1);
+    if (has_head) {
+        if (!ptx::mbar_wait(ptx::smem_u32(head_counted_bar), 0, abort_flag) && lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xE00000);
+        fr_consumer_sync();
+        if (*s_head_last) reduce_band((uint32_t)*s_head_last - 1);
+    }
     stamp(3);
 }
 
