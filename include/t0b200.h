@@ -261,6 +261,15 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
 /* `count` launches from an array, submitted back to back from native code (the batch form of the above; the reference's
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
+/* The same launches with x, b, y (and bias) as HOST addresses: operands are uploaded, the product is computed and the
+ * result is downloaded, and consecutive problems overlap - problem i+1 crosses the link while problem i is computed and
+ * read back (three queues, two staging sets on the device).  This is the upload / dispatch / read-back sequence of the
+ * reference's host-facing GEMM calls (T0BlasLib::gemm, src/universal/math/blas.rs:18-100; dispatch_gemm_forward,
+ * src/ignis/ops/bf16_matmul.rs:61-190) for an array of problems.  x is bf16 [m][k]; b is bf16 [n][k] (NT) or [k][n] (NN);
+ * y is f32 (or bf16 with out_bf16) [m][n]; bias f32 [n]; `planes` must be 0.  Returns when every result is in host memory.
+ * Page-locked host memory is needed for the copies to overlap. */
+int t0_gemm_launch_host_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
+int t0_gemm_launch_host(t0_runtime* rt, const t0_gemm_args* args);
 
 /* ------------------------------------------------------- cost-model records */
 /* TileConfig (src/t0/cost_model.rs:130-168) and TileCost (:171-190): the cost model's own candidate record and its

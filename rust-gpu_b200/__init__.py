@@ -624,6 +624,34 @@ class GpuRuntime:
         arr = (GemmArgs * len(args_list))(*args_list)
         _check(lib().t0_gemm_launch_batch(self._h, arr, len(args_list)))
 
+    def gemm_host_batch(self, args_list: list[GemmArgs]) -> None:
+        """``t0_gemm_launch_host_batch``: x, b, y (and bias) of every problem are HOST addresses; uploads, kernels and
+        downloads of consecutive problems overlap.  Returns when every result is in host memory."""
+        arr = (GemmArgs * len(args_list))(*args_list)
+        _check(lib().t0_gemm_launch_host_batch(self._h, arr, len(args_list)))
+
+    @staticmethod
+    def gemm_args(x: int, b: int, y: int, m: int, n: int, k: int, **kw) -> GemmArgs:
+        """The argument record of ``gemm`` / ``gemm_batch`` / ``gemm_host_batch`` (same keywords as ``gemm``)."""
+        return GpuRuntime._fill_gemm_args(x, b, y, m, n, k, **kw)
+
+    @staticmethod
+    def _fill_gemm_args(x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
+                        transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False,
+                        swap_grid: bool = True, pair_cta: int = 0, tile_epilogue: list[str] | None = None, scale: float = 1.0,
+                        clamp_min: float = 0.0, clamp_max: float = 0.0) -> GemmArgs:
+        a = GemmArgs()
+        a.x, a.b, a.y, a.bias = x, b, y, bias
+        a.m, a.n, a.k, a.tile_n, a.split_k = m, n, k, tile_n, split_k
+        a.transpose, a.epilogue, a.out_bf16, a.planes, a.swap_grid = transpose, epilogue, int(out_bf16), int(planes), int(swap_grid)
+        a.pair_cta = pair_cta
+        ops = tile_epilogue or []
+        a.n_tile_epilogue = len(ops)
+        for i, o in enumerate(ops):
+            a.tile_epilogue[i] = TEPI[o]
+        a.scale, a.clamp_min, a.clamp_max = scale, clamp_min, clamp_max
+        return a
+
     def gemm(self, x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
              transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False, swap_grid: bool = True,
              pair_cta: int = 0, tile_epilogue: list[str] | None = None, scale: float = 1.0, clamp_min: float = 0.0,
@@ -927,6 +955,8 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_dispatch_bench", i32, vp, vp, u32p, u8p, sz)
     sig("t0_gemm_launch", i32, vp, C.POINTER(GemmArgs))
     sig("t0_gemm_launch_batch", i32, vp, C.POINTER(GemmArgs), sz)
+    sig("t0_gemm_launch_host_batch", i32, vp, C.POINTER(GemmArgs), sz)
+    sig("t0_gemm_launch_host", i32, vp, C.POINTER(GemmArgs))
     sig("t0_rt_submit", i32, vp, vp, u32p, u8p, sz)
     sig("t0_rt_flush", i32, vp)
     sig("t0_shard_columns", i32, u32, u32, u32, u32p, u32p)

@@ -283,6 +283,7 @@ void t0_rt_free(t0_runtime* rt) {
     if (!rt) return;
     DeviceGuard guard(rt->device);
     cudaStreamSynchronize(rt->stream);
+    host_pipe_free(rt);
     t0_rt_pool_clear(rt);
     for (Scratch* s : {&rt->scratch_a, &rt->scratch_b, &rt->scratch_planes, &rt->scratch_w4, &rt->scratch_w, &rt->scratch_cvt_a, &rt->scratch_cvt_b, &rt->scratch_cvt_c})
         if (s->ptr) cudaFree(s->ptr);

@@ -53,9 +53,12 @@ struct t0_runtime {
     Scratch scratch_w4;          // W4A16: slab arrival counters + straddling pieces
     Scratch scratch_w;           // W4A16 general path: dequantised weights
     Scratch scratch_cvt_a, scratch_cvt_b, scratch_cvt_c;   // f32 entries: bf16 copies of the operands, f32 product before alpha/beta
+    void* host_pipe = nullptr;   // host-operand GEMM pipeline (streams, events, staging sets), made on first use
 };
 
 namespace t0 {
+
+void host_pipe_free(t0_runtime* rt);   // host_pipeline.cu
 
 #define T0_CUDA(expr)                                                                                  \
     do {                                                                                               \

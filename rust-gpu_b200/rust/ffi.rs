@@ -240,6 +240,8 @@ extern "C" {
     pub fn t0_rt_timer_stop(rt: *mut t0_runtime, ms: *mut f32) -> c_int;
     pub fn t0_gemm_launch(rt: *mut t0_runtime, args: *const t0_gemm_args) -> c_int;
     pub fn t0_gemm_launch_batch(rt: *mut t0_runtime, args: *const t0_gemm_args, count: usize) -> c_int;
+    pub fn t0_gemm_launch_host_batch(rt: *mut t0_runtime, args: *const t0_gemm_args, count: usize) -> c_int;
+    pub fn t0_gemm_launch_host(rt: *mut t0_runtime, args: *const t0_gemm_args) -> c_int;
     pub fn t0_auto_schedule_tile_costs(m: u32, n: u32, k: u32, out: *mut t0_tile_cost, cap: c_int) -> c_int;
     pub fn t0_tile_config_name(c: *const t0_tile_config, buf: *mut c_char, buf_len: usize) -> c_int;
     pub fn t0_tile_config_to_gemm_config(c: *const t0_tile_config, out: *mut t0_gemm_config) -> c_int;
