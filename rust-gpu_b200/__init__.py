@@ -630,43 +630,14 @@ class GpuRuntime:
         arr = (GemmArgs * len(args_list))(*args_list)
         _check(lib().t0_gemm_launch_host_batch(self._h, arr, len(args_list)))
 
-    @staticmethod
-    def gemm_args(x: int, b: int, y: int, m: int, n: int, k: int, **kw) -> GemmArgs:
-        """The argument record of ``gemm`` / ``gemm_batch`` / ``gemm_host_batch`` (same keywords as ``gemm``)."""
-        return GpuRuntime._fill_gemm_args(x, b, y, m, n, k, **kw)
-
-    @staticmethod
-    def _fill_gemm_args(x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
-                        transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False,
-                        swap_grid: bool = True, pair_cta: int = 0, tile_epilogue: list[str] | None = None, scale: float = 1.0,
-                        clamp_min: float = 0.0, clamp_max: float = 0.0) -> GemmArgs:
-        a = GemmArgs()
-        a.x, a.b, a.y, a.bias = x, b, y, bias
-        a.m, a.n, a.k, a.tile_n, a.split_k = m, n, k, tile_n, split_k
-        a.transpose, a.epilogue, a.out_bf16, a.planes, a.swap_grid = transpose, epilogue, int(out_bf16), int(planes), int(swap_grid)
-        a.pair_cta = pair_cta
-        ops = tile_epilogue or []
-        a.n_tile_epilogue = len(ops)
-        for i, o in enumerate(ops):
-            a.tile_epilogue[i] = TEPI[o]
-        a.scale, a.clamp_min, a.clamp_max = scale, clamp_min, clamp_max
-        return a
-
     def gemm(self, x: int, b: int, y: int, m: int, n: int, k: int, *, bias: int = 0, tile_n: int = 0, split_k: int = 1,
              transpose: int = NT, epilogue: int = 0, out_bf16: bool = False, planes: bool = False, swap_grid: bool = True,
              pair_cta: int = 0, tile_epilogue: list[str] | None = None, scale: float = 1.0, clamp_min: float = 0.0,
              clamp_max: float = 0.0) -> None:
         """Explicit-argument launch (``t0_gemm_launch``); device addresses as integers."""
-        a = GemmArgs()
-        a.x, a.b, a.y, a.bias = x, b, y, bias
-        a.m, a.n, a.k, a.tile_n, a.split_k = m, n, k, tile_n, split_k
-        a.transpose, a.epilogue, a.out_bf16, a.planes, a.swap_grid = transpose, epilogue, int(out_bf16), int(planes), int(swap_grid)
-        a.pair_cta = pair_cta
-        ops = tile_epilogue or []
-        a.n_tile_epilogue = len(ops)
-        for i, o in enumerate(ops):
-            a.tile_epilogue[i] = TEPI[o]
-        a.scale, a.clamp_min, a.clamp_max = scale, clamp_min, clamp_max
+        a = self.gemm_args(x, b, y, m, n, k, bias=bias, tile_n=tile_n, split_k=split_k, transpose=transpose, epilogue=epilogue,
+                           out_bf16=out_bf16, planes=planes, swap_grid=swap_grid, pair_cta=pair_cta, tile_epilogue=tile_epilogue,
+                           scale=scale, clamp_min=clamp_min, clamp_max=clamp_max)
         _check(lib().t0_gemm_launch(self._h, C.byref(a)))
 
     def ensure_dequant_kernel(self, group_size_log2: int, out_bf16: bool) -> GpuKernel:

@@ -92,10 +92,16 @@ struct ClockProbe {
     }
 };
 
-// One 32-column chunk of one accumulator row: epilogue, then the store (vectorised when the row
-// stride and base allow 16-byte accesses, element-wise with bounds checks otherwise).
-__device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r)[32], uint32_t row, bool row_ok, uint32_t col0,
-                                            uint32_t split, bool vec32, bool vec16) {
+constexpr uint32_t kEpiStageBytes = 4096;   // per epilogue warp: one 32 x 32 f32 chunk on its way to global memory
+
+// One 32-row x 32-column chunk of the accumulator (this lane holds row `row_base + lane`): epilogue, then the store.
+// A lane holds 32 consecutive columns of ONE row, so storing straight from registers makes every warp instruction touch
+// 32 different 128-byte lines (16 bytes of each): 256 line accesses per chunk, which made the epilogue of a 128 x 256 tile
+// cost about 5 us.  Full chunks therefore go through `stage` (this warp's 4 KiB of shared memory, 16-byte slots XOR-swizzled
+// so that neither the row-wise write nor the line-wise read has bank conflicts) and leave as whole lines: a warp instruction
+// stores four complete 128-byte row segments.  Ragged chunks (N edge, unaligned y or N) keep the element-wise path.
+__device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r)[32], uint32_t row_base, uint32_t lane, uint32_t col0,
+                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage) {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -113,34 +119,57 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
             if (p.epilogue == T0_EPI_BIAS_ADD_RELU_STORE_F32) v[j] = fmaxf(v[j], 0.0f);
         }
     }
-    if (!row_ok) return;
-    const size_t off = (size_t)split * p.plane_stride + (size_t)row * p.N + col0;
+    const size_t plane = (size_t)split * p.plane_stride;
+    const bool full = col0 + 32 <= p.N;          // warp-uniform
+    if (!p.out_bf16 && vec32 && full) {
+        float4* s4 = (float4*)stage;             // [32 rows][8 slots of 16 bytes], slot index XOR (row & 7)
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) s4[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        __syncwarp();
+        const uint32_t slot = lane & 7;
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t rr = i * 4 + (lane >> 3), row = row_base + rr;
+            const float4 q = s4[rr * 8 + (slot ^ (rr & 7))];
+            if (row < p.M) *(float4*)((float*)p.y + plane + (size_t)row * p.N + col0 + 4 * slot) = q;
+        }
+        __syncwarp();
+        return;
+    }
+    if (p.out_bf16 && vec16 && full) {
+        uint4* s4 = (uint4*)stage;               // [32 rows][4 slots of 16 bytes], slot index XOR ((row >> 1) & 3)
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            uint4 q;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+            __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+            __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+            q.x = *(uint32_t*)&h0; q.y = *(uint32_t*)&h1; q.z = *(uint32_t*)&h2; q.w = *(uint32_t*)&h3;
+            s4[lane * 4 + (j ^ ((lane >> 1) & 3))] = q;
+        }
+        __syncwarp();
+        const uint32_t slot = lane & 3;
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t rr = i * 8 + (lane >> 2), row = row_base + rr;
+            const uint4 q = s4[rr * 4 + (slot ^ ((rr >> 1) & 3))];
+            if (row < p.M) *(uint4*)((__nv_bfloat16*)p.y + plane + (size_t)row * p.N + col0 + 8 * slot) = q;
+        }
+        __syncwarp();
+        return;
+    }
+    const uint32_t row = row_base + lane;
+    if (row >= p.M) return;
+    const size_t off = plane + (size_t)row * p.N + col0;
     if (!p.out_bf16) {
         float* dst = (float*)p.y + off;
-        if (vec32 && col0 + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) ((float4*)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-        } else {
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = v[j];
-        }
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dst[j] = v[j];
     } else {
         __nv_bfloat16* dst = (__nv_bfloat16*)p.y + off;
-        if (vec16 && col0 + 32 <= p.N) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                uint4 q;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
-                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
-                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
-                q.x = *(uint32_t*)&h0; q.y = *(uint32_t*)&h1; q.z = *(uint32_t*)&h2; q.w = *(uint32_t*)&h3;
-                ((uint4*)dst)[j] = q;
-            }
-        } else {
-            for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
-        }
+        for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
     }
 }
 

@@ -43,6 +43,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + kStages * kAStageBytes;
     uint64_t* bars = (uint64_t*)(smem + kStages * kStageBytes);
+    uint8_t* epi_stage = smem + kStages * kStageBytes + 256;   // 4 x kEpiStageBytes
     uint64_t* full_bar = bars;                       // [kStages] TMA bytes landed
     uint64_t* empty_bar = bars + kStages;            // [kStages] UMMAs finished reading the stage
     uint64_t* tmem_full_bar = bars + 2 * kStages;    // [2] accumulator complete
@@ -165,8 +166,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 break;
             }
             ptx::tc_fence_after_sync();
-            const uint32_t row = wi.m_blk * BM + quarter * 32 + lane;
-            const bool row_ok = row < p.M;
+            const uint32_t row_base = wi.m_blk * BM + quarter * 32;
 #pragma unroll 1
             for (uint32_t c = 0; c < BN / 32; ++c) {
                 const uint32_t col0 = wi.n_blk * BN + c * 32;
@@ -174,7 +174,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * BN + c * 32, r);
                 ptx::tmem_ld_wait();
-                store_chunk(p, r, row, row_ok, col0, wi.split, vec32, vec16);
+                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * kEpiStageBytes);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -222,8 +222,8 @@ uint32_t gemm_stage_count(uint32_t tile_n) { return stages_for(snap_tile_n(tile_
 
 uint32_t gemm_smem_bytes(uint32_t tile_n) {
     const uint32_t bn = snap_tile_n(tile_n);
-    // tiles + barriers/holder (256 B) + slack for the 1024-byte alignment of the dynamic segment
-    return stages_for(bn) * (kAStageBytes + bn * BK * 2) + 256 + 1024;
+    // tiles + barriers/holder (256 B) + the epilogue warps' staging chunks + slack for the 1024-byte alignment of the dynamic segment
+    return stages_for(bn) * (kAStageBytes + bn * BK * 2) + 256 + 4 * kEpiStageBytes + 1024;
 }
 
 int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {

@@ -52,6 +52,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + kStages * kAStageBytes;
     uint64_t* bars = (uint64_t*)(smem + kStages * kStageBytes);
+    uint8_t* epi_stage = smem + kStages * kStageBytes + 256;   // 4 x kEpiStageBytes, one chunk per epilogue warp
     uint64_t* full_bar = bars;                          // used in the even CTA only
     uint64_t* empty_bar = bars + kStages;
     uint64_t* tmem_full_bar = bars + 2 * kStages;
@@ -197,8 +198,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 break;
             }
             ptx::tc_fence_after_sync();
-            const uint32_t row = wi.m_blk * kPairM + cta_rank * BM + quarter * 32 + lane;
-            const bool row_ok = row < p.M;
+            const uint32_t row_base = wi.m_blk * kPairM + cta_rank * BM + quarter * 32;
 #pragma unroll 1
             for (uint32_t c = 0; c < n_chunks; ++c) {
                 const uint32_t col0 = wi.n_blk * kPairN + half * kHalfN + c * 32;
@@ -206,7 +206,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * kPairN + c * 32, r);
                 ptx::tmem_ld_wait();
-                store_chunk(p, r, row, row_ok, col0, wi.split, vec32, vec16);
+                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * kEpiStageBytes);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -236,7 +236,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
 }  // namespace
 
 uint32_t gemm_pair_smem_bytes(uint32_t pair_n) {
-    return pair_stages(pair_n) * (kAStageBytes + (pair_n / 2) * BK * 2) + 256 + 1024;
+    return pair_stages(pair_n) * (kAStageBytes + (pair_n / 2) * BK * 2) + 256 + 4 * kEpiStageBytes + 1024;
 }
 
 namespace {
