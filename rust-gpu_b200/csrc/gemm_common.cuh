@@ -21,6 +21,7 @@ struct KParams {
     const float* bias;
     int* status;
     unsigned long long* probe;   // optional: {SM cycles, nanoseconds} of CTA 0, for the in-kernel clock estimate
+    unsigned long long* trace;   // optional (T0_GEMM_TRACE=1): eight nanosecond stamps of CTA 0's roles, see trace_stamp
     uint64_t plane_stride;
     uint32_t M, N, K;
     uint32_t tiles_m, tiles_n, split_k;
@@ -75,6 +76,14 @@ __device__ __forceinline__ float apply_chain(float v, float bias, const KParams&
     return v;
 }
 
+
+// Debugging aid, compiled in only with -DT0_GEMM_TRACE (the stamps cost the pair kernel 40 registers): CTA 0 records when
+// its roles pass a few points of the kernel; with T0_GEMM_TRACE=1 in the environment t0_rt_last_kernel_clock prints them.
+__device__ __forceinline__ void trace_stamp(const KParams& p, int i) {
+#ifdef T0_GEMM_TRACE
+    if (p.trace && blockIdx.x == 0) p.trace[i] = ptx::globaltimer_ns();
+#endif
+}
 
 // CTA 0 stamps the SM cycle counter and the global nanosecond timer at entry and exit; the host turns
 // the two deltas into the SM clock the kernel actually ran at (power management moves it).

@@ -242,7 +242,7 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
 
     KParams p;
     memset(&p, 0, sizeof p);
-    p.y = g.y; p.bias = g.bias; p.status = g.status; p.probe = g.probe; p.plane_stride = g.plane_stride;
+    p.y = g.y; p.bias = g.bias; p.status = g.status; p.probe = g.probe; p.trace = nullptr; p.plane_stride = g.plane_stride;
     p.M = g.m; p.N = g.n; p.K = g.k;
     p.tiles_m = ceil_div(g.m, BM); p.tiles_n = ceil_div(g.n, bn); p.split_k = split;
     p.kb_per_split = ceil_div(kps, BK);

@@ -21,7 +21,7 @@ namespace t0 {
 namespace {
 
 using namespace gemm;
-constexpr uint32_t kThreads = 192;
+constexpr uint32_t kThreads = 192;   // producer, UMMA issuer, four epilogue warps
 constexpr uint32_t kPairM = 256;         // output rows per pair
 
 __host__ __device__ constexpr uint32_t pair_stages(uint32_t pair_n) { return pair_n == 256 ? 6 : 8; }
@@ -70,6 +70,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     const uint32_t total_work = tail_start + 2 * (n_tiles - tail_start);
 
     if (threadIdx.x == 0) {
+        trace_stamp(p, 0);
         for (uint32_t s = 0; s < kStages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), 1);
@@ -94,8 +95,10 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     // everything above touched only shared and tensor memory; global memory comes after the previous grid is done
+    if (threadIdx.x == 0) trace_stamp(p, 2);
     ptx::grid_launch_dependents();
     ptx::grid_dependency_wait();
+    if (threadIdx.x == 0) trace_stamp(p, 1);
     ClockProbe probe;
     probe.begin(p);
 
@@ -158,6 +161,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                         break;
                     }
                     ptx::tc_fence_after_sync();
+                    if (kb == 0 && w == pair_id) trace_stamp(p, 3);
                     const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * kAStageBytes);
                     const uint32_t b_addr = ptx::smem_u32(b_tiles + stage * kBStageBytes);
 #pragma unroll
@@ -183,7 +187,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
-        const uint32_t quarter = warp & 3;
+        const uint32_t quarter = warp & 3;          // tensor-memory lanes 32*quarter .. +31 are the ones this warp may read
         const bool vec32 = (p.N % 4 == 0) && (((uintptr_t)p.y & 15) == 0);
         const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
         uint32_t iter = 0;
@@ -198,6 +202,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 break;
             }
             ptx::tc_fence_after_sync();
+            if (iter == 0 && threadIdx.x == 64) trace_stamp(p, 4);
             const uint32_t row_base = wi.m_blk * kPairM + cta_rank * BM + quarter * 32;
 #pragma unroll 1
             for (uint32_t c = 0; c < n_chunks; ++c) {
@@ -216,6 +221,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 else ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
             }
         }
+        if (threadIdx.x == 64) trace_stamp(p, 5);
     }
 
     // ---------------------------------------------------------------- common exit
@@ -227,6 +233,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     ptx::tc_fence_before_sync();
     __syncthreads();
     ptx::cluster_sync_all();          // the partner is done with this CTA's barriers and tensor memory
+    if (threadIdx.x == 0) trace_stamp(p, 6);
     if (warp == 1) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
@@ -296,6 +303,12 @@ int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
     KParams p;
     memset(&p, 0, sizeof p);
     p.y = g.y; p.bias = g.bias; p.status = g.status; p.probe = g.probe; p.plane_stride = g.plane_stride;
+    {
+        // T0_GEMM_TRACE=1: a ring of eight launches' stamps behind the two clock words (printed by t0_rt_last_kernel_clock)
+        static const bool tracing = getenv("T0_GEMM_TRACE") != nullptr;
+        static unsigned n_traced = 0;
+        p.trace = (tracing && g.probe) ? g.probe + 2 + 8 * (n_traced++ % 8) : nullptr;
+    }
     p.M = g.m; p.N = g.n; p.K = g.k;
     p.tiles_m = ceil_div(g.m, kPairM); p.tiles_n = ceil_div(g.n, pair_n); p.split_k = split;
     p.kb_per_split = ceil_div(kps, BK);

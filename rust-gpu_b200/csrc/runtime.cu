@@ -271,8 +271,8 @@ int t0_rt_new(int device, t0_runtime** out) {
     T0_CUDA(cudaEventCreate(&rt->ev_stop));
     T0_CUDA(cudaMalloc(&rt->d_status, sizeof(int)));
     T0_CUDA(cudaMemset(rt->d_status, 0, sizeof(int)));
-    T0_CUDA(cudaMalloc(&rt->d_probe, 2 * sizeof(unsigned long long)));
-    T0_CUDA(cudaMemset(rt->d_probe, 0, 2 * sizeof(unsigned long long)));
+    T0_CUDA(cudaMalloc(&rt->d_probe, (2 + 64) * sizeof(unsigned long long)));   // clock words + eight launches' trace stamps
+    T0_CUDA(cudaMemset(rt->d_probe, 0, (2 + 64) * sizeof(unsigned long long)));
     T0_CUDA(cudaMallocHost(&rt->h_status, sizeof(int)));
     *rt->h_status = 0;
     *out = rt.release();
@@ -324,6 +324,23 @@ int t0_rt_last_kernel_clock(t0_runtime* rt, double* sm_mhz, double* kernel_us) {
     T0_CUDA(cudaStreamSynchronize(rt->stream));
     *sm_mhz = w[1] ? (double)w[0] / (double)w[1] * 1e3 : 0.0;
     if (kernel_us) *kernel_us = (double)w[1] * 1e-3;
+    if (getenv("T0_GEMM_TRACE")) {
+        // the pair kernel's CTA 0, last eight launches: entry, prologue done, dependency wait passed, first operands landed,
+        // first tile accumulated, last store issued, exit (microseconds after the entry; then the gap to the next entry)
+        unsigned long long t[64];
+        T0_CUDA(cudaMemcpy(t, rt->d_probe + 2, sizeof t, cudaMemcpyDeviceToHost));
+        std::vector<int> order;
+        for (int i = 0; i < 8; ++i) if (t[i * 8]) order.push_back(i);
+        std::sort(order.begin(), order.end(), [&](int a, int b) { return t[a * 8] < t[b * 8]; });
+        for (size_t k = 0; k < order.size(); ++k) {
+            const unsigned long long* s = t + order[k] * 8;
+            auto us = [&](int i) { return s[i] ? (double)(s[i] - s[0]) * 1e-3 : -1.0; };
+            fprintf(stderr, "[gemm trace] prologue %.2f  dep-wait %.2f  first-load %.2f  first-tile %.2f  last-store %.2f  exit %.2f", us(2), us(1), us(3),
+                    us(4), us(5), us(6));
+            if (k + 1 < order.size()) fprintf(stderr, "  | next entry %+.2f after exit", ((double)t[order[k + 1] * 8] - (double)s[6]) * 1e-3);
+            fprintf(stderr, "\n");
+        }
+    }
     return T0_OK;
 }
 
