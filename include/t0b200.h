@@ -241,7 +241,9 @@ int t0_rt_timer_stop(t0_runtime* rt, float* ms);
 /* The launch that generate()+dispatch() amounts to, with explicit arguments instead of a kernarg blob.
  * y[M,N] (f32, or bf16 when out_bf16) = x[M,K] (bf16) * op(b): transpose T0_NT: b is [N,K]; T0_NN: b is [K,N].
  * split_k > 1 with planes != 0 writes split_k f32 planes of M*N (gemm_gen.rs:447-448); with planes == 0 the
- * partial sums are reduced on the device in split order into y.  epilogue as t0_gemm_config.epilogue. */
+ * partial sums are reduced on the device in split order into y.  epilogue as t0_gemm_config.epilogue.
+ * A request that leaves tile_n, split_k, pair_cta and planes all 0 is scheduled by the cost model (t0_cached_auto_select):
+ * tile, CTA pair or not, and possibly split-K with the device-side reduction; the result in y is complete either way. */
 typedef struct t0_gemm_args {
     uint64_t x, b, y, bias;
     uint32_t m, n, k;
