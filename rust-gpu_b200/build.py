@@ -23,6 +23,8 @@ SOURCES = ["host_config.cpp", "cost_model.cpp", "tuner.cpp", "runtime.cu", "gemm
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
+# extra compiler flags, e.g. T0_NVCC_EXTRA=-DT0_GEMM_TRACE (per-role time stamps in the pair GEMM kernel); use with --force
+NVCC_FLAGS += os.environ.get("T0_NVCC_EXTRA", "").split()
 
 
 def _headers():

@@ -131,15 +131,21 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
     const size_t plane = (size_t)split * p.plane_stride;
     const bool full = col0 + 32 <= p.N;          // warp-uniform
     if (!p.out_bf16 && vec32 && full) {
-        float4* s4 = (float4*)stage;             // [32 rows][8 slots of 16 bytes], slot index XOR (row & 7)
+        // [32 rows][8 slots of 16 bytes], slot index XOR (row & 7); explicit shared-space accesses (the pointer went
+        // through an integer for alignment, so the compiler would otherwise use generic loads and stores)
+        const uint32_t sb = ptx::smem_u32(stage);
 #pragma unroll
-        for (uint32_t j = 0; j < 8; ++j) s4[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        for (uint32_t j = 0; j < 8; ++j)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sb + (lane * 8 + (j ^ (lane & 7))) * 16), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                         "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
+                         : "memory");
         __syncwarp();
         const uint32_t slot = lane & 7;
 #pragma unroll
         for (uint32_t i = 0; i < 8; ++i) {
             const uint32_t rr = i * 4 + (lane >> 3), row = row_base + rr;
-            const float4 q = s4[rr * 8 + (slot ^ (rr & 7))];
+            float4 q;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w) : "r"(sb + (rr * 8 + (slot ^ (rr & 7))) * 16) : "memory");
             if (row < p.M) *(float4*)((float*)p.y + plane + (size_t)row * p.N + col0 + 4 * slot) = q;
         }
         __syncwarp();
