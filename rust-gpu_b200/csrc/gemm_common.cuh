@@ -29,6 +29,7 @@ struct KParams {
     uint32_t swap_grid, raster_group;
     uint32_t tail_start;         // pair kernel: work items from here on are half-width tiles (two per output tile); = total when unused
     uint32_t out_bf16, epilogue, n_ops;
+    uint32_t tma_store;          // pair kernel: full f32 chunks leave through the output tensor map
     float scale, clamp_min, clamp_max;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
 };
@@ -109,8 +110,12 @@ constexpr uint32_t kEpiStageBytes = 4096;   // per epilogue warp: one 32 x 32 f3
 // cost about 5 us.  Full chunks therefore go through `stage` (this warp's 4 KiB of shared memory, 16-byte slots XOR-swizzled
 // so that neither the row-wise write nor the line-wise read has bank conflicts) and leave as whole lines: a warp instruction
 // stores four complete 128-byte row segments.  Ragged chunks (N edge, unaligned y or N) keep the element-wise path.
+// With `map_y` (an f32 output the TMA unit can address: 16-byte aligned base and row pitch) the staged block leaves as ONE
+// tiled TMA store instead of eight loads from the block and eight line-wise stores: the block's XOR pattern is the 128-byte
+// swizzle of the tensor map, rows beyond M are clipped by the copy.  `stage` must then be 1024-byte aligned, the caller
+// alternates between two blocks from chunk to chunk, and waits for its stores (ptx::bulk_wait_group_all by lane 0) before shared memory goes away.
 __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r)[32], uint32_t row_base, uint32_t lane, uint32_t col0,
-                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage) {
+                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage, const CUtensorMap* map_y = nullptr) {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -134,11 +139,24 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
         // [32 rows][8 slots of 16 bytes], slot index XOR (row & 7); explicit shared-space accesses (the pointer went
         // through an integer for alignment, so the compiler would otherwise use generic loads and stores)
         const uint32_t sb = ptx::smem_u32(stage);
+        if (map_y) {
+            if (lane == 0) ptx::bulk_wait_group_read_but_one();   // two blocks alternate: the store before the previous one has read this block
+            __syncwarp();
+        }
 #pragma unroll
         for (uint32_t j = 0; j < 8; ++j)
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sb + (lane * 8 + (j ^ (lane & 7))) * 16), "f"(v[4 * j]), "f"(v[4 * j + 1]),
                          "f"(v[4 * j + 2]), "f"(v[4 * j + 3])
                          : "memory");
+        if (map_y) {
+            ptx::fence_proxy_async_smem();                    // the copy reads the block through the async proxy
+            __syncwarp();
+            if (lane == 0 && row_base < p.M) {               // a box that starts below the last row has nothing to write
+                ptx::tma_store_3d(map_y, sb, (int32_t)col0, (int32_t)row_base, (int32_t)split);
+                ptx::bulk_commit_group();
+            }
+            return;
+        }
         __syncwarp();
         const uint32_t slot = lane & 7;
 #pragma unroll
@@ -257,6 +275,21 @@ inline int make_map_2d_plain(CUtensorMap* map, const void* base, uint32_t elem_b
                      strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (plain 2-D, %llu x %llu) failed: %d", (unsigned long long)rows, (unsigned long long)cols, (int)r);
+    return T0_OK;
+}
+
+// 3-D view [planes][M][N] of the f32 output (or of split-K planes `plane_stride` elements apart), box 32 x 32, 128-byte
+// swizzle: what the epilogue's TMA store writes through.  Needs a 16-byte aligned base and N % 4 == 0.
+inline int make_map_out_f32(CUtensorMap* map, const void* base, uint32_t M, uint32_t N, uint32_t planes, uint64_t plane_stride) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {N, M, planes > 1 ? planes : 1};
+    cuuint64_t strides[2] = {(cuuint64_t)N * 4, planes > 1 ? (cuuint64_t)plane_stride * 4 : (cuuint64_t)M * N * 4};
+    cuuint32_t box[3] = {32, 32, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (f32 output %u x %u) failed: %d", M, N, (int)r);
     return T0_OK;
 }
 

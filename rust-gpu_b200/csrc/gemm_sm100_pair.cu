@@ -33,7 +33,7 @@ __host__ __device__ constexpr uint32_t pair_stages(uint32_t pair_n) { return pai
 template <uint32_t kPairN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                              const __grid_constant__ CUtensorMap map_b_half, const KParams p) {
+                              const __grid_constant__ CUtensorMap map_b_half, const __grid_constant__ CUtensorMap map_y, const KParams p) {
     constexpr uint32_t kBHalfRows = kPairN / 2;                    // rows of B each CTA loads
     constexpr uint32_t kBStageBytes = kBHalfRows * BK * 2;
     constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;  // per CTA
@@ -51,8 +51,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + kStages * kAStageBytes;
-    uint64_t* bars = (uint64_t*)(smem + kStages * kStageBytes);
-    uint8_t* epi_stage = smem + kStages * kStageBytes + 256;   // 4 x kEpiStageBytes, one chunk per epilogue warp
+    uint8_t* epi_stage = smem + kStages * kStageBytes;          // 4 warps x 2 blocks of kEpiStageBytes; 1024-byte aligned
+    uint64_t* bars = (uint64_t*)(epi_stage + 8 * kEpiStageBytes);
     uint64_t* full_bar = bars;                          // used in the even CTA only
     uint64_t* empty_bar = bars + kStages;
     uint64_t* tmem_full_bar = bars + 2 * kStages;
@@ -84,6 +84,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         ptx::fence_proxy_async_smem();
         ptx::tma_prefetch_desc(&map_a);
         ptx::tma_prefetch_desc(&map_b);
+        if (p.tma_store) ptx::tma_prefetch_desc(&map_y);
     }
     if (warp == 1) {
         ptx::tmem_alloc_pair(ptx::smem_u32(tmem_holder), kTmemCols);
@@ -211,7 +212,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * kPairN + c * 32, r);
                 ptx::tmem_ld_wait();
-                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * kEpiStageBytes);
+                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + (quarter * 2 + (c & 1)) * kEpiStageBytes, p.tma_store ? &map_y : nullptr);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -221,6 +222,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 else ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
             }
         }
+        if (p.tma_store && lane == 0) ptx::bulk_wait_group_all();   // this warp's stores are complete before shared memory goes away
         if (threadIdx.x == 64) trace_stamp(p, 5);
     }
 
@@ -243,13 +245,13 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
 }  // namespace
 
 uint32_t gemm_pair_smem_bytes(uint32_t pair_n) {
-    return pair_stages(pair_n) * (kAStageBytes + (pair_n / 2) * BK * 2) + 256 + 4 * kEpiStageBytes + 1024;
+    return pair_stages(pair_n) * (kAStageBytes + (pair_n / 2) * BK * 2) + 256 + 8 * kEpiStageBytes + 1024;
 }
 
 namespace {
 
 template <uint32_t kPairN, bool B_MN>
-int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_half, KParams p, uint64_t total, uint32_t n_sms,
+int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb_half, const CUtensorMap& my, KParams p, uint64_t total, uint32_t n_sms,
                          cudaStream_t stream) {
     auto kern = gemm_bf16_tcgen05_pair_kernel<kPairN, B_MN>;
     const uint32_t smem = gemm_pair_smem_bytes(kPairN);
@@ -279,7 +281,7 @@ int launch_pair_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUt
     p.tail_start = (uint32_t)total;
     const bool tail_ok = !(B_MN && kPairN == 128);   // B[K,N] boxes are 64 columns wide: a quarter of a 128-wide tile is too narrow
     if (!no_tail && tail_ok && p.split_k == 1 && total > pairs && rest != 0 && 2 * rest <= pairs) p.tail_start = (uint32_t)total - rest;
-    cudaError_t e = launch_pdl(kern, 2 * pairs, kThreads, smem, stream, ma, mb, mb_half, p);
+    cudaError_t e = launch_pdl(kern, 2 * pairs, kThreads, smem, stream, ma, mb, mb_half, my, p);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "pair GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
 }
@@ -332,12 +334,20 @@ int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
     if (rc != T0_OK) return rc;
     const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * split;
     if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
+    // f32 output the TMA unit can address (16-byte aligned base, row pitch and plane pitch): full chunks leave as TMA stores
+    static const bool no_tma_store = getenv("T0_NO_TMA_STORE") != nullptr;
+    CUtensorMap my = ma;   // a valid map either way; only read when p.tma_store is set
+    if (!no_tma_store && !g.out_bf16 && g.n % 4 == 0 && ((uintptr_t)g.y & 15) == 0 && (split == 1 || g.plane_stride % 4 == 0)) {
+        rc = make_map_out_f32(&my, g.y, g.m, g.n, split, g.plane_stride);
+        if (rc != T0_OK) return rc;
+        p.tma_store = 1;
+    }
     const uint32_t n_sms = g.n_sms ? g.n_sms : 148;
     if (g.nn)
-        return pair_n == 256 ? launch_pair_instance<256, true>(ma, mb, mb_half, p, total, n_sms, stream)
-                             : launch_pair_instance<128, true>(ma, mb, mb_half, p, total, n_sms, stream);
-    return pair_n == 256 ? launch_pair_instance<256, false>(ma, mb, mb_half, p, total, n_sms, stream)
-                         : launch_pair_instance<128, false>(ma, mb, mb_half, p, total, n_sms, stream);
+        return pair_n == 256 ? launch_pair_instance<256, true>(ma, mb, mb_half, my, p, total, n_sms, stream)
+                             : launch_pair_instance<128, true>(ma, mb, mb_half, my, p, total, n_sms, stream);
+    return pair_n == 256 ? launch_pair_instance<256, false>(ma, mb, mb_half, my, p, total, n_sms, stream)
+                         : launch_pair_instance<128, false>(ma, mb, mb_half, my, p, total, n_sms, stream);
 }
 
 }  // namespace t0

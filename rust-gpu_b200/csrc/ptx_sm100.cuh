@@ -223,6 +223,21 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtens
         : "memory");
 }
 
+// Tiled TMA store of one box from shared to global memory (bulk async-group completion).  Rows and columns of the box
+// that lie outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t smem_src, int32_t c0, int32_t c1, int32_t c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"((uint64_t)map), "r"(smem_src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the shared-memory source of every committed store has been read (the buffer may be overwritten)
+__device__ __forceinline__ void bulk_wait_group_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... of every committed store but the latest one
+__device__ __forceinline__ void bulk_wait_group_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// every committed store is complete
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------ descriptors
 // Shared-memory matrix descriptor (sm_100 format): start address, leading/stride byte offsets in
 // 16-byte units, descriptor version 1 at bit 46, swizzle mode at bits 61..63 (2 = 128-byte swizzle).
