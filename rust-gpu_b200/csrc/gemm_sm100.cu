@@ -30,7 +30,8 @@ __host__ __device__ constexpr uint32_t stages_for(uint32_t bn) { return bn == 25
 
 template <uint32_t BN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_y, const KParams p) {
     constexpr uint32_t kStages = stages_for(BN);
     constexpr uint32_t kBStageBytes = BN * BK * 2;
     constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;
@@ -42,8 +43,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* a_tiles = smem;
     uint8_t* b_tiles = smem + kStages * kAStageBytes;
-    uint64_t* bars = (uint64_t*)(smem + kStages * kStageBytes);
-    uint8_t* epi_stage = smem + kStages * kStageBytes + 256;   // 4 x kEpiStageBytes
+    uint8_t* epi_stage = smem + kStages * kStageBytes;          // 4 warps x 2 blocks of kEpiStageBytes; 1024-byte aligned
+    uint64_t* bars = (uint64_t*)(epi_stage + 8 * kEpiStageBytes);
     uint64_t* full_bar = bars;                       // [kStages] TMA bytes landed
     uint64_t* empty_bar = bars + kStages;            // [kStages] UMMAs finished reading the stage
     uint64_t* tmem_full_bar = bars + 2 * kStages;    // [2] accumulator complete
@@ -69,6 +70,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         ptx::fence_proxy_async_smem();
         ptx::tma_prefetch_desc(&map_a);
         ptx::tma_prefetch_desc(&map_b);
+        if (p.tma_store) ptx::tma_prefetch_desc(&map_y);
     }
     if (warp == 1) {
         ptx::tmem_alloc(ptx::smem_u32(tmem_holder), kTmemCols);
@@ -174,12 +176,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * BN + c * 32, r);
                 ptx::tmem_ld_wait();
-                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * kEpiStageBytes);
+                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + (quarter * 2 + (c & 1)) * kEpiStageBytes,
+                            p.tma_store ? &map_y : nullptr);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tmem_empty_bar[buf]));
         }
+        if (p.tma_store && lane == 0) ptx::bulk_wait_group_all();   // this warp's stores are complete before shared memory goes away
     }
 
     // ---------------------------------------------------------------- common exit
@@ -200,7 +204,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 // ------------------------------------------------------------------ host side
 
 template <uint32_t BN, bool B_MN>
-int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KParams& p, uint32_t grid, cudaStream_t stream) {
+int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const KParams& p, uint32_t grid, cudaStream_t stream) {
     auto kern = gemm_bf16_tcgen05_kernel<BN, B_MN>;
     const uint32_t smem = gemm_smem_bytes(BN);
     static bool attr_set[64] = {};   // per instantiation, per device
@@ -211,7 +215,7 @@ int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const KParams&
         if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaFuncSetAttribute(smem=%u): %s", smem, cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    cudaError_t e = launch_pdl(kern, grid, kThreads, smem, stream, ma, mb, p);
+    cudaError_t e = launch_pdl(kern, grid, kThreads, smem, stream, ma, mb, my, p);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
 }
@@ -223,7 +227,7 @@ uint32_t gemm_stage_count(uint32_t tile_n) { return stages_for(snap_tile_n(tile_
 uint32_t gemm_smem_bytes(uint32_t tile_n) {
     const uint32_t bn = snap_tile_n(tile_n);
     // tiles + barriers/holder (256 B) + the epilogue warps' staging chunks + slack for the 1024-byte alignment of the dynamic segment
-    return stages_for(bn) * (kAStageBytes + bn * BK * 2) + 256 + 4 * kEpiStageBytes + 1024;
+    return stages_for(bn) * (kAStageBytes + bn * BK * 2) + 256 + 8 * kEpiStageBytes + 1024;
 }
 
 int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
@@ -260,19 +264,27 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
     const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * split;
     if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
     const uint32_t grid = (uint32_t)std::min<uint64_t>(total, g.n_sms ? g.n_sms : 148);
+    // f32 output the TMA unit can address (16-byte aligned base, row pitch and plane pitch): full chunks leave as TMA stores
+    static const bool no_tma_store = getenv("T0_NO_TMA_STORE") != nullptr;
+    CUtensorMap my = ma;   // a valid map either way; only read when p.tma_store is set
+    if (!no_tma_store && !g.out_bf16 && g.n % 4 == 0 && ((uintptr_t)g.y & 15) == 0 && (split == 1 || g.plane_stride % 4 == 0)) {
+        rc = make_map_out_f32(&my, g.y, g.m, g.n, split, g.plane_stride);
+        if (rc != T0_OK) return rc;
+        p.tma_store = 1;
+    }
 
     if (g.nn) {
         switch (bn) {
-            case 64: return launch_instance<64, true>(ma, mb, p, grid, stream);
-            case 128: return launch_instance<128, true>(ma, mb, p, grid, stream);
-            default: return launch_instance<256, true>(ma, mb, p, grid, stream);
+            case 64: return launch_instance<64, true>(ma, mb, my, p, grid, stream);
+            case 128: return launch_instance<128, true>(ma, mb, my, p, grid, stream);
+            default: return launch_instance<256, true>(ma, mb, my, p, grid, stream);
         }
     }
     switch (bn) {
-        case 32: return launch_instance<32, false>(ma, mb, p, grid, stream);
-        case 64: return launch_instance<64, false>(ma, mb, p, grid, stream);
-        case 128: return launch_instance<128, false>(ma, mb, p, grid, stream);
-        default: return launch_instance<256, false>(ma, mb, p, grid, stream);
+        case 32: return launch_instance<32, false>(ma, mb, my, p, grid, stream);
+        case 64: return launch_instance<64, false>(ma, mb, my, p, grid, stream);
+        case 128: return launch_instance<128, false>(ma, mb, my, p, grid, stream);
+        default: return launch_instance<256, false>(ma, mb, my, p, grid, stream);
     }
 }
 
