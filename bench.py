@@ -46,8 +46,8 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from the ncu capture summarised
 # in profiles/ (bytes); None until a capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": 127.5e6, "w4a16_m1_n11008": 23.46e6,
-                     "gemm_bf16_skinny_64x4096x16384_sk4": 143.2e6 + 5.2e6}   # GEMM kernel + plane reduction
+NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": 142.4e6, "w4a16_m1_n11008": 23.47e6,
+                     "gemm_bf16_skinny_64x4096x16384_sk4": 144.0e6 + 5.2e6}   # GEMM kernel + plane reduction
 W4_GROUP = 128
 
 
