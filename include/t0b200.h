@@ -79,7 +79,10 @@ int t0_sweep_configs(t0_gemm_config* out, int cap);
 int t0_standard_configs(t0_gemm_config* out, int cap);
 
 /* ------------------------------------------------- selection (a6, a7, a8) */
-/* auto_select(m, k, n) (gemm_gen.rs:340-342 -> cost_model.rs:660-668). Argument order (m, k, n). */
+/* auto_select(m, k, n) (gemm_gen.rs:340-342 -> cost_model.rs:660-668). Argument order (m, k, n).
+ * Environment: T0_FORCE_CFG=<preset name> (a GemmConfig constructor name such as tile_128x64_k32, optionally followed by
+ * ":sk<N>" for split-K) makes auto_select and cached_auto_select return that config for every shape - an A/B and
+ * debugging switch of the same family as the reference's T0_* ablation variables (gpu_context.rs:327,335). */
 int t0_auto_select(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out);
 /* auto_select_legacy(m, k, n) (gemm_gen.rs:351-404): the hand-tuned table, verbatim semantics. */
 int t0_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out);
@@ -174,6 +177,16 @@ void t0_rt_mark_poisoned(t0_runtime* rt);
 /* queue.synchronize() / wait_idle() (src/kfd/aql.rs:473): drain the stream; a device-side failure poisons the runtime. */
 int t0_rt_synchronize(t0_runtime* rt);
 int t0_rt_wait_idle(t0_runtime* rt);
+/* The wait limit of AqlQueue::wait_read_ptr (src/kfd/aql.rs:529-549: the reference gives up on a dispatch after a fixed time,
+ * returns Err and the runtime is poisoned, gpu_context.rs:352-355).  Here the limit applies to every single barrier wait
+ * inside a GEMM kernel (default 2 s; 0 restores the default): a wait that runs out makes the kernel unwind, release its tensor
+ * memory and write a status word; the next synchronising call returns T0_ERR_TIMEOUT and poisons the runtime. */
+int t0_rt_set_wait_limit_ns(t0_runtime* rt, uint64_t ns);
+/* Self-test of that path (no counterpart in the reference): the NEXT GEMM launch of this runtime leaves out the first
+ * operand load of its first tile, so that tile's accumulate wait runs out after the wait limit.  Nothing faults and the
+ * kernel returns by itself; the call that synchronises reports T0_ERR_TIMEOUT, the runtime is poisoned, the output of
+ * that launch is incomplete.  Set a short limit first (milliseconds).  For tests of the error handling only. */
+int t0_rt_selftest_drop_one_load(t0_runtime* rt);
 /* the CUDA stream handle (cudaStream_t) and device ordinal, for callers that time or order work themselves */
 void* t0_rt_stream(const t0_runtime* rt);
 int t0_rt_device(const t0_runtime* rt);
@@ -421,10 +434,21 @@ int t0_w4a16_gemm_prepacked_batch(t0_runtime* rt, const t0_w4a16_args* args, siz
  * frees.  Limits: M <= 16, K % 128 == 0, group % 128 == 0, N % 32 == 0, N <= 1048576, at most 160 SMs; anything else
  * returns T0_ERR_UNSUPPORTED (there is no two-step fallback here).  The first call on a device looks up the array's
  * address: make it before starting a stream capture.  All calls on one device share the array: calls that overlap in
- * time (different runtimes or streams) race; calls on one runtime are ordered by its stream. */
+ * time (different runtimes or streams) race; calls on one runtime are ordered by its stream.  The array holds arrival
+ * counters that a completed call leaves at zero; a call that ended in T0_ERR_TIMEOUT may not, so every runtime clears them
+ * (a stream-ordered memset, no allocation) before its first static call: after such a failure make a new runtime, and do
+ * not go on using this entry from other runtimes of the same device that were created before the failure. */
 int t0_w4a16_gemm_static(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
                          uint32_t K, uint32_t group);
 size_t t0_w4a16_gemm_static_scratch_bytes(void);
+/* Int4WmmaConfig (quant_kernels.rs:316-336): the INT4 tile record {tile_m, tile_n, tile_k} with its two constructors,
+ * k16() = 16 x 16 x 16 and k32() = 16 x 16 x 32.  The reference only describes its integer WMMA tile with it and no kernel
+ * reads it; it is kept so that code that builds or prints one still compiles against this library. */
+typedef struct t0_int4_wmma_config {
+    uint32_t tile_m, tile_n, tile_k;
+} t0_int4_wmma_config;
+int t0_int4_wmma_config_k16(t0_int4_wmma_config* out);
+int t0_int4_wmma_config_k32(t0_int4_wmma_config* out);
 /* GptqWeight::from_bytes (quant_kernels.rs:242-286): header rows, cols, group_size (u32 LE), packed codes, f32 scales,
  * i32 zero points.  Fills the three section offsets; the asserts of the reference are error codes here. */
 int t0_gptq_parse(const uint8_t* raw, size_t len, uint32_t* rows, uint32_t* cols, uint32_t* group_size, size_t* packed_off,

@@ -271,6 +271,23 @@ class W4A16Args(C.Structure):
                 ("m", C.c_uint32), ("n", C.c_uint32), ("k", C.c_uint32), ("group", C.c_uint32)]
 
 
+class Int4WmmaConfig(C.Structure):
+    """``Int4WmmaConfig`` (quant_kernels.rs:316-336): the INT4 tile record and its two constructors."""
+    _fields_ = [("tile_m", C.c_uint32), ("tile_n", C.c_uint32), ("tile_k", C.c_uint32)]
+
+    @classmethod
+    def k16(cls) -> "Int4WmmaConfig":
+        out = cls()
+        _check(lib().t0_int4_wmma_config_k16(C.byref(out)))
+        return out
+
+    @classmethod
+    def k32(cls) -> "Int4WmmaConfig":
+        out = cls()
+        _check(lib().t0_int4_wmma_config_k32(C.byref(out)))
+        return out
+
+
 # --------------------------------------------------------------------------- selection / grids / kernargs
 
 def auto_select(m: int, k: int, n: int) -> GemmConfig:
@@ -496,6 +513,14 @@ class GpuRuntime:
         _check(lib().t0_rt_synchronize(self._h))
 
     wait_idle = synchronize
+
+    def set_wait_limit_ns(self, ns: int) -> None:
+        """Limit of every single device-side barrier wait of the GEMM kernels (0 = default, 2 s)."""
+        _check(lib().t0_rt_set_wait_limit_ns(self._h, ns))
+
+    def selftest_drop_one_load(self) -> None:
+        """Arms the failure-path self-test: the next GEMM launch leaves out one operand load (see the header)."""
+        _check(lib().t0_rt_selftest_drop_one_load(self._h))
 
     def stream(self) -> int:
         return int(lib().t0_rt_stream(self._h) or 0)
@@ -892,6 +917,10 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_mark_poisoned", None, vp)
     sig("t0_rt_synchronize", i32, vp)
     sig("t0_rt_wait_idle", i32, vp)
+    sig("t0_rt_set_wait_limit_ns", i32, vp, u64)
+    sig("t0_rt_selftest_drop_one_load", i32, vp)
+    sig("t0_int4_wmma_config_k16", i32, vp)
+    sig("t0_int4_wmma_config_k32", i32, vp)
     sig("t0_rt_stream", vp, vp)
     sig("t0_rt_device", i32, vp)
     sig("t0_rt_sm_count", i32, vp)

@@ -17,6 +17,8 @@ uint32_t gemm_pair_smem_bytes(uint32_t pair_n);   // gemm_sm100_pair.cu
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
+#include <string>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -241,8 +243,29 @@ int t0_auto_select_legacy(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* ou
     return T0_OK;
 }
 
+// T0_FORCE_CFG=<preset>[:sk<N>]: one config for every shape (read on every call, so a test can set and clear it).
+static int forced_config(t0_gemm_config* out) {
+    const char* f = getenv("T0_FORCE_CFG");
+    if (!f || !*f) return -1;
+    std::string name(f);
+    uint32_t sk = 0;
+    const size_t colon = name.find(":sk");
+    if (colon != std::string::npos) {
+        sk = (uint32_t)strtoul(name.c_str() + colon + 3, nullptr, 10);
+        name.resize(colon);
+    }
+    int rc = t0_gemm_config_preset(name.c_str(), out);
+    if (rc != T0_OK) return fail(T0_ERR_INVALID, "T0_FORCE_CFG=%s does not name a GemmConfig preset", f);
+    if (sk > 1) {
+        if (sk & (sk - 1)) return fail(T0_ERR_INVALID, "T0_FORCE_CFG=%s: split_k must be a power of 2", f);
+        out->split_k = sk;
+    }
+    return T0_OK;
+}
+
 int t0_auto_select(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out) {
     if (!out) return fail(T0_ERR_INVALID, "null output");
+    { const int fr = forced_config(out); if (fr >= 0) return fr; }
     std::vector<Candidate> c = schedule(m, n, k);
     if (!c.empty()) { *out = c[0].cfg; return T0_OK; }
     // cost_model.rs:662-667: fall back to the hand table when the search finds nothing
@@ -259,6 +282,7 @@ int t0_auto_select_backward_weight(uint32_t m, uint32_t n_orig, uint32_t k_orig,
 
 int t0_cached_auto_select(uint32_t m, uint32_t k, uint32_t n, t0_gemm_config* out) {
     if (!out) return fail(T0_ERR_INVALID, "null output");
+    { const int fr = forced_config(out); if (fr >= 0) return fr; }   // a forced config is never cached
     auto key = std::make_tuple(m, k, n);
     {
         std::lock_guard<std::mutex> g(g_cache_mu);

@@ -23,13 +23,15 @@ struct KParams {
     unsigned long long* probe;   // optional: {SM cycles, nanoseconds} of CTA 0, for the in-kernel clock estimate
     unsigned long long* trace;   // optional (T0_GEMM_TRACE=1): eight nanosecond stamps of CTA 0's roles, see trace_stamp
     uint64_t plane_stride;
+    uint64_t wait_limit_ns;      // limit of every single barrier wait in this launch
     uint32_t M, N, K;
     uint32_t tiles_m, tiles_n, split_k;
     uint32_t kb_per_split;
     uint32_t swap_grid, raster_group;
     uint32_t tail_start;         // pair kernel: work items from here on are half-width tiles (two per output tile); = total when unused
     uint32_t out_bf16, epilogue, n_ops;
-    uint32_t tma_store;          // pair kernel: full f32 chunks leave through the output tensor map
+    uint32_t tma_store;          // full f32 chunks leave through the output tensor map
+    uint32_t drop_load;          // self-test of the failure path: the producer of CTA 0 leaves out its first operand load
     float scale, clamp_min, clamp_max;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
 };
@@ -112,10 +114,14 @@ constexpr uint32_t kEpiStageBytes = 4096;   // per epilogue warp: one 32 x 32 f3
 // stores four complete 128-byte row segments.  Ragged chunks (N edge, unaligned y or N) keep the element-wise path.
 // With `map_y` (an f32 output the TMA unit can address: 16-byte aligned base and row pitch) the staged block leaves as ONE
 // tiled TMA store instead of eight loads from the block and eight line-wise stores: the block's XOR pattern is the 128-byte
-// swizzle of the tensor map, rows beyond M are clipped by the copy.  `stage` must then be 1024-byte aligned, the caller
-// alternates between two blocks from chunk to chunk, and waits for its stores (ptx::bulk_wait_group_all by lane 0) before shared memory goes away.
+// swizzle of the tensor map, rows beyond M are clipped by the copy.  `stage` is the warp's pair of blocks (1024-byte aligned,
+// kEpiStageBytes each).  `n_stores` is the warp's running count of committed TMA stores, carried across chunks AND tiles: store
+// i leaves from block i & 1, and before block i & 1 is rewritten the warp waits until every committed store but the latest
+// (which left from the other block) has read its source.  Counting only committed stores keeps that true when a tile has
+// an odd number of full chunks, a single chunk, or rows the copy would clip entirely.  The caller waits for its stores
+// (ptx::bulk_wait_group_all by lane 0) before shared memory goes away.
 __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r)[32], uint32_t row_base, uint32_t lane, uint32_t col0,
-                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage, const CUtensorMap* map_y = nullptr) {
+                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage, uint32_t& n_stores, const CUtensorMap* map_y = nullptr) {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -138,9 +144,10 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
     if (!p.out_bf16 && vec32 && full) {
         // [32 rows][8 slots of 16 bytes], slot index XOR (row & 7); explicit shared-space accesses (the pointer went
         // through an integer for alignment, so the compiler would otherwise use generic loads and stores)
-        const uint32_t sb = ptx::smem_u32(stage);
+        if (map_y && row_base >= p.M) return;                 // warp-uniform: a box that starts below the last row has nothing to write
+        const uint32_t sb = ptx::smem_u32(stage) + (map_y ? (n_stores & 1u) * kEpiStageBytes : 0u);
         if (map_y) {
-            if (lane == 0) ptx::bulk_wait_group_read_but_one();   // two blocks alternate: the store before the previous one has read this block
+            if (lane == 0) ptx::bulk_wait_group_read_but_one();   // the latest committed store left from the other block
             __syncwarp();
         }
 #pragma unroll
@@ -151,10 +158,11 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
         if (map_y) {
             ptx::fence_proxy_async_smem();                    // the copy reads the block through the async proxy
             __syncwarp();
-            if (lane == 0 && row_base < p.M) {               // a box that starts below the last row has nothing to write
+            if (lane == 0) {
                 ptx::tma_store_3d(map_y, sb, (int32_t)col0, (int32_t)row_base, (int32_t)split);
                 ptx::bulk_commit_group();
             }
+            ++n_stores;
             return;
         }
         __syncwarp();

@@ -94,12 +94,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
                 const WorkItem wi = decode_work(w, p);
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.wait_limit_ns)) {
                         atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(w & 0xFFFFFF));
                         ok = false;
                         break;
                     }
                     const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
+                    // self-test of the failure path: this stage is never filled, so the issuer's bounded wait must run out
+                    if (p.drop_load && blockIdx.x == 0 && w == 0 && kb == 0) { if (++stage == kStages) { stage = 0; phase ^= 1; } continue; }
                     ptx::mbar_arrive_expect_tx(fb, kStageBytes);
                     ptx::tma_load_3d(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
                                      (int32_t)(kb * BK), (int32_t)(wi.m_blk * BM), (int32_t)wi.split);
@@ -124,14 +126,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x, ++iter) {
                 const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
-                if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, abort_flag)) {
+                if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, abort_flag, p.wait_limit_ns)) {
                     atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(w & 0xFFFFFF));
                     break;
                 }
                 ptx::tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag, p.wait_limit_ns)) {
                         atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000 | (int)(w & 0x7FFFFF));
                         ok = false;
                         break;
@@ -159,11 +161,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         const uint32_t quarter = warp & 3;   // tensor-memory lanes 32*quarter .. +31 belong to this warp
         const bool vec32 = (p.N % 4 == 0) && (((uintptr_t)p.y & 15) == 0);
         const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
-        uint32_t iter = 0;
+        uint32_t iter = 0, n_stores = 0;     // n_stores: this warp's committed TMA stores, see store_chunk
         for (uint32_t w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
             const WorkItem wi = decode_work(w, p);
             const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
-            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag)) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag, p.wait_limit_ns)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(w & 0xFFFFFF));
                 break;
             }
@@ -176,7 +178,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * BN + c * 32, r);
                 ptx::tmem_ld_wait();
-                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + (quarter * 2 + (c & 1)) * kEpiStageBytes,
+                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * 2 * kEpiStageBytes, n_stores,
                             p.tma_store ? &map_y : nullptr);
             }
             ptx::tc_fence_before_sync();
@@ -246,6 +248,7 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
 
     KParams p;
     memset(&p, 0, sizeof p);
+    p.wait_limit_ns = g.wait_limit_ns ? g.wait_limit_ns : ptx::kWaitLimitNs; p.drop_load = g.drop_load ? 1 : 0;
     p.y = g.y; p.bias = g.bias; p.status = g.status; p.probe = g.probe; p.trace = nullptr; p.plane_stride = g.plane_stride;
     p.M = g.m; p.N = g.n; p.K = g.k;
     p.tiles_m = ceil_div(g.m, BM); p.tiles_n = ceil_div(g.n, bn); p.split_k = split;

@@ -113,12 +113,14 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 const uint32_t half = tail ? ((w - tail_start) & 1u) : 0u;
                 const WorkItem wi = decode_work(tail ? tail_start + ((w - tail_start) >> 1) : w, p);
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.wait_limit_ns)) {
                         atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(w & 0xFFFFFF));
                         ok = false;
                         break;
                     }
                     const uint32_t fb_local = ptx::smem_u32(&full_bar[stage]);
+                    // self-test of the failure path: neither CTA of pair 0 fills this stage, so the issuer's bounded wait must run out
+                    if (p.drop_load && pair_id == 0 && w == 0 && kb == 0) { if (++stage == kStages) { stage = 0; phase ^= 1; } continue; }
                     if (cta_rank == 0) ptx::mbar_arrive_expect_tx(fb_local, 2 * (kAStageBytes + (tail ? kBHalfStageBytes : kBStageBytes)));   // bytes of both CTAs
                     const uint32_t fb = ptx::mapa(fb_local, 0);   // the even CTA's barrier, from either CTA
                     ptx::tma_load_3d_pair(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
@@ -148,7 +150,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
             bool ok = true;
             for (uint32_t w = pair_id; ok && w < total_work; w += n_pairs, ++iter) {
                 const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
-                if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, abort_flag)) {
+                if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, abort_flag, p.wait_limit_ns)) {
                     atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(w & 0xFFFFFF));
                     break;
                 }
@@ -156,7 +158,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 const uint32_t tmem_d = tmem_base + buf * kPairN;
                 const uint32_t idesc = w >= tail_start ? kIdescHalf : kIdesc;
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
+                    if (!ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag, p.wait_limit_ns)) {
                         atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000 | (int)(w & 0x7FFFFF));
                         ok = false;
                         break;
@@ -191,14 +193,14 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
         const uint32_t quarter = warp & 3;          // tensor-memory lanes 32*quarter .. +31 are the ones this warp may read
         const bool vec32 = (p.N % 4 == 0) && (((uintptr_t)p.y & 15) == 0);
         const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
-        uint32_t iter = 0;
+        uint32_t iter = 0, n_stores = 0;     // n_stores: this warp's committed TMA stores, see store_chunk
         for (uint32_t w = pair_id; w < total_work; w += n_pairs, ++iter) {
             const bool tail = w >= tail_start;
             const uint32_t half = tail ? ((w - tail_start) & 1u) : 0u;
             const WorkItem wi = decode_work(tail ? tail_start + ((w - tail_start) >> 1) : w, p);
             const uint32_t n_chunks = tail ? kHalfN / 32 : kPairN / 32;
             const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
-            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag)) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag, p.wait_limit_ns)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(w & 0xFFFFFF));
                 break;
             }
@@ -212,7 +214,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const _
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * kPairN + c * 32, r);
                 ptx::tmem_ld_wait();
-                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + (quarter * 2 + (c & 1)) * kEpiStageBytes, p.tma_store ? &map_y : nullptr);
+                store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * 2 * kEpiStageBytes, n_stores, p.tma_store ? &map_y : nullptr);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -304,6 +306,7 @@ int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
     const uint32_t pair_n = g.tile_n && g.tile_n <= 128 ? 128 : 256;
     KParams p;
     memset(&p, 0, sizeof p);
+    p.wait_limit_ns = g.wait_limit_ns ? g.wait_limit_ns : ptx::kWaitLimitNs; p.drop_load = g.drop_load ? 1 : 0;
     p.y = g.y; p.bias = g.bias; p.status = g.status; p.probe = g.probe; p.plane_stride = g.plane_stride;
     {
         // T0_GEMM_TRACE=1: a ring of eight launches' stamps behind the two clock words (printed by t0_rt_last_kernel_clock)

@@ -492,6 +492,19 @@ int t0_plan_flash_attention_warps(uint32_t n_warps, uint32_t m, uint32_t n, uint
     return t0_warp_layout_row_dominant(av_warps, std::max(m, av_warps * 16), d, av);
 }
 
+// Int4WmmaConfig::k16 / k32 (quant_kernels.rs:325-335)
+int t0_int4_wmma_config_k16(t0_int4_wmma_config* out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    out->tile_m = 16; out->tile_n = 16; out->tile_k = 16;
+    return T0_OK;
+}
+
+int t0_int4_wmma_config_k32(t0_int4_wmma_config* out) {
+    if (!out) return fail(T0_ERR_INVALID, "null output");
+    out->tile_m = 16; out->tile_n = 16; out->tile_k = 32;
+    return T0_OK;
+}
+
 int t0_plan_single_dot_warps(uint32_t n_warps, uint32_t tile_m, uint32_t tile_n, t0_warp_layout* out) {
     if (tile_n >= tile_m * 2 && tile_m < tile_n * 2) return t0_warp_layout_col_dominant(n_warps, tile_m, tile_n, out);   // wide
     return t0_warp_layout_row_dominant(n_warps, tile_m, tile_n, out);                                                      // tall or square-ish

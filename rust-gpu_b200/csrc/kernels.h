@@ -29,6 +29,8 @@ struct GemmLaunch {
     int* status;          // device error word
     unsigned long long* probe;   // optional device buffer of two words (cycles, ns) written by CTA 0
     uint32_t n_sms;
+    uint64_t wait_limit_ns;      // 0 = the default limit (ptx::kWaitLimitNs)
+    bool drop_load;              // self-test: CTA 0's producer leaves out its first load, so a bounded wait must run out
 };
 
 // Launches the tcgen05 GEMM. Requirements (checked): x and b 16-byte aligned, row strides and

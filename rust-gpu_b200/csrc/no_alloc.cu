@@ -12,14 +12,18 @@
 // T0_ERR_UNSUPPORTED and a message.
 //
 // The array is shared by every call on a device.  The counters must be zero when a call starts: the module loader
-// zero-fills the array, and the kernel returns every counter it used to zero.  Two calls that overlap in time on the same
-// device (different streams or runtimes) would race on the counters and pieces; calls on one runtime's stream are ordered
-// and safe.  The first call on a device looks up the array's address (`cudaGetSymbolAddress`), so make that first call
-// before starting any stream capture.
+// zero-fills the array, and a kernel that runs to completion returns every counter it used to zero.  A kernel that gave up
+// on a bounded wait does not: its runtime is poisoned, and a caller recovers by making a new runtime, so the FIRST static
+// call of every runtime clears the counter region with a stream-ordered memset (no allocation) before its kernel.  Do not
+// keep using the static entry from other, still healthy runtimes of the same device after such a failure without making
+// them anew: they would read the stale counters.  Two calls that overlap in time on the same device (different streams or
+// runtimes) race on the counters and pieces; calls on one runtime's stream are ordered and safe.  The first call on a
+// device looks up the array's address (`cudaGetSymbolAddress`), so make that first call before starting any stream capture.
 #include "runtime_internal.h"
 
 namespace t0 {
 size_t w4a16_fixed_scratch_bytes(uint32_t ctas);
+size_t w4a16_counter_region_bytes();
 int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
                              uint32_t K, uint32_t group, void* scratch, size_t scratch_bytes);
 }  // namespace t0
@@ -61,6 +65,12 @@ int t0_w4a16_gemm_static(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t s
             g_scratch_ptr[rt->device] = ptr;
         }
         scratch = g_scratch_ptr[rt->device];
+    }
+    if (!rt->static_scratch_cleared) {
+        // counters left behind by a kernel that unwound on an expired wait (in a runtime since poisoned) would make this
+        // runtime's bands never see their last contributor: start from zero, ordered before the kernel on the same stream
+        T0_CUDA(cudaMemsetAsync(scratch, 0, w4a16_counter_region_bytes(), rt->stream));
+        rt->static_scratch_cleared = true;
     }
     return w4a16_fused_launch_fixed(rt, a, packed, scales, zeros, y, M, N, K, group, scratch, kScratchBytes);
 }

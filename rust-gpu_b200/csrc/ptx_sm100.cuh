@@ -53,8 +53,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // output tile's main loop (tens of microseconds); the limit is generous for a time-sliced GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-// Returns false when the wait expired or another role raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Returns false when the wait expired (after `limit_ns`) or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t_start = 0;
     for (uint32_t spin = 1;; ++spin) {
@@ -63,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t_start == 0) t_start = now;
-            else if (now - t_start > kWaitLimitNs) { *abort_flag = 1; return false; }
+            else if (now - t_start > limit_ns) { *abort_flag = 1; return false; }
         }
     }
 }

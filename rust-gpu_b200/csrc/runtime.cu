@@ -75,6 +75,8 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q_in) {
     g.m = q.m; g.n = q.n; g.k = q.k;
     g.nn = q.nn; g.swap_grid = q.swap_grid;
     g.status = rt->d_status; g.probe = rt->d_probe; g.n_sms = (uint32_t)rt->sm_count;
+    g.wait_limit_ns = rt->wait_limit_ns.load(std::memory_order_relaxed);
+    g.drop_load = rt->drop_next_load.exchange(0) != 0;
     g.split_k = split;
     g.tile_n = q.tile_n ? snap_tile_n(q.tile_n) : choose_tile_n(rt, q.m, q.n, q.k, split);
     if (q.nn && g.tile_n < 64) g.tile_n = 64;
@@ -327,6 +329,18 @@ int t0_rt_synchronize(t0_runtime* rt) {
 }
 
 int t0_rt_wait_idle(t0_runtime* rt) { return t0_rt_synchronize(rt); }
+
+int t0_rt_set_wait_limit_ns(t0_runtime* rt, uint64_t ns) {
+    if (!rt) return fail(T0_ERR_INVALID, "null runtime");
+    rt->wait_limit_ns.store(ns);
+    return T0_OK;
+}
+
+int t0_rt_selftest_drop_one_load(t0_runtime* rt) {
+    if (!rt) return fail(T0_ERR_INVALID, "null runtime");
+    rt->drop_next_load.store(1);
+    return T0_OK;
+}
 void* t0_rt_stream(const t0_runtime* rt) { return rt ? (void*)rt->stream : nullptr; }
 int t0_rt_device(const t0_runtime* rt) { return rt ? rt->device : -1; }
 int t0_rt_sm_count(const t0_runtime* rt) { return rt ? rt->sm_count : 0; }

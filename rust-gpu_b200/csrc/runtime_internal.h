@@ -46,6 +46,9 @@ struct t0_runtime {
     std::atomic<bool> poisoned{false};
     std::atomic<uint64_t> launches{0};
     std::atomic<size_t> slot{0};
+    std::atomic<uint64_t> wait_limit_ns{0};   // limit of a single device-side barrier wait; 0 = the kernels' default
+    std::atomic<int> drop_next_load{0};       // self-test hook: the next GEMM launch leaves out one operand load
+    bool static_scratch_cleared = false;      // t0_w4a16_gemm_static: this runtime has zeroed the shared counters once
     int* d_status = nullptr;     // device error word written by kernels whose bounded wait expired
     int* h_status = nullptr;     // pinned mirror
     unsigned long long* d_probe = nullptr;   // {cycles, ns} of the last GEMM kernel's CTA 0

@@ -1142,25 +1142,15 @@ namespace t0 {
 // Bytes of caller-provided scratch the fused kernel needs for a grid of `ctas` CTAs: the arrival counters, then two
 // 16 x 256 pieces per CTA.
 size_t w4a16_fixed_scratch_bytes(uint32_t ctas) { return kCounterRegion + (size_t)ctas * 2 * kPieceFloats * sizeof(float); }
+size_t w4a16_counter_region_bytes() { return kCounterRegion; }
 
-// The fused kernel on scratch memory the caller owns (first kCounterRegion bytes: counters, zero before the first use;
-// the kernel leaves them zero).  Takes only the shapes the fused kernel handles and never allocates: there is no
-// two-step fallback here.
-int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
-                             uint32_t K, uint32_t group, void* scratch, size_t scratch_bytes) {
-    if (M == 0 || N == 0) return T0_OK;
-    if (!a || !packed || !scales || !zeros || !y || !scratch) return fail(T0_ERR_INVALID, "null device pointer");
-    if (M > 16) return fail(T0_ERR_UNSUPPORTED, "M=%u: this entry takes M <= 16 only (larger M needs a K x N scratch matrix)", M);
-    if (K == 0 || K % kUnitK || group == 0 || group % kUnitK || K % group || N % 32)
-        return fail(T0_ERR_UNSUPPORTED, "shape K=%u N=%u group=%u: this entry needs K %% 128 == 0, group %% 128 == 0, group | K, N %% 32 == 0", K, N, group);
-    if (((a | packed | scales | zeros) & 15) != 0 || (y & 3) != 0) return fail(T0_ERR_INVALID, "operands must be 16-byte aligned (y: 4-byte)");
+// The one launch of the row-layout fused kernel (shapes already checked by the caller): tensor maps over the three weight
+// arrays, kernel choice by steps per CTA, programmatic dependent launch.  `scratch` starts with kCounterRegion bytes of
+// arrival counters (zero between calls) followed by two pieces per CTA; `stamps` is the optional trace buffer.
+static int launch_w4_row_fused(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
+                        uint32_t K, uint32_t group, void* scratch, uint32_t grid, unsigned long long* stamps) {
     const uint32_t n_bands = ceil_div(N, kBandCols), ksteps = K / kUnitK;
     const uint64_t total = (uint64_t)n_bands * ksteps;
-    if (total > 0x7FFFFFFFull || n_bands * sizeof(int) > kCounterRegion)
-        return fail(T0_ERR_UNSUPPORTED, "N=%u is beyond the fixed scratch: at most %zu bands of 256 columns", N, kCounterRegion / sizeof(int));
-    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
-    if (w4a16_fixed_scratch_bytes(grid) > scratch_bytes)
-        return fail(T0_ERR_UNSUPPORTED, "a grid of %u CTAs needs %zu bytes of scratch, the fixed area holds %zu", grid, w4a16_fixed_scratch_bytes(grid), scratch_bytes);
     W4Params p;
     memset(&p, 0, sizeof p);
     p.a = (const uint16_t*)a;
@@ -1171,7 +1161,8 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
     p.M = M; p.N = N; p.K = K;
     p.units_per_group = group / kUnitK;
     p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
-    // the same kernel choice as t0_w4a16_gemm, so both entries give the same bits
+    p.stamps = stamps;
+    // the tensor-memory kernel needs the activations of all of a CTA's steps resident beside the ring
     static const bool legacy = getenv("T0_W4_LEGACY") != nullptr;
     const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
     const bool use_tc = !legacy && units_per_cta <= (uint32_t)kTcMaxUnits;
@@ -1192,16 +1183,58 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
                                      (int)(1024 + (size_t)kTcMaxUnits * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256)));
         attr_set[rt->device] = true;
     }
+    // programmatic dependent launch: the next kernel's launch and barrier set-up overlap this one's tail; the kernel
+    // touches global memory only after griddepcontrol.wait
+    static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
     cfg.blockDim = dim3(use_tc ? kTcThreads : kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = rt->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = use_pdl ? 1 : 0;
     cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel, map_w, map_s, map_z, p)
                             : cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
     if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     rt->launches.fetch_add(1);
     return T0_OK;
+}
+
+// Trace buffer of the T0_W4_TRACE debugging aid: freed on every path out of the entry point that made it.
+struct StampBuffer {
+    unsigned long long* d = nullptr;
+    size_t words = 0;
+    int make(uint32_t grid) {
+        words = (size_t)grid * 8;
+        T0_CUDA(cudaMalloc(&d, words * sizeof(unsigned long long)));
+        T0_CUDA(cudaMemset(d, 0, words * sizeof(unsigned long long)));
+        return T0_OK;
+    }
+    ~StampBuffer() { if (d) cudaFree(d); }
+};
+
+// The fused kernel on scratch memory the caller owns (first kCounterRegion bytes: counters, zero before the first use;
+// the kernel leaves them zero).  Takes only the shapes the fused kernel handles and never allocates: there is no
+// two-step fallback here.
+int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
+                             uint32_t K, uint32_t group, void* scratch, size_t scratch_bytes) {
+    if (M == 0 || N == 0) return T0_OK;
+    if (!a || !packed || !scales || !zeros || !y || !scratch) return fail(T0_ERR_INVALID, "null device pointer");
+    if (M > 16) return fail(T0_ERR_UNSUPPORTED, "M=%u: this entry takes M <= 16 only (larger M needs a K x N scratch matrix)", M);
+    if (K == 0 || K % kUnitK || group == 0 || group % kUnitK || K % group || N % 32)
+        return fail(T0_ERR_UNSUPPORTED, "shape K=%u N=%u group=%u: this entry needs K %% 128 == 0, group %% 128 == 0, group | K, N %% 32 == 0", K, N, group);
+    if (((a | packed | scales | zeros) & 15) != 0 || (y & 3) != 0) return fail(T0_ERR_INVALID, "operands must be 16-byte aligned (y: 4-byte)");
+    const uint32_t n_bands = ceil_div(N, kBandCols), ksteps = K / kUnitK;
+    const uint64_t total = (uint64_t)n_bands * ksteps;
+    if (total > 0x7FFFFFFFull || n_bands * sizeof(int) > kCounterRegion)
+        return fail(T0_ERR_UNSUPPORTED, "N=%u is beyond the fixed scratch: at most %zu bands of 256 columns", N, kCounterRegion / sizeof(int));
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
+    if (w4a16_fixed_scratch_bytes(grid) > scratch_bytes)
+        return fail(T0_ERR_UNSUPPORTED, "a grid of %u CTAs needs %zu bytes of scratch, the fixed area holds %zu", grid, w4a16_fixed_scratch_bytes(grid), scratch_bytes);
+    return launch_w4_row_fused(rt, a, packed, scales, zeros, y, M, N, K, group, scratch, grid, nullptr);
 }
 
 }  // namespace t0
@@ -1271,70 +1304,19 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         if (rc != T0_OK) return rc;
         T0_CUDA(cudaMemsetAsync(rt->scratch_w4.ptr, 0, kCounterRegion, rt->stream));
     }
-    W4Params p;
-    memset(&p, 0, sizeof p);
-    p.a = (const uint16_t*)a;
-    p.y = (float*)y;
-    p.counters = (int*)rt->scratch_w4.ptr;
-    p.partials = (float*)((uint8_t*)rt->scratch_w4.ptr + kCounterRegion);
-    p.status = rt->d_status;
-    p.M = M; p.N = N; p.K = K;
-    p.units_per_group = group / kUnitK;
-    p.n_bands = n_bands; p.ksteps = ksteps; p.total_units = (uint32_t)total;
-    // the tensor-memory kernel needs the activations of all of a CTA's steps resident beside the ring
-    static const bool legacy = getenv("T0_W4_LEGACY") != nullptr;
-    const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
-    const bool use_tc = !legacy && units_per_cta <= (uint32_t)kTcMaxUnits;
-    p.a_units = use_tc ? units_per_cta : std::min<uint32_t>(units_per_cta, kMaxAUnits);
-    const size_t smem = use_tc ? 1024 + (size_t)p.a_units * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256
-                               : 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)p.a_units * (kUnitK / 8) * kARecord;
-
-    CUtensorMap map_w, map_s, map_z;
-    rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kBandCols, kUnitK / 8);
-    if (rc != T0_OK) return rc;
-    rc = gemm::make_map_2d_plain(&map_s, (const void*)scales, 2, K / group, N, kBandCols, 1);
-    if (rc != T0_OK) return rc;
-    rc = gemm::make_map_2d_plain(&map_z, (const void*)zeros, 4, K / group, N / 8, kBandCols / 8, 1);
-    if (rc != T0_OK) return rc;
-
-    static bool attr_set[64] = {};
-    if (rt->device < 64 && !attr_set[rt->device]) {
-        T0_CUDA(cudaFuncSetAttribute(w4a16_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem));
-        T0_CUDA(cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)(1024 + (size_t)kTcMaxUnits * kTcBUnitBytes + (size_t)kStages * kStageBytes + 256)));
-        attr_set[rt->device] = true;
-    }
     // T0_W4_TRACE=1: per-CTA stage stamps, summarised on stderr after a blocking wait (a debugging aid, off by default)
     static const bool trace = getenv("T0_W4_TRACE") != nullptr;
-    unsigned long long* d_stamps = nullptr;
+    StampBuffer stamps;
     if (trace) {
-        T0_CUDA(cudaMalloc(&d_stamps, (size_t)grid * 8 * sizeof(unsigned long long)));
-        T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 8 * sizeof(unsigned long long)));
-        p.stamps = d_stamps;
+        rc = stamps.make(grid);
+        if (rc != T0_OK) return rc;
     }
-    {
-        // programmatic dependent launch: the next kernel's launch and barrier set-up overlap this one's tail; the
-        // kernel touches global memory only after griddepcontrol.wait
-        static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid, 1, 1);
-        cfg.blockDim = dim3(use_tc ? kTcThreads : kThreads, 1, 1);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = rt->stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = use_pdl ? 1 : 0;
-        cudaError_t le = use_tc ? cudaLaunchKernelEx(&cfg, w4a16_tc_kernel, map_w, map_s, map_z, p)
-                                : cudaLaunchKernelEx(&cfg, w4a16_gemm_kernel, map_w, map_s, map_z, p);
-        if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
-    }
+    rc = launch_w4_row_fused(rt, a, packed, scales, zeros, y, M, N, K, group, rt->scratch_w4.ptr, grid, stamps.d);
+    if (rc != T0_OK) return rc;
     if (trace) {
-        std::vector<unsigned long long> h((size_t)grid * 8);
+        std::vector<unsigned long long> h(stamps.words);
         T0_CUDA(cudaStreamSynchronize(rt->stream));
-        T0_CUDA(cudaMemcpy(h.data(), d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        cudaFree(d_stamps);
+        T0_CUDA(cudaMemcpy(h.data(), stamps.d, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
         unsigned long long t_min = ~0ull, t_max = 0;
         double stage = 0, loop = 0, tail = 0;
         for (uint32_t c = 0; c < grid; ++c) {
@@ -1344,9 +1326,6 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
         fprintf(stderr, "[w4a16 trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: staging %.2f us, main loop %.2f us, flush+exit %.2f us\n",
                 M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3);
     }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(e));
-    rt->launches.fetch_add(1);
     return T0_OK;
 }
 
@@ -1370,9 +1349,17 @@ int t0_gptq_parse(const uint8_t* raw, size_t len, uint32_t* rows, uint32_t* cols
     auto rd = [&](size_t o) { return (uint32_t)raw[o] | ((uint32_t)raw[o + 1] << 8) | ((uint32_t)raw[o + 2] << 16) | ((uint32_t)raw[o + 3] << 24); };
     *rows = rd(0); *cols = rd(4); *group_size = rd(8);
     if (*group_size == 0) return fail(T0_ERR_INVALID, "GPTQ group size is zero");
-    const size_t n_params = (size_t)(*cols / *group_size) * *rows;
-    const size_t packed_len = (size_t)*rows * *cols / 2;
-    const size_t expected = 12 + packed_len + n_params * 8;
+    // the sizes below come from an untrusted header: every product and sum is checked for overflow before it is compared
+    // with `len`, and the shapes t0_gptq_to_b200 cannot repack are refused here already
+    if (*cols % *group_size) return fail(T0_ERR_INVALID, "GPTQ cols=%u is not a multiple of the group size %u", *cols, *group_size);
+    size_t n_elems = 0, n_params = 0, param_bytes = 0, expected = 0;
+    if (__builtin_mul_overflow((size_t)*rows, (size_t)*cols, &n_elems)) return fail(T0_ERR_BOUNDS, "GPTQ header: rows*cols overflows");
+    if (n_elems & 1) return fail(T0_ERR_INVALID, "GPTQ rows*cols=%zu is odd: two codes share a byte", n_elems);
+    if (__builtin_mul_overflow((size_t)(*cols / *group_size), (size_t)*rows, &n_params) || __builtin_mul_overflow(n_params, (size_t)8, &param_bytes))
+        return fail(T0_ERR_BOUNDS, "GPTQ header: parameter count overflows");
+    const size_t packed_len = n_elems / 2;
+    if (__builtin_add_overflow(packed_len, param_bytes, &expected) || __builtin_add_overflow(expected, (size_t)12, &expected))
+        return fail(T0_ERR_BOUNDS, "GPTQ header: total size overflows");
     if (len < expected) return fail(T0_ERR_BOUNDS, "GPTQ data truncated: need %zu bytes, got %zu", expected, len);
     *packed_off = 12; *scales_off = 12 + packed_len; *zero_points_off = 12 + packed_len + n_params * 4;
     return T0_OK;

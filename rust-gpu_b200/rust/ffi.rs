@@ -158,6 +158,14 @@ pub struct t0_w4a16_args {
     pub group: u32,
 }
 
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct t0_int4_wmma_config {
+    pub tile_m: u32,
+    pub tile_n: u32,
+    pub tile_k: u32,
+}
+
 extern "C" {
     pub fn t0_last_error() -> *const c_char;
     pub fn t0_version() -> c_int;
@@ -204,6 +212,8 @@ extern "C" {
     pub fn t0_rt_mark_poisoned(rt: *mut t0_runtime);
     pub fn t0_rt_synchronize(rt: *mut t0_runtime) -> c_int;
     pub fn t0_rt_wait_idle(rt: *mut t0_runtime) -> c_int;
+    pub fn t0_rt_set_wait_limit_ns(rt: *mut t0_runtime, ns: u64) -> c_int;
+    pub fn t0_rt_selftest_drop_one_load(rt: *mut t0_runtime) -> c_int;
     pub fn t0_rt_stream(rt: *const t0_runtime) -> *mut c_void;
     pub fn t0_rt_device(rt: *const t0_runtime) -> c_int;
     pub fn t0_rt_sm_count(rt: *const t0_runtime) -> c_int;
@@ -294,6 +304,8 @@ extern "C" {
     pub fn t0_w4a16_gemm_prepacked_batch(rt: *mut t0_runtime, args: *const t0_w4a16_args, count: usize) -> c_int;
     pub fn t0_w4a16_gemm_static(rt: *mut t0_runtime, a: u64, packed: u64, scales: u64, zeros: u64, y: u64, M: u32, N: u32, K: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm_static_scratch_bytes() -> usize;
+    pub fn t0_int4_wmma_config_k16(out: *mut t0_int4_wmma_config) -> c_int;
+    pub fn t0_int4_wmma_config_k32(out: *mut t0_int4_wmma_config) -> c_int;
     pub fn t0_gptq_parse(raw: *const u8, len: usize, rows: *mut u32, cols: *mut u32, group_size: *mut u32, packed_off: *mut usize, scales_off: *mut usize, zero_points_off: *mut usize) -> c_int;
     pub fn t0_gptq_gpu_buffer_size(rows: u32, cols: u32, group_size: u32) -> usize;
     pub fn t0_gptq_to_b200(packed: *const u8, scales: *const f32, zero_points: *const i32, rows: u32, cols: u32, group_size: u32, packed_out: *mut u32, scales_out: *mut u16, zeros_out: *mut u32) -> c_long;

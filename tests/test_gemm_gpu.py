@@ -82,7 +82,7 @@ def run_tile(t0, rt, spec, a, b, m, n, k, pad_rows=0, **epi):
     return out
 
 
-# ----------------------------------------------------------------------------- BASELINE config 1
+# ----------------------------------------------------------------------------- the 256^3 configuration
 
 def test_config1_256_cubed_through_auto_select(t0, oracle, rt):
     m = n = k = 256
@@ -253,7 +253,7 @@ def test_split_k_planes_abi(t0, oracle, rt, sk):
 
 
 def test_split_k_reduced_on_device(t0, oracle, rt):
-    # BASELINE config 3b in small: the fp32 sum of per-split fp32 partials, in split order
+    # the split-K skinny configuration in small: the fp32 sum of per-split fp32 partials, in split order
     m, n, k, sk = 64, 256, 4096, 4
     a = oracle.fill_uniform_bf16(m * k, 42 + m)
     b = oracle.fill_uniform_bf16(n * k, 137 + n)
@@ -438,7 +438,7 @@ def test_dispatch_async_keeps_queue_order(t0, oracle, rt):
 # ----------------------------------------------------------------------------- full-size properties
 
 def test_square_4096_properties(t0, oracle, rt):
-    # BASELINE config 2 at full size: the oracle needs minutes here, so check size-independent properties:
+    # 4096^3, size-independent properties on top of the full compares below:
     # (1) integer-valued inputs give exact outputs whose column sums have a closed form,
     # (2) sampled rows of the seeded random case agree with the oracle, (3) bit-identical reruns.
     m = n = k = 4096
@@ -472,7 +472,7 @@ def test_square_4096_properties(t0, oracle, rt):
 
 @pytest.mark.parametrize("m,n,k,sk", [(128, 4096, 4096, 1), (64, 4096, 16384, 4)])
 def test_skinny_configs_full_size(t0, oracle, rt, m, n, k, sk):
-    # BASELINE config 3 at full size (the oracle finishes these in seconds)
+    # the skinny configurations at full size (the oracle finishes these in seconds)
     a = oracle.fill_uniform_bf16(m * k, 42 + m)
     b = oracle.fill_uniform_bf16(n * k, 137 + n)
     xa, xb = rt.upload(a), rt.upload(b)
@@ -531,3 +531,172 @@ def test_pair_kernel_nn_layout_full_compare(t0, oracle, rt, m, n, k):
     assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == -9999.0)
     for buf in (xa, xb, y):
         buf.free()
+
+
+# ----------------------------------------------------------------------------- square sweep, every element compared
+
+def assert_bf16_close(oracle, got_bits, ref, k):
+    """bf16 output: each element is the f32 accumulator rounded once (nearest even).  The accumulator differs from the
+    oracle's within the GEMM tolerance, so an element may land on the neighbouring bf16 value; nearly all are identical."""
+    got = oracle.bf16_to_f32(got_bits).reshape(ref.shape)
+    want = oracle.bf16_to_f32(oracle.f32_to_bf16_rne(ref.reshape(-1))).reshape(ref.shape)
+    ulp = np.maximum(np.abs(want), 2.0 ** -126) * 2.0 ** -7
+    assert np.all(np.abs(got - want) <= np.maximum(ulp, tol_abs(k))), "a bf16 output is more than one step from the rounded oracle value"
+    assert np.mean(got == want) > 0.97
+    assert np.linalg.norm(got.astype(np.float64) - ref) / np.linalg.norm(ref.astype(np.float64)) <= 3e-3   # bf16 rounding alone is 1.1e-3
+
+
+@pytest.mark.parametrize("size", [2048, 4096])
+def test_square_sweep_full_compare(t0, oracle, rt, size):
+    # the square sweep, f32 and bf16 output, WT[N,K] and B[K,N]: every element against the oracle
+    # (examples/full_matrix_check.rs:118-157 compares whole matrices wherever its CPU check is affordable)
+    m = n = k = size
+    a = oracle.fill_uniform_bf16(m * k, 42 + m)
+    wt = oracle.fill_uniform_bf16(n * k, 137 + n)
+    ref = oracle.gemm_nt(a, wt, m, k, n)
+    xa, xb = rt.upload(a), rt.upload(wt)
+    y = rt.alloc(m * n * 4 + 4096)
+    for layout in (t0.NT, t0.NN):
+        if layout == t0.NN:
+            xb.write(np.ascontiguousarray(wt.reshape(n, k).T))       # the same weights as B[K,N]
+        y.write_bytes(m * n * 4, np.full(1024, SENTINEL, np.float32))
+        rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, transpose=layout)
+        rt.synchronize()
+        assert_gemm_close(y.read(m * n * 4, np.float32).reshape(m, n), ref, k)
+        assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == SENTINEL)
+        y.write_bytes(m * n * 2, np.full(1024, SENTINEL, np.float32))
+        rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, transpose=layout, out_bf16=True)
+        rt.synchronize()
+        assert_bf16_close(oracle, y.read(m * n * 2, np.uint16), ref, k)
+        assert np.all(y.read_bytes(m * n * 2, 4096, np.float32) == SENTINEL)
+    for buf in (xa, xb, y):
+        buf.free()
+
+
+def test_square_8192_full_compare(t0, oracle, rt):
+    # 8192^3: 14 waves of 256 x 256 tiles, both accumulator buffers cycle seven times; inputs generated on the device
+    # by the counter-based generator the oracle shares, every element of the f32 result compared
+    m = n = k = 8192
+    xa, xb, y = rt.alloc(m * k * 2), rt.alloc(n * k * 2), rt.alloc(m * n * 4)
+    rt.fill_uniform_bf16(xa.gpu_addr(), m * k, 42 + m)
+    rt.fill_uniform_bf16(xb.gpu_addr(), n * k, 137 + n)
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k)
+    got = rt.read_f32(y, m * n).reshape(m, n)
+    a = oracle.fill_uniform_bf16(m * k, 42 + m)
+    wt = oracle.fill_uniform_bf16(n * k, 137 + n)
+    ref = oracle.gemm_nt(a, wt, m, k, n)
+    assert_gemm_close(got, ref, k)
+    # bf16 output at the same size: 512 rows spread over every tile row
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, out_bf16=True)
+    rt.synchronize()
+    rows = np.arange(0, m, 16)
+    got16 = y.read(m * n * 2, np.uint16).reshape(m, n)[rows]
+    assert_bf16_close(oracle, got16.reshape(-1), ref[rows], k)
+    for buf in (xa, xb, y):
+        buf.free()
+
+
+# ----------------------------------------------------------------------------- epilogue store path, tile after tile
+
+@pytest.mark.parametrize("m,n,k,tile_n,pair", [
+    (1280, 1280, 64, 32, 2),      # 400 tiles of one 32-column chunk each: every tile of a persistent CTA reuses a staging block
+    (1280, 1280, 128, 32, 2),
+    (25600, 96, 64, 64, 2),       # N % 64 = 32: the edge tile ends after an odd number of full chunks, 400 tiles
+    (1024, 4128, 64, 64, 2),      # 65 x 8 tiles, the last column tile has one full chunk
+    (4136, 512, 64, 128, 2),      # M = 4096 + 40: an M-edge tile (three of four warps own no row) follows full tiles
+    (4136, 4128, 64, 256, 1),     # the CTA-pair kernel with both edges
+    (4136, 4128, 128, 256, 2),    # the single-CTA 256-wide instance
+])
+def test_tma_store_epilogue_tile_sequences(t0, oracle, rt, m, n, k, tile_n, pair):
+    # Short K makes the epilogue the bottleneck, so consecutive tiles' stores are in flight together.  The output leaves
+    # through two alternating staging blocks per warp; these shapes make a warp commit an odd number of stores per tile,
+    # a single one, or none.  Every element is compared and the guard area behind y must stay untouched.
+    a = oracle.fill_uniform_bf16(m * k, 42 + m)
+    b = oracle.fill_uniform_bf16(n * k, 137 + n)
+    ref = oracle.gemm_nt(a, b, m, k, n)
+    xa, xb = rt.upload(a), rt.upload(b)
+    y = rt.alloc(m * n * 4 + 4096)
+    for _ in range(3):
+        y.write(np.full(m * n + 1024, SENTINEL, np.float32))
+        rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, tile_n=tile_n, pair_cta=pair)
+        rt.synchronize()
+        assert_gemm_close(y.read(m * n * 4, np.float32).reshape(m, n), ref, k)
+        assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == SENTINEL)
+    for buf in (xa, xb, y):
+        buf.free()
+
+
+# ----------------------------------------------------------------------------- submit / flush, bounded waits
+
+def test_submit_flush_batch(t0, oracle, rt):
+    # DispatchQueue::submit x N then flush (src/t0/prefill_dispatch.rs:61-206): fire-and-forget submits, one wait;
+    # results equal those of blocking dispatches; a poisoned runtime refuses the submit
+    m, n, k = 256, 384, 512
+    a = oracle.fill_uniform_bf16(m * k, 11)
+    cfg = t0.GemmConfig.tile_128x64_k32()
+    kern = rt.ensure_kernel_t0(cfg)
+    grid = list(t0.compute_grid_auto(cfg, m, n)) + [1]
+    xa = rt.upload(a)
+    ws = [rt.upload(oracle.fill_uniform_bf16(n * k, 100 + i)) for i in range(6)]
+    ys = [rt.alloc(m * n * 4) for _ in range(6)]
+    before = rt.launch_count()
+    for w, y in zip(ws, ys):
+        rt.submit(kern, grid, t0.build_kernargs(xa.gpu_addr(), w.gpu_addr(), y.gpu_addr(), k, n, m, cfg))
+    assert rt.launch_count() - before == 6
+    rt.flush()
+    y_ref = rt.alloc(m * n * 4)
+    for i, (w, y) in enumerate(zip(ws, ys)):
+        rt.dispatch(kern, grid, t0.build_kernargs(xa.gpu_addr(), w.gpu_addr(), y_ref.gpu_addr(), k, n, m, cfg))
+        got = rt.read_f32(y, m * n)
+        assert np.array_equal(got, rt.read_f32(y_ref, m * n))
+        assert_gemm_close(got.reshape(m, n), oracle.gemm_nt(a, oracle.fill_uniform_bf16(n * k, 100 + i), m, k, n), k)
+    r = t0.GpuRuntime(0)
+    kern2 = r.ensure_kernel_t0(cfg)
+    x2, y2 = r.alloc_zero(m * k * 2), r.alloc_zero(m * n * 4)
+    w2 = r.alloc_zero(n * k * 2)
+    ka = t0.build_kernargs(x2.gpu_addr(), w2.gpu_addr(), y2.gpu_addr(), k, n, m, cfg)
+    r.submit(kern2, grid, ka)
+    r.flush()
+    r.mark_poisoned()
+    with pytest.raises(t0.T0Error) as e:            # prefill_dispatch.rs: submit checks the poison flag
+        r.submit(kern2, grid, ka)
+    assert e.value.code == 3
+    for buf in (x2, w2, y2):
+        buf.free()
+    r.close()
+
+
+@pytest.mark.parametrize("pair", [2, 1])
+def test_bounded_wait_reports_timeout_and_poisons(t0, oracle, pair):
+    # The reference turns a dispatch that never finishes into Err and poisons the runtime (src/kfd/aql.rs:529-549,
+    # src/ignis/gpu_context.rs:352-355).  Here every device-side wait is bounded: with the self-test switch one operand
+    # load of the first tile is left out, that tile's wait runs out after the (shortened) limit, the kernel unwinds by
+    # itself, releases its tensor memory and leaves a status word.  Nothing faults; the context stays usable.
+    m, n, k = 1024, 1024, 512
+    a = oracle.fill_uniform_bf16(m * k, 5)
+    b = oracle.fill_uniform_bf16(n * k, 6)
+    r = t0.GpuRuntime(0)
+    xa, xb, y = r.upload(a), r.upload(b), r.alloc_zero(m * n * 4)
+    r.set_wait_limit_ns(3_000_000)                  # 3 ms instead of 2 s
+    r.selftest_drop_one_load()
+    r.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, tile_n=256 if pair == 1 else 128, pair_cta=pair)
+    with pytest.raises(t0.T0Error) as e:
+        r.synchronize()
+    assert e.value.code == 4 and "wait expired" in str(e.value)
+    assert r.is_poisoned()
+    with pytest.raises(t0.T0Error) as e:            # fail fast from here on (gpu_context.rs:311-313)
+        r.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k)
+    assert e.value.code == 3
+    for buf in (xa, xb, y):
+        buf.free()
+    r.close()
+    # a fresh runtime on the same device works: the kernel released its tensor memory and the context is intact
+    r2 = t0.GpuRuntime(0)
+    xa, xb, y = r2.upload(a), r2.upload(b), r2.alloc_zero(m * n * 4)
+    r2.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, tile_n=256 if pair == 1 else 128, pair_cta=pair)
+    assert_gemm_close(r2.read_f32(y, m * n).reshape(m, n), oracle.gemm_nt(a, b, m, k, n), k)
+    # the switch is one-shot and the limit is per runtime: the next launch of an armed runtime is normal again
+    r2.set_wait_limit_ns(0)
+    for buf in (xa, xb, y):
+        buf.free()
+    r2.close()

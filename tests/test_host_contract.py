@@ -304,3 +304,48 @@ def test_cost_model_records(t0):
     assert ok.can_use_tile_ir()
     assert not t0.TileConfig(tile_m=128, tile_n=64, tile_k=48, waves_per_wg=4, use_lds=1, swap_grid=1, split_k=1).can_use_tile_ir()   # tile_k not a power of two
     assert not t0.TileConfig(tile_m=128, tile_n=64, tile_k=32, waves_per_wg=8, use_lds=1, swap_grid=1, split_k=1).can_use_tile_ir()   # waves != tile_m / 32
+
+
+def test_int4_wmma_config_constructors(t0):
+    # quant_kernels.rs:316-336
+    c = t0.Int4WmmaConfig.k16()
+    assert (c.tile_m, c.tile_n, c.tile_k) == (16, 16, 16)
+    c = t0.Int4WmmaConfig.k32()
+    assert (c.tile_m, c.tile_n, c.tile_k) == (16, 16, 32)
+
+
+def test_force_cfg_switch(t0, monkeypatch):
+    # T0_FORCE_CFG pins auto_select / cached_auto_select to one preset, is never cached, and bad values are errors
+    free = t0.auto_select(4096, 4096, 4096)
+    monkeypatch.setenv("T0_FORCE_CFG", "tile_64x64_k32")
+    assert t0.auto_select(4096, 4096, 4096).name() == t0.GemmConfig.preset("tile_64x64_k32").name()
+    t0.clear_cache()
+    assert t0.cached_auto_select(128, 4096, 4096).name() == t0.GemmConfig.preset("tile_64x64_k32").name()
+    assert t0.cache_size() == 0
+    monkeypatch.setenv("T0_FORCE_CFG", "tile_128x64_k16:sk4")
+    forced = t0.auto_select(64, 16384, 4096)
+    assert forced.split() == 4 and forced.tile_m == 128 and forced.tile_n == 64
+    monkeypatch.setenv("T0_FORCE_CFG", "tile_128x64_k16:sk3")
+    with pytest.raises(t0.T0Error):
+        t0.auto_select(64, 16384, 4096)
+    monkeypatch.setenv("T0_FORCE_CFG", "no_such_preset")
+    with pytest.raises(t0.T0Error):
+        t0.auto_select(256, 256, 256)
+    monkeypatch.delenv("T0_FORCE_CFG")
+    assert t0.auto_select(4096, 4096, 4096).name() == free.name()
+
+
+def test_gptq_parse_rejects_crafted_headers(t0):
+    # sizes come from an untrusted header (quant_kernels.rs:251-286): overflowing or inconsistent ones are errors, not offsets
+    def raw(rows, cols, group, payload=b""):
+        return struct.pack("<III", rows, cols, group) + payload
+    with pytest.raises(t0.T0Error):
+        t0.gptq_parse(raw(0xFFFFFFFF, 0xFFFFFFFE, 2))              # rows*cols/2 + params*8 wraps a 64-bit size
+    with pytest.raises(t0.T0Error):
+        t0.gptq_parse(raw(4, 100, 64, b"\0" * 4096))                # cols not a multiple of the group
+    with pytest.raises(t0.T0Error):
+        t0.gptq_parse(raw(3, 5, 5, b"\0" * 4096))                   # odd element count: two codes share a byte
+    with pytest.raises(t0.T0Error):
+        t0.gptq_parse(raw(4, 128, 0, b"\0" * 4096))                 # zero group
+    ok = t0.gptq_parse(raw(4, 128, 64, b"\0" * (4 * 128 // 2 + 8 * 8)))
+    assert (ok["rows"], ok["cols"], ok["group_size"]) == (4, 128, 64)
