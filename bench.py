@@ -76,7 +76,10 @@ def run_hbm_workload(args, name):
     n_sets = max(2, -(-3 * 126 * 2 ** 20 // set_bytes))      # rotating weight sets: together three times the L2
     a_host = oracle.fill_normal_bf16(M * K, 7 + M) if w4 else oracle.fill_uniform_bf16(M * K, 42 + M)
     xa = rt.upload(a_host)
-    y = rt.alloc(M * N * 4)
+    # the problems of one batched launch run concurrently, so consecutive steps write distinct outputs
+    n_out = 32 if w4 else 1
+    ys = [rt.alloc(M * N * 4) for _ in range(n_out)]
+    y = ys[(steps - 1) % n_out]          # the output of the last step, checked against the oracle below
     sets = []
     for s in range(n_sets):
         if w4:
@@ -96,11 +99,11 @@ def run_hbm_workload(args, name):
         for st in sets:
             for b in st:
                 b.free()
-        calls = [t0.W4A16Args(xa.gpu_addr(), pre[i % n_sets].gpu_addr(), 0, 0, y.gpu_addr(), M, N, K, G) for i in range(steps)]
+        calls = [t0.W4A16Args(xa.gpu_addr(), pre[i % n_sets].gpu_addr(), 0, 0, ys[i % n_out].gpu_addr(), M, N, K, G) for i in range(steps)]
         submit = rt.w4a16_gemm_prepacked_batch
-        kernel = "w4a16_frag_kernel (streaming layout, mma.sync fragment order)"
+        kernel = "w4a16_stream_kernel (streaming layout, one persistent launch per 32 problems)"
     elif w4:
-        calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), y.gpu_addr(), M, N, K, G) for i in range(steps)]
+        calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), ys[i % n_out].gpu_addr(), M, N, K, G) for i in range(steps)]
         submit = rt.w4a16_gemm_batch
         kernel = "w4a16_tc_kernel (row layout, tcgen05)" if M <= 16 else "dequant_w4_b200_kernel + gemm"
     else:

@@ -17,7 +17,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libt0b200.so")
+# T0B200_LIB names another build of the library (e.g. one compiled with tracing flags); the default is the in-tree build
+LIB_PATH = os.environ.get("T0B200_LIB") or os.path.join(_HERE, "lib", "libt0b200.so")
 HEADER_PATH = os.path.join(_HERE, "..", "include", "t0b200.h")
 
 NT, NN = 0, 1

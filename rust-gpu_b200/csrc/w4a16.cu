@@ -22,80 +22,12 @@
 //   * the k slices of a slab are summed through shared memory in a fixed order; a band finished by one
 //     CTA is stored directly, otherwise each CTA leaves its M x 256 piece in a scratch area and the CTA
 //     that arrives last adds the pieces in k order (no CTA ever waits for another).
-#include "runtime_internal.h"
-#include "gemm_common.cuh"
-
-#include <cuda_bf16.h>
+#include "w4a16_common.cuh"
 
 using namespace t0;
+using namespace t0::w4;
 
 namespace {
-
-constexpr int kWarps = 16;               // consumer warps; one more warp feeds them through TMA
-constexpr int kThreads = (kWarps + 1) * 32;
-constexpr int kSlabCols = 32;            // columns one warp owns
-constexpr int kBandSlabs = 8;            // slabs side by side in a CTA: 256 columns = 1 KiB of every packed row
-constexpr int kBandCols = kSlabCols * kBandSlabs;
-constexpr int kSlices = kWarps / kBandSlabs;   // k slices of 64 per step
-constexpr int kUnitK = kSlices * 64;     // k depth of one step of the CTA: 128
-constexpr int kStages = 8;               // steps in flight per CTA (TMA ring)
-constexpr int kARecord = 288;            // bytes per 8-k activation record (256 + 32: conflict-free quad reads)
-constexpr int kWeightBytes = (kUnitK / 8) * kBandCols * 4;   // 16 packed rows x 1 KiB
-constexpr int kScaleBytes = kBandCols * 2;
-constexpr int kZeroBytes = (kBandCols / 8) * 4;
-constexpr int kStageBytes = kWeightBytes + kScaleBytes + kZeroBytes + 128;   // 17152, keeps every stage 128-byte aligned
-constexpr int kRedBytes = kWarps * 16 * 33 * 4;
-constexpr int kPieceFloats = 16 * kBandCols;
-constexpr int kMaxAUnits = 12;           // steps of activations staged at a time (54 KiB)
-constexpr size_t kMaxSmem = 128 + (size_t)kStages * kStageBytes + kRedBytes + 256 + (size_t)kMaxAUnits * (kUnitK / 8) * kARecord;
-constexpr size_t kCounterRegion = 16 * 1024;   // arrival counters: up to 4096 bands (N <= 1048576)
-
-struct W4Params {
-    const uint16_t* a;
-    float* y;
-    float* partials;     // [grid][2][16*256]
-    int* counters;       // [n_bands], zero between calls
-    int* status;         // error word of the runtime (bounded waits)
-    uint32_t M, N, K;
-    uint32_t units_per_group;   // group / 128: steps that share one row of scales and zero points
-    uint32_t n_bands, ksteps, total_units;
-    uint32_t a_units;    // steps of activations the shared-memory area holds (max steps of one CTA)
-    const uint8_t* tiles;      // streaming layout only: [band][kstep][16][256] u32
-    const uint8_t* scales_t;   //   [band][K/G][256] bf16
-    const uint8_t* zeros_t;    //   [band][K/G][32] u32
-    uint32_t groups;           //   K / G
-    unsigned long long* stamps;   // optional trace: 4 nanosecond stamps per CTA (entry, staged, loop done, exit)
-};
-
-__device__ __forceinline__ uint32_t owner_of(uint32_t unit, uint32_t grid, uint32_t total) {
-    return (uint32_t)((((uint64_t)unit + 1) * grid - 1) / total);
-}
-__device__ __forceinline__ uint32_t range_begin(uint32_t cta, uint32_t grid, uint32_t total) {
-    return (uint32_t)((uint64_t)cta * total / grid);
-}
-
-__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
-    __nv_bfloat162 r = __hsub2(*(__nv_bfloat162*)&a, *(__nv_bfloat162*)&b);
-    return *(uint32_t*)&r;
-}
-__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
-    __nv_bfloat162 r = __hmul2(*(__nv_bfloat162*)&a, *(__nv_bfloat162*)&b);
-    return *(uint32_t*)&r;
-}
-
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// (x & mask) | magic in one LOP3; mask and magic must sit in registers (the instruction takes one immediate at most)
-__device__ __forceinline__ uint32_t and_or(uint32_t x, uint32_t mask, uint32_t magic) {
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(x), "r"(mask), "r"(magic));
-    return r;
-}
 
 // 32 k of one lane: 4 columns x 8 codes against the matching activation quads
 __device__ __forceinline__ void consume_word4(float (&acc)[4][4], const uint4& wq, const uint32_t (&zz)[4], const uint32_t (&ss)[4],
@@ -702,330 +634,6 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
 }
 
-// ------------------------------------------------------------------ K2, fragment-ordered streaming form
-//
-// The kernel `bench.py` measures.  Weights come in the streaming layout of t0_w4_prepack: per (256-column band, 128-deep
-// k step) one contiguous 16 KiB tile whose words are already in mma.sync fragment order, so a lane reads its eight words
-// of a step with two LDS.128 and each word IS the A fragment (16 weight columns x 16 k) of one m16n8k16 after dequantising
-// (nibble c / c+4 of a word -> register a_c).  The activations are the 8-column B operand (two column groups when M > 8).
-// A stand-alone probe of this inner loop (7 integer + 8 bf16x2 operations + 1 MMA per word) runs at 477 cycles per step
-// per SM, under the 700 cycles HBM needs to deliver a step, which neither the tensor-memory form (about 100 cycles per
-// small UMMA, 16 per step) nor the first form (activations as the 16-row operand: twice the MMAs) can do.
-constexpr int kFrWarps = 16;                         // consumer warps: warp w owns columns 16w .. 16w+15 of the band, all k
-constexpr int kFrThreads = (kFrWarps + 2) * 32;      // + the producer warp + the warp that counts a head piece in
-constexpr int kFrMaxUnits = 20;                      // steps of one CTA whose activations fit beside the ring
-constexpr int kFrAUnitBytes = 2048;                  // activations of one step and one group of eight rows, in fragment order
-__device__ __forceinline__ void fr_consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kFrWarps * 32) : "memory"); }
-
-template <int kMGroups>    // 1: M <= 8, 2: M <= 16
-__global__ void __launch_bounds__(kFrThreads, 1)
-w4a16_frag_kernel(const W4Params p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
-    uint8_t* ring = smem;                                              // kStages x 16 KiB tiles
-    uint8_t* s_area = ring + kStages * kWeightBytes;                   // [a_units][256] bf16 scales ...
-    uint8_t* z_area = s_area + (size_t)p.a_units * kScaleBytes;        // ... and [a_units][32] u32 zero points
-    uint8_t* a_area = z_area + (size_t)p.a_units * kZeroBytes;         // [a_units][kMGroups][2][2][32] uint4 B fragments
-    uint64_t* full_bar = (uint64_t*)(a_area + (size_t)p.a_units * kMGroups * kFrAUnitBytes);
-    uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* sz_full_bar = empty_bar + kStages;
-    uint64_t* head_written_bar = sz_full_bar + 1;      // all 16 consumer warps have stored their part of the head piece
-    uint64_t* head_counted_bar = head_written_bar + 1; // the head piece is counted in and s_head_last is valid
-    volatile int* abort_flag = (volatile int*)(head_counted_bar + 1);
-    int* s_last = (int*)(abort_flag + 1);
-    int* s_head_last = s_last + 1;       // band + 1 when this CTA turned out to be the last contributor of its head band
-
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t u0 = range_begin(blockIdx.x, gridDim.x, p.total_units);
-    const uint32_t u1 = range_begin(blockIdx.x + 1, gridDim.x, p.total_units);
-    if (u0 >= u1) return;
-    auto stamp = [&](int i) {
-        if (p.stamps && tid == 0) { unsigned long long t_ns; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_ns)); p.stamps[blockIdx.x * 4 + i] = t_ns; }
-    };
-    if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&full_bar[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&empty_bar[s]), kFrWarps);
-        }
-        ptx::mbar_init(ptx::smem_u32(sz_full_bar), 1);
-        ptx::mbar_init(ptx::smem_u32(head_written_bar), kFrWarps);
-        ptx::mbar_init(ptx::smem_u32(head_counted_bar), 1);
-        *abort_flag = 0;
-        *s_head_last = 0;
-        ptx::fence_barrier_init();
-        ptx::fence_proxy_async_smem();
-    }
-    __syncthreads();
-    ptx::grid_launch_dependents();
-    ptx::grid_dependency_wait();      // global memory is touched only after the previous grid in the stream is done
-    stamp(0);
-    const uint32_t band_first = u0 / p.ksteps;
-    const uint32_t ks_first = u0 - band_first * p.ksteps;
-    // A head piece: the range starts inside a band (or the band is longer than the range's part of it) and goes on into
-    // the next band.  Counting it in (fence, atomic round trip) is the helper warp's job, so no consumer warp falls
-    // behind the others while the range goes on.
-    const bool has_head = (band_first + 1) * p.ksteps < u1 && ks_first != 0;
-
-    if (warp == kFrWarps + 1) {
-        // ------------------------------------------------------------ helper: counts the head piece in
-        if (lane == 0 && has_head) {
-            int last = 0;
-            if (ptx::mbar_wait(ptx::smem_u32(head_written_bar), 0, abort_flag)) {
-                const uint32_t first_unit = band_first * p.ksteps;
-                const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
-                const uint32_t c_last = owner_of(first_unit + p.ksteps - 1, gridDim.x, p.total_units);
-                __threadfence();                   // the piece is visible before this CTA is counted
-                last = atomicAdd(&p.counters[band_first], 1) == (int)(c_last - c_first);
-                if (last) __threadfence();
-            } else {
-                atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xD00000);
-            }
-            *s_head_last = last ? (int)band_first + 1 : 0;   // looked at when the range is done
-            ptx::mbar_arrive(ptx::smem_u32(head_counted_bar));
-        }
-        return;
-    }
-    if (warp == kFrWarps) {
-        // ------------------------------------------------------------ producer: bulk copies
-        if (lane == 0) {
-            uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
-            {
-                // scales and zero points of every (band, group) the CTA's steps touch, into consecutive slots
-                uint32_t left = u1 - u0, slot = 0, bytes = 0, b2 = band, k2 = ks;
-                const uint32_t sb = ptx::smem_u32(sz_full_bar);
-                while (left) {
-                    const uint32_t n_here = min(left, p.ksteps - k2);
-                    const uint32_t g_lo = k2 / p.units_per_group, ng = (k2 + n_here - 1) / p.units_per_group - g_lo + 1;
-                    const size_t row = (size_t)b2 * p.groups + g_lo;
-                    ptx::bulk_load(ptx::smem_u32(s_area + slot * kScaleBytes), p.scales_t + row * kScaleBytes, ng * kScaleBytes, sb);
-                    ptx::bulk_load(ptx::smem_u32(z_area + slot * kZeroBytes), p.zeros_t + row * kZeroBytes, ng * kZeroBytes, sb);
-                    bytes += ng * (kScaleBytes + kZeroBytes);
-                    slot += ng; left -= n_here; k2 = 0; ++b2;
-                }
-                ptx::mbar_arrive_expect_tx(sb, bytes);
-            }
-            for (uint32_t u = u0; u < u1; ++u) {
-                if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag)) {
-                    atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(u & 0xFFFFFF));
-                    break;
-                }
-                // The consumers read the stage through the generic proxy (their reads are ordered before this point by
-                // their release-arrive and the acquire-wait above); the copy overwrites it through the async proxy, and
-                // this fence orders the two.  Without a proxy fence, launches with cold TLBs consumed sectors of the
-                // step loaded into the same stage eight steps later.  One fence here instead of one per consumer
-                // thread: the per-thread fence cost more than the dequantisation itself.
-                ptx::fence_proxy_async_smem();
-                const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
-                ptx::mbar_arrive_expect_tx(fb, kWeightBytes);
-                ptx::bulk_load(ptx::smem_u32(ring + stage * kWeightBytes), p.tiles + ((size_t)band * p.ksteps + ks) * kWeightBytes, kWeightBytes, fb);
-                if (++stage == kStages) { stage = 0; phase ^= 1; }
-                if (++ks == p.ksteps) { ks = 0; ++band; }
-            }
-        }
-        return;
-    }
-
-    // ---------------------------------------------------------------- consumers (16 warps)
-    const uint32_t g = lane >> 2, t = lane & 3;
-    const uint32_t n_units = u1 - u0;
-
-    // Activations -> B fragments: for step u, row group mg, half j, pair pr, lane (g, t) one uint4
-    // {b0(s), b1(s), b0(s+1), b1(s+1)}, s = 4j + 2pr, b0(s) = a[m][k0 + 16s + 2t .. +1], b1(s) = a[m][k0 + 16s + 2t + 8 .. +9], m = 8mg + g.
-    // Four items per thread and pass, all their loads issued before the first store: the set-up costs one memory round
-    // trip per pass instead of one per item.
-    {
-        constexpr uint32_t kBatch = 4;
-        const uint32_t items = n_units * kMGroups * 128;
-        for (uint32_t base = 0; base < items; base += kBatch * kFrWarps * 32) {
-            uint4 v[kBatch];
-#pragma unroll
-            for (uint32_t r = 0; r < kBatch; ++r) {
-                const uint32_t i = base + r * (kFrWarps * 32) + tid;
-                const uint32_t ln = i & 31, pr = (i >> 5) & 1, j = (i >> 6) & 1, mg = kMGroups == 2 ? (i >> 7) & 1 : 0, unit = i / (128 * kMGroups);
-                const uint32_t m = mg * 8 + (ln >> 2), tt = ln & 3;
-                v[r] = make_uint4(0, 0, 0, 0);
-                if (i < items && m < p.M) {
-                    const uint32_t kks = (ks_first + unit) % p.ksteps;
-                    const uint32_t* row = (const uint32_t*)(p.a + (size_t)m * p.K + kks * kUnitK + (4 * j + 2 * pr) * 16 + 2 * tt);   // 4-byte aligned
-                    v[r].x = __ldg(row); v[r].y = __ldg(row + 4); v[r].z = __ldg(row + 8); v[r].w = __ldg(row + 12);
-                }
-            }
-#pragma unroll
-            for (uint32_t r = 0; r < kBatch; ++r) {
-                const uint32_t i = base + r * (kFrWarps * 32) + tid;
-                const uint32_t ln = i & 31, pr = (i >> 5) & 1, j = (i >> 6) & 1, mg = kMGroups == 2 ? (i >> 7) & 1 : 0, unit = i / (128 * kMGroups);
-                if (i < items) *(uint4*)(a_area + ((((size_t)unit * kMGroups + mg) * 2 + j) * 2 + pr) * 512 + ln * 16) = v[r];
-            }
-        }
-    }
-    fr_consumer_sync();
-    stamp(1);
-
-    // four accumulator sets, one per k step modulo 4: consecutive MMAs must not wait for each other's result
-    constexpr int kAccSets = 4;
-    float acc[kMGroups][kAccSets][4];
-#pragma unroll
-    for (int mg = 0; mg < kMGroups; ++mg)
-#pragma unroll
-        for (int a = 0; a < kAccSets; ++a)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[mg][a][j] = 0.0f;
-    uint32_t mask, magic;
-    asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
-    asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
-    uint32_t band = band_first, ks = ks_first, stage = 0, phase = 0;
-    uint32_t sz_slot = 0, in_group = ks_first % p.units_per_group;
-    bool ok = true;    // false after a wait expired: the warp keeps walking (barriers stay matched) but does no work
-    if (!ptx::mbar_wait(ptx::smem_u32(sz_full_bar), 0, abort_flag)) {
-        if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xC00000);
-        ok = false;
-    }
-    const uint32_t col0 = warp * 16 + g;                     // this lane's two columns within the band: col0 and col0 + 8
-    const uint32_t w_off = warp * 1024 + lane * 16;           // [w][j][lane] uint4
-
-    // The CTA that contributes last to a band adds the pieces in k order (CTA order) and stores; nobody waits for anybody.
-    // Only the first contributor can hold the band in slot 1 (its range began in the band before).
-    auto reduce_band = [&](uint32_t rb) {
-        const uint32_t first_unit = rb * p.ksteps;
-        const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
-        const uint32_t c_last = owner_of(first_unit + p.ksteps - 1, gridDim.x, p.total_units);
-        const uint32_t first_slot = range_begin(c_first, gridDim.x, p.total_units) < first_unit ? 1u : 0u;
-        constexpr int kPer = kMGroups * 8 * kBandCols / (kFrWarps * 32);   // outputs per thread: 4 for M <= 8, 8 for M <= 16
-        constexpr int kCo = 4;                                              // contributors whose pieces are in flight together
-        float total[kPer];
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) total[j] = 0.0f;
-        for (uint32_t c = c_first; c <= c_last; c += kCo) {
-            float v[kCo][kPer];
-#pragma unroll
-            for (int b = 0; b < kCo; ++b) {
-                const uint32_t cc = c + b;
-                const float* src = p.partials + ((size_t)cc * 2 + (cc == c_first ? first_slot : 0u)) * kPieceFloats;
-#pragma unroll
-                for (int j = 0; j < kPer; ++j) {
-                    const uint32_t idx = tid + j * (kFrWarps * 32);
-                    v[b][j] = (cc <= c_last && idx < p.M * kBandCols) ? __ldcg(src + idx) : 0.0f;
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < kCo; ++b)       // still added in CTA order, one contributor after the other
-#pragma unroll
-                for (int j = 0; j < kPer; ++j) total[j] += v[b][j];
-        }
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) {
-            const uint32_t idx = tid + j * (kFrWarps * 32);
-            if (idx < p.M * kBandCols) {
-                const uint32_t row = idx / kBandCols, col = idx - row * kBandCols;
-                const uint32_t nc = rb * kBandCols + col;
-                if (nc < p.N) p.y[(size_t)row * p.N + nc] = total[j];
-            }
-        }
-        if (tid == 0) p.counters[rb] = 0;   // ready for the next call
-    };
-
-    // walked piece by piece (the steps of one band this CTA owns), so the inner loop carries no band logic
-    const uint8_t* af = a_area + lane * 16;                  // B fragments of the current step
-    uint32_t u = u0;
-    while (u < u1) {
-      const uint32_t piece_end = min(u1, u + (p.ksteps - ks));
-      for (; u < piece_end; ++u) {
-        if (ok && !ptx::mbar_wait(ptx::smem_u32(&full_bar[stage]), phase, abort_flag)) {
-            if (lane == 0) atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(u & 0xFFFFFF));
-            ok = false;
-        }
-        if (ok) {
-            const uint8_t* st = ring + stage * kWeightBytes;
-            const uint4 q0 = *(const uint4*)(st + w_off);
-            const uint4 q1 = *(const uint4*)(st + w_off + 512);
-            // scale and zero point of the lane's two columns for this step's group
-            const uint32_t s0 = *(const uint16_t*)(s_area + sz_slot * kScaleBytes + col0 * 2);
-            const uint32_t s1 = *(const uint16_t*)(s_area + sz_slot * kScaleBytes + (col0 + 8) * 2);
-            const uint32_t zw = *(const uint32_t*)(z_area + sz_slot * kZeroBytes + (col0 >> 3) * 4);          // columns 8(col0/8) .. +7
-            const uint32_t zw8 = *(const uint32_t*)(z_area + sz_slot * kZeroBytes + ((col0 >> 3) + 1) * 4);
-            const uint32_t zsh = (col0 & 7) * 4;
-            const uint32_t zz0 = ((zw >> zsh) & 0xFu) * 0x00010001u + 0x43004300u, zz1 = ((zw8 >> zsh) & 0xFu) * 0x00010001u + 0x43004300u;
-            const uint32_t ss0 = s0 * 0x00010001u, ss1 = s1 * 0x00010001u;
-            const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-#pragma unroll
-                for (int pr = 0; pr < 2; ++pr) {
-                    uint4 bf[kMGroups];
-#pragma unroll
-                    for (int mg = 0; mg < kMGroups; ++mg) bf[mg] = *(const uint4*)(af + ((mg * 2 + j) * 2 + pr) * 512);
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const uint32_t wd = words[j * 4 + pr * 2 + e];
-                        const uint32_t a0 = bf16x2_mul(bf16x2_sub(and_or(wd, mask, magic), zz0), ss0);
-                        const uint32_t a1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz1), ss1);
-                        const uint32_t a2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz0), ss0);
-                        const uint32_t a3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz1), ss1);
-#pragma unroll
-                        for (int mg = 0; mg < kMGroups; ++mg)
-                            mma_bf16_16816(acc[mg][pr * 2 + e], a0, a1, a2, a3, e ? bf[mg].z : bf[mg].x, e ? bf[mg].w : bf[mg].y);
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&empty_bar[stage]));          // this warp has read the stage
-        }
-        if (++stage == kStages) { stage = 0; phase ^= 1; }
-        af += kMGroups * kFrAUnitBytes;
-        if (++in_group == p.units_per_group) { in_group = 0; ++sz_slot; }
-      }
-      if (u == u1) stamp(2);
-      {
-            const uint32_t first_unit = band * p.ksteps, last_unit = first_unit + p.ksteps;   // [first, last)
-            const bool whole = first_unit >= u0 && last_unit <= u1;
-            const uint32_t c_first = owner_of(first_unit, gridDim.x, p.total_units);
-            const uint32_t c_last = owner_of(last_unit - 1, gridDim.x, p.total_units);
-            const uint32_t slot = (first_unit <= u0) ? 0u : 1u;   // the piece of the band holding this CTA's first unit is slot 0
-            float* piece = p.partials + ((size_t)blockIdx.x * 2 + slot) * kPieceFloats;
-            // accumulator fragment: c0,c1 = (column col0, rows 2t, 2t+1), c2,c3 = (column col0 + 8, same rows)
-#pragma unroll
-            for (int mg = 0; mg < kMGroups; ++mg) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t m = mg * 8 + 2 * t + (j & 1), col = col0 + (j >> 1) * 8;
-                    const uint32_t ncol = band * kBandCols + col;
-                    const float v = (acc[mg][0][j] + acc[mg][1][j]) + (acc[mg][2][j] + acc[mg][3][j]);
-                    if (m < p.M) {
-                        if (!whole) piece[m * kBandCols + col] = v;
-                        else if (ncol < p.N) p.y[(size_t)m * p.N + ncol] = v;
-                    }
-#pragma unroll
-                    for (int a = 0; a < kAccSets; ++a) acc[mg][a][j] = 0.0f;
-                }
-            }
-            if (!whole) {
-                if (u < u1) {
-                    // head piece, more steps follow: hand it to the helper warp and go on
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(head_written_bar));
-                } else {
-                    fr_consumer_sync();                    // every thread's part of the piece is written ...
-                    if (tid == 0) {
-                        __threadfence();                   // ... and made visible before this CTA is counted
-                        *s_last = atomicAdd(&p.counters[band], 1) == (int)(c_last - c_first);
-                        if (*s_last) __threadfence();
-                    }
-                    fr_consumer_sync();
-                    if (*s_last) reduce_band(band);
-                }
-            }
-        }
-      ks = 0;          // a further piece starts a new band
-      ++band;
-    }
-    if (has_head) {
-        if (!ptx::mbar_wait(ptx::smem_u32(head_counted_bar), 0, abort_flag) && lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xE00000);
-        fr_consumer_sync();
-        if (*s_head_last) reduce_band((uint32_t)*s_head_last - 1);
-    }
-    stamp(3);
-}
-
 // ------------------------------------------------------------------ K3: stand-alone dequantisation
 
 // Reference wire format (quant_kernels.rs:53-171): one thread per 32 consecutive elements.
@@ -1202,19 +810,6 @@ static int launch_w4_row_fused(t0_runtime* rt, uint64_t a, uint64_t packed, uint
     rt->launches.fetch_add(1);
     return T0_OK;
 }
-
-// Trace buffer of the T0_W4_TRACE debugging aid: freed on every path out of the entry point that made it.
-struct StampBuffer {
-    unsigned long long* d = nullptr;
-    size_t words = 0;
-    int make(uint32_t grid) {
-        words = (size_t)grid * 8;
-        T0_CUDA(cudaMalloc(&d, words * sizeof(unsigned long long)));
-        T0_CUDA(cudaMemset(d, 0, words * sizeof(unsigned long long)));
-        return T0_OK;
-    }
-    ~StampBuffer() { if (d) cudaFree(d); }
-};
 
 // The fused kernel on scratch memory the caller owns (first kCounterRegion bytes: counters, zero before the first use;
 // the kernel leaves them zero).  Takes only the shapes the fused kernel handles and never allocates: there is no
@@ -1400,200 +995,6 @@ long t0_gptq_to_b200(const uint8_t* packed, const float* scales, const int32_t* 
         }
     }
     return inexact;
-}
-
-}  // extern "C"
-// ------------------------------------------------------------------ streaming (tile-major) weight layout
-
-namespace {
-
-struct PrepackLayout { size_t off_tiles, off_scales, off_zeros, total; uint32_t bands, ksteps, groups; };
-
-PrepackLayout prepack_layout(uint32_t K, uint32_t N, uint32_t group) {
-    PrepackLayout L;
-    L.bands = ceil_div(N, kBandCols); L.ksteps = K / kUnitK; L.groups = K / group;
-    L.off_tiles = 0;
-    L.off_scales = (size_t)L.bands * L.ksteps * kWeightBytes;
-    L.off_zeros = L.off_scales + (size_t)L.bands * L.groups * kScaleBytes;
-    L.total = L.off_zeros + (size_t)L.bands * L.groups * kZeroBytes;
-    return L;
-}
-
-// Row layout -> streaming layout.  One thread per output element: a tile word (eight codes in mma.sync fragment order),
-// a scale, or a word of eight zero points.  Columns past N are written as zero.
-__global__ void w4_prepack_kernel(const uint32_t* __restrict__ packed, const uint16_t* __restrict__ scales, const uint32_t* __restrict__ zeros,
-                                  uint8_t* __restrict__ out, uint32_t K, uint32_t N, uint32_t nz, PrepackLayout L) {
-    const uint64_t n_words = (uint64_t)L.bands * L.ksteps * 16 * kBandCols;
-    const uint64_t n_scales = (uint64_t)L.bands * L.groups * kBandCols;
-    const uint64_t n_zwords = (uint64_t)L.bands * L.groups * (kBandCols / 8);
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words + n_scales + n_zwords; i += stride) {
-        if (i < n_words) {
-            // word (tile, w, j, lane, e) of the fragment order: k step s = 4j + e of column tile w, lane (g, t);
-            // nibble c / c+4 = codes (k, k+1) of column n = 16w + g + 8(c & 1) at k = 16s + 2t + 8(c >> 1)
-            const uint32_t e = (uint32_t)(i & 3), ln = (uint32_t)((i >> 2) & 31), j = (uint32_t)((i >> 7) & 1), w = (uint32_t)((i >> 8) & 15);
-            const uint64_t tile = i >> 12;
-            const uint32_t ks = (uint32_t)(tile % L.ksteps), band = (uint32_t)(tile / L.ksteps);
-            const uint32_t g = ln >> 2, t = ln & 3, sstep = 4 * j + e;
-            uint32_t v = 0;
-#pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {
-                const uint32_t n = band * kBandCols + w * 16 + g + 8 * (c & 1);
-                const uint32_t k = ks * kUnitK + sstep * 16 + 2 * t + 8 * (c >> 1);
-                if (n < N) {
-                    const uint32_t src = packed[(size_t)(k >> 3) * N + n] >> (4 * (k & 7));
-                    v |= (src & 0xFu) << (4 * c);
-                    v |= ((src >> 4) & 0xFu) << (4 * (c + 4));
-                }
-            }
-            ((uint32_t*)(out + L.off_tiles))[i] = v;
-        } else if (i < n_words + n_scales) {
-            const uint64_t j = i - n_words;
-            const uint32_t c = (uint32_t)(j % kBandCols);
-            const uint64_t row = j / kBandCols;
-            const uint32_t g = (uint32_t)(row % L.groups), band = (uint32_t)(row / L.groups);
-            const uint32_t n = band * kBandCols + c;
-            ((uint16_t*)(out + L.off_scales))[j] = n < N ? scales[(size_t)g * N + n] : (uint16_t)0;
-        } else {
-            const uint64_t j = i - n_words - n_scales;
-            const uint32_t wz = (uint32_t)(j % (kBandCols / 8));
-            const uint64_t row = j / (kBandCols / 8);
-            const uint32_t g = (uint32_t)(row % L.groups), band = (uint32_t)(row / L.groups);
-            const uint32_t n0 = band * kBandCols + wz * 8;     // eight columns, aligned to a source word
-            ((uint32_t*)(out + L.off_zeros))[j] = n0 < N ? zeros[(size_t)g * nz + (n0 >> 3)] : 0u;
-        }
-    }
-}
-
-}  // namespace
-
-extern "C" {
-
-size_t t0_w4_prepacked_bytes(uint32_t K, uint32_t N, uint32_t group) {
-    if (K == 0 || N == 0 || group == 0 || K % kUnitK || group % kUnitK || K % group) return 0;
-    return prepack_layout(K, N, group).total;
-}
-
-int t0_w4_prepack(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group) {
-    int rc = check_rt(rt);
-    if (rc != T0_OK) return rc;
-    if (!packed || !scales || !zeros || !out) return fail(T0_ERR_INVALID, "null device pointer");
-    if (K == 0 || N == 0 || group == 0 || K % kUnitK || group % kUnitK || K % group)
-        return fail(T0_ERR_UNSUPPORTED, "the streaming layout needs K %% 128 == 0 and group %% 128 == 0 with group | K (K=%u, group=%u)", K, group);
-    if (N % 8) return fail(T0_ERR_UNSUPPORTED, "N=%u must be a multiple of 8 (eight zero points per word)", N);
-    if (out & 127) return fail(T0_ERR_INVALID, "the output buffer must be 128-byte aligned");
-    DeviceGuard guard(rt->device);
-    const PrepackLayout L = prepack_layout(K, N, group);
-    const uint64_t n = L.total / 2;
-    w4_prepack_kernel<<<grid_for(n, 256), 256, 0, rt->stream>>>((const uint32_t*)packed, (const uint16_t*)scales, (const uint32_t*)zeros,
-                                                               (uint8_t*)out, K, N, (N + 7) / 8, L);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "prepack launch failed: %s", cudaGetErrorString(e));
-    rt->launches.fetch_add(1);
-    return T0_OK;
-}
-
-int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
-    int rc = check_rt(rt);
-    if (rc != T0_OK) return rc;
-    if (M == 0 || N == 0) return T0_OK;
-    if (!a || !prepacked || !y) return fail(T0_ERR_INVALID, "null device pointer");
-    if (M > 16) return fail(T0_ERR_UNSUPPORTED, "M=%u: the streaming-layout kernel takes M <= 16; use t0_w4a16_gemm on the row layout for larger M", M);
-    if (K == 0 || K % kUnitK || group == 0 || group % kUnitK || K % group || N % 8)
-        return fail(T0_ERR_UNSUPPORTED, "shape K=%u N=%u group=%u: needs K %% 128 == 0, group %% 128 == 0, group | K, N %% 8 == 0", K, N, group);
-    if ((a & 15) || (prepacked & 127) || (y & 3)) return fail(T0_ERR_INVALID, "a must be 16-byte, the weights 128-byte and y 4-byte aligned");
-    DeviceGuard guard(rt->device);
-    const PrepackLayout L = prepack_layout(K, N, group);
-    const uint64_t total = (uint64_t)L.bands * L.ksteps;
-    if (total > 0x7FFFFFFFull || L.bands * sizeof(int) > kCounterRegion) return fail(T0_ERR_UNSUPPORTED, "problem too large");
-    // enough CTAs that the activations of one CTA's steps fit in shared memory, at most one per SM
-    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, (uint64_t)rt->sm_count);
-    const uint32_t units_per_cta = (uint32_t)ceil_div((uint32_t)total, grid);
-    if (units_per_cta > (uint32_t)kFrMaxUnits)
-        return fail(T0_ERR_UNSUPPORTED, "K*N too large for one wave: %u steps per CTA, at most %d", units_per_cta, kFrMaxUnits);
-    const size_t need = kCounterRegion + (size_t)grid * 2 * kPieceFloats * sizeof(float);
-    if (need > rt->scratch_w4.size) {
-        rc = ensure_scratch(rt, rt->scratch_w4, need);
-        if (rc != T0_OK) return rc;
-        T0_CUDA(cudaMemsetAsync(rt->scratch_w4.ptr, 0, kCounterRegion, rt->stream));
-    }
-    W4Params p;
-    memset(&p, 0, sizeof p);
-    p.a = (const uint16_t*)a;
-    p.y = (float*)y;
-    p.counters = (int*)rt->scratch_w4.ptr;
-    p.partials = (float*)((uint8_t*)rt->scratch_w4.ptr + kCounterRegion);
-    p.status = rt->d_status;
-    p.M = M; p.N = N; p.K = K;
-    p.units_per_group = group / kUnitK;
-    p.n_bands = L.bands; p.ksteps = L.ksteps; p.total_units = (uint32_t)total;
-    p.a_units = units_per_cta;
-    p.tiles = (const uint8_t*)prepacked + L.off_tiles;
-    p.scales_t = (const uint8_t*)prepacked + L.off_scales;
-    p.zeros_t = (const uint8_t*)prepacked + L.off_zeros;
-    p.groups = L.groups;
-    const uint32_t m_groups = M <= 8 ? 1 : 2;
-    auto smem_for = [](uint32_t units, uint32_t mg) {
-        return (size_t)128 + (size_t)kStages * kWeightBytes + (size_t)units * (kScaleBytes + kZeroBytes + mg * kFrAUnitBytes) + 256;
-    };
-    const size_t smem = smem_for(units_per_cta, m_groups);
-    static bool attr_set[64] = {};
-    if (rt->device < 64 && !attr_set[rt->device]) {
-        T0_CUDA(cudaFuncSetAttribute(w4a16_frag_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_for(kFrMaxUnits, 1)));
-        T0_CUDA(cudaFuncSetAttribute(w4a16_frag_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_for(kFrMaxUnits, 2)));
-        attr_set[rt->device] = true;
-    }
-    static const bool trace = getenv("T0_W4_TRACE") != nullptr;
-    unsigned long long* d_stamps = nullptr;
-    if (trace) {
-        T0_CUDA(cudaMalloc(&d_stamps, (size_t)grid * 8 * sizeof(unsigned long long)));
-        T0_CUDA(cudaMemset(d_stamps, 0, (size_t)grid * 8 * sizeof(unsigned long long)));
-        p.stamps = d_stamps;
-    }
-    static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kFrThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = rt->stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = use_pdl ? 1 : 0;
-    cudaError_t le = m_groups == 1 ? cudaLaunchKernelEx(&cfg, w4a16_frag_kernel<1>, p) : cudaLaunchKernelEx(&cfg, w4a16_frag_kernel<2>, p);
-    if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
-    if (trace) {
-        std::vector<unsigned long long> h((size_t)grid * 8);
-        T0_CUDA(cudaStreamSynchronize(rt->stream));
-        T0_CUDA(cudaMemcpy(h.data(), d_stamps, h.size() * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-        cudaFree(d_stamps);
-        unsigned long long t_min = ~0ull, t_max = 0;
-        double stage = 0, loop = 0, tail = 0;
-        for (uint32_t c = 0; c < grid; ++c) {
-            t_min = std::min(t_min, h[c * 4]); t_max = std::max(t_max, h[c * 4 + 3]);
-            stage += (double)(h[c * 4 + 1] - h[c * 4]); loop += (double)(h[c * 4 + 2] - h[c * 4 + 1]); tail += (double)(h[c * 4 + 3] - h[c * 4 + 2]);
-        }
-        uint32_t slow = 0;
-        for (uint32_t c = 1; c < grid; ++c)
-            if (h[c * 4 + 3] - h[c * 4] > h[slow * 4 + 3] - h[slow * 4]) slow = c;
-        fprintf(stderr, "[w4a16 stream trace] M=%u N=%u K=%u: first entry -> last exit %.2f us; per CTA mean: set-up %.2f us, main loop %.2f us, flush+exit %.2f us; "
-                "slowest CTA %u: entered %.2f us after the first, set-up %.2f, main loop %.2f, flush+exit %.2f\n",
-                M, N, K, (t_max - t_min) * 1e-3, stage / grid * 1e-3, loop / grid * 1e-3, tail / grid * 1e-3, slow, (h[slow * 4] - t_min) * 1e-3,
-                (h[slow * 4 + 1] - h[slow * 4]) * 1e-3, (h[slow * 4 + 2] - h[slow * 4 + 1]) * 1e-3, (h[slow * 4 + 3] - h[slow * 4 + 2]) * 1e-3);
-    }
-    rt->launches.fetch_add(1);
-    return T0_OK;
-}
-
-int t0_w4a16_gemm_prepacked_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count) {
-    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
-    for (size_t i = 0; i < count; ++i) {
-        const t0_w4a16_args& a = args[i];
-        int rc = t0_w4a16_gemm_prepacked(rt, a.a, a.packed, a.y, a.m, a.n, a.k, a.group);
-        if (rc != T0_OK) return rc;
-    }
-    return T0_OK;
 }
 
 }  // extern "C"

@@ -191,8 +191,8 @@ def test_fused_small_shapes(t0, oracle, rt, M, K, N, G):
 
 @pytest.mark.parametrize("M", [1, 16, 128])
 @pytest.mark.parametrize("N", [11008, 14336])
-def test_baseline_config4_full_size(t0, oracle, rt, M, N):
-    # BASELINE config 4: K = 4096, group 128, activations N(0,1), codes uniform, scales U(0.001, 0.02), zero points uniform
+def test_w4a16_full_size(t0, oracle, rt, M, N):
+    # the W4A16 configuration at full size: K = 4096, group 128, activations N(0,1), codes uniform, scales U(0.001, 0.02), zero points uniform
     K, G = 4096, 128
     a = oracle.fill_normal_bf16(M * K, 7 + M)
     packed, scales, zeros = make_w4(oracle, K, N, G, seed=N)
@@ -293,7 +293,7 @@ def test_prepacked_small_shapes(t0, oracle, rt, M, K, N, G):
 
 @pytest.mark.parametrize("M", [1, 16])
 @pytest.mark.parametrize("N", [11008, 14336])
-def test_prepacked_baseline_config4_full_size(t0, oracle, rt, M, N):
+def test_prepacked_w4a16_full_size(t0, oracle, rt, M, N):
     K, G = 4096, 128
     a = oracle.fill_normal_bf16(M * K, 7 + M)
     packed, scales, zeros = make_w4(oracle, K, N, G, seed=N)
@@ -310,7 +310,6 @@ def test_prepacked_argument_errors(t0, rt):
     assert lib.t0_w4_prepacked_bytes(100, 64, 128) == 0
     assert lib.t0_w4a16_gemm_prepacked(rt._h, p, p, p, 17, 256, 128, 128) == 6        # M beyond the fused kernel
     assert lib.t0_w4a16_gemm_prepacked(rt._h, p, p, p, 4, 256, 192, 64) == 6          # K, group not multiples of 128
-    assert lib.t0_w4a16_gemm_prepacked(rt._h, p, p, p, 1, 28672, 8192, 128) == 6      # more than one wave of steps
     assert lib.t0_w4a16_gemm_prepacked(rt._h, p, 0, p, 1, 256, 128, 128) == 1         # null pointer
     assert not rt.is_poisoned()
     buf.free()
@@ -318,7 +317,7 @@ def test_prepacked_argument_errors(t0, rt):
 
 def test_row_layout_more_than_one_wave_of_steps(t0, oracle, rt):
     # K*N large enough that a CTA owns more than 20 steps: the row-layout entry then runs the first fused kernel, which
-    # restages its activations in batches of 12 steps; the streaming-layout entry refuses (covered above)
+    # restages its activations in batches of 12 steps
     M, K, N, G = 4, 8192, 16384, 128
     a = oracle.fill_normal_bf16(M * K, 5)
     packed, scales, zeros = make_w4(oracle, K, N, G, seed=3)
@@ -328,3 +327,97 @@ def test_row_layout_more_than_one_wave_of_steps(t0, oracle, rt):
         outs.append(run_w4a16(rt, a, packed, scales, zeros, M, N, K, G))
     assert_close(outs[0], ref, K)
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_prepacked_long_ranges(t0, oracle, rt):
+    # K*N large enough that a CTA walks dozens of steps and several whole bands: the ring wraps many times
+    M, K, N, G = 4, 8192, 16384, 128
+    a = oracle.fill_normal_bf16(M * K, 5)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=3)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    outs = run_w4a16_prepacked(rt, a, packed, scales, zeros, M, N, K, G, repeats=2)
+    assert_close(outs[0], ref, K)
+    assert np.array_equal(outs[0], outs[1])
+
+
+def _batch_problems(oracle, rt, shapes, seed0):
+    """Uploads and prepacks one problem per (M, K, N, G); returns (args, per-problem host data, buffers)."""
+    probs, bufs = [], []
+    for i, (M, K, N, G) in enumerate(shapes):
+        a = oracle.fill_normal_bf16(M * K, seed0 + i)
+        packed, scales, zeros = make_w4(oracle, K, N, G, seed=seed0 + 100 + i)
+        xa, xp, xs, xz = rt.upload(a), rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+        pre = rt.w4_prepack(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G)
+        y = rt.alloc(M * N * 4 + 4096)
+        y.write(np.full(M * N + 1024, -9999.0, np.float32))
+        rt.synchronize()
+        for b in (xp, xs, xz):
+            b.free()
+        probs.append(dict(M=M, K=K, N=N, G=G, a=a, packed=packed, scales=scales, zeros=zeros, xa=xa, pre=pre, y=y))
+        bufs += [xa, pre, y]
+    return probs, bufs
+
+
+def test_prepacked_batch_of_mixed_problems(t0, oracle, rt):
+    # one launch walks the steps of every problem of the list: different M (both row-group forms), K, N, group sizes,
+    # ranges that start and end inside bands of different problems
+    shapes = [(1, 4096, 11008, 128), (16, 512, 264, 128), (5, 1024, 1024, 256), (8, 256, 8, 128), (2, 2048, 3000, 512),
+              (16, 4096, 1536, 128), (1, 128, 40, 128), (9, 1024, 4096, 128)]
+    probs, bufs = _batch_problems(oracle, rt, shapes, 50)
+    calls = [t0.W4A16Args(p["xa"].gpu_addr(), p["pre"].gpu_addr(), 0, 0, p["y"].gpu_addr(), p["M"], p["N"], p["K"], p["G"]) for p in probs]
+    before = rt.launch_count()
+    rt.w4a16_gemm_prepacked_batch(calls)
+    rt.synchronize()
+    assert rt.launch_count() - before == 1                    # one launch for the whole list
+    batch_out = []
+    for p in probs:
+        M, N, K, G = p["M"], p["N"], p["K"], p["G"]
+        got = p["y"].read(M * N * 4, np.float32).reshape(M, N)
+        assert np.all(p["y"].read_bytes(M * N * 4, 4096, np.float32) == -9999.0), "wrote past the output"
+        assert_close(got, oracle.w4a16_gemm(p["a"], p["packed"], p["scales"], p["zeros"], M, N, K, G), K)
+        batch_out.append(got)
+    # the same list again: where a band is cut between CTAs depends on the list, not on timing, so reruns agree bit for bit
+    for p in probs:
+        p["y"].zero()
+    rt.w4a16_gemm_prepacked_batch(calls)
+    rt.synchronize()
+    for p, got in zip(probs, batch_out):
+        assert np.array_equal(p["y"].read(p["M"] * p["N"] * 4, np.float32).reshape(p["M"], p["N"]), got)
+    # and one call at a time (bands are cut elsewhere, so the last bits of a sum may differ: tolerance, not equality)
+    for p in probs:
+        M, N, K, G = p["M"], p["N"], p["K"], p["G"]
+        p["y"].zero()
+        rt.w4a16_gemm_prepacked(p["xa"].gpu_addr(), p["pre"].gpu_addr(), p["y"].gpu_addr(), M, N, K, G)
+        rt.synchronize()
+        assert_close(p["y"].read(M * N * 4, np.float32).reshape(M, N), oracle.w4a16_gemm(p["a"], p["packed"], p["scales"], p["zeros"], M, N, K, G), K)
+    for b in bufs:
+        b.free()
+
+
+def test_prepacked_batch_longer_than_one_launch(t0, oracle, rt):
+    # 70 problems: the list is cut into launches of at most 32; activations differ per problem, two weight sets alternate
+    K, N, G = 1024, 2048, 128
+    w = [make_w4(oracle, K, N, G, seed=900 + i) for i in range(2)]
+    pres = []
+    for packed, scales, zeros in w:
+        xp, xs, xz = rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+        pres.append(rt.w4_prepack(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G))
+        rt.synchronize()
+        for b in (xp, xs, xz):
+            b.free()
+    n_prob = 70
+    ms = [1 + (i * 7) % 16 for i in range(n_prob)]
+    a_host = [oracle.fill_normal_bf16(ms[i] * K, 300 + i) for i in range(n_prob)]
+    xas = [rt.upload(a) for a in a_host]
+    ys = [rt.alloc(ms[i] * N * 4) for i in range(n_prob)]
+    calls = [t0.W4A16Args(xas[i].gpu_addr(), pres[i % 2].gpu_addr(), 0, 0, ys[i].gpu_addr(), ms[i], N, K, G) for i in range(n_prob)]
+    before = rt.launch_count()
+    rt.w4a16_gemm_prepacked_batch(calls)
+    rt.synchronize()
+    assert rt.launch_count() - before == 3
+    for i in range(n_prob):
+        packed, scales, zeros = w[i % 2]
+        got = ys[i].read(ms[i] * N * 4, np.float32).reshape(ms[i], N)
+        assert_close(got, oracle.w4a16_gemm(a_host[i], packed, scales, zeros, ms[i], N, K, G), K)
+    for b in pres + xas + ys:
+        b.free()
