@@ -3,16 +3,22 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
 
 N = 1   workload `gemm_bf16_4096`: bf16 4096^3 GEMM, fp32 accumulate and output (the configuration the
-        headline metric is quoted on).  A step is one GEMM over one of several resident input sets.
+        headline metric is quoted on).  A step is one GEMM over one of several resident input sets.  The line also
+        carries, under "secondary", short runs of the other single-GPU workloads of the metric (the skinny GEMMs and
+        the W4A16 shapes, HBM-bound, reported in GB/s against the measured copy bandwidth; the other square sizes).
 N > 1   workload `gemm_bf16_16384_sharded`: the 16384^3 GEMM sharded by N-column blocks, A replicated,
-        each rank computes C[:, N/g slice]; no data-path collective (strong scaling).
+        each rank computes C[:, N/g slice]; no data-path collective (strong scaling).  Rank 0 then runs the whole
+        16384^3 on its one GPU, so the line carries the single-GPU time and the speed-up over it.
 `value` is whole-job TFLOP/s with inputs resident in HBM, timed with CUDA events on the launching
 stream, max over ranks.  `e2e` is the same metric through the C-ABI call with pinned HOST buffers:
 host->device copies of the step's operands and the device->host read of its result are inside the
 timed region; the steps are handed over as one array (`t0_gemm_launch_host_batch`) so that consecutive
-steps overlap on the link, and `e2e.serial_value` is the same steps made one blocking call after the other.  `--impl reference` times the CPU restatement of the reference's own CPU GEMM on the
+steps overlap on the link, and `e2e.serial_value` is the same steps made one blocking call after the other.
+With N > 1 every rank uploads 1/N of A and the ranks complete it over NVLink, so A crosses the host link once.
+`--impl reference` times the CPU restatement of the reference's own CPU GEMM on the
 host cores for the same config (the reference's GPU path targets AMD RDNA through /dev/kfd and its Rust
 toolchain is absent, so its CPU reference GEMM is the only part of it that can run on this box).
+`--lib-ab` (measurement only, never on the product path) times the vendor library's bf16 GEMM beside the repo's kernel.
 """
 from __future__ import annotations
 
@@ -35,7 +41,7 @@ WORKLOADS = {
     "gemm_bf16_2048": dict(m=2048, n=2048, k=2048),
     "gemm_bf16_8192": dict(m=8192, n=8192, k=8192),
     "gemm_bf16_16384_sharded": dict(m=16384, n=16384, k=16384),
-    # HBM-bound secondary workloads (BASELINE configs 3 and 4); metric: algorithmic GB/s
+    # HBM-bound workloads (the skinny and the W4A16 configurations); metric: algorithmic GB/s
     "gemm_bf16_skinny_128x4096x4096": dict(m=128, n=4096, k=4096, hbm=True),
     "gemm_bf16_skinny_64x4096x16384_sk4": dict(m=64, n=4096, k=16384, split_k=4, hbm=True),
     "w4a16_m1_n11008": dict(m=1, n=11008, k=4096, w4=True, hbm=True),
@@ -43,149 +49,22 @@ WORKLOADS = {
     "w4a16_m1_n14336": dict(m=1, n=14336, k=4096, w4=True, hbm=True),
     "w4a16_m16_n14336": dict(m=16, n=14336, k=4096, w4=True, hbm=True),
     "w4a16_m128_n11008": dict(m=128, n=11008, k=4096, w4=True, hbm=True),
+    "w4a16_m128_n14336": dict(m=128, n=14336, k=4096, w4=True, hbm=True),
 }
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, from the ncu capture summarised
-# in profiles/ (bytes); None until a capture of that workload exists.
-NCU_TRAFFIC_BYTES = {"gemm_bf16_4096": 142.4e6, "w4a16_m1_n11008": 23.47e6,
-                     "gemm_bf16_skinny_64x4096x16384_sk4": 144.0e6 + 5.2e6}   # GEMM kernel + plane reduction
+SECONDARY = ["w4a16_m1_n11008", "w4a16_m16_n11008", "w4a16_m1_n14336", "w4a16_m16_n14336", "w4a16_m128_n11008", "w4a16_m128_n14336",
+             "gemm_bf16_skinny_128x4096x4096", "gemm_bf16_skinny_64x4096x16384_sk4", "gemm_bf16_2048", "gemm_bf16_8192"]
 W4_GROUP = 128
 
 
-def run_hbm_workload(args, name):
-    """Secondary single-GPU workloads that are HBM-bound: the skinny GEMMs and the W4A16 GEMM.  One JSON line with the
-    same keys as the headline; `value` is algorithmic bytes / second (the bytes formula is in `config.bytes`)."""
-    import torch
-    t0 = importlib.import_module("rust-gpu_b200")
-    t0.lib()
-    import oracle
-    oracle.build()
-    w = WORKLOADS[name]
-    M, N, K = w["m"], w["n"], w["k"]
-    w4 = bool(w.get("w4"))
-    G = W4_GROUP
-    steps = args.steps if args.steps is not None else 200
-    warmup = max(3, args.warmup if args.warmup is not None else 10)
-    torch.cuda.set_device(0)
-    rt = t0.GpuRuntime(0)
-    if w4:
-        alg_bytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2 + M * K * 2 + M * N * 4
-        set_bytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2
-    else:
-        alg_bytes = M * K * 2 + N * K * 2 + M * N * 4
-        set_bytes = N * K * 2
-    n_sets = max(2, -(-3 * 126 * 2 ** 20 // set_bytes))      # rotating weight sets: together three times the L2
-    a_host = oracle.fill_normal_bf16(M * K, 7 + M) if w4 else oracle.fill_uniform_bf16(M * K, 42 + M)
-    xa = rt.upload(a_host)
-    # the problems of one batched launch run concurrently, so consecutive steps write distinct outputs
-    n_out = 32 if w4 else 1
-    ys = [rt.alloc(M * N * 4) for _ in range(n_out)]
-    y = ys[(steps - 1) % n_out]          # the output of the last step, checked against the oracle below
-    sets = []
-    for s in range(n_sets):
-        if w4:
-            xp, xs, xz = rt.alloc((K // 8) * N * 4), rt.alloc((K // G) * N * 2), rt.alloc((K // G) * (N // 8) * 4)
-            rt.fill_u32(xp.gpu_addr(), (K // 8) * N, 1000 + s)
-            rt.fill_range_bf16(xs.gpu_addr(), (K // G) * N, 2000 + s, 0.001, 0.02)
-            rt.fill_u32(xz.gpu_addr(), (K // G) * (N // 8), 3000 + s)
-            sets.append((xp, xs, xz))
-        else:
-            xb = rt.alloc(N * K * 2)
-            rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N + 1000 * s)
-            sets.append((xb,))
-    if w4 and M <= 16 and not args.row_layout:
-        # weights go to the streaming layout once, outside the timed region (a weight-load-time conversion)
-        pre = [rt.w4_prepack(*(b.gpu_addr() for b in st), K, N, G) for st in sets]
-        rt.synchronize()
-        for st in sets:
-            for b in st:
-                b.free()
-        calls = [t0.W4A16Args(xa.gpu_addr(), pre[i % n_sets].gpu_addr(), 0, 0, ys[i % n_out].gpu_addr(), M, N, K, G) for i in range(steps)]
-        submit = rt.w4a16_gemm_prepacked_batch
-        kernel = "w4a16_stream_kernel (streaming layout, one persistent launch per 32 problems)"
-    elif w4:
-        calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), ys[i % n_out].gpu_addr(), M, N, K, G) for i in range(steps)]
-        submit = rt.w4a16_gemm_batch
-        kernel = "w4a16_tc_kernel (row layout, tcgen05)" if M <= 16 else "dequant_w4_b200_kernel + gemm"
-    else:
-        cfg = t0.auto_select(M, K, N)
-        sk = w.get("split_k", cfg.split())
-        kw = dict(tile_n=cfg.tile_n, split_k=sk, swap_grid=bool(cfg.swap_grid), pair_cta=2)
-        calls = [rt.gemm_args(xa.gpu_addr(), sets[i % n_sets][0].gpu_addr(), y.gpu_addr(), M, N, K, **kw) for i in range(steps)]
-        submit = rt.gemm_batch
-        kernel = cfg.copy(split_k=sk).name()
-    submit(calls[:warmup])
-    rt.synchronize()
-    sampler = ClockSampler(0)
-    sampler.start()
-    before = rt.launch_count()
-    best = float("inf")
-    for _ in range(3):
-        rt.timer_start()
-        submit(calls)
-        best = min(best, rt.timer_stop())
-    clocks = sampler.stop()
-    launches = (rt.launch_count() - before) // 3
-    per_launch_s = best * 1e-3 / steps
-    gbs = alg_bytes / per_launch_s / 1e9
-
-    # parity of the last step against the oracle (full result: these shapes are small)
-    s_idx = (steps - 1) % n_sets
-    got = y.read(M * N * 4, np.float32).reshape(M, N)
-    if w4:
-        ref = oracle.w4a16_gemm(a_host, oracle.fill_u32((K // 8) * N, 1000 + s_idx), oracle.fill_range_bf16((K // G) * N, 2000 + s_idx, 0.001, 0.02),
-                                oracle.fill_u32((K // G) * (N // 8), 3000 + s_idx), M, N, K, G)
-    else:
-        ref = oracle.gemm_nt(a_host, oracle.fill_uniform_bf16(N * K, 137 + N + 1000 * s_idx), M, K, N)
-    err = float(np.abs(got - ref).max())
-    tol = 5e-3 * (K / 256) ** 0.5
-    if not err <= tol:
-        print(json.dumps({"error": "parity check failed", "max_abs_err": err, "tol": tol}), flush=True)
-        sys.exit(1)
-
-    # end to end: the step's activations go up from pinned host memory, the result comes back; weights stay resident
-    a_pin = torch.from_numpy(a_host.view(np.int16).copy()).pin_memory().numpy()
-    y_pin = torch.empty(M * N, dtype=torch.float32).pin_memory().numpy()
-    C = __import__("ctypes")
-    e2e_steps = min(steps, 50)
-    t_start = time.perf_counter()
-    for i in range(e2e_steps):
-        xa.write(a_pin)
-        submit([calls[i]])
-        t0._check(t0.lib().t0_rt_read_f32(rt._h, y._h, M * N, y_pin.ctypes.data_as(C.c_void_p)))
-    e2e_s = (time.perf_counter() - t_start) / e2e_steps
-
-    # CPU baseline on a bounded sample: all rows, the first n_cpu columns
-    n_cpu = min(N, 2048)
-    t_cpu = float("inf")
-    if w4:
-        pk = oracle.fill_u32((K // 8) * N, 1000).reshape(K // 8, N)[:, :n_cpu].copy().reshape(-1)
-        sc = oracle.fill_range_bf16((K // G) * N, 2000, 0.001, 0.02).reshape(K // G, N)[:, :n_cpu].copy().reshape(-1)
-        zp = oracle.fill_u32((K // G) * (n_cpu // 8), 3000)
-        for _ in range(3):
-            t = time.perf_counter(); oracle.w4a16_gemm(a_host, pk, sc, zp, M, n_cpu, K, G); t_cpu = min(t_cpu, time.perf_counter() - t)
-    else:
-        bh = oracle.fill_uniform_bf16(n_cpu * K, 137 + N)
-        for _ in range(3):
-            t = time.perf_counter(); oracle.gemm_nt(a_host, bh, M, K, n_cpu); t_cpu = min(t_cpu, time.perf_counter() - t)
-    cpu_gbs = alg_bytes * (n_cpu / N) / t_cpu / 1e9
-
-    peaks = measured_peaks()
-    line = {"metric": "w4a16_hbm_gbs" if w4 else "skinny_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-            "ms_per_step": per_launch_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int4 x bf16 -> f32" if w4 else "bf16", "data": "synthetic",
-            "config": {"workload": name, "m": M, "n": N, "k": K, "group": G if w4 else None, "kernel": kernel, "bytes": alg_bytes,
-                       "tflops": 2.0 * M * N * K / per_launch_s / 1e12, "input_sets": n_sets,
-                       "l2": f"{n_sets} resident weight sets of {set_bytes >> 20} MiB rotate (> 126 MB L2)",
-                       "pct_of_nominal_hbm": round(100.0 * gbs / 8000.0, 1)},
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                         "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peaks['source']} (copy bandwidth)"},
-            "clocks": clocks, "gpu_launches": int(launches), "parity": {"max_abs_err": err, "tol": tol},
-            "e2e": {"value": alg_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 4,
-                    "steps": e2e_steps, "note": "weights resident; the step's activations and result cross PCIe"},
-            "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": oracle.host_threads(), "kind": "port",
-                             "sample": f"all {M} rows, the first {n_cpu} of {N} columns, best of 3, {t_cpu:.3f} s per pass"}}
-    print(json.dumps(line), flush=True)
-    rt.close()
+def ncu_traffic(name):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's dominant kernel, from the ncu capture recorded
+    in profiles/ncu_traffic.json (bytes, with the commit and date the capture was taken at); None when no capture exists."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            entry = json.load(f).get(name)
+        return float(entry["bytes_per_launch"]) if entry else None
+    except (OSError, ValueError, KeyError, TypeError):
+        return None
 
 
 def measured_peaks():
@@ -196,6 +75,13 @@ def measured_peaks():
         return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
                     bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+def tensor_peak(peaks, timed_ms):
+    """The tensor-bound denominator: the burst figure for a timed region under a second, the sustained one beyond."""
+    if timed_ms < 1000.0:
+        return peaks["bf16_tflops"], f"{peaks['source']} (burst cuBLAS bf16: the timed region lasted {timed_ms:.0f} ms)"
+    return peaks["bf16_tflops_sustained"], f"{peaks['source']} (sustained cuBLAS bf16: the timed region lasted {timed_ms:.0f} ms)"
 
 
 class ClockSampler:
@@ -247,13 +133,218 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
+# ----------------------------------------------------------------------------- HBM-bound workloads
+
+def run_hbm_workload(args, name, rt=None, brief=False):
+    """The single-GPU workloads that are HBM-bound: the skinny GEMMs and the W4A16 GEMM.  Returns one line with the
+    same keys as the headline; `value` is algorithmic bytes / second (the bytes formula is in `config.bytes`).
+    `brief` leaves out the end-to-end and CPU legs (the form the default run embeds under "secondary")."""
+    import torch
+    t0 = importlib.import_module("rust-gpu_b200")
+    t0.lib()
+    import oracle
+    oracle.build()
+    w = WORKLOADS[name]
+    M, N, K = w["m"], w["n"], w["k"]
+    w4 = bool(w.get("w4"))
+    G = W4_GROUP
+    steps = 96 if brief else (args.steps if args.steps is not None else 256)
+    warmup = 8 if brief else max(3, args.warmup if args.warmup is not None else 10)
+    torch.cuda.set_device(0)
+    own_rt = rt is None
+    if own_rt:
+        rt = t0.GpuRuntime(0)
+    bufs = []
+
+    def alloc(n):
+        b = rt.alloc(n)
+        bufs.append(b)
+        return b
+
+    if w4:
+        alg_bytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2 + M * K * 2 + M * N * 4
+        set_bytes = K * N // 2 + (K // G) * N * 2 + (K // G) * N // 2
+    else:
+        alg_bytes = M * K * 2 + N * K * 2 + M * N * 4
+        set_bytes = N * K * 2
+    n_sets = max(2, -(-3 * 126 * 2 ** 20 // set_bytes))      # rotating weight sets: together three times the L2
+    a_host = oracle.fill_normal_bf16(M * K, 7 + M) if w4 else oracle.fill_uniform_bf16(M * K, 42 + M)
+    xa = alloc(M * K * 2)
+    xa.write(a_host)
+    # the problems of one batched launch run concurrently, so consecutive steps write distinct outputs
+    n_out = 32 if w4 else 1
+    ys = [alloc(M * N * 4) for _ in range(n_out)]
+    y = ys[(steps - 1) % n_out]          # the output of the last step, checked against the oracle below
+    sets = []
+    for s in range(n_sets):
+        if w4:
+            xp, xs, xz = rt.alloc((K // 8) * N * 4), rt.alloc((K // G) * N * 2), rt.alloc((K // G) * (N // 8) * 4)
+            rt.fill_u32(xp.gpu_addr(), (K // 8) * N, 1000 + s)
+            rt.fill_range_bf16(xs.gpu_addr(), (K // G) * N, 2000 + s, 0.001, 0.02)
+            rt.fill_u32(xz.gpu_addr(), (K // G) * (N // 8), 3000 + s)
+            sets.append((xp, xs, xz))
+        else:
+            xb = rt.alloc(N * K * 2)
+            rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N + 1000 * s)
+            sets.append((xb,))
+    if w4 and M <= 16 and not args.row_layout:
+        # weights go to the streaming layout once, outside the timed region (a weight-load-time conversion)
+        pre = [rt.w4_prepack(*(b.gpu_addr() for b in st), K, N, G) for st in sets]
+        bufs += pre
+        rt.synchronize()
+        for st in sets:
+            for b in st:
+                b.free()
+        calls = [t0.W4A16Args(xa.gpu_addr(), pre[i % n_sets].gpu_addr(), 0, 0, ys[i % n_out].gpu_addr(), M, N, K, G) for i in range(steps)]
+        submit = rt.w4a16_gemm_prepacked_batch
+        kernel = "w4a16_stream_kernel (streaming layout, one persistent launch per 32 problems)"
+    elif w4:
+        bufs += [b for st in sets for b in st]
+        calls = [t0.W4A16Args(xa.gpu_addr(), *(b.gpu_addr() for b in sets[i % n_sets]), ys[i % n_out].gpu_addr(), M, N, K, G) for i in range(steps)]
+        submit = rt.w4a16_gemm_batch
+        kernel = "w4a16_tc_kernel (row layout, tcgen05)" if M <= 16 else "dequant_w4_b200_kernel + gemm (two steps through a K x N bf16 scratch)"
+    else:
+        bufs += [b for st in sets for b in st]
+        cfg = t0.auto_select(M, K, N)
+        sk = w.get("split_k", cfg.split())
+        kw = dict(tile_n=cfg.tile_n, split_k=sk, swap_grid=bool(cfg.swap_grid), pair_cta=2)
+        calls = [rt.gemm_args(xa.gpu_addr(), sets[i % n_sets][0].gpu_addr(), y.gpu_addr(), M, N, K, **kw) for i in range(steps)]
+        submit = rt.gemm_batch
+        kernel = cfg.copy(split_k=sk).name()
+    submit(calls[:warmup])
+    rt.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    before = rt.launch_count()
+    best = float("inf")
+    for _ in range(3):
+        rt.timer_start()
+        submit(calls)
+        best = min(best, rt.timer_stop())
+    clocks = sampler.stop()
+    launches = (rt.launch_count() - before) // 3
+    per_launch_s = best * 1e-3 / steps
+    gbs = alg_bytes / per_launch_s / 1e9
+
+    # parity of the last step against the oracle (full result: these shapes are small)
+    s_idx = (steps - 1) % n_sets
+    got = y.read(M * N * 4, np.float32).reshape(M, N)
+    if w4:
+        ref = oracle.w4a16_gemm(a_host, oracle.fill_u32((K // 8) * N, 1000 + s_idx), oracle.fill_range_bf16((K // G) * N, 2000 + s_idx, 0.001, 0.02),
+                                oracle.fill_u32((K // G) * (N // 8), 3000 + s_idx), M, N, K, G)
+    else:
+        ref = oracle.gemm_nt(a_host, oracle.fill_uniform_bf16(N * K, 137 + N + 1000 * s_idx), M, K, N)
+    err = float(np.abs(got - ref).max())
+    tol = 5e-3 * (K / 256) ** 0.5
+    if not err <= tol:
+        print(json.dumps({"error": "parity check failed", "workload": name, "max_abs_err": err, "tol": tol}), flush=True)
+        sys.exit(1)
+
+    peaks = measured_peaks()
+    tflops = 2.0 * M * N * K / per_launch_s / 1e12
+    line = {"metric": "w4a16_hbm_gbs" if w4 else "skinny_gemm_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+            "ms_per_step": per_launch_s * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int4 x bf16 -> f32" if w4 else "bf16", "data": "synthetic",
+            "config": {"workload": name, "m": M, "n": N, "k": K, "group": G if w4 else None, "kernel": kernel, "bytes": alg_bytes,
+                       "tflops": tflops, "input_sets": n_sets,
+                       "l2": f"{n_sets} resident weight sets of {set_bytes >> 20} MiB rotate (> 126 MB L2)",
+                       "pct_of_nominal_hbm": round(100.0 * gbs / 8000.0, 1)},
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                         "traffic": ncu_traffic(name), "peak_source": f"{peaks['source']} (copy bandwidth)"},
+            "clocks": clocks, "gpu_launches": int(launches), "parity": {"max_abs_err": err, "tol": tol}}
+    if w4 and M > 16:
+        # above the ridge point both roofs apply: also the tensor-bound fraction
+        line["roofline"]["tensor_frac"] = tflops / peaks["bf16_tflops"]
+
+    if not brief:
+        # end to end: the step's activations go up from pinned host memory, the result comes back; weights stay resident
+        a_pin = torch.from_numpy(a_host.view(np.int16).copy()).pin_memory().numpy()
+        y_pin = torch.empty(M * N, dtype=torch.float32).pin_memory().numpy()
+        C = __import__("ctypes")
+        e2e_steps = min(steps, 50)
+        t_start = time.perf_counter()
+        for i in range(e2e_steps):
+            xa.write(a_pin)
+            submit([calls[i]])
+            t0._check(t0.lib().t0_rt_read_f32(rt._h, ys[i % n_out]._h, M * N, y_pin.ctypes.data_as(C.c_void_p)))
+        e2e_s = (time.perf_counter() - t_start) / e2e_steps
+        line["e2e"] = {"value": alg_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 4,
+                       "steps": e2e_steps, "note": "weights resident; the step's activations and result cross PCIe"}
+        # CPU baseline on a bounded sample: all rows, the first n_cpu columns
+        n_cpu = min(N, 2048)
+        t_cpu = float("inf")
+        if w4:
+            pk = oracle.fill_u32((K // 8) * N, 1000).reshape(K // 8, N)[:, :n_cpu].copy().reshape(-1)
+            sc = oracle.fill_range_bf16((K // G) * N, 2000, 0.001, 0.02).reshape(K // G, N)[:, :n_cpu].copy().reshape(-1)
+            zp = oracle.fill_u32((K // G) * (n_cpu // 8), 3000)
+            for _ in range(3):
+                t = time.perf_counter(); oracle.w4a16_gemm(a_host, pk, sc, zp, M, n_cpu, K, G); t_cpu = min(t_cpu, time.perf_counter() - t)
+        else:
+            bh = oracle.fill_uniform_bf16(n_cpu * K, 137 + N)
+            for _ in range(3):
+                t = time.perf_counter(); oracle.gemm_nt(a_host, bh, M, K, n_cpu); t_cpu = min(t_cpu, time.perf_counter() - t)
+        line["cpu_baseline"] = {"value": alg_bytes * (n_cpu / N) / t_cpu / 1e9, "unit": "GB/s", "cores": oracle.host_threads(), "kind": "port",
+                                "sample": f"all {M} rows, the first {n_cpu} of {N} columns, best of 3, {t_cpu:.3f} s per pass"}
+    rt.synchronize()
+    for b in bufs:
+        b.free()
+    if own_rt:
+        rt.close()
+    return line
+
+
+def run_square_brief(t0, rt, name):
+    """A short device-resident run of another size of the square sweep, for the default line's "secondary" list."""
+    import oracle
+    w = WORKLOADS[name]
+    M, N, K = w["m"], w["n"], w["k"]
+    set_bytes = M * K * 2 + N * K * 2 + M * N * 4
+    n_sets = max(2, min(4, -(-3 * 126 * 2 ** 20 // set_bytes)))
+    sets = []
+    for s in range(n_sets):
+        xa, xb, y = rt.alloc(M * K * 2), rt.alloc(N * K * 2), rt.alloc(M * N * 4)
+        rt.fill_uniform_bf16(xa.gpu_addr(), M * K, 42 + M + 1000 * s)
+        rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N + 1000 * s)
+        sets.append((xa, xb, y))
+    steps = 60 if M <= 4096 else 20
+    calls = [rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K) for (xa, xb, y) in sets]
+    rt.gemm_batch([calls[i % n_sets] for i in range(6)])
+    rt.synchronize()
+    best = float("inf")
+    for _ in range(3):
+        rt.timer_start()
+        rt.gemm_batch([calls[i % n_sets] for i in range(steps)])
+        best = min(best, rt.timer_stop())
+    s_idx = (steps - 1) % n_sets
+    xa, xb, y = sets[s_idx]
+    rows = [0, M // 2 + 1, M - 1]
+    b_host = oracle.fill_uniform_bf16(N * K, 137 + N + 1000 * s_idx)
+    worst = 0.0
+    for r in rows:
+        ref = oracle.gemm_nt(oracle.fill_uniform_bf16(K, 42 + M + 1000 * s_idx, r * K), b_host, 1, K, N)
+        worst = max(worst, float(np.abs(ref[0] - y.read_bytes(r * N * 4, N * 4, np.float32)).max()))
+    tol = 5e-3 * (K / 256) ** 0.5
+    if not worst <= tol:
+        print(json.dumps({"error": "parity check failed", "workload": name, "max_abs_err": worst, "tol": tol}), flush=True)
+        sys.exit(1)
+    for st in sets:
+        for b in st:
+            b.free()
+    peaks = measured_peaks()
+    tf = 2.0 * M * N * K * steps / (best * 1e-3) / 1e12
+    peak, src = tensor_peak(peaks, best)
+    return {"workload": name, "metric": "bf16_gemm_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": best / steps, "steps": steps,
+            "roofline": {"bound": "tensor", "frac": tf / peak, "peak": peak, "peak_source": src},
+            "parity": {"sampled_rows": rows, "max_abs_err": worst, "tol": tol}}
+
+
 def cpu_baseline(oracle, m, n, k, rows, threads=0):
     """Times the oracle's reference GEMM on `rows` rows of the workload; returns (TFLOP/s, seconds, cores)."""
     a = oracle.fill_uniform_bf16(rows * k, 42 + m)
     b = oracle.fill_uniform_bf16(n * k, 137 + n)
     oracle.gemm_nt(a[: 8 * k], b, 8, k, n, threads)   # page in, spin up
     best = float("inf")
-    for _ in range(3):                                # BASELINE plan: steady clock around the region, best of 3
+    for _ in range(3):                                # steady clock around the region, best of 3
         t = time.perf_counter()
         oracle.gemm_nt(a, b, rows, k, n, threads)
         best = min(best, time.perf_counter() - t)
@@ -295,6 +386,78 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def device_alias(ptr, n_elems, np_dtype):
+    """A torch tensor over device memory the runtime owns (no copy): what torch.distributed needs to move that memory."""
+    import torch
+
+    class _Raw:
+        pass
+    raw = _Raw()
+    raw.__cuda_array_interface__ = {"shape": (n_elems,), "typestr": np.dtype(np_dtype).str, "data": (ptr, False), "version": 2}
+    return torch.as_tensor(raw, device="cuda")
+
+
+def run_lib_ab(t0, rt, torch):
+    """Measurement only: the vendor library's bf16 GEMM (torch.matmul, bf16 output: it writes half the bytes of the repo's f32
+    output) timed right after the repo's kernel, in the same process, on buffers of the same sizes, with the same step
+    count, warm-up and CUDA-event timing.  Reported per arm: TFLOP/s, the SM clock (the repo's kernel stamps cycles and
+    nanoseconds itself; the library arm uses the NVML median) and time x clock = SM cycles per launch."""
+    out = []
+    for size in (2048, 4096, 8192):
+        M = N = K = size
+        n_sets = max(2, min(4, -(-3 * 126 * 2 ** 20 // (M * K * 2 + N * K * 2 + M * N * 4))))
+        steps = 200 if size <= 4096 else 40
+        sets = []
+        for s in range(n_sets):
+            xa, xb, y = rt.alloc(M * K * 2), rt.alloc(N * K * 2), rt.alloc(M * N * 4)
+            rt.fill_uniform_bf16(xa.gpu_addr(), M * K, 42 + M + 1000 * s)
+            rt.fill_uniform_bf16(xb.gpu_addr(), N * K, 137 + N + 1000 * s)
+            sets.append((xa, xb, y))
+        calls = [rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K) for (xa, xb, y) in sets]
+        rt.gemm_batch([calls[i % n_sets] for i in range(10)])
+        rt.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        ms_ours = float("inf")
+        for _ in range(3):
+            rt.timer_start()
+            rt.gemm_batch([calls[i % n_sets] for i in range(steps)])
+            ms_ours = min(ms_ours, rt.timer_stop())
+        clk_ours = sampler.stop()
+        mhz_kernel, _ = rt.last_kernel_clock()
+        # the library arm on torch tensors aliasing the same device buffers
+        ta = [device_alias(xa.gpu_addr(), M * K, np.int16).view(torch.bfloat16).view(M, K) for (xa, _, _) in sets]
+        tb = [device_alias(xb.gpu_addr(), N * K, np.int16).view(torch.bfloat16).view(N, K) for (_, xb, _) in sets]
+        tc = [torch.empty(M, N, dtype=torch.bfloat16, device="cuda") for _ in sets]
+        for i in range(10):
+            torch.matmul(ta[i % n_sets], tb[i % n_sets].t(), out=tc[i % n_sets])
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        ms_lib = float("inf")
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(steps):
+                torch.matmul(ta[i % n_sets], tb[i % n_sets].t(), out=tc[i % n_sets])
+            e1.record()
+            torch.cuda.synchronize()
+            ms_lib = min(ms_lib, e0.elapsed_time(e1))
+        clk_lib = sampler.stop()
+        flop = 2.0 * M * N * K
+        ours = {"tflops": flop * steps / (ms_ours * 1e-3) / 1e12, "us_per_launch": ms_ours * 1e3 / steps, "sm_mhz_in_kernel": round(mhz_kernel),
+                "sm_mhz_nvml_median": clk_ours["sm_mhz"], "sm_cycles_per_launch": ms_ours * 1e3 / steps * mhz_kernel, "output": "f32"}
+        lib = {"tflops": flop * steps / (ms_lib * 1e-3) / 1e12, "us_per_launch": ms_lib * 1e3 / steps, "sm_mhz_nvml_median": clk_lib["sm_mhz"],
+               "sm_cycles_per_launch_at_nvml_clock": ms_lib * 1e3 / steps * (clk_lib["sm_mhz"] or 0), "output": "bf16 (half the output bytes)",
+               "what": "torch.matmul(A[M,K] bf16, WT[N,K].t()) -> bf16, the vendor library's choice of kernel"}
+        out.append({"size": size, "steps": steps, "ours": ours, "library": lib, "ours_over_library": ours["tflops"] / lib["tflops"]})
+        del ta, tb, tc
+        for st in sets:
+            for b in st:
+                b.free()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -305,9 +468,11 @@ def main():
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true", help="default single-GPU run: leave out the short runs of the other workloads")
     ap.add_argument("--layout", default="nt", choices=["nt", "nn"], help="B as WT[N,K] (the reference's native layout) or as B[K,N]")
     ap.add_argument("--gather", action="store_true", help="sharded workload: also time GEMM + in-place NCCL all-gather of C (reported under \"gather\")")
     ap.add_argument("--row-layout", action="store_true", help="W4A16 workloads: weights in the row layout instead of the streaming layout")
+    ap.add_argument("--lib-ab", action="store_true", help="measurement only: time the vendor library's bf16 GEMM beside the repo's kernel (single GPU)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -328,18 +493,26 @@ def main():
     t0 = importlib.import_module("rust-gpu_b200")
     t0.lib()   # raises if the CUDA library is missing: there is no fallback path
 
+    if args.lib_ab:
+        torch.cuda.set_device(0)
+        rt = t0.GpuRuntime(0)
+        print(json.dumps({"lib_ab": run_lib_ab(t0, rt, torch)}), flush=True)
+        rt.close()
+        return
+
+    default_run = args.workload is None
     name = args.workload or ("gemm_bf16_4096" if world == 1 else "gemm_bf16_16384_sharded")
     if WORKLOADS[name].get("hbm"):
         if world != 1:
             print(f"workload {name} is single-GPU (replicas only)", file=sys.stderr)
             sys.exit(2)
-        run_hbm_workload(args, name)
+        print(json.dumps(run_hbm_workload(args, name)), flush=True)
         return
     sharded = name.endswith("_sharded")
     w = WORKLOADS[name]
     M, N_total, K = w["m"], w["n"], w["k"]
     N = N_total // world if sharded else N_total
-    steps = args.steps if args.steps is not None else (200 if not sharded else 5)
+    steps = args.steps if args.steps is not None else (200 if not sharded else 20)
     warmup = max(3, args.warmup if args.warmup is not None else (10 if not sharded else 3))
 
     torch.cuda.set_device(local_rank)
@@ -433,47 +606,39 @@ def main():
         ok = bool(torch.equal(probe, owner[(rank + 1) % world]))
         gather = {"ms_per_step": g_ms / steps, "value": 2.0 * M * N_total * K * steps / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                   "gathered_bytes_per_rank": M * N * 4 * (world - 1), "layout": "C_g[g][M][N/g]", "remote_block_matches": ok}
+        del c_g
 
-    # parity spot check on rank 0 (the full parity suite is tests/ -m gpu)
-    parity = None
-    if rank == 0:
-        import oracle
-        oracle.build()
-        xa, xb, y = sets[(steps - 1) % n_sets]
-        s_idx = (steps - 1) % n_sets
-        rows = [0, M // 2 + 1, M - 1]
-        b_host = oracle.fill_uniform_bf16(N * K, 137 + N_total + 1000 * s_idx)
-        worst = 0.0
-        for r in rows:
-            a_row = oracle.fill_uniform_bf16(K, 42 + M + 1000 * s_idx, r * K)
-            ref = oracle.gemm_nn(a_row, b_host, 1, K, N) if nn else oracle.gemm_nt(a_row, b_host, 1, K, N)
-            got = y.read_bytes(r * N * 4, N * 4, np.float32)
-            worst = max(worst, float(np.abs(ref[0] - got).max()))
-        parity = {"sampled_rows": rows, "max_abs_err": worst, "tol": 5e-3 * (K / 256) ** 0.5}
-        if worst > parity["tol"]:
+    # parity spot check on every rank of its own block (the full parity suite is tests/ -m gpu)
+    import oracle
+    oracle.build()
+    xa, xb, y = sets[(steps - 1) % n_sets]
+    s_idx = (steps - 1) % n_sets
+    rows = [0, M // 2 + 1, M - 1]
+    b_host = oracle.fill_uniform_bf16(N * K, 137 + N_total + 1000 * s_idx, rank * N * K if sharded else 0)
+    worst = 0.0
+    for r in rows:
+        a_row = oracle.fill_uniform_bf16(K, 42 + M + 1000 * s_idx, r * K)
+        ref = oracle.gemm_nn(a_row, b_host, 1, K, N) if nn else oracle.gemm_nt(a_row, b_host, 1, K, N)
+        got = y.read_bytes(r * N * 4, N * 4, np.float32)
+        worst = max(worst, float(np.abs(ref[0] - got).max()))
+    del b_host
+    tw = torch.tensor([worst], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+    parity = {"sampled_rows": rows, "ranks_checked": world, "max_abs_err": float(tw.item()), "tol": 5e-3 * (K / 256) ** 0.5}
+    if parity["max_abs_err"] > parity["tol"]:
+        if rank == 0:
             print(json.dumps({"error": "parity check failed", "parity": parity}), flush=True)
-            sys.exit(1)
+        sys.exit(1)
 
     # ---- end to end through the C ABI with pinned host buffers (copies inside the timed region)
     e2e = None
     if not args.no_e2e:
-        e2e_steps = max(1, min(steps, 20 if not sharded else 2))
-        a_host = torch.empty(M * K, dtype=torch.int16).pin_memory()
-        b_host_t = torch.empty(N * K, dtype=torch.int16).pin_memory()
-        y_host = torch.empty(M * N, dtype=torch.float32).pin_memory()
+        e2e_steps = max(1, min(steps, 20 if not sharded else 3))
         xa, xb, y = sets[0]
-        a_host.numpy()[:] = xa.read(M * K * 2, np.int16)
-        b_host_t.numpy()[:] = xb.read(N * K * 2, np.int16)
-        a_np, b_np, y_np = a_host.numpy(), b_host_t.numpy(), y_host.numpy()
         C = __import__("ctypes")
 
-        def e2e_step():
-            xa.write(a_np)
-            xb.write(b_np)
-            rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K, **gemm_kw)
-            t0._check(t0.lib().t0_rt_read_f32(rt._h, y._h, M * N, y_np.ctypes.data_as(C.c_void_p)))
-
-        def timed(fn):
+        def timed_region(fn):
             barrier()
             t_start = time.perf_counter()
             fn()
@@ -483,31 +648,103 @@ def main():
                 dist.all_reduce(td, op=dist.ReduceOp.MAX)
             return float(td.item())
 
-        # (1) one problem after the other, as the reference's host-facing calls do: write, write, launch, blocking read
-        e2e_step()
-        dt_serial = timed(lambda: [e2e_step() for _ in range(e2e_steps)])
-        # (2) the same steps as one array of host-operand problems: every step still uploads its operands and downloads
-        # its product, but step i+1 crosses the link while step i is computed and read back
-        host_args = [t0.GpuRuntime.gemm_args(a_np.ctypes.data, b_np.ctypes.data, y_np.ctypes.data, M, N, K, **gemm_kw)
-                     for _ in range(e2e_steps)]
-        rt.gemm_host_batch(host_args[:2])
-        dt = timed(lambda: rt.gemm_host_batch(host_args))
-        got_row = y_np.reshape(M, N)[M - 1].copy()
-        dev_row = y.read_bytes((M - 1) * N * 4, N * 4, np.float32)
-        if not np.array_equal(got_row, dev_row):
-            print(json.dumps({"error": "host-operand GEMM differs from the device-resident result"}), flush=True)
-            sys.exit(1)
-        e2e = {"value": flops_per_step * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": (M * K * 2 + N * K * 2) * (world if sharded else 1),
-               "d2h_bytes_per_step": M * N * 4 * (world if sharded else 1), "steps": e2e_steps,
-               "call": "t0_gemm_launch_host_batch (uploads, kernels and downloads of consecutive steps overlap)",
-               "serial_value": flops_per_step * e2e_steps / dt_serial / 1e12,
-               "serial_call": "t0_buf_write x2, t0_gemm_launch, t0_rt_read_f32 per step"}
+        b_host_t = torch.empty(N * K, dtype=torch.int16).pin_memory()
+        y_host = torch.empty(M * N, dtype=torch.float32).pin_memory()
+        b_host_t.numpy()[:] = xb.read(N * K * 2, np.int16)
+        b_np, y_np = b_host_t.numpy(), y_host.numpy()
+        if not sharded or world == 1:
+            a_host = torch.empty(M * K, dtype=torch.int16).pin_memory()
+            a_host.numpy()[:] = xa.read(M * K * 2, np.int16)
+            a_np = a_host.numpy()
+
+            def e2e_step():
+                xa.write(a_np)
+                xb.write(b_np)
+                rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K, **gemm_kw)
+                t0._check(t0.lib().t0_rt_read_f32(rt._h, y._h, M * N, y_np.ctypes.data_as(C.c_void_p)))
+
+            # (1) one problem after the other, as the reference's host-facing calls do: write, write, launch, blocking read
+            e2e_step()
+            dt_serial = timed_region(lambda: [e2e_step() for _ in range(e2e_steps)])
+            # (2) the same steps as one array of host-operand problems: every step still uploads its operands and downloads
+            # its product, but step i+1 crosses the link while step i is computed and read back
+            host_args = [t0.GpuRuntime.gemm_args(a_np.ctypes.data, b_np.ctypes.data, y_np.ctypes.data, M, N, K, **gemm_kw)
+                         for _ in range(e2e_steps)]
+            rt.gemm_host_batch(host_args[:2])
+            dt = timed_region(lambda: rt.gemm_host_batch(host_args))
+            got_row = y_np.reshape(M, N)[M - 1].copy()
+            dev_row = y.read_bytes((M - 1) * N * 4, N * 4, np.float32)
+            if not np.array_equal(got_row, dev_row):
+                print(json.dumps({"error": "host-operand GEMM differs from the device-resident result"}), flush=True)
+                sys.exit(1)
+            e2e = {"value": flops_per_step * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
+                   "h2d_bytes_per_step": M * K * 2 + N * K * 2, "d2h_bytes_per_step": M * N * 4, "steps": e2e_steps,
+                   "call": "t0_gemm_launch_host_batch (uploads, kernels and downloads of consecutive steps overlap)",
+                   "serial_value": flops_per_step * e2e_steps / dt_serial / 1e12,
+                   "serial_call": "t0_buf_write x2, t0_gemm_launch, t0_rt_read_f32 per step"}
+        else:
+            # Sharded: A is replicated on the devices but crosses the host link ONCE: rank r uploads rows
+            # [r M/g, (r+1) M/g) into its copy and one in-place all-gather over NVLink (on the runtime's stream) completes
+            # every copy; then each rank uploads its block of WT, multiplies, and downloads its block of C.
+            rows_per = M // world
+            a_slice = torch.empty(rows_per * K, dtype=torch.int16).pin_memory()
+            a_slice.numpy()[:] = xa.read_bytes(rank * rows_per * K * 2, rows_per * K * 2, np.int16)
+            a_np = a_slice.numpy()
+            a_dev = device_alias(xa.gpu_addr(), M * K, np.int16).view(torch.bfloat16)      # (NCCL moves bf16, not int16)
+            ext = torch.cuda.ExternalStream(rt.stream())
+            ref_row = y.read_bytes((M - 1) * N * 4, N * 4, np.float32)
+
+            def e2e_step():
+                xa.write_bytes(rank * rows_per * K * 2, a_np)
+                with torch.cuda.stream(ext):
+                    dist.all_gather_into_tensor(a_dev, a_dev[rank * rows_per * K:(rank + 1) * rows_per * K])
+                xb.write(b_np)
+                rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), M, N, K, **gemm_kw)
+                t0._check(t0.lib().t0_rt_read_f32(rt._h, y._h, M * N, y_np.ctypes.data_as(C.c_void_p)))
+
+            rt.fill_uniform_bf16(xa.gpu_addr(), M * K, 999)          # scribble: the exchange must rebuild A from the uploaded slices
+            rt.synchronize()
+            e2e_step()
+            if not np.array_equal(y_np.reshape(M, N)[M - 1], ref_row):
+                print(json.dumps({"error": "sharded host-operand GEMM differs from the device-resident result", "rank": rank}), flush=True)
+                sys.exit(1)
+            dt = timed_region(lambda: [e2e_step() for _ in range(e2e_steps)])
+            e2e = {"value": flops_per_step * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
+                   "h2d_bytes_per_step": M * K * 2 + N_total * K * 2, "d2h_bytes_per_step": M * N_total * 4, "steps": e2e_steps,
+                   "call": "per rank: t0_buf_write_bytes (its 1/g of A), all-gather of A over NVLink, t0_buf_write (its block of WT), "
+                           "t0_gemm_launch, t0_rt_read_f32 (its block of C)",
+                   "nvlink_bytes_per_rank_per_step": (world - 1) * rows_per * K * 2}
+
+    # ---- sharded runs: the same 16384^3 on ONE GPU (rank 0), the denominator of the scaling claim
+    single = None
+    if sharded and world > 1:
+        if rank == 0:
+            for (xa_, xb_, y_) in sets:
+                xb_.free()
+                y_.free()
+            xa = sets[0][0]
+            rt.fill_uniform_bf16(xa.gpu_addr(), M * K, 42 + M)
+            xb1, y1 = rt.alloc(N_total * K * 2), rt.alloc(M * N_total * 4)
+            rt.fill_uniform_bf16(xb1.gpu_addr(), N_total * K, 137 + N_total)
+            cfg1 = t0.auto_select(M, K, N_total)
+            kw1 = dict(tile_n=cfg1.tile_n, split_k=cfg1.split(), swap_grid=bool(cfg1.swap_grid),
+                       pair_cta=1 if (cfg1.wgp_mode and cfg1.tile_m == 256) else 2)
+            one = [rt.gemm_args(xa.gpu_addr(), xb1.gpu_addr(), y1.gpu_addr(), M, N_total, K, **kw1)]
+            s1 = max(3, steps // 4)
+            rt.gemm_batch(one * 2)
+            rt.synchronize()
+            rt.timer_start()
+            rt.gemm_batch(one * s1)
+            ms1 = rt.timer_stop() / s1
+            # the sharded ranks' blocks are column slices of this product: the spot check above covers the arithmetic
+            single = {"ms_per_step": ms1, "value": flops_per_step / (ms1 * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": s1,
+                      "what": f"the whole {M}x{N_total}x{K} GEMM on rank 0's GPU alone, device-timed the same way"}
+            sets = []
+        barrier()
 
     if rank == 0:
         peaks = measured_peaks()
-        # the kernel is timed inside a run of back-to-back launches: a burst for the default run, a long step when sharded
-        peak = peaks["bf16_tflops_sustained"] if sharded else peaks["bf16_tflops"]
+        peak, peak_src = tensor_peak(peaks, ms_max)
         per_launch_ms = ms_max / steps
         achieved = 2.0 * M * N * K / (per_launch_ms * 1e-3) / 1e12     # this rank's kernel: algorithmic FLOPs / event time
         line = {"metric": "bf16_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
@@ -520,20 +757,38 @@ def main():
                                  else f"operands {set_bytes >> 20} MiB per rank (> 126 MB L2)",
                            "pct_of_nominal_dense_peak": round(100.0 * value / world / 2250.0, 1)},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                             "traffic": NCU_TRAFFIC_BYTES.get(name), "peak_source": f"{peaks['source']} "
-                             f"({'sustained' if sharded else 'burst'} cuBLAS bf16)"},
+                             "traffic": ncu_traffic(name), "peak_source": peak_src},
                 "clocks": clocks, "gpu_launches": int(launches), "parity": parity}
         if e2e:
             line["e2e"] = e2e
         if gather:
             line["gather"] = gather
-        if not args.no_cpu and world == 1:
-            import oracle
+        if single:
+            line["single_gpu"] = single
+            line["speedup_vs_1gpu"] = single["ms_per_step"] / (ms_max / steps)
+        if not args.no_cpu:
             rows = max(32, min(M, int(M * (2.0 * 4096 ** 3) / (2.0 * M * N_total * K))))
             tf, sec, cores = cpu_baseline(oracle, M, N_total, K, rows)
             what = f"the full {M}x{N_total}x{K} GEMM" if rows == M else f"rows 0..{rows - 1} of {M} (extrapolate linearly)"
             line["cpu_baseline"] = {"value": tf, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": f"{what}, best of 3, {sec:.2f} s per pass"}
+        if default_run and world == 1 and not args.no_secondary:
+            # the other clauses of the metric, as short device-resident runs (each parity-checked), so that one line carries them all
+            for (xa_, xb_, y_) in sets:
+                xa_.free()
+                xb_.free()
+                y_.free()
+            sec_lines = []
+            for sname in SECONDARY:
+                if WORKLOADS[sname].get("hbm"):
+                    ln = run_hbm_workload(args, sname, rt=rt, brief=True)
+                    sec_lines.append({"workload": sname, "metric": ln["metric"], "value": ln["value"], "unit": ln["unit"], "ms_per_step": ln["ms_per_step"],
+                                      "steps": ln["steps"], "kernel": ln["config"]["kernel"], "bytes": ln["config"]["bytes"], "tflops": ln["config"]["tflops"],
+                                      "roofline": {k: ln["roofline"][k] for k in ("bound", "frac", "peak", "traffic", "tensor_frac") if k in ln["roofline"]},
+                                      "gpu_launches": ln["gpu_launches"], "parity": ln["parity"]})
+                else:
+                    sec_lines.append(run_square_brief(t0, rt, sname))
+            line["secondary"] = sec_lines
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -477,6 +477,13 @@ int t0_mg_synchronize(t0_mg* mg);
  * WT, y_slice[r] = where its [M, N/g] f32 block goes (slot r of the gather buffer when a gathered C is wanted). */
 int t0_mg_gemm_sharded(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, const uint64_t* y_slice, uint32_t m, uint32_t n, uint32_t k,
                        uint32_t tile_n, int pair_cta);
+/* The same product with HOST operands (the upload / dispatch / read-back sequence of the reference's host-facing calls,
+ * src/universal/math/blas.rs:18-100, spread over the GPUs): x_host = A[M,K] bf16, wt_host = WT[N,K] bf16, y_host = C[M,N] f32
+ * row-major.  A is replicated on the devices but crosses the host link once: GPU r uploads rows [r M/g, (r+1) M/g) and
+ * the GPUs complete their copies from each other over NVLink (plain peer copies); each uploads its N/g rows of WT, multiplies,
+ * and writes its column block into y_host.  Returns when y_host is complete.  Page-locked host memory lets the GPUs' copies
+ * run concurrently.  The device buffers belong to the handle and are reused by later calls. */
+int t0_mg_gemm_sharded_host(t0_mg* mg, const void* x_host, const void* wt_host, void* y_host, uint32_t m, uint32_t n, uint32_t k);
 /* optional: every GPU ends up with all of C in the rank-major layout C_g[g][M][N/g]; c_gathered[r] is that buffer on GPU r,
  * whose slot r the GEMM already filled.  One in-place ncclAllGather over NVLink (NCCL is loaded at run time). */
 int t0_mg_all_gather_c(t0_mg* mg, const uint64_t* c_gathered, uint32_t m, uint32_t n);

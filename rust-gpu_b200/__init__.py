@@ -762,6 +762,11 @@ class MultiGpu:
         arr = lambda v: (C.c_uint64 * len(v))(*v)
         _check(lib().t0_mg_gemm_sharded(self._h, arr(x), arr(b_slice), arr(y_slice), m, n, k, tile_n, pair_cta))
 
+    def gemm_sharded_host(self, x_host: np.ndarray, wt_host: np.ndarray, y_host: np.ndarray, m: int, n: int, k: int) -> None:
+        """Host operands: A uploaded once in total (1/g per GPU, completed over NVLink), C written into ``y_host``."""
+        _check(lib().t0_mg_gemm_sharded_host(self._h, x_host.ctypes.data_as(C.c_void_p), wt_host.ctypes.data_as(C.c_void_p),
+                                             y_host.ctypes.data_as(C.c_void_p), m, n, k))
+
     def all_gather_c(self, c_gathered: list[int], m: int, n: int) -> None:
         _check(lib().t0_mg_all_gather_c(self._h, (C.c_uint64 * len(c_gathered))(*c_gathered), m, n))
 
@@ -967,6 +972,7 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_mg_runtime", vp, vp, i32)
     sig("t0_mg_synchronize", i32, vp)
     sig("t0_mg_gemm_sharded", i32, vp, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64), u32, u32, u32, u32, i32)
+    sig("t0_mg_gemm_sharded_host", i32, vp, vp, vp, vp, u32, u32, u32)
     sig("t0_mg_all_gather_c", i32, vp, C.POINTER(u64), u32, u32)
     sig("t0_tuner_new", i32, C.POINTER(vp))
     sig("t0_tuner_with_cache_dir", i32, C.c_char_p, C.POINTER(vp))

@@ -54,6 +54,9 @@ NcclApi* nccl() {
 struct t0_mg {
     std::vector<t0_runtime*> rts;
     std::vector<ncclComm_t> comms;   // created on first gather
+    // host-operand call: per-GPU operand buffers (grow-only) and the event that marks a GPU's slice of A as uploaded
+    std::vector<Scratch> dev_a, dev_b, dev_c;
+    std::vector<cudaEvent_t> a_ready;
 };
 
 extern "C" {
@@ -90,6 +93,13 @@ void t0_mg_free(t0_mg* mg) {
     if (!mg) return;
     NcclApi* api = nccl();
     for (ncclComm_t c : mg->comms) if (api && api->CommDestroy) api->CommDestroy(c);
+    for (size_t r = 0; r < mg->rts.size(); ++r) {
+        DeviceGuard guard(mg->rts[r]->device);
+        cudaStreamSynchronize(mg->rts[r]->stream);
+        for (std::vector<Scratch>* v : {&mg->dev_a, &mg->dev_b, &mg->dev_c})
+            if (r < v->size() && (*v)[r].ptr) cudaFree((*v)[r].ptr);
+        if (r < mg->a_ready.size() && mg->a_ready[r]) cudaEventDestroy(mg->a_ready[r]);
+    }
     for (t0_runtime* r : mg->rts) t0_rt_free(r);
     delete mg;
 }
@@ -121,6 +131,71 @@ int t0_mg_gemm_sharded(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, co
         if (rc != T0_OK) return rc;
     }
     return T0_OK;
+}
+
+int t0_mg_gemm_sharded_host(t0_mg* mg, const void* x_host, const void* wt_host, void* y_host, uint32_t m, uint32_t n, uint32_t k) {
+    if (!mg || !x_host || !wt_host || !y_host) return fail(T0_ERR_INVALID, "null argument");
+    const uint32_t g = (uint32_t)mg->rts.size();
+    if (m == 0 || n == 0) return T0_OK;
+    if (k == 0 || k % 8) return fail(T0_ERR_UNSUPPORTED, "K=%u must be a positive multiple of 8", k);
+    uint32_t first = 0, n_local = 0;
+    int rc = t0_shard_columns(n, g, 0, &first, &n_local);
+    if (rc != T0_OK) return rc;
+    if (mg->dev_a.size() != g) {
+        mg->dev_a.resize(g); mg->dev_b.resize(g); mg->dev_c.resize(g); mg->a_ready.resize(g, nullptr);
+        for (uint32_t r = 0; r < g; ++r) {
+            DeviceGuard guard(mg->rts[r]->device);
+            T0_CUDA(cudaEventCreateWithFlags(&mg->a_ready[r], cudaEventDisableTiming));
+            // direct peer copies over NVLink where the devices allow it (an error here only means the copies are staged)
+            for (uint32_t s2 = 0; s2 < g; ++s2)
+                if (s2 != r && cudaDeviceEnablePeerAccess(mg->rts[s2]->device, 0) != cudaSuccess) cudaGetLastError();
+        }
+    }
+    const size_t row_bytes = (size_t)k * 2;
+    const uint32_t rows_per = ceil_div(m, g);
+    // 1. every GPU uploads ITS rows of A (A crosses the host link once in total), then its block of WT
+    for (uint32_t r = 0; r < g; ++r) {
+        t0_runtime* rt = mg->rts[r];
+        rc = check_rt(rt);
+        if (rc != T0_OK) return rc;
+        DeviceGuard guard(rt->device);
+        rc = ensure_scratch(rt, mg->dev_a[r], (size_t)m * row_bytes);
+        if (rc == T0_OK) rc = ensure_scratch(rt, mg->dev_b[r], (size_t)n_local * row_bytes);
+        if (rc == T0_OK) rc = ensure_scratch(rt, mg->dev_c[r], (size_t)m * n_local * 4);
+        if (rc != T0_OK) return rc;
+        const uint32_t r0 = std::min(m, r * rows_per), r1 = std::min(m, (r + 1) * rows_per);
+        if (r1 > r0)
+            T0_CUDA(cudaMemcpyAsync((uint8_t*)mg->dev_a[r].ptr + (size_t)r0 * row_bytes, (const uint8_t*)x_host + (size_t)r0 * row_bytes,
+                                    (size_t)(r1 - r0) * row_bytes, cudaMemcpyHostToDevice, rt->stream));
+        T0_CUDA(cudaEventRecord(mg->a_ready[r], rt->stream));
+        T0_CUDA(cudaMemcpyAsync(mg->dev_b[r].ptr, (const uint8_t*)wt_host + (size_t)r * n_local * row_bytes, (size_t)n_local * row_bytes,
+                                cudaMemcpyHostToDevice, rt->stream));
+    }
+    // 2. every GPU pulls the other GPUs' rows of A from their memories (plain peer copies), multiplies, and returns its
+    //    column block of C into the caller's row-major y (a strided copy)
+    for (uint32_t r = 0; r < g; ++r) {
+        t0_runtime* rt = mg->rts[r];
+        DeviceGuard guard(rt->device);
+        for (uint32_t d = 1; d < g; ++d) {
+            const uint32_t s2 = (r + d) % g;                       // staggered, so the sources are not all asked at once
+            const uint32_t r0 = std::min(m, s2 * rows_per), r1 = std::min(m, (s2 + 1) * rows_per);
+            if (r1 == r0) continue;
+            T0_CUDA(cudaStreamWaitEvent(rt->stream, mg->a_ready[s2], 0));
+            T0_CUDA(cudaMemcpyPeerAsync((uint8_t*)mg->dev_a[r].ptr + (size_t)r0 * row_bytes, rt->device,
+                                        (const uint8_t*)mg->dev_a[s2].ptr + (size_t)r0 * row_bytes, mg->rts[s2]->device,
+                                        (size_t)(r1 - r0) * row_bytes, rt->stream));
+        }
+        t0_gemm_args a;
+        memset(&a, 0, sizeof a);
+        a.x = (uint64_t)(uintptr_t)mg->dev_a[r].ptr; a.b = (uint64_t)(uintptr_t)mg->dev_b[r].ptr; a.y = (uint64_t)(uintptr_t)mg->dev_c[r].ptr;
+        a.m = m; a.n = n_local; a.k = k; a.transpose = T0_NT; a.swap_grid = 1;
+        rc = t0_gemm_launch(rt, &a);
+        if (rc != T0_OK) return rc;
+        T0_CUDA(cudaMemcpy2DAsync((uint8_t*)y_host + (size_t)r * n_local * 4, (size_t)n * 4, mg->dev_c[r].ptr, (size_t)n_local * 4,
+                                  (size_t)n_local * 4, m, cudaMemcpyDeviceToHost, rt->stream));
+    }
+    // a GPU's copy of A may still be read by its peers when its own work is done: wait for all of them
+    return t0_mg_synchronize(mg);
 }
 
 int t0_mg_all_gather_c(t0_mg* mg, const uint64_t* c_gathered, uint32_t m, uint32_t n) {

@@ -316,6 +316,7 @@ extern "C" {
     pub fn t0_mg_runtime(mg: *mut t0_mg, rank: c_int) -> *mut t0_runtime;
     pub fn t0_mg_synchronize(mg: *mut t0_mg) -> c_int;
     pub fn t0_mg_gemm_sharded(mg: *mut t0_mg, x: *const u64, b_slice: *const u64, y_slice: *const u64, m: u32, n: u32, k: u32, tile_n: u32, pair_cta: c_int) -> c_int;
+    pub fn t0_mg_gemm_sharded_host(mg: *mut t0_mg, x_host: *const c_void, wt_host: *const c_void, y_host: *mut c_void, m: u32, n: u32, k: u32) -> c_int;
     pub fn t0_mg_all_gather_c(mg: *mut t0_mg, c_gathered: *const u64, m: u32, n: u32) -> c_int;
     pub fn t0_fill_uniform_bf16(rt: *mut t0_runtime, dst: u64, n: u64, seed: u64, first_index: u64) -> c_int;
     pub fn t0_fill_u32(rt: *mut t0_runtime, dst: u64, n: u64, seed: u64, first_index: u64) -> c_int;

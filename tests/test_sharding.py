@@ -105,3 +105,60 @@ def test_multi_device_sharded_gemm_and_gather(t0, oracle):
         rebuilt = np.concatenate(list(blocks), axis=1)
         assert np.abs(rebuilt - full).max() <= 5e-3 and np.linalg.norm(rebuilt - full) / np.linalg.norm(full) <= 1e-3
     mg.free()
+
+
+@pytest.mark.gpu
+def test_multi_device_host_operands_upload_a_once(t0, oracle):
+    # host operands: every GPU uploads 1/g of A, the GPUs complete their copies over NVLink, each returns its column block
+    # of C into the caller's row-major matrix; ragged M (rows not a multiple of g) included
+    import torch
+    g = min(torch.cuda.device_count(), 4)
+    if g < 2:
+        pytest.skip("needs at least two GPUs")
+    mg = t0.MultiGpu(g)
+    for (M, N, K) in [(1000, 256 * g, 512), (4096, 1024 * g, 1024)]:
+        a = oracle.fill_uniform_bf16(M * K, 42 + M)
+        b = oracle.fill_uniform_bf16(N * K, 137 + N)
+        y = np.full(M * N, -9999.0, np.float32)
+        for _ in range(2):                      # the second call reuses the handle's device buffers
+            y[:] = -9999.0
+            mg.gemm_sharded_host(a, b, y, M, N, K)
+            full = oracle.gemm_nt(a, b, M, K, N)
+            got = y.reshape(M, N)
+            assert np.abs(got - full).max() <= 5e-3 * np.sqrt(K / 256) and np.linalg.norm(got - full) / np.linalg.norm(full) <= 1e-3
+    mg.free()
+
+
+@pytest.mark.gpu
+def test_sharded_16384_every_rank_checked(t0, oracle):
+    # the sharded configuration at full size: GPU r computes the 16384 x (16384/g) x 16384 block of its rows of WT (the same
+    # seeded stream, offset by the block's first element); 64 rows spread over the whole matrix are compared on EVERY rank
+    import torch
+    g = min(torch.cuda.device_count(), 8)
+    if g < 2:
+        pytest.skip("needs at least two GPUs")
+    M = N = K = 16384
+    n_local = N // g
+    mg = t0.MultiGpu(g)
+    xs, bs, cs = [], [], []
+    for r in range(g):
+        rt = mg.runtime(r)
+        first, cnt = t0.shard_columns(N, g, r)
+        assert (first, cnt) == (r * n_local, n_local)
+        xa, xb, y = rt.alloc(M * K * 2), rt.alloc(cnt * K * 2), rt.alloc(M * cnt * 4)
+        rt.fill_uniform_bf16(xa.gpu_addr(), M * K, 42 + M)
+        rt.fill_uniform_bf16(xb.gpu_addr(), cnt * K, 137 + N, first * K)
+        xs.append(xa); bs.append(xb); cs.append(y)
+    mg.gemm_sharded([x.gpu_addr() for x in xs], [x.gpu_addr() for x in bs], [c.gpu_addr() for c in cs], M, N, K)
+    mg.synchronize()
+    rows = [(i * 257 + 13) % M for i in range(64)]
+    a_rows = np.concatenate([oracle.fill_uniform_bf16(K, 42 + M, r * K) for r in rows])
+    for r in range(g):
+        b_slice = oracle.fill_uniform_bf16(n_local * K, 137 + N, r * n_local * K)
+        ref = oracle.gemm_nt(a_rows, b_slice, len(rows), K, n_local)
+        got = np.stack([cs[r].read_bytes(row * n_local * 4, n_local * 4, np.float32) for row in rows])
+        assert np.abs(got - ref).max() <= 5e-3 * np.sqrt(K / 256), f"rank {r}"
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) <= 1e-3, f"rank {r}"
+    for b in xs + bs + cs:
+        b.free()
+    mg.free()
