@@ -28,6 +28,7 @@ struct KParams {
     uint32_t tiles_m, tiles_n, split_k;
     uint32_t kb_per_split;
     uint32_t swap_grid, raster_group;
+    uint32_t sk_stages, sk_alias; // split-K cluster kernel: ring depth; 1 = the accumulator is parked over the ring (one tile per cluster)
     uint32_t tail_start;         // pair kernel: work items from here on are half-width tiles (two per output tile); = total when unused
     uint32_t out_bf16, epilogue, n_ops;
     uint32_t tma_store;          // full f32 chunks leave through the output tensor map

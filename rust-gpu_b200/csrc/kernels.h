@@ -41,6 +41,11 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream);
 int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream);
 uint32_t gemm_pair_smem_bytes(uint32_t pair_n);
 
+// Split-K inside one launch: the split_k CTAs of an output tile form a cluster and add their partial sums through
+// distributed shared memory (same sum, in split order, as planes + reduction).  NT layout, split_k 2 / 4 / 8, tile_n 64 / 128.
+bool gemm_splitk_cluster_supported(const GemmLaunch& g);
+int launch_gemm_sm100_splitk(const GemmLaunch& g, cudaStream_t stream);
+
 // y[i] = sum_s planes[s][i] in split order, then the epilogue; K4.
 int launch_splitk_reduce(const float* planes, void* y, const float* bias, uint32_t m, uint32_t n, uint32_t split_k,
                          bool out_bf16, uint8_t epilogue, uint8_t n_ops, const uint8_t* ops, float scale, float clamp_min,

@@ -122,6 +122,22 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q_in) {
     }
 
     const bool fused_reduce = split > 1 && !q.planes;
+    if (fused_reduce && !use_pair) {
+        // one launch: the CTAs that share a tile form a cluster and add their partial sums through distributed shared
+        // memory (T0_NO_CLUSTER_SPLITK=1 keeps the two-launch form below for comparison)
+        static const bool no_cluster = getenv("T0_NO_CLUSTER_SPLITK") != nullptr;
+        GemmLaunch gc = g;
+        gc.y = (void*)q.y; gc.plane_stride = 0; gc.bias = (const float*)q.bias;
+        gc.out_bf16 = q.out_bf16; gc.epilogue = q.epilogue; gc.n_ops = q.n_ops;
+        memcpy(gc.ops, q.ops, sizeof gc.ops);
+        gc.scale = q.scale; gc.clamp_min = q.clamp_min; gc.clamp_max = q.clamp_max;
+        if (!no_cluster && !x_bad && !b_bad && gemm_splitk_cluster_supported(gc)) {
+            int rc = launch_gemm_sm100_splitk(gc, rt->stream);
+            if (rc != T0_OK) return rc;
+            rt->launches.fetch_add(1);
+            return T0_OK;
+        }
+    }
     if (fused_reduce) {
         // partial planes go to scratch; K4 sums them in split order and applies the epilogue
         const size_t mn = (size_t)q.m * q.n;

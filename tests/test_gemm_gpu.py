@@ -700,3 +700,50 @@ def test_bounded_wait_reports_timeout_and_poisons(t0, oracle, pair):
     for buf in (xa, xb, y):
         buf.free()
     r2.close()
+
+
+# ----------------------------------------------------------------------------- split-K inside one launch (CTA clusters)
+
+@pytest.mark.parametrize("m,n,k,sk,tile_n", [(128, 4096, 4096, 4, 128),      # the skinny configuration
+                                              (64, 4096, 16384, 4, 128),      # the split-K skinny configuration
+                                              (1000, 4000, 2048, 4, 128),     # 8 x 32 tiles for ~36 clusters: several tiles per cluster, ragged edges
+                                              (300, 1000, 1024, 2, 64),
+                                              (130, 520, 4096, 8, 64),
+                                              (256, 768, 512, 8, 128)])
+def test_cluster_split_k_equals_planes_summed_in_split_order(t0, oracle, rt, m, n, k, sk, tile_n):
+    # gemm_gen.rs:447-448 leaves split_k planes for the host to add (examples/test_gemm_correctness.rs:203-207).  The
+    # one-launch form adds the same partial sums in the same order inside the kernel: bit-identical to the planes added
+    # on the host, within tolerance of the oracle, untouched guard area, identical reruns.
+    a = oracle.fill_uniform_bf16(m * k, 42 + m)
+    b = oracle.fill_uniform_bf16(n * k, 137 + n)
+    xa, xb = rt.upload(a), rt.upload(b)
+    planes_buf = rt.alloc(m * n * 4 * sk)
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), planes_buf.gpu_addr(), m, n, k, split_k=sk, planes=True, tile_n=tile_n, pair_cta=2)
+    planes = rt.read_f32(planes_buf, m * n * sk).reshape(sk, m, n)
+    want = np.zeros((m, n), np.float32)
+    for s in range(sk):
+        want = want + planes[s]
+    y = rt.alloc(m * n * 4 + 4096)
+    for _ in range(2):
+        y.write(np.full(m * n + 1024, SENTINEL, np.float32))
+        before = rt.launch_count()
+        rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, split_k=sk, tile_n=tile_n, pair_cta=2)
+        rt.synchronize()
+        assert rt.launch_count() - before == 1                       # one launch: no planes, no reduction pass
+        got = y.read(m * n * 4, np.float32).reshape(m, n)
+        assert np.array_equal(got, want)
+        assert np.all(y.read_bytes(m * n * 4, 4096, np.float32) == SENTINEL)
+    _, ysum = oracle.gemm_nt_splitk(a, b, m, k, n, sk)
+    assert_gemm_close(want, ysum, k)
+    # with a bias + ReLU epilogue and bf16 output: applied once, after the sum
+    bias = ((np.arange(n) % 9) - 4).astype(np.float32)
+    bb = rt.upload(bias)
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, split_k=sk, tile_n=tile_n, pair_cta=2, bias=bb.gpu_addr(), epilogue=2)
+    rt.synchronize()
+    assert np.array_equal(y.read(m * n * 4, np.float32).reshape(m, n), np.maximum(want + bias[None, :], 0.0).astype(np.float32))
+    rt.gemm(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), m, n, k, split_k=sk, tile_n=tile_n, pair_cta=2, out_bf16=True)
+    rt.synchronize()
+    got16 = y.read(m * n * 2, np.uint16)
+    assert np.array_equal(got16, oracle.f32_to_bf16_rne(want.reshape(-1)))
+    for buf in (xa, xb, planes_buf, y, bb):
+        buf.free()
