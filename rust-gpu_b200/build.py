@@ -19,7 +19,7 @@ LIB = os.path.join(HERE, "lib")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 SOURCES = ["host_config.cpp", "cost_model.cpp", "tuner.cpp", "runtime.cu", "gemm_sm100.cu", "gemm_sm100_pair.cu", "gemm_sm100_splitk.cu", "aux_kernels.cu",
-           "w4a16.cu", "w4a16_stream.cu", "multi_gpu.cu", "no_alloc.cu", "matmul_f32.cu", "host_pipeline.cu"]
+           "w4a16.cu", "w4a16_stream.cu", "w4a16_umma.cu", "multi_gpu.cu", "no_alloc.cu", "matmul_f32.cu", "host_pipeline.cu"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-Xptxas", "-v", "--expt-relaxed-constexpr"]

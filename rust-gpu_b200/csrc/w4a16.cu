@@ -834,6 +834,12 @@ int w4a16_fused_launch_fixed(t0_runtime* rt, uint64_t a, uint64_t packed, uint64
 
 }  // namespace t0
 
+namespace t0 {
+bool w4a16_umma_supported(uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group);
+int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K,
+                      uint32_t group);
+}  // namespace t0
+
 extern "C" {
 
 int t0_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out_bf16, uint32_t K, uint32_t N, uint32_t group) {
@@ -878,6 +884,9 @@ int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, 
     const bool fused = M <= 16 && (N % 32 == 0) && (K % kUnitK == 0) && (group % kUnitK == 0) && total <= 0x7FFFFFFFull &&
                        n_bands * sizeof(int) <= kCounterRegion &&
                        ((a | packed | scales | zeros) & 15) == 0 && (y & 3) == 0;
+    static const bool two_step = getenv("T0_W4_TWO_STEP") != nullptr;     // comparison switch: never the fused tcgen05 kernel
+    if (!fused && !two_step && M > 16 && w4a16_umma_supported(a, packed, scales, zeros, y, M, N, K, group))
+        return launch_w4a16_umma(rt, a, packed, scales, zeros, y, M, N, K, group);     // 16 < M <= 128: dequantisation in the main loop of a tcgen05 GEMM
     if (!fused) {
         // general shapes: dequantise once into scratch, then the tcgen05 GEMM on B[K,N]
         rc = ensure_scratch(rt, rt->scratch_w, (size_t)K * N * 2);

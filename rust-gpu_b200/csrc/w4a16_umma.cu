@@ -1,0 +1,480 @@
+// K2 for 16 < M <= 128: the fused W4A16 GEMM on tcgen05, weights in the row layout (packed[K/8][N], scales[K/G][N],
+// zeros[K/G][N/8]), dequantisation in the main loop, no K x N scratch matrix.
+//
+// No counterpart kernel exists in the reference (its INT4 support stops at the stand-alone dequantisation kernels,
+// src/t0/quant_kernels.rs:53-171).  y[m,n] = sum_k a[m,k] * w[k,n],  w = RNE_bf16((q - z) * s),  fp32 accumulate.
+//
+// One CTA owns a 256-column tile of y and a range of K; the CTAs that share a tile form a cluster and add their partial
+// sums through distributed shared memory (split order, deterministic), as the split-K GEMM does.  Per 64-deep k chunk:
+//   * the producer lane fetches the chunk's packed words (8 rows x 256 columns), its scales and zero points with three
+//     TMA boxes into a ring of raw stages;
+//   * sixteen dequantisation warps turn the words into bf16 (one LOP3 per nibble pair: 0x4300 | q is the bf16 128+q,
+//     minus 128+z, times s - bit-identical to the oracle because (q-z)*s is rounded once) and write them as the UMMA's B
+//     operand: 256 rows (n) x 64 k, K-major, 128-byte swizzle.  A packed word holds eight consecutive k of one column
+//     and the nibble pairs come out as (k, k+4): within every group of eight the k order is 0,4,1,5,2,6,3,7.  The same
+//     warps stage the activations (the 128-row A operand) in that order, so the products pair up;
+//   * one thread issues four tcgen05.mma (128 x 256 x 16) per chunk into a 128 x 256 fp32 accumulator in tensor memory.
+// At the end the sixteen warps read the accumulator, park it in shared memory (over the rings, idle by then), exchange
+// across the cluster and store.  Every wait is bounded.
+#include "w4a16_common.cuh"
+
+using namespace t0;
+using namespace t0::w4;
+
+namespace {
+
+constexpr uint32_t kUmDqWarps = 16;
+constexpr uint32_t kUmThreads = (kUmDqWarps + 2) * 32;      // + producer warp + issuer warp
+constexpr uint32_t kUmBN = 256;                             // columns of y per tile
+constexpr uint32_t kUmBK = 64;                              // k per chunk: one 128-byte swizzle atom of bf16
+constexpr uint32_t kUmRawStages = 6;
+constexpr uint32_t kUmRawBytes = 8 * kUmBN * 4 + kUmBN * 2 + (kUmBN / 8) * 4;      // 8832: words, scales, zero points
+constexpr uint32_t kUmRawStride = 9216;                     // keeps every stage 1024-byte aligned
+constexpr uint32_t kUmAbStages = 3;
+constexpr uint32_t kUmBBytes = kUmBN * kUmBK * 2;           // 32 KiB
+constexpr uint32_t kUmABytes = 128 * kUmBK * 2;             // 16 KiB
+constexpr uint32_t kUmRingBytes = kUmRawStages * kUmRawStride + kUmAbStages * (kUmABytes + kUmBBytes);   // 202752
+constexpr uint32_t kUmPitch = kUmBN + 4;                    // floats per parked row
+constexpr uint32_t kUmParkBytes = 128 * kUmPitch * 4;       // 133120, over the rings
+static_assert(kUmParkBytes <= kUmRingBytes, "the parked accumulator must fit over the rings");
+constexpr uint32_t kUmSmem = kUmRingBytes + 512 + 1024;
+constexpr uint32_t kUmTmemCols = 256;
+
+struct UmParams {
+    const uint16_t* a;
+    float* y;
+    int* status;
+    uint64_t wait_limit_ns;
+    uint32_t M, N, K;
+    uint32_t group;          // k per scale / zero-point row (a multiple of 64)
+    uint32_t n_tiles, n_chunks, split;
+};
+
+__device__ __forceinline__ bool um_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool um_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns) {
+    if (um_try_wait_cluster(bar, parity)) return true;
+    uint64_t t_start = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (um_try_wait_cluster(bar, parity)) return true;
+        if ((spin & 0xFF) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = ptx::globaltimer_ns();
+            if (t_start == 0) t_start = now;
+            else if (now - t_start > limit_ns) { *abort_flag = 1; return false; }
+        }
+    }
+}
+__device__ __forceinline__ uint32_t um_cluster_id() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t um_n_clusters() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t um_lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t um_lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void um_sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ float4 um_ld_cluster_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(kUmThreads, 1)
+w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+                  const __grid_constant__ CUtensorMap map_z, const UmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t raw_ring = smem;
+    const uint32_t a_ring = smem + kUmRawStages * kUmRawStride;
+    const uint32_t b_ring = a_ring + kUmAbStages * kUmABytes;
+    const uint32_t park = smem;                                   // [128][260] f32 over the rings, used when they are idle
+    const uint32_t bars = smem + kUmRingBytes;
+    const uint32_t raw_full = bars, raw_empty = bars + 8 * kUmRawStages;
+    const uint32_t ab_full = raw_empty + 8 * kUmRawStages, ab_empty = ab_full + 8 * kUmAbStages;
+    const uint32_t acc_full = ab_empty + 8 * kUmAbStages, acc_empty = acc_full + 8;
+    const uint32_t parked_bar = acc_empty + 8, read_bar = parked_bar + 8;
+    __shared__ uint32_t tmem_holder;
+    __shared__ int s_abort;
+    volatile int* abort_flag = &s_abort;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t split = ptx::cluster_ctarank();
+    const uint32_t c_begin = (uint32_t)((uint64_t)split * p.n_chunks / p.split), c_end = (uint32_t)((uint64_t)(split + 1) * p.n_chunks / p.split);
+    const uint32_t my_chunks = c_end - c_begin;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kUmRawStages; ++s) {
+            ptx::mbar_init(raw_full + 8 * s, 1);
+            ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps);
+        }
+        for (uint32_t s = 0; s < kUmAbStages; ++s) {
+            ptx::mbar_init(ab_full + 8 * s, kUmDqWarps);
+            ptx::mbar_init(ab_empty + 8 * s, 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, kUmDqWarps);
+        ptx::mbar_init(parked_bar, kUmDqWarps * p.split);
+        ptx::mbar_init(read_bar, kUmDqWarps * p.split);
+        s_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_s);
+        ptx::tma_prefetch_desc(&map_z);
+    }
+    if (warp == kUmDqWarps + 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_holder), kUmTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();          // every CTA's barriers exist before anyone signals across the cluster
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+
+    if (warp == kUmDqWarps) {
+        // ------------------------------------------------------------ producer: three TMA boxes per chunk
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t tile = um_cluster_id(); ok && tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+                // the rings double as the parking area: the previous tile's copy must have been read by the whole cluster
+                if (iter > 0 && !um_wait_cluster(read_bar, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
+                    atomicCAS(p.status, 0, kStatusProducerTimeout | 0x800000);
+                    break;
+                }
+                const uint32_t n0 = tile * kUmBN;
+                for (uint32_t c = c_begin; c < c_end; ++c) {
+                    if (!ptx::mbar_wait_relaxed(raw_empty + 8 * stage, phase ^ 1, abort_flag, p.wait_limit_ns, 64)) {
+                        atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(c & 0xFFFFFF));
+                        ok = false;
+                        break;
+                    }
+                    ptx::fence_proxy_async_smem();           // the stage was read through the generic proxy, the copies write it through the async proxy
+                    const uint32_t fb = raw_full + 8 * stage, dst = raw_ring + stage * kUmRawStride;
+                    const uint32_t grp = c * kUmBK / p.group;
+                    ptx::mbar_arrive_expect_tx(fb, kUmRawBytes);
+                    ptx::tma_load_2d(dst, &map_w, fb, (int32_t)n0, (int32_t)(c * (kUmBK / 8)));
+                    ptx::tma_load_2d(dst + 8 * kUmBN * 4, &map_s, fb, (int32_t)n0, (int32_t)grp);
+                    ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, &map_z, fb, (int32_t)(n0 / 8), (int32_t)grp);
+                    if (++stage == kUmRawStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == kUmDqWarps + 1) {
+        // ------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(128, kUmBN, 0u);
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t tile = um_cluster_id(); ok && tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+                if (iter > 0 && !ptx::mbar_wait(acc_empty, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
+                    atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000);
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                for (uint32_t c = 0; c < my_chunks; ++c) {
+                    if (!ptx::mbar_wait(ab_full + 8 * stage, phase, abort_flag, p.wait_limit_ns)) {
+                        atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(c & 0x7FFFFF));
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t a_addr = a_ring + stage * kUmABytes, b_addr = b_ring + stage * kUmBBytes;
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < kUmBK / 16; ++k4) {
+                        const uint64_t da = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024);
+                        const uint64_t db = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024);
+                        ptx::umma_bf16_ss(tmem_base, da, db, kIdesc, (c | k4) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(ab_empty + 8 * stage);
+                    if (++stage == kUmAbStages) { stage = 0; phase ^= 1; }
+                }
+                if (ok) ptx::umma_commit(acc_full);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ sixteen warps: dequantise, stage activations, then the epilogue
+        const uint32_t n = tid & 255, jh = tid >> 8;               // this thread's column of the tile and half of a chunk's eight words
+        uint32_t mask, magic;
+        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
+        asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
+        uint32_t rs = 0, rphase = 0, as = 0, aphase = 0, iter = 0;
+        bool ok = true;
+        // activations: unit u = (row m, eight k): this thread stages units tid and tid + 512 of every chunk
+        const uint32_t um0 = tid >> 3, uj = tid & 7, um1 = um0 + 64;
+        const uint32_t a_off0 = (um0 >> 3) * 1024 + (um0 & 7) * 128 + ((uj ^ (um0 & 7)) << 4);
+        const uint32_t a_off1 = (um1 >> 3) * 1024 + (um1 & 7) * 128 + ((uj ^ (um1 & 7)) << 4);
+        const uint32_t b_off = (n >> 3) * 1024 + (n & 7) * 128;
+        for (uint32_t tile = um_cluster_id(); tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+            const uint32_t n0 = tile * kUmBN;
+            if (ok && iter > 0 && !um_wait_cluster(read_bar, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x400000);
+                ok = false;
+            }
+            // the activations of the next two chunks are always on their way (their L2 latency is longer than a chunk takes)
+            auto load_a = [&](uint32_t c, uint4& x0, uint4& x1) {
+                x0 = make_uint4(0, 0, 0, 0); x1 = make_uint4(0, 0, 0, 0);
+                if (c < c_end) {
+                    if (um0 < p.M) x0 = __ldg((const uint4*)(p.a + (size_t)um0 * p.K + c * kUmBK + uj * 8));
+                    if (um1 < p.M) x1 = __ldg((const uint4*)(p.a + (size_t)um1 * p.K + c * kUmBK + uj * 8));
+                }
+            };
+            uint4 pa0, pa1, pb0, pb1;
+            load_a(c_begin, pa0, pa1);
+            load_a(c_begin + 1, pb0, pb1);
+            for (uint32_t c = c_begin; ok && c < c_end; ++c) {
+                const uint4 ca0 = pa0, ca1 = pa1;
+                pa0 = pb0; pa1 = pb1;
+                load_a(c + 2, pb0, pb1);
+                if (!ptx::mbar_wait(raw_full + 8 * rs, rphase, abort_flag, p.wait_limit_ns)) {
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(c & 0x3FFFFF));
+                    ok = false;
+                    break;
+                }
+                const uint32_t raw = raw_ring + rs * kUmRawStride;
+                uint32_t words[4];
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) words[i] = um_lds32(raw + (jh * 4 + i) * (kUmBN * 4) + n * 4);
+                const uint32_t sbits = um_lds16(raw + 8 * kUmBN * 4 + n * 2);
+                const uint32_t zword = um_lds32(raw + 8 * kUmBN * 4 + kUmBN * 2 + (n >> 3) * 4);
+                const uint32_t zz = ((zword >> ((n & 7) * 4)) & 0xFu) * 0x00010001u + 0x43004300u;     // bf16x2 (128+z, 128+z)
+                const uint32_t ss = sbits * 0x00010001u;                                               // (s, s)
+                if (!ptx::mbar_wait(ab_empty + 8 * as, aphase ^ 1, abort_flag, p.wait_limit_ns)) {
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x800000 | (int)(c & 0x3FFFFF));
+                    ok = false;
+                    break;
+                }
+                const uint32_t b_stage = b_ring + as * kUmBBytes + b_off, a_stage = a_ring + as * kUmABytes;
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    const uint32_t wd = words[i], j = jh * 4 + i;
+                    const uint32_t v0 = bf16x2_mul(bf16x2_sub(and_or(wd, mask, magic), zz), ss);            // k 0, 4
+                    const uint32_t v1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz), ss);       // k 1, 5
+                    const uint32_t v2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz), ss);       // k 2, 6
+                    const uint32_t v3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz), ss);      // k 3, 7
+                    um_sts128(b_stage + ((j ^ (n & 7)) << 4), v0, v1, v2, v3);
+                }
+                // activations in the same k order within every group of eight: 0,4,1,5,2,6,3,7
+                um_sts128(a_stage + a_off0, __byte_perm(ca0.x, ca0.z, 0x5410), __byte_perm(ca0.x, ca0.z, 0x7632),
+                          __byte_perm(ca0.y, ca0.w, 0x5410), __byte_perm(ca0.y, ca0.w, 0x7632));
+                um_sts128(a_stage + a_off1, __byte_perm(ca1.x, ca1.z, 0x5410), __byte_perm(ca1.x, ca1.z, 0x7632),
+                          __byte_perm(ca1.y, ca1.w, 0x5410), __byte_perm(ca1.y, ca1.w, 0x7632));
+                // The UMMAs read these bytes through the async proxy.  The warp's writes are ordered before lane 0 by the warp
+                // barrier; lane 0's proxy fence and release-arrive then publish them (one fence per warp instead of 32:
+                // the fence is the most expensive instruction of the chunk).
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::fence_proxy_async_smem();
+                    ptx::mbar_arrive(raw_empty + 8 * rs);
+                    ptx::mbar_arrive(ab_full + 8 * as);
+                }
+                if (++rs == kUmRawStages) { rs = 0; rphase ^= 1; }
+                if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
+            }
+            // ---- epilogue: the accumulator of this CTA's part of K
+            if (ok && !ptx::mbar_wait(acc_full, iter & 1, abort_flag, p.wait_limit_ns)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xC00000);
+                ok = false;
+            }
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            const uint32_t q = warp & 3, cg = warp >> 2;             // tensor-memory lane quarter, 64-column group
+            const uint32_t row_in = q * 32 + lane;
+            if (p.split == 1) {
+                // no exchange: straight from tensor memory to y
+#pragma unroll 1
+                for (uint32_t h = 0; h < 2; ++h) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(tmem_base + ((q * 32) << 16) + cg * 64 + h * 32, r);
+                    ptx::tmem_ld_wait();
+                    const uint32_t col = n0 + cg * 64 + h * 32;
+                    if (row_in < p.M) {
+                        float* dst = p.y + (size_t)row_in * p.N + col;
+#pragma unroll
+                        for (uint32_t j = 0; j < 32; ++j)
+                            if (col + j < p.N) dst[j] = __uint_as_float(r[j]);
+                    }
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(acc_empty);
+                    ptx::mbar_arrive(read_bar);          // (nothing was parked; the next tile's waits are the same either way)
+                }
+                continue;
+            }
+            // park (the rings are idle: every chunk has been consumed), tell the cluster, wait for everyone
+#pragma unroll 1
+            for (uint32_t h = 0; h < 2; ++h) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + ((q * 32) << 16) + cg * 64 + h * 32, r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (uint32_t j = 0; j < 8; ++j)
+                    um_sts128(park + (row_in * kUmPitch + cg * 64 + h * 32 + 4 * j) * 4, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(acc_empty);
+                for (uint32_t s = 0; s < p.split; ++s) ptx::mbar_arrive_cluster(ptx::mapa(parked_bar, s));
+            }
+            if (!um_wait_cluster(parked_bar, iter & 1, abort_flag, p.wait_limit_ns)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xD00000);
+                ok = false;
+                break;
+            }
+            {
+                // this CTA's column slice of the tile (whole float4s), every row; splits added in split order
+                const uint32_t slice_w = ((kUmBN / p.split + 3) / 4) * 4;
+                const uint32_t s_begin = split * slice_w, s_end = min(kUmBN, s_begin + slice_w);
+                const uint32_t f4_per_row = s_end > s_begin ? (s_end - s_begin) / 4 : 0;
+                const uint32_t items = 128 * f4_per_row;
+                const bool vec = ((uintptr_t)p.y & 15) == 0;         // (N % 32 == 0 is a condition of this kernel)
+                constexpr uint32_t kU = 2;
+                for (uint32_t i0 = tid; i0 < items; i0 += kU * kUmDqWarps * 32) {
+                    float4 part[kU][4];
+#pragma unroll
+                    for (uint32_t u = 0; u < kU; ++u) {
+                        const uint32_t i = i0 + u * kUmDqWarps * 32;
+                        const uint32_t row = i / f4_per_row, c4 = i - row * f4_per_row;
+#pragma unroll
+                        for (uint32_t s = 0; s < 4; ++s)
+                            part[u][s] = (i < items && s < p.split) ? um_ld_cluster_f4(ptx::mapa(park + (row * kUmPitch + s_begin + c4 * 4) * 4, s))
+                                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+#pragma unroll
+                    for (uint32_t u = 0; u < kU; ++u) {
+                        const uint32_t i = i0 + u * kUmDqWarps * 32;
+                        if (i >= items) break;
+                        const uint32_t row = i / f4_per_row, c4 = i - row * f4_per_row;
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (uint32_t s = 0; s < 4; ++s)
+                            if (s < p.split) { acc.x += part[u][s].x; acc.y += part[u][s].y; acc.z += part[u][s].z; acc.w += part[u][s].w; }
+                        const uint32_t col = n0 + s_begin + c4 * 4;
+                        if (row >= p.M || col >= p.N) continue;
+                        float* dst = p.y + (size_t)row * p.N + col;
+                        if (vec && col + 4 <= p.N) *(float4*)dst = acc;
+                        else {
+                            const float o[4] = {acc.x, acc.y, acc.z, acc.w};
+                            for (uint32_t j = 0; j < 4 && col + j < p.N; ++j) dst[j] = o[j];
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0)
+                for (uint32_t s = 0; s < p.split; ++s) ptx::mbar_arrive_cluster(ptx::mapa(read_bar, s));      // this warp has read every copy
+        }
+    }
+
+    // ---------------------------------------------------------------- common exit
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();          // no CTA's shared memory goes away while a peer may still read its copy or signal its barriers
+    if (warp == kUmDqWarps + 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kUmTmemCols);
+    }
+}
+
+}  // namespace
+
+namespace t0 {
+
+// Whether the fused tcgen05 kernel takes this W4A16 problem.
+bool w4a16_umma_supported(uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
+    if (M == 0 || M > 128 || N % 32 || K == 0 || K % kUmBK || group == 0 || group % kUmBK || K % group) return false;
+    if (((a | packed | scales | zeros) & 15) != 0 || (y & 3) != 0) return false;
+    return true;
+}
+
+int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K,
+                      uint32_t group) {
+    UmParams p;
+    memset(&p, 0, sizeof p);
+    p.a = (const uint16_t*)a; p.y = (float*)y; p.status = rt->d_status;
+    const uint64_t limit = rt->wait_limit_ns.load(std::memory_order_relaxed);
+    p.wait_limit_ns = limit ? limit : ptx::kWaitLimitNs;
+    p.M = M; p.N = N; p.K = K; p.group = group;
+    p.n_tiles = ceil_div(N, kUmBN);
+    p.n_chunks = K / kUmBK;
+    // as many parts of K as fill the machine (the parts of a tile form a cluster of at most four CTAs)
+    uint32_t split = std::max<uint32_t>(1, std::min<uint32_t>(4, (uint32_t)rt->sm_count / std::max<uint32_t>(1, p.n_tiles)));
+    split = std::min(split, p.n_chunks);
+    CUtensorMap map_w, map_s, map_z;
+    int rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kUmBN, kUmBK / 8);
+    if (rc != T0_OK) return rc;
+    rc = gemm::make_map_2d_plain(&map_s, (const void*)scales, 2, K / group, N, kUmBN, 1);
+    if (rc != T0_OK) return rc;
+    rc = gemm::make_map_2d_plain(&map_z, (const void*)zeros, 4, K / group, N / 8, kUmBN / 8, 1);
+    if (rc != T0_OK) return rc;
+    static bool attr_set[64] = {};
+    static int max_clusters[64][5] = {};
+    if (rt->device >= 64) return fail(T0_ERR_INVALID, "device ordinal out of range");
+    if (!attr_set[rt->device]) {
+        T0_CUDA(cudaFuncSetAttribute(w4a16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmSmem));
+        attr_set[rt->device] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kUmThreads, 1, 1);
+    cfg.dynamicSmemBytes = kUmSmem;
+    cfg.stream = rt->stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    if (!max_clusters[rt->device][split]) {
+        cfg.gridDim = dim3(split * ((uint32_t)rt->sm_count / split), 1, 1);
+        cfg.numAttrs = 1;
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, w4a16_umma_kernel, &cfg);
+        if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = (int)((uint32_t)rt->sm_count / split) * 3 / 4; }
+        max_clusters[rt->device][split] = std::max(n, 1);
+    }
+    p.split = split;
+    static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
+    const uint32_t clusters = std::min<uint32_t>(p.n_tiles, (uint32_t)max_clusters[rt->device][split]);
+    cfg.gridDim = dim3(clusters * split, 1, 1);
+    cfg.numAttrs = use_pdl ? 2 : 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_umma_kernel, map_w, map_s, map_z, p);
+    if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
+    rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+}  // namespace t0

@@ -421,3 +421,37 @@ def test_prepacked_batch_longer_than_one_launch(t0, oracle, rt):
         assert_close(got, oracle.w4a16_gemm(a_host[i], packed, scales, zeros, ms[i], N, K, G), K)
     for b in pres + xas + ys:
         b.free()
+
+
+# ----------------------------------------------------------------------------- K2 for 16 < M <= 128 (tcgen05, dequantisation in the main loop)
+
+@pytest.mark.parametrize("M", [17, 64, 100, 128])
+@pytest.mark.parametrize("K,N,G", [(64, 32, 64), (512, 288, 128), (1024, 1024, 256), (4096, 1536, 128), (2048, 11008, 128), (192, 8192, 64)])
+def test_fused_large_m_shapes(t0, oracle, rt, M, K, N, G):
+    # one launch, no K x N scratch: partial column tiles (N = 32, 288), one to four parts of K per tile, three group sizes
+    a = oracle.fill_normal_bf16(M * K, 7 + M)
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=M + K)
+    ref = oracle.w4a16_gemm(a, packed, scales, zeros, M, N, K, G)
+    before = rt.launch_count()
+    got = run_w4a16(rt, a, packed, scales, zeros, M, N, K, G)
+    assert rt.launch_count() - before == 1
+    assert_close(got, ref, K)
+
+
+def test_fused_large_m_dequantises_bit_exactly(t0, oracle, rt):
+    # one-hot activations: row m of y is row base + m of the dequantised weights, exactly
+    K, G, M = 256, 128, 128
+    N = 8192
+    rng = np.random.default_rng(11)
+    packed = rng.integers(0, 2 ** 32, size=(K // 8, N), dtype=np.uint64).astype(np.uint32)
+    col = np.arange(N, dtype=np.uint32)
+    sbits = np.stack([(0x3A00 + (col % 0x400)).astype(np.uint16) | ((col // 0x400 % 2) << 15).astype(np.uint16),
+                      (0x3B80 + (col % 0x300)).astype(np.uint16)])
+    zeros = rng.integers(0, 2 ** 32, size=(K // G, N // 8), dtype=np.uint64).astype(np.uint32)
+    want = oracle.bf16_to_f32(oracle.dequant_w4_b200(packed, sbits, zeros, K, N, G)).reshape(K, N)
+    for base in (0, 128):
+        a = np.zeros((M, K), np.uint16)
+        for m in range(M):
+            a[m, base + m] = 0x3F80
+        got = run_w4a16(rt, a, packed, sbits, zeros, M, N, K, G)
+        assert np.array_equal(got.view(np.uint32) & 0x7FFFFFFF, want[base:base + M].view(np.uint32) & 0x7FFFFFFF), base
