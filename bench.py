@@ -51,6 +51,9 @@ WORKLOADS = {
     "w4a16_m128_n11008": dict(m=128, n=11008, k=4096, w4=True, hbm=True),
     "w4a16_m128_n14336": dict(m=128, n=14336, k=4096, w4=True, hbm=True),
 }
+# the callers and data formats either side of the path (reference wire-format dequantisation, the weight prepack, the f32
+# framework entry): device-timed with --workload, not part of the default line
+AUX_WORKLOADS = ["dequant_int4_f32_11008x4096", "dequant_int4_bf16_11008x4096", "w4_prepack_4096x11008", "matmul_f32_4096"]
 SECONDARY = ["w4a16_m1_n11008", "w4a16_m16_n11008", "w4a16_m1_n14336", "w4a16_m16_n14336", "w4a16_m128_n11008", "w4a16_m128_n14336",
              "gemm_bf16_skinny_128x4096x4096", "gemm_bf16_skinny_64x4096x16384_sk4", "gemm_bf16_2048", "gemm_bf16_8192"]
 W4_GROUP = 128
@@ -293,6 +296,119 @@ def run_hbm_workload(args, name, rt=None, brief=False):
     return line
 
 
+def run_aux_workload(args, name):
+    """Kernels beside the GEMM itself, each at a size larger than L2: the stand-alone dequantisation in the reference's wire
+    format (quant_kernels.rs:53-171), the one-time weight prepack, and the f32 entry matmul(x f32, w f32)
+    (bf16_matmul.rs:33-59: two conversion passes plus the GEMM).  One JSON line each; parity on a sample."""
+    import torch
+    t0 = importlib.import_module("rust-gpu_b200")
+    t0.lib()
+    import oracle
+    oracle.build()
+    torch.cuda.set_device(0)
+    rt = t0.GpuRuntime(0)
+    peaks = measured_peaks()
+    steps = args.steps if args.steps is not None else 40
+    warmup = max(3, args.warmup if args.warmup is not None else 4)
+    line = {"n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic"}
+
+    def time_steps(fn):
+        for i in range(warmup):
+            fn(i)
+        rt.synchronize()
+        best = float("inf")
+        before = rt.launch_count()
+        for _ in range(3):
+            rt.timer_start()
+            for i in range(steps):
+                fn(i)
+            best = min(best, rt.timer_stop())
+        return best * 1e-3 / steps, (rt.launch_count() - before) // 3
+
+    if name.startswith("dequant_int4"):
+        rows, cols, glog = 11008, 4096, 7
+        bf16 = "bf16" in name
+        n_groups = cols >> glog
+        n_sets = 8                                              # 8 x 22 MiB of packed codes rotate; the output alone exceeds the L2
+        scales_h = (0.001 + 0.019 * (np.arange(rows * n_groups) % 97) / 97.0).astype(np.float32)
+        zps_h = (np.arange(rows * n_groups) % 16).astype(np.int32)
+        xs, xz = rt.upload(scales_h), rt.upload(zps_h)
+        packs = []
+        for s in range(n_sets):
+            b = rt.alloc(rows * cols // 2)
+            rt.fill_u32(b.gpu_addr(), rows * cols // 8, 500 + s)
+            packs.append(b)
+        outs = [rt.alloc(rows * cols * (2 if bf16 else 4)) for _ in range(2)]
+        sec, launches = time_steps(lambda i: rt.dequant_int4(packs[i % n_sets].gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), outs[i % 2].gpu_addr(),
+                                                            rows, cols, glog, bf16))
+        alg = rows * cols // 2 + rows * n_groups * 8 + rows * cols * (2 if bf16 else 4)
+        # parity: the first 64 rows of the last step, bit for bit
+        s_idx, o_idx, r = (steps - 1) % n_sets, (steps - 1) % 2, 64
+        pk = oracle.fill_u32(rows * cols // 8, 500 + s_idx)[: r * cols // 8].view(np.uint8)
+        want = oracle.dequant_int4_ref(pk, scales_h[: r * n_groups], zps_h[: r * n_groups], r, cols, glog, bf16)
+        got = outs[o_idx].read(r * cols * (2 if bf16 else 4), np.uint16 if bf16 else np.float32).reshape(r, cols)
+        ok = bool(np.array_equal(got, want))
+        line.update({"metric": "dequant_hbm_gbs", "value": alg / sec / 1e9, "unit": "GB/s", "ms_per_step": sec * 1e3,
+                     "dtype": "int4 -> " + ("bf16 (truncated)" if bf16 else "f32"),
+                     "config": {"workload": name, "rows": rows, "cols": cols, "group": 1 << glog, "kernel": "dequant_int4_ref_kernel", "bytes": alg},
+                     "roofline": {"bound": "hbm", "achieved": alg / sec / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": alg / sec / 1e9 / peaks["hbm_gbs"],
+                                  "traffic": ncu_traffic(name), "peak_source": f"{peaks['source']} (copy bandwidth)"},
+                     "gpu_launches": int(launches), "parity": {"rows_compared": r, "bit_exact": ok}})
+    elif name.startswith("w4_prepack"):
+        K, N, G = 4096, 11008, 128
+        n_sets = 8
+        sets = []
+        for s in range(n_sets):
+            xp, xs, xz = rt.alloc((K // 8) * N * 4), rt.alloc((K // G) * N * 2), rt.alloc((K // G) * (N // 8) * 4)
+            rt.fill_u32(xp.gpu_addr(), (K // 8) * N, 1000 + s)
+            rt.fill_range_bf16(xs.gpu_addr(), (K // G) * N, 2000 + s, 0.001, 0.02)
+            rt.fill_u32(xz.gpu_addr(), (K // G) * (N // 8), 3000 + s)
+            sets.append((xp, xs, xz))
+        nbytes = t0.lib().t0_w4_prepacked_bytes(K, N, G)
+        outs = [rt.alloc(nbytes) for _ in range(8)]
+        C = __import__("ctypes")
+        sec, launches = time_steps(lambda i: t0._check(t0.lib().t0_w4_prepack(rt._h, *(b.gpu_addr() for b in sets[i % n_sets]), outs[i % 8].gpu_addr(), K, N, G)))
+        alg = 2 * nbytes
+        s_idx = (steps - 1) % n_sets
+        want = oracle.w4_prepack(oracle.fill_u32((K // 8) * N, 1000 + s_idx), oracle.fill_range_bf16((K // G) * N, 2000 + s_idx, 0.001, 0.02),
+                                 oracle.fill_u32((K // G) * (N // 8), 3000 + s_idx), K, N, G)
+        ok = bool(np.array_equal(outs[(steps - 1) % 8].read(nbytes, np.uint8), want))
+        line.update({"metric": "prepack_hbm_gbs", "value": alg / sec / 1e9, "unit": "GB/s", "ms_per_step": sec * 1e3, "dtype": "u32",
+                     "config": {"workload": name, "k": K, "n": N, "group": G, "kernel": "w4_prepack_kernel", "bytes": alg},
+                     "roofline": {"bound": "hbm", "achieved": alg / sec / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": alg / sec / 1e9 / peaks["hbm_gbs"],
+                                  "traffic": ncu_traffic(name), "peak_source": f"{peaks['source']} (copy bandwidth)"},
+                     "gpu_launches": int(launches), "parity": {"bit_exact": ok}})
+    else:
+        M = N = K = 4096
+        rng = np.random.default_rng(3)
+        x_h = rng.uniform(-1, 1, size=M * K).astype(np.float32)
+        w_h = rng.uniform(-1, 1, size=K * N).astype(np.float32)
+        xs_ = [rt.upload(x_h), rt.upload(x_h)]
+        ws_ = [rt.upload(w_h), rt.upload(w_h)]
+        ys_ = [rt.alloc(M * N * 4) for _ in range(2)]
+        sec, launches = time_steps(lambda i: rt.matmul_f32(xs_[i % 2].gpu_addr(), ws_[i % 2].gpu_addr(), ys_[i % 2].gpu_addr(), M, K, N))
+        rows = [0, 2049, 4095]
+        xb = oracle.f32_to_bf16_rne(x_h.reshape(M, K)[rows].reshape(-1))
+        wb = oracle.f32_to_bf16_rne(w_h)
+        ref = oracle.gemm_nn(xb, wb, len(rows), K, N)
+        got = np.stack([ys_[(steps - 1) % 2].read_bytes(r * N * 4, N * 4, np.float32) for r in rows])
+        err = float(np.abs(got - ref).max())
+        tol = 5e-3 * (K / 256) ** 0.5
+        ok = err <= tol
+        tf = 2.0 * M * N * K / sec / 1e12
+        line.update({"metric": "matmul_f32_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": sec * 1e3, "dtype": "f32 in, bf16 multiply, f32 accumulate and out",
+                     "config": {"workload": name, "m": M, "n": N, "k": K, "kernel": "cvt_f32_bf16_kernel x2 + gemm (B[K,N] layout)",
+                                "extra_bytes": "two conversion passes: 2 x (64 MiB read + 32 MiB written)"},
+                     "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
+                                  "traffic": ncu_traffic(name), "peak_source": f"{peaks['source']} (burst cuBLAS bf16)"},
+                     "gpu_launches": int(launches), "parity": {"sampled_rows": rows, "max_abs_err": err, "tol": tol}})
+    rt.close()
+    if not ok:
+        print(json.dumps({"error": "parity check failed", "workload": name, "parity": line["parity"]}), flush=True)
+        sys.exit(1)
+    return line
+
+
 def run_square_brief(t0, rt, name):
     """A short device-resident run of another size of the square sweep, for the default line's "secondary" list."""
     import oracle
@@ -464,7 +580,7 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + AUX_WORKLOADS)
     ap.add_argument("--tile-n", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -500,6 +616,9 @@ def main():
         rt.close()
         return
 
+    if args.workload in AUX_WORKLOADS:
+        print(json.dumps(run_aux_workload(args, args.workload)), flush=True)
+        return
     default_run = args.workload is None
     name = args.workload or ("gemm_bf16_4096" if world == 1 else "gemm_bf16_16384_sharded")
     if WORKLOADS[name].get("hbm"):

@@ -25,9 +25,27 @@ __device__ __forceinline__ uint16_t bf16_rne_bits(float v) {
 
 // dst[r][c] = bf16(src[r * ld_src + c]), dense rows x cols
 __global__ void cvt_f32_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, uint32_t rows, uint32_t cols, uint32_t ld_src) {
-    const uint64_t total = (uint64_t)rows * cols;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const uint64_t gtid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if ((cols % 8 == 0) && (ld_src % 4 == 0) && (((uintptr_t)src | (uintptr_t)dst) & 15) == 0) {
+        // eight elements per thread: two 16-byte streaming loads (the f32 source is read once), one 16-byte store
+        const uint32_t units_per_row = cols / 8;
+        const uint64_t units = (uint64_t)rows * units_per_row;
+        for (uint64_t u = gtid; u < units; u += stride) {
+            const uint32_t r = (uint32_t)(u / units_per_row), c = (uint32_t)(u - (uint64_t)r * units_per_row) * 8;
+            const float4* s4 = (const float4*)(src + (size_t)r * ld_src + c);
+            const float4 lo = __ldcs(s4), hi = __ldcs(s4 + 1);
+            uint4 o;
+            o.x = (uint32_t)bf16_rne_bits(lo.x) | ((uint32_t)bf16_rne_bits(lo.y) << 16);
+            o.y = (uint32_t)bf16_rne_bits(lo.z) | ((uint32_t)bf16_rne_bits(lo.w) << 16);
+            o.z = (uint32_t)bf16_rne_bits(hi.x) | ((uint32_t)bf16_rne_bits(hi.y) << 16);
+            o.w = (uint32_t)bf16_rne_bits(hi.z) | ((uint32_t)bf16_rne_bits(hi.w) << 16);
+            *(uint4*)(dst + (size_t)r * cols + c) = o;
+        }
+        return;
+    }
+    const uint64_t total = (uint64_t)rows * cols;
+    for (uint64_t i = gtid; i < total; i += stride) {
         const uint32_t r = (uint32_t)(i / cols), c = (uint32_t)(i - (uint64_t)r * cols);
         dst[i] = bf16_rne_bits(src[(size_t)r * ld_src + c]);
     }
@@ -90,7 +108,7 @@ int convert(t0_runtime* rt, Scratch& s, uint64_t src, uint32_t rows, uint32_t co
     if (rc != T0_OK) return rc;
     if ((uint64_t)rows * cols) {
         if (!transpose) {
-            cvt_f32_bf16_kernel<<<blocks_for((uint64_t)rows * cols, 1024, rt->sm_count), 256, 0, rt->stream>>>((const float*)src, (uint16_t*)s.ptr, rows, cols, ld_src);
+            cvt_f32_bf16_kernel<<<blocks_for((uint64_t)rows * cols, 2048, rt->sm_count), 256, 0, rt->stream>>>((const float*)src, (uint16_t*)s.ptr, rows, cols, ld_src);
         } else {
             const uint64_t tiles = (uint64_t)((rows + 31) / 32) * ((cols + 31) / 32);
             cvt_f32_bf16_transpose_kernel<<<blocks_for(tiles, 1, rt->sm_count), dim3(32, 8), 0, rt->stream>>>((const float*)src, (uint16_t*)s.ptr, rows, cols);

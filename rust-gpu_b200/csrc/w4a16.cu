@@ -636,28 +636,45 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 // ------------------------------------------------------------------ K3: stand-alone dequantisation
 
-// Reference wire format (quant_kernels.rs:53-171): one thread per 32 consecutive elements.
+// Reference wire format (quant_kernels.rs:53-171): byte e/2 holds element e in its low nibble for even e, one f32 scale and
+// one i32 zero point per group of 2^group_log2 elements.  One thread per packed 32-bit word (eight elements): a warp reads
+// 128 contiguous bytes and writes 1 KiB (f32) or 512 bytes (bf16) contiguous, 16 bytes per store.
 __global__ void dequant_int4_ref_kernel(const uint8_t* __restrict__ packed, const float* __restrict__ scales,
                                         const int32_t* __restrict__ zps, void* __restrict__ out, uint64_t total,
                                         uint32_t group_log2, uint32_t out_bf16) {
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x * 32;
-    for (uint64_t e0 = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 32; e0 < total; e0 += stride) {
-        const bool fast = e0 + 32 <= total && (((uintptr_t)packed & 15) == 0);
-        uint32_t words[4];
-        if (fast) {
-            const uint4 v = __ldcs((const uint4*)(packed + (e0 >> 1)));
-            words[0] = v.x; words[1] = v.y; words[2] = v.z; words[3] = v.w;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    const uint64_t units = (total + 7) / 8;
+    // a group of at least eight elements never splits a word; the 16-byte stores need the output aligned
+    const bool vec = group_log2 >= 3 && (((uintptr_t)packed & 3) == 0) && (((uintptr_t)out & 15) == 0);
+    for (uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += stride) {
+        const uint64_t e0 = u * 8;
+        if (vec && e0 + 8 <= total) {
+            const uint32_t word = __ldcs((const uint32_t*)(packed + (e0 >> 1)));
+            const uint64_t grp = e0 >> group_log2;
+            const int32_t zp = __ldg(zps + grp);
+            const float sc = __ldg(scales + grp);
+            uint32_t bits[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                bits[i] = __float_as_uint(__fmul_rn((float)((int32_t)((word >> (4 * i)) & 0xFu) - zp), sc));
+            if (out_bf16) {
+                // truncating store (quant_kernels.rs:167-168): the upper halves of two values side by side
+                uint4 o;
+                o.x = __byte_perm(bits[0], bits[1], 0x7632); o.y = __byte_perm(bits[2], bits[3], 0x7632);
+                o.z = __byte_perm(bits[4], bits[5], 0x7632); o.w = __byte_perm(bits[6], bits[7], 0x7632);
+                __stcs((uint4*)((uint16_t*)out + e0), o);
+            } else {
+                __stcs((uint4*)((float*)out + e0), make_uint4(bits[0], bits[1], bits[2], bits[3]));
+                __stcs((uint4*)((float*)out + e0) + 1, make_uint4(bits[4], bits[5], bits[6], bits[7]));
+            }
+            continue;
         }
-#pragma unroll 4
-        for (int i = 0; i < 32; ++i) {
-            const uint64_t e = e0 + i;
-            if (e >= total) break;
-            uint32_t code;
-            if (fast) code = (words[i >> 3] >> (4 * (i & 7))) & 0xFu;          // byte e/2, low nibble for even e
-            else { const uint8_t b = packed[e >> 1]; code = (e & 1) ? (b >> 4) : (b & 0xFu); }
+        for (uint64_t e = e0; e < e0 + 8 && e < total; ++e) {
+            const uint8_t b = packed[e >> 1];
+            const uint32_t code = (e & 1) ? (b >> 4) : (b & 0xFu);
             const uint64_t grp = e >> group_log2;
             const float v = __fmul_rn((float)((int32_t)code - __ldg(zps + grp)), __ldg(scales + grp));
-            if (out_bf16) ((uint16_t*)out)[e] = (uint16_t)(__float_as_uint(v) >> 16);   // truncating store (quant_kernels.rs:167-168)
+            if (out_bf16) ((uint16_t*)out)[e] = (uint16_t)(__float_as_uint(v) >> 16);
             else ((float*)out)[e] = v;
         }
     }
@@ -679,18 +696,33 @@ __global__ void dequant_w4_b200_kernel(const uint32_t* __restrict__ packed, cons
         uint32_t words[8];
         uint16_t sbits[8];
         if (vec) {
+            // Two columns at a time in bf16x2: (code | 0x4300) is the bf16 128 + code, so (128 + q) - (128 + z) and the product with
+            // the scale, rounded once to nearest even, are the same bits as the scalar path below.
             const uint4 w0 = __ldcs((const uint4*)(packed + (size_t)kg * N + col)), w1 = __ldcs((const uint4*)(packed + (size_t)kg * N + col + 4));
-            words[0] = w0.x; words[1] = w0.y; words[2] = w0.z; words[3] = w0.w; words[4] = w1.x; words[5] = w1.y; words[6] = w1.z; words[7] = w1.w;
             const uint4 sv = __ldg((const uint4*)(scales + (size_t)grp * N + col));
-            sbits[0] = (uint16_t)sv.x; sbits[1] = (uint16_t)(sv.x >> 16); sbits[2] = (uint16_t)sv.y; sbits[3] = (uint16_t)(sv.y >> 16);
-            sbits[4] = (uint16_t)sv.z; sbits[5] = (uint16_t)(sv.z >> 16); sbits[6] = (uint16_t)sv.w; sbits[7] = (uint16_t)(sv.w >> 16);
-        } else {
+            const uint32_t wp[4][2] = {{w0.x, w0.y}, {w0.z, w0.w}, {w1.x, w1.y}, {w1.z, w1.w}};
+            const uint32_t sp[4] = {sv.x, sv.y, sv.z, sv.w};
+            uint32_t o[8][4];
 #pragma unroll
-            for (uint32_t c = 0; c < 8; ++c) {
-                const bool in = col + c < N;
-                words[c] = in ? packed[(size_t)kg * N + col + c] : 0u;
-                sbits[c] = in ? scales[(size_t)grp * N + col + c] : (uint16_t)0;
+            for (uint32_t pr = 0; pr < 4; ++pr) {
+                const uint32_t zz = (((zword >> (8 * pr)) & 0xFu) | (((zword >> (8 * pr + 4)) & 0xFu) << 16)) + 0x43004300u;
+                const uint32_t lo = __byte_perm(wp[pr][0], wp[pr][1], 0x5410), hi = __byte_perm(wp[pr][0], wp[pr][1], 0x7632);   // k 0..3, k 4..7
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; ++kk) {
+                    o[kk][pr] = bf16x2_mul(bf16x2_sub(((lo >> (4 * kk)) & 0x000F000Fu) | 0x43004300u, zz), sp[pr]);
+                    o[kk + 4][pr] = bf16x2_mul(bf16x2_sub(((hi >> (4 * kk)) & 0x000F000Fu) | 0x43004300u, zz), sp[pr]);
+                }
             }
+#pragma unroll
+            for (uint32_t kk = 0; kk < 8; ++kk)
+                __stcs((uint4*)(out + (size_t)(kg * 8 + kk) * N + col), make_uint4(o[kk][0], o[kk][1], o[kk][2], o[kk][3]));
+            continue;
+        }
+#pragma unroll
+        for (uint32_t c = 0; c < 8; ++c) {
+            const bool in = col + c < N;
+            words[c] = in ? packed[(size_t)kg * N + col + c] : 0u;
+            sbits[c] = in ? scales[(size_t)grp * N + col + c] : (uint16_t)0;
         }
         float s[8];
         int32_t z[8];
@@ -710,15 +742,9 @@ __global__ void dequant_w4_b200_kernel(const uint32_t* __restrict__ packed, cons
                 o[c] = (uint16_t)((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
             }
             uint16_t* dst = out + (size_t)(kg * 8 + kk) * N + col;
-            if (vec) {
-                uint4 q;
-                q.x = o[0] | ((uint32_t)o[1] << 16); q.y = o[2] | ((uint32_t)o[3] << 16); q.z = o[4] | ((uint32_t)o[5] << 16); q.w = o[6] | ((uint32_t)o[7] << 16);
-                __stcs((uint4*)dst, q);
-            } else {
 #pragma unroll
-                for (uint32_t c = 0; c < 8; ++c)
-                    if (col + c < N) dst[c] = o[c];
-            }
+            for (uint32_t c = 0; c < 8; ++c)
+                if (col + c < N) dst[c] = o[c];
         }
     }
 }
@@ -859,7 +885,7 @@ int t0_dequant_int4(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t z
     if (!packed || !scales || !zero_points || !out) return fail(T0_ERR_INVALID, "null device pointer");
     if (group_size_log2 > 31) return fail(T0_ERR_INVALID, "group_size_log2=%u out of range", group_size_log2);
     DeviceGuard guard(rt->device);
-    dequant_int4_ref_kernel<<<grid_for((total + 31) / 32, 256), 256, 0, rt->stream>>>(
+    dequant_int4_ref_kernel<<<grid_for((total + 7) / 8, 256), 256, 0, rt->stream>>>(
         (const uint8_t*)packed, (const float*)scales, (const int32_t*)zero_points, (void*)out, total, group_size_log2, out_bf16 ? 1u : 0u);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "dequant launch failed: %s", cudaGetErrorString(e));

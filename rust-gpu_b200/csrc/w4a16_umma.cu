@@ -7,12 +7,12 @@
 // One CTA owns a 256-column tile of y and a range of K; the CTAs that share a tile form a cluster and add their partial
 // sums through distributed shared memory (split order, deterministic), as the split-K GEMM does.  Per 64-deep k chunk:
 //   * the producer lane fetches the chunk's packed words (8 rows x 256 columns), its scales and zero points with three
-//     TMA boxes into a ring of raw stages;
+//     TMA boxes into a ring of raw stages, and the chunk's activations with a fourth into the operand ring;
 //   * sixteen dequantisation warps turn the words into bf16 (one LOP3 per nibble pair: 0x4300 | q is the bf16 128+q,
 //     minus 128+z, times s - bit-identical to the oracle because (q-z)*s is rounded once) and write them as the UMMA's B
 //     operand: 256 rows (n) x 64 k, K-major, 128-byte swizzle.  A packed word holds eight consecutive k of one column
-//     and the nibble pairs come out as (k, k+4): within every group of eight the k order is 0,4,1,5,2,6,3,7.  The same
-//     warps stage the activations (the 128-row A operand) in that order, so the products pair up;
+//     and the nibble pairs come out as (k, k+4); four byte permutes put them back into k order, so that the activations
+//     (the 128-row A operand) can come straight from global memory through TMA (rows beyond M are zero-filled);
 //   * one thread issues four tcgen05.mma (128 x 256 x 16) per chunk into a 128 x 256 fp32 accumulator in tensor memory.
 // At the end the sixteen warps read the accumulator, park it in shared memory (over the rings, idle by then), exchange
 // across the cluster and store.  Every wait is bounded.
@@ -105,7 +105,7 @@ __device__ __forceinline__ float4 um_ld_cluster_f4(uint32_t addr) {
 
 __global__ void __launch_bounds__(kUmThreads, 1)
 w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
-                  const __grid_constant__ CUtensorMap map_z, const UmParams p) {
+                  const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_a, const UmParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t raw_ring = smem;
@@ -132,7 +132,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps);
         }
         for (uint32_t s = 0; s < kUmAbStages; ++s) {
-            ptx::mbar_init(ab_full + 8 * s, kUmDqWarps);
+            ptx::mbar_init(ab_full + 8 * s, kUmDqWarps + 1);      // sixteen warps' weights + the activations' bytes (producer)
             ptx::mbar_init(ab_empty + 8 * s, 1);
         }
         ptx::mbar_init(acc_full, 1);
@@ -145,6 +145,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         ptx::tma_prefetch_desc(&map_w);
         ptx::tma_prefetch_desc(&map_s);
         ptx::tma_prefetch_desc(&map_z);
+        ptx::tma_prefetch_desc(&map_a);
     }
     if (warp == kUmDqWarps + 1) {
         ptx::tmem_alloc(ptx::smem_u32(&tmem_holder), kUmTmemCols);
@@ -184,6 +185,24 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     ptx::tma_load_2d(dst + 8 * kUmBN * 4, &map_s, fb, (int32_t)n0, (int32_t)grp);
                     ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, &map_z, fb, (int32_t)(n0 / 8), (int32_t)grp);
                     if (++stage == kUmRawStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        } else if (lane == 1) {
+            // the activations of every chunk, one 128-row box each, as soon as the UMMAs that read the operand stage are done
+            uint32_t as = 0, aphase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t tile = um_cluster_id(); ok && tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+                if (iter > 0 && !um_wait_cluster(read_bar, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) break;
+                for (uint32_t c = c_begin; c < c_end; ++c) {
+                    if (!ptx::mbar_wait_relaxed(ab_empty + 8 * as, aphase ^ 1, abort_flag, p.wait_limit_ns, 64)) {
+                        atomicCAS(p.status, 0, kStatusProducerTimeout | 0x400000 | (int)(c & 0x3FFFFF));
+                        ok = false;
+                        break;
+                    }
+                    ptx::fence_proxy_async_smem();           // the rings were the parking area of the previous tile (generic proxy)
+                    ptx::mbar_arrive_expect_tx(ab_full + 8 * as, kUmABytes);
+                    ptx::tma_load_3d(a_ring + as * kUmABytes, &map_a, ab_full + 8 * as, (int32_t)(c * kUmBK), 0, 0);
+                    if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
                 }
             }
         }
@@ -227,10 +246,6 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
         uint32_t rs = 0, rphase = 0, as = 0, aphase = 0, iter = 0;
         bool ok = true;
-        // activations: unit u = (row m, eight k): this thread stages units tid and tid + 512 of every chunk
-        const uint32_t um0 = tid >> 3, uj = tid & 7, um1 = um0 + 64;
-        const uint32_t a_off0 = (um0 >> 3) * 1024 + (um0 & 7) * 128 + ((uj ^ (um0 & 7)) << 4);
-        const uint32_t a_off1 = (um1 >> 3) * 1024 + (um1 & 7) * 128 + ((uj ^ (um1 & 7)) << 4);
         const uint32_t b_off = (n >> 3) * 1024 + (n & 7) * 128;
         for (uint32_t tile = um_cluster_id(); tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
             const uint32_t n0 = tile * kUmBN;
@@ -238,21 +253,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x400000);
                 ok = false;
             }
-            // the activations of the next two chunks are always on their way (their L2 latency is longer than a chunk takes)
-            auto load_a = [&](uint32_t c, uint4& x0, uint4& x1) {
-                x0 = make_uint4(0, 0, 0, 0); x1 = make_uint4(0, 0, 0, 0);
-                if (c < c_end) {
-                    if (um0 < p.M) x0 = __ldg((const uint4*)(p.a + (size_t)um0 * p.K + c * kUmBK + uj * 8));
-                    if (um1 < p.M) x1 = __ldg((const uint4*)(p.a + (size_t)um1 * p.K + c * kUmBK + uj * 8));
-                }
-            };
-            uint4 pa0, pa1, pb0, pb1;
-            load_a(c_begin, pa0, pa1);
-            load_a(c_begin + 1, pb0, pb1);
             for (uint32_t c = c_begin; ok && c < c_end; ++c) {
-                const uint4 ca0 = pa0, ca1 = pa1;
-                pa0 = pb0; pa1 = pb1;
-                load_a(c + 2, pb0, pb1);
                 if (!ptx::mbar_wait(raw_full + 8 * rs, rphase, abort_flag, p.wait_limit_ns)) {
                     if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(c & 0x3FFFFF));
                     ok = false;
@@ -271,7 +272,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     ok = false;
                     break;
                 }
-                const uint32_t b_stage = b_ring + as * kUmBBytes + b_off, a_stage = a_ring + as * kUmABytes;
+                const uint32_t b_stage = b_ring + as * kUmBBytes + b_off;
 #pragma unroll
                 for (uint32_t i = 0; i < 4; ++i) {
                     const uint32_t wd = words[i], j = jh * 4 + i;
@@ -279,13 +280,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     const uint32_t v1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz), ss);       // k 1, 5
                     const uint32_t v2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz), ss);       // k 2, 6
                     const uint32_t v3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz), ss);      // k 3, 7
-                    um_sts128(b_stage + ((j ^ (n & 7)) << 4), v0, v1, v2, v3);
+                    // back into k order: (0,1) (2,3) (4,5) (6,7)
+                    um_sts128(b_stage + ((j ^ (n & 7)) << 4), __byte_perm(v0, v1, 0x5410), __byte_perm(v2, v3, 0x5410),
+                              __byte_perm(v0, v1, 0x7632), __byte_perm(v2, v3, 0x7632));
                 }
-                // activations in the same k order within every group of eight: 0,4,1,5,2,6,3,7
-                um_sts128(a_stage + a_off0, __byte_perm(ca0.x, ca0.z, 0x5410), __byte_perm(ca0.x, ca0.z, 0x7632),
-                          __byte_perm(ca0.y, ca0.w, 0x5410), __byte_perm(ca0.y, ca0.w, 0x7632));
-                um_sts128(a_stage + a_off1, __byte_perm(ca1.x, ca1.z, 0x5410), __byte_perm(ca1.x, ca1.z, 0x7632),
-                          __byte_perm(ca1.y, ca1.w, 0x5410), __byte_perm(ca1.y, ca1.w, 0x7632));
                 // The UMMAs read these bytes through the async proxy.  The warp's writes are ordered before lane 0 by the warp
                 // barrier; lane 0's proxy fence and release-arrive then publish them (one fence per warp instead of 32:
                 // the fence is the most expensive instruction of the chunk).
@@ -441,6 +439,9 @@ int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scal
     if (rc != T0_OK) return rc;
     rc = gemm::make_map_2d_plain(&map_z, (const void*)zeros, 4, K / group, N / 8, kUmBN / 8, 1);
     if (rc != T0_OK) return rc;
+    CUtensorMap map_a;      // the activations [M][K] as the 128-row operand: K-major boxes of 64, 128-byte swizzle, rows beyond M read as zero
+    rc = gemm::make_map_kmajor(&map_a, (const void*)a, M, K, K, 1, 128);
+    if (rc != T0_OK) return rc;
     static bool attr_set[64] = {};
     static int max_clusters[64][5] = {};
     if (rt->device >= 64) return fail(T0_ERR_INVALID, "device ordinal out of range");
@@ -471,7 +472,7 @@ int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scal
     const uint32_t clusters = std::min<uint32_t>(p.n_tiles, (uint32_t)max_clusters[rt->device][split]);
     cfg.gridDim = dim3(clusters * split, 1, 1);
     cfg.numAttrs = use_pdl ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_umma_kernel, map_w, map_s, map_z, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_umma_kernel, map_w, map_s, map_z, map_a, p);
     if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     rt->launches.fetch_add(1);
     return T0_OK;
