@@ -187,6 +187,29 @@ int t0_rt_set_wait_limit_ns(t0_runtime* rt, uint64_t ns);
  * kernel returns by itself; the call that synchronises reports T0_ERR_TIMEOUT, the runtime is poisoned, the output of
  * that launch is incomplete.  Set a short limit first (milliseconds).  For tests of the error handling only. */
 int t0_rt_selftest_drop_one_load(t0_runtime* rt);
+/* Scratch buffers (no counterpart in the reference, whose dispatch paths allocate per call).  Some launch paths keep a
+ * per-runtime device buffer that grows on first use at each larger size: growing drains the stream, frees and allocates,
+ * so the first such call stalls a pipeline and is illegal inside a stream capture.  The paths and their buffers:
+ *   t0_gemm_launch / t0_gemm_batch / t0_gemm_submit with a K that is not a multiple of 8 (or N in the NN layout) or an
+ *     operand that is not 16-byte aligned: padded copies of the operands, T0_SCRATCH_OPERAND_A = M * roundup(K, 8) * 2 bytes, T0_SCRATCH_OPERAND_B = N * roundup(K, 8) * 2
+ *     (NT) or K * roundup(N, 8) * 2 (NN);
+ *   split_k > 1 where the one-launch cluster form does not apply (pair tiles, padded operands, bf16 partial planes):
+ *     T0_SCRATCH_SPLITK_PLANES = M * N * split_k * 4;
+ *   t0_w4a16_gemm outside the fused shapes: T0_SCRATCH_W4_WEIGHTS = K * N * 2;
+ *   every fused W4A16 call (row layout and streaming layout): T0_SCRATCH_W4_FUSED, t0_rt_w4_fused_scratch_bytes(rt) bytes,
+ *     a fixed size per device, so only the first fused call of a runtime allocates;
+ *   t0_matmul_f32*, t0_blas_gemm_f32: bf16 copies of the operands, T0_SCRATCH_F32_A / _B = elements * 2, and, for
+ *     alpha/beta other than 1/0 or ldc != n, T0_SCRATCH_F32_C = m * n * 4;
+ *   t0_gemm_host and the multi-GPU host entry: pinned staging sets and device operands made on first use per shape.
+ * Everything else (aligned shapes of the bf16 GEMM, the cluster split-K, t0_w4a16_gemm_static) never allocates.
+ * t0_rt_reserve_scratch grows one buffer to at least `bytes` ahead of time, so that later launches up to that size
+ * neither allocate nor synchronise. */
+enum {
+    T0_SCRATCH_OPERAND_A = 0, T0_SCRATCH_OPERAND_B = 1, T0_SCRATCH_SPLITK_PLANES = 2, T0_SCRATCH_W4_WEIGHTS = 3,
+    T0_SCRATCH_W4_FUSED = 4, T0_SCRATCH_F32_A = 5, T0_SCRATCH_F32_B = 6, T0_SCRATCH_F32_C = 7
+};
+int t0_rt_reserve_scratch(t0_runtime* rt, int which, size_t bytes);
+size_t t0_rt_w4_fused_scratch_bytes(const t0_runtime* rt);
 /* the CUDA stream handle (cudaStream_t) and device ordinal, for callers that time or order work themselves */
 void* t0_rt_stream(const t0_runtime* rt);
 int t0_rt_device(const t0_runtime* rt);
@@ -402,7 +425,13 @@ int t0_rt_ensure_dequant_kernel(t0_runtime* rt, uint32_t group_size_log2, int ou
 int t0_w4_dequant(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out_bf16, uint32_t K, uint32_t N, uint32_t group);
 /* Fused W4A16 GEMM (no counterpart kernel in the reference; nearest items GptqWeight and the dequant kernels above):
  * y[M,N] f32 = a[M,K] bf16 * w[K,N], w dequantised in the main loop as above, fp32 accumulation.
- * M <= 16 runs the HBM-bound fused kernel; other shapes dequantise once into scratch and run the bf16 GEMM. */
+ * Three paths, chosen by shape:
+ *   M <= 16 (N % 32 == 0, K % 128 == 0, group % 128 == 0): one fused kernel on this row layout.  The row layout puts the 16 KiB
+ *     a CTA needs per step in sixteen pieces 4N bytes apart, so this entry is the slower of the two M <= 16 entries;
+ *     the fast one is t0_w4a16_gemm_prepacked below, on weights rewritten once by t0_w4_prepack;
+ *   16 < M <= 128 (N % 32 == 0, K % 64 == 0, group % 64 == 0, 16-byte aligned pointers): one fused tcgen05 kernel, weights
+ *     dequantised into the shared-memory operand inside the main loop, split along K across a thread-block cluster;
+ *   anything else: dequantise once into runtime scratch (allocated on first use, K*N*2 bytes), then the bf16 GEMM. */
 int t0_w4a16_gemm(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N,
                   uint32_t K, uint32_t group);
 /* The same call with its arguments in a record, and `count` of them submitted back to back from native code
@@ -421,9 +450,13 @@ int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count)
  *     (g = lane/4, t = lane%4), in nibbles c and c+4 (c = 0..3) the codes (k, k+1) of column 16w + g + 8(c&1) at
  *     k = 16s + 2t + 8(c>>1);
  *   then scales[N/256][K/group][256] bf16, then zero points [N/256][K/group][32] u32 (columns past N are zero).
- * t0_w4a16_gemm_prepacked computes the same y as t0_w4a16_gemm from that buffer (M <= 16, K % 128 == 0, group % 128 == 0,
- * N % 8 == 0, K*N small enough for one wave: at most 20 steps of 128 x 256 per SM); the batch form reads
- * t0_w4a16_args.packed as the prepacked buffer and ignores .scales / .zeros. */
+ * t0_w4a16_gemm_prepacked computes the same product as t0_w4a16_gemm from that buffer (M <= 16, K % 128 == 0,
+ * group % 128 == 0, N % 8 == 0, any K*N; a 16-byte aligned, the buffer 128-byte aligned); other shapes return
+ * T0_ERR_UNSUPPORTED.  The fp32 sums are added in a fixed order that depends only on the shapes in the call, so a call
+ * repeats bit for bit; the order differs from the row-layout entry's, so the two agree to rounding, not bit for bit.
+ * The batch form reads t0_w4a16_args.packed as the prepacked buffer and ignores .scales / .zeros.  It runs up to 32
+ * problems per launch, all of them at the same time on one persistent grid: the problems of one call must be independent
+ * (no y of one may be the a or the y of another); order dependent projections with separate calls. */
 size_t t0_w4_prepacked_bytes(uint32_t K, uint32_t N, uint32_t group);
 int t0_w4_prepack(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group);
 int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group);

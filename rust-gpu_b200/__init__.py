@@ -523,6 +523,17 @@ class GpuRuntime:
         """Arms the failure-path self-test: the next GEMM launch leaves out one operand load (see the header)."""
         _check(lib().t0_rt_selftest_drop_one_load(self._h))
 
+    SCRATCH_KINDS = {"operand_a": 0, "operand_b": 1, "splitk_planes": 2, "w4_weights": 3, "w4_fused": 4,
+                     "f32_a": 5, "f32_b": 6, "f32_c": 7}
+
+    def reserve_scratch(self, kind: str, n_bytes: int) -> None:
+        """Grows one of the runtime's scratch buffers ahead of time so that later launches up to that size neither
+        allocate nor synchronise (the header lists which paths use which buffer)."""
+        _check(lib().t0_rt_reserve_scratch(self._h, self.SCRATCH_KINDS[kind], n_bytes))
+
+    def w4_fused_scratch_bytes(self) -> int:
+        return int(lib().t0_rt_w4_fused_scratch_bytes(self._h))
+
     def stream(self) -> int:
         return int(lib().t0_rt_stream(self._h) or 0)
 
@@ -924,6 +935,8 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_synchronize", i32, vp)
     sig("t0_rt_wait_idle", i32, vp)
     sig("t0_rt_set_wait_limit_ns", i32, vp, u64)
+    sig("t0_rt_reserve_scratch", i32, vp, i32, sz)
+    sig("t0_rt_w4_fused_scratch_bytes", sz, vp)
     sig("t0_rt_selftest_drop_one_load", i32, vp)
     sig("t0_int4_wmma_config_k16", i32, vp)
     sig("t0_int4_wmma_config_k32", i32, vp)

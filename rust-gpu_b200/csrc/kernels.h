@@ -62,4 +62,8 @@ int launch_fill_range_bf16(void* dst, uint64_t n, uint64_t seed, uint64_t first,
 uint32_t gemm_stage_count(uint32_t tile_n);
 uint32_t gemm_smem_bytes(uint32_t tile_n);
 
+// Scratch of the fused W4A16 kernels: the arrival-counter region, and counters plus two pieces per CTA for a grid of `ctas`.
+size_t w4a16_counter_region_bytes();
+size_t w4a16_fixed_scratch_bytes(uint32_t ctas);
+
 }  // namespace t0

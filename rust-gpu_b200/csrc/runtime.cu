@@ -357,6 +357,38 @@ int t0_rt_selftest_drop_one_load(t0_runtime* rt) {
     rt->drop_next_load.store(1);
     return T0_OK;
 }
+int t0_rt_reserve_scratch(t0_runtime* rt, int which, size_t bytes) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    DeviceGuard guard(rt->device);
+    Scratch* s = nullptr;
+    switch (which) {
+        case T0_SCRATCH_OPERAND_A: s = &rt->scratch_a; break;
+        case T0_SCRATCH_OPERAND_B: s = &rt->scratch_b; break;
+        case T0_SCRATCH_SPLITK_PLANES: s = &rt->scratch_planes; break;
+        case T0_SCRATCH_W4_WEIGHTS: s = &rt->scratch_w; break;
+        case T0_SCRATCH_F32_A: s = &rt->scratch_cvt_a; break;
+        case T0_SCRATCH_F32_B: s = &rt->scratch_cvt_b; break;
+        case T0_SCRATCH_F32_C: s = &rt->scratch_cvt_c; break;
+        case T0_SCRATCH_W4_FUSED: {
+            // arrival counters (must start at zero) followed by two pieces per CTA; the size depends only on the device
+            const size_t need = std::max(bytes, t0_rt_w4_fused_scratch_bytes(rt));
+            if (need > rt->scratch_w4.size) {
+                rc = ensure_scratch(rt, rt->scratch_w4, need);
+                if (rc != T0_OK) return rc;
+                T0_CUDA(cudaMemsetAsync(rt->scratch_w4.ptr, 0, w4a16_counter_region_bytes(), rt->stream));
+            }
+            return T0_OK;
+        }
+        default: return fail(T0_ERR_INVALID, "unknown scratch kind %d", which);
+    }
+    return ensure_scratch(rt, *s, bytes);
+}
+
+size_t t0_rt_w4_fused_scratch_bytes(const t0_runtime* rt) {
+    return rt ? w4a16_fixed_scratch_bytes((uint32_t)rt->sm_count) : 0;
+}
+
 void* t0_rt_stream(const t0_runtime* rt) { return rt ? (void*)rt->stream : nullptr; }
 int t0_rt_device(const t0_runtime* rt) { return rt ? rt->device : -1; }
 int t0_rt_sm_count(const t0_runtime* rt) { return rt ? rt->sm_count : 0; }

@@ -636,6 +636,23 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
 // ------------------------------------------------------------------ K3: stand-alone dequantisation
 
+// Eight elements of the reference wire format from one packed word: value = (code - zero point) * scale in f32
+// (quant_kernels.rs:53-171); bf16 output keeps the upper 16 bits (truncation, quant_kernels.rs:167-168).
+__device__ __forceinline__ void dequant_ref_word(uint32_t word, int32_t zp, float sc, void* out, uint64_t e0, uint32_t out_bf16) {
+    uint32_t bits[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bits[i] = __float_as_uint(__fmul_rn((float)((int32_t)((word >> (4 * i)) & 0xFu) - zp), sc));
+    if (out_bf16) {
+        uint4 o;
+        o.x = __byte_perm(bits[0], bits[1], 0x7632); o.y = __byte_perm(bits[2], bits[3], 0x7632);
+        o.z = __byte_perm(bits[4], bits[5], 0x7632); o.w = __byte_perm(bits[6], bits[7], 0x7632);
+        __stcs((uint4*)((uint16_t*)out + e0), o);
+    } else {
+        __stcs((uint4*)((float*)out + e0), make_uint4(bits[0], bits[1], bits[2], bits[3]));
+        __stcs((uint4*)((float*)out + e0) + 1, make_uint4(bits[4], bits[5], bits[6], bits[7]));
+    }
+}
+
 // Reference wire format (quant_kernels.rs:53-171): byte e/2 holds element e in its low nibble for even e, one f32 scale and
 // one i32 zero point per group of 2^group_log2 elements.  One thread per packed 32-bit word (eight elements): a warp reads
 // 128 contiguous bytes and writes 1 KiB (f32) or 512 bytes (bf16) contiguous, 16 bytes per store.
@@ -646,27 +663,30 @@ __global__ void dequant_int4_ref_kernel(const uint8_t* __restrict__ packed, cons
     const uint64_t units = (total + 7) / 8;
     // a group of at least eight elements never splits a word; the 16-byte stores need the output aligned
     const bool vec = group_log2 >= 3 && (((uintptr_t)packed & 3) == 0) && (((uintptr_t)out & 15) == 0);
-    for (uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += stride) {
+    uint64_t u = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (vec) {
+        // four independent words per round: all twelve loads are issued before the first is used
+        const uint64_t full = total / 8;
+        for (; u + 3 * stride < full; u += 4 * stride) {
+            uint32_t word[4];
+            int32_t zp[4];
+            float sc[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint64_t e0 = (u + j * stride) * 8, grp = e0 >> group_log2;
+                word[j] = __ldcs((const uint32_t*)(packed + (e0 >> 1)));
+                zp[j] = __ldg(zps + grp);
+                sc[j] = __ldg(scales + grp);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) dequant_ref_word(word[j], zp[j], sc[j], out, (u + j * stride) * 8, out_bf16);
+        }
+    }
+    for (; u < units; u += stride) {
         const uint64_t e0 = u * 8;
         if (vec && e0 + 8 <= total) {
-            const uint32_t word = __ldcs((const uint32_t*)(packed + (e0 >> 1)));
             const uint64_t grp = e0 >> group_log2;
-            const int32_t zp = __ldg(zps + grp);
-            const float sc = __ldg(scales + grp);
-            uint32_t bits[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                bits[i] = __float_as_uint(__fmul_rn((float)((int32_t)((word >> (4 * i)) & 0xFu) - zp), sc));
-            if (out_bf16) {
-                // truncating store (quant_kernels.rs:167-168): the upper halves of two values side by side
-                uint4 o;
-                o.x = __byte_perm(bits[0], bits[1], 0x7632); o.y = __byte_perm(bits[2], bits[3], 0x7632);
-                o.z = __byte_perm(bits[4], bits[5], 0x7632); o.w = __byte_perm(bits[6], bits[7], 0x7632);
-                __stcs((uint4*)((uint16_t*)out + e0), o);
-            } else {
-                __stcs((uint4*)((float*)out + e0), make_uint4(bits[0], bits[1], bits[2], bits[3]));
-                __stcs((uint4*)((float*)out + e0) + 1, make_uint4(bits[4], bits[5], bits[6], bits[7]));
-            }
+            dequant_ref_word(__ldcs((const uint32_t*)(packed + (e0 >> 1))), __ldg(zps + grp), __ldg(scales + grp), out, e0, out_bf16);
             continue;
         }
         for (uint64_t e = e0; e < e0 + 8 && e < total; ++e) {

@@ -25,6 +25,14 @@ pub const T0_TEPI_GELU: u32 = 4;
 pub const T0_TEPI_ABS: u32 = 5;
 pub const T0_TEPI_NEG: u32 = 6;
 pub const T0_TEPI_CLAMP: u32 = 7;
+pub const T0_SCRATCH_OPERAND_A: u32 = 0;
+pub const T0_SCRATCH_OPERAND_B: u32 = 1;
+pub const T0_SCRATCH_SPLITK_PLANES: u32 = 2;
+pub const T0_SCRATCH_W4_WEIGHTS: u32 = 3;
+pub const T0_SCRATCH_W4_FUSED: u32 = 4;
+pub const T0_SCRATCH_F32_A: u32 = 5;
+pub const T0_SCRATCH_F32_B: u32 = 6;
+pub const T0_SCRATCH_F32_C: u32 = 7;
 pub const T0_WARP_ROW_DOMINANT: u32 = 0;
 pub const T0_WARP_COL_DOMINANT: u32 = 1;
 pub const T0_WARP_SQUARE: u32 = 2;
@@ -214,6 +222,8 @@ extern "C" {
     pub fn t0_rt_wait_idle(rt: *mut t0_runtime) -> c_int;
     pub fn t0_rt_set_wait_limit_ns(rt: *mut t0_runtime, ns: u64) -> c_int;
     pub fn t0_rt_selftest_drop_one_load(rt: *mut t0_runtime) -> c_int;
+    pub fn t0_rt_reserve_scratch(rt: *mut t0_runtime, which: c_int, bytes: usize) -> c_int;
+    pub fn t0_rt_w4_fused_scratch_bytes(rt: *const t0_runtime) -> usize;
     pub fn t0_rt_stream(rt: *const t0_runtime) -> *mut c_void;
     pub fn t0_rt_device(rt: *const t0_runtime) -> c_int;
     pub fn t0_rt_sm_count(rt: *const t0_runtime) -> c_int;

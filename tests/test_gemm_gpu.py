@@ -747,3 +747,23 @@ def test_cluster_split_k_equals_planes_summed_in_split_order(t0, oracle, rt, m, 
     assert np.array_equal(got16, oracle.f32_to_bf16_rne(want.reshape(-1)))
     for buf in (xa, xb, planes_buf, y, bb):
         buf.free()
+
+
+def test_reserve_scratch_then_padded_and_planes_paths(t0, oracle):
+    # The scratch-growing launch paths (K not a multiple of 8: padded operand copies; the two-launch split-K: fp32 planes)
+    # after their buffers were reserved ahead of time; an unknown kind is an error, not a crash.
+    rt = t0.GpuRuntime(0)
+    try:
+        m, k, n = 70, 1001, 136
+        rt.reserve_scratch("operand_a", m * 1008 * 2)
+        rt.reserve_scratch("operand_b", n * 1008 * 2)
+        rt.reserve_scratch("splitk_planes", 128 * 256 * 4 * 4)
+        rt.reserve_scratch("w4_fused", 0)
+        assert rt.w4_fused_scratch_bytes() > 16384
+        with pytest.raises(t0.T0Error):
+            t0._check(t0.lib().t0_rt_reserve_scratch(rt._h, 99, 16))
+        a, b = oracle.fill_uniform_bf16(m * k, 5), oracle.fill_uniform_bf16(n * k, 6)
+        got = run_tile(t0, rt, t0.tile_auto_select(m, k, n), a, b, m, n, k)
+        assert_gemm_close(got, oracle.gemm_nt(a, b, m, k, n), k)
+    finally:
+        rt.close()
