@@ -296,7 +296,7 @@ def run_hbm_workload(args, name, rt=None, brief=False):
     return line
 
 
-def run_aux_workload(args, name):
+def run_aux_workload(args, name, rt=None, brief=False):
     """Kernels beside the GEMM itself, each at a size larger than L2: the stand-alone dequantisation in the reference's wire
     format (quant_kernels.rs:53-171), the one-time weight prepack, and the f32 entry matmul(x f32, w f32)
     (bf16_matmul.rs:33-59: two conversion passes plus the GEMM).  One JSON line each; parity on a sample."""
@@ -305,11 +305,23 @@ def run_aux_workload(args, name):
     t0.lib()
     import oracle
     oracle.build()
-    torch.cuda.set_device(0)
-    rt = t0.GpuRuntime(0)
+    own_rt = rt is None
+    if own_rt:
+        torch.cuda.set_device(0)
+        rt = t0.GpuRuntime(0)
     peaks = measured_peaks()
-    steps = args.steps if args.steps is not None else 40
-    warmup = max(3, args.warmup if args.warmup is not None else 4)
+    steps = 20 if brief else (args.steps if args.steps is not None else 40)
+    warmup = 3 if brief else max(3, args.warmup if args.warmup is not None else 4)
+    bufs = []
+
+    def A(n_bytes):
+        bufs.append(rt.alloc(n_bytes))
+        return bufs[-1]
+
+    def U(host):
+        bufs.append(rt.upload(host))
+        return bufs[-1]
+
     line = {"n_gpus": 1, "steps": steps, "warmup": warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic"}
 
     def time_steps(fn):
@@ -332,13 +344,13 @@ def run_aux_workload(args, name):
         n_sets = 8                                              # 8 x 22 MiB of packed codes rotate; the output alone exceeds the L2
         scales_h = (0.001 + 0.019 * (np.arange(rows * n_groups) % 97) / 97.0).astype(np.float32)
         zps_h = (np.arange(rows * n_groups) % 16).astype(np.int32)
-        xs, xz = rt.upload(scales_h), rt.upload(zps_h)
+        xs, xz = U(scales_h), U(zps_h)
         packs = []
         for s in range(n_sets):
-            b = rt.alloc(rows * cols // 2)
+            b = A(rows * cols // 2)
             rt.fill_u32(b.gpu_addr(), rows * cols // 8, 500 + s)
             packs.append(b)
-        outs = [rt.alloc(rows * cols * (2 if bf16 else 4)) for _ in range(2)]
+        outs = [A(rows * cols * (2 if bf16 else 4)) for _ in range(2)]
         sec, launches = time_steps(lambda i: rt.dequant_int4(packs[i % n_sets].gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), outs[i % 2].gpu_addr(),
                                                             rows, cols, glog, bf16))
         alg = rows * cols // 2 + rows * n_groups * 8 + rows * cols * (2 if bf16 else 4)
@@ -359,13 +371,13 @@ def run_aux_workload(args, name):
         n_sets = 8
         sets = []
         for s in range(n_sets):
-            xp, xs, xz = rt.alloc((K // 8) * N * 4), rt.alloc((K // G) * N * 2), rt.alloc((K // G) * (N // 8) * 4)
+            xp, xs, xz = A((K // 8) * N * 4), A((K // G) * N * 2), A((K // G) * (N // 8) * 4)
             rt.fill_u32(xp.gpu_addr(), (K // 8) * N, 1000 + s)
             rt.fill_range_bf16(xs.gpu_addr(), (K // G) * N, 2000 + s, 0.001, 0.02)
             rt.fill_u32(xz.gpu_addr(), (K // G) * (N // 8), 3000 + s)
             sets.append((xp, xs, xz))
         nbytes = t0.lib().t0_w4_prepacked_bytes(K, N, G)
-        outs = [rt.alloc(nbytes) for _ in range(8)]
+        outs = [A(nbytes) for _ in range(8)]
         C = __import__("ctypes")
         sec, launches = time_steps(lambda i: t0._check(t0.lib().t0_w4_prepack(rt._h, *(b.gpu_addr() for b in sets[i % n_sets]), outs[i % 8].gpu_addr(), K, N, G)))
         alg = 2 * nbytes
@@ -383,9 +395,9 @@ def run_aux_workload(args, name):
         rng = np.random.default_rng(3)
         x_h = rng.uniform(-1, 1, size=M * K).astype(np.float32)
         w_h = rng.uniform(-1, 1, size=K * N).astype(np.float32)
-        xs_ = [rt.upload(x_h), rt.upload(x_h)]
-        ws_ = [rt.upload(w_h), rt.upload(w_h)]
-        ys_ = [rt.alloc(M * N * 4) for _ in range(2)]
+        xs_ = [U(x_h), U(x_h)]
+        ws_ = [U(w_h), U(w_h)]
+        ys_ = [A(M * N * 4) for _ in range(2)]
         sec, launches = time_steps(lambda i: rt.matmul_f32(xs_[i % 2].gpu_addr(), ws_[i % 2].gpu_addr(), ys_[i % 2].gpu_addr(), M, K, N))
         rows = [0, 2049, 4095]
         xb = oracle.f32_to_bf16_rne(x_h.reshape(M, K)[rows].reshape(-1))
@@ -402,7 +414,11 @@ def run_aux_workload(args, name):
                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / peaks["bf16_tflops"],
                                   "traffic": ncu_traffic(name), "peak_source": f"{peaks['source']} (burst cuBLAS bf16)"},
                      "gpu_launches": int(launches), "parity": {"sampled_rows": rows, "max_abs_err": err, "tol": tol}})
-    rt.close()
+    if own_rt:
+        rt.close()
+    else:
+        for b in bufs:
+            b.free()
     if not ok:
         print(json.dumps({"error": "parity check failed", "workload": name, "parity": line["parity"]}), flush=True)
         sys.exit(1)
@@ -586,7 +602,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="default single-GPU run: leave out the short runs of the other workloads")
     ap.add_argument("--layout", default="nt", choices=["nt", "nn"], help="B as WT[N,K] (the reference's native layout) or as B[K,N]")
-    ap.add_argument("--gather", action="store_true", help="sharded workload: also time GEMM + in-place NCCL all-gather of C (reported under \"gather\")")
+    ap.add_argument("--gather", action="store_true", help="sharded workload: also time GEMM + in-place NCCL all-gather of C, and the one-kernel form whose epilogue stores to every rank (reported under \"gather\")")
     ap.add_argument("--row-layout", action="store_true", help="W4A16 workloads: weights in the row layout instead of the streaming layout")
     ap.add_argument("--lib-ab", action="store_true", help="measurement only: time the vendor library's bf16 GEMM beside the repo's kernel (single GPU)")
     args = ap.parse_args()
@@ -724,7 +740,45 @@ def main():
         dist.all_gather(owner, c_g[rank, 0, :8].clone())
         ok = bool(torch.equal(probe, owner[(rank + 1) % world]))
         gather = {"ms_per_step": g_ms / steps, "value": 2.0 * M * N_total * K * steps / (g_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                  "gathered_bytes_per_rank": M * N * 4 * (world - 1), "layout": "C_g[g][M][N/g]", "remote_block_matches": ok}
+                  "gathered_bytes_per_rank": M * N * 4 * (world - 1), "layout": "C_g[g][M][N/g]", "remote_block_matches": ok,
+                  "call": "t0_gemm_launch into slot `rank`, then one in-place NCCL all-gather on the same stream"}
+
+        # The same result from ONE kernel per GPU: the GEMM's epilogue stores every block into slot `rank` of all the
+        # ranks' buffers (its own and, over NVLink, the others' mapped through CUDA IPC).  No collective call at all.
+        c_buf = rt.alloc(world * M * N * 4)
+        handles = [None] * world
+        dist.all_gather_object(handles, c_buf.ipc_export())
+        mapped = {d: rt.ipc_open(handles[d]) for d in range(world) if d != rank}
+        slot = rank * M * N * 4
+        f_args = rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), c_buf.gpu_addr() + slot, M, N, K, **gemm_kw)
+        peers = [mapped[d] + slot for d in sorted(mapped)]
+        for _ in range(warmup):
+            rt.gemm_gather(f_args, peers)
+        barrier()
+        rt.timer_start()
+        for _ in range(steps):
+            rt.gemm_gather(f_args, peers)
+        f_ms = rt.timer_stop()
+        barrier()                                   # every rank's stores have landed before anyone reads
+        tf_ = torch.tensor([f_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tf_, op=dist.ReduceOp.MAX)
+        f_ms = float(tf_.item())
+        # every slot of this rank's buffer against the NCCL-gathered result, three rows each, bit for bit
+        same = True
+        for d in range(world):
+            for r_ in (0, M // 2 + 1, M - 1):
+                got = c_buf.read_bytes((d * M + r_) * N * 4, N * 4, np.float32)
+                same = same and bool(np.array_equal(got, c_g[d, r_].cpu().numpy()))
+        ts = torch.tensor([1.0 if same else 0.0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(ts, op=dist.ReduceOp.MIN)
+        gather["fused"] = {"ms_per_step": f_ms / steps, "value": 2.0 * M * N_total * K * steps / (f_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                           "nvlink_bytes_out_per_rank": M * N * 4 * (world - 1), "equals_nccl_gather_on_every_rank": bool(ts.item() == 1.0),
+                           "call": "t0_gemm_launch_gather: the epilogue's TMA stores write each block to every rank's buffer (peer memory over NVLink)"}
+        barrier()
+        for ptr in mapped.values():
+            rt.ipc_close(ptr)
+        barrier()
+        c_buf.free()
         del c_g
 
     # parity spot check on every rank of its own block (the full parity suite is tests/ -m gpu)
@@ -907,6 +961,12 @@ def main():
                                       "gpu_launches": ln["gpu_launches"], "parity": ln["parity"]})
                 else:
                     sec_lines.append(run_square_brief(t0, rt, sname))
+            for sname in AUX_WORKLOADS:
+                ln = run_aux_workload(args, sname, rt=rt, brief=True)
+                sec_lines.append({"workload": sname, "metric": ln["metric"], "value": ln["value"], "unit": ln["unit"], "ms_per_step": ln["ms_per_step"],
+                                  "steps": ln["steps"], "kernel": ln["config"]["kernel"],
+                                  "roofline": {k: ln["roofline"][k] for k in ("bound", "frac", "peak", "traffic") if k in ln["roofline"]},
+                                  "gpu_launches": ln["gpu_launches"], "parity": ln["parity"]})
             line["secondary"] = sec_lines
         print(json.dumps(line), flush=True)
     if world > 1:

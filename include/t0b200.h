@@ -299,6 +299,20 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
 /* `count` launches from an array, submitted back to back from native code (the batch form of the above; the reference's
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
+/* GEMM with a gathered output (no counterpart in the reference, which is single-GPU; it is the compute step and the
+ * all-gather of the sharded GEMM in one kernel).  The product goes to args->y and, in the same epilogue, to n_peers further
+ * f32 [M,N] buffers (at most 7), normally slot `rank` of the other GPUs' rank-major result C_g[g][M][N/g]: the epilogue
+ * issues one TMA store per destination for every 32 x 32 block, so the blocks cross NVLink while the main loop runs.
+ * peer_y[i] are device addresses valid in this process: memory of a GPU with peer access enabled, or a mapping opened with
+ * t0_rt_ipc_open.  Needs N % 32 == 0, 16-byte aligned destinations, f32 output, no split-K (T0_ERR_UNSUPPORTED otherwise).
+ * The stores are complete when the launch is: order readers on the other GPUs after it (an event, a barrier). */
+int t0_gemm_launch_gather(t0_runtime* rt, const t0_gemm_args* args, const uint64_t* peer_y, uint32_t n_peers);
+/* Sharing a buffer with another process on the same machine (one process per GPU): t0_buf_ipc_export writes the 64-byte
+ * handle of the buffer's allocation, t0_rt_ipc_open maps it into this process (peer access over NVLink) and returns the
+ * device address of the allocation's start, t0_rt_ipc_close drains the runtime's stream and unmaps it. */
+int t0_buf_ipc_export(const t0_buffer* buf, uint8_t handle[64]);
+int t0_rt_ipc_open(t0_runtime* rt, const uint8_t handle[64], uint64_t* device_ptr);
+int t0_rt_ipc_close(t0_runtime* rt, uint64_t device_ptr);
 /* The same launches with x, b, y (and bias) as HOST addresses: operands are uploaded, the product is computed and the
  * result is downloaded, and consecutive problems overlap - problem i+1 crosses the link while problem i is computed and
  * read back (three queues, two staging sets on the device).  This is the upload / dispatch / read-back sequence of the
@@ -510,6 +524,12 @@ int t0_mg_synchronize(t0_mg* mg);
  * WT, y_slice[r] = where its [M, N/g] f32 block goes (slot r of the gather buffer when a gathered C is wanted). */
 int t0_mg_gemm_sharded(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, const uint64_t* y_slice, uint32_t m, uint32_t n, uint32_t k,
                        uint32_t tile_n, int pair_cta);
+/* The sharded GEMM and the all-gather of C in one kernel per GPU: GPU r computes its [M, N/g] block and its epilogue stores
+ * every 32 x 32 block into slot r of ALL the buffers c_gathered[0..g) (its own and, over NVLink, the other GPUs'), so when
+ * the g launches are complete (t0_mg_synchronize) every GPU holds all of C in the rank-major layout C_g[g][M][N/g].  No
+ * second pass, no NCCL; needs peer access between the GPUs and (N/g) % 32 == 0. */
+int t0_mg_gemm_sharded_gathered(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, const uint64_t* c_gathered, uint32_t m, uint32_t n,
+                                uint32_t k);
 /* The same product with HOST operands (the upload / dispatch / read-back sequence of the reference's host-facing calls,
  * src/universal/math/blas.rs:18-100, spread over the GPUs): x_host = A[M,K] bf16, wt_host = WT[N,K] bf16, y_host = C[M,N] f32
  * row-major.  A is replicated on the devices but crosses the host link once: GPU r uploads rows [r M/g, (r+1) M/g) and

@@ -468,6 +468,12 @@ class GpuBuffer:
     def zero(self) -> None:
         _check(lib().t0_buf_zero(self._h))
 
+    def ipc_export(self) -> bytes:
+        """The 64-byte handle another process on this machine passes to ``GpuRuntime.ipc_open``."""
+        h = (C.c_uint8 * 64)()
+        _check(lib().t0_buf_ipc_export(self._h, h))
+        return bytes(h)
+
     def free(self) -> None:
         if self._h:
             lib().t0_buf_free(self._h)
@@ -661,6 +667,23 @@ class GpuRuntime:
         arr = (GemmArgs * len(args_list))(*args_list)
         _check(lib().t0_gemm_launch_batch(self._h, arr, len(args_list)))
 
+    def gemm_gather(self, args: GemmArgs, peer_y: list[int]) -> None:
+        """``t0_gemm_launch_gather``: the product goes to ``args.y`` and, in the same epilogue, to every address of
+        ``peer_y`` (other GPUs' memory mapped into this process)."""
+        arr = (C.c_uint64 * max(1, len(peer_y)))(*peer_y)
+        _check(lib().t0_gemm_launch_gather(self._h, C.byref(args), arr, len(peer_y)))
+
+    def ipc_open(self, handle: bytes) -> int:
+        """Maps a buffer exported by another process (``GpuBuffer.ipc_export``) and returns its device address here."""
+        if len(handle) != 64:
+            raise ValueError("an IPC handle is 64 bytes")
+        ptr = C.c_uint64()
+        _check(lib().t0_rt_ipc_open(self._h, (C.c_uint8 * 64)(*handle), C.byref(ptr)))
+        return int(ptr.value)
+
+    def ipc_close(self, device_ptr: int) -> None:
+        _check(lib().t0_rt_ipc_close(self._h, device_ptr))
+
     def gemm_host_batch(self, args_list: list[GemmArgs]) -> None:
         """``t0_gemm_launch_host_batch``: x, b, y (and bias) of every problem are HOST addresses; uploads, kernels and
         downloads of consecutive problems overlap.  Returns when every result is in host memory."""
@@ -777,6 +800,11 @@ class MultiGpu:
         """Host operands: A uploaded once in total (1/g per GPU, completed over NVLink), C written into ``y_host``."""
         _check(lib().t0_mg_gemm_sharded_host(self._h, x_host.ctypes.data_as(C.c_void_p), wt_host.ctypes.data_as(C.c_void_p),
                                              y_host.ctypes.data_as(C.c_void_p), m, n, k))
+
+    def gemm_sharded_gathered(self, x: list[int], b_slice: list[int], c_gathered: list[int], m: int, n: int, k: int) -> None:
+        """GEMM and all-gather in one kernel per GPU: every GPU's epilogue stores its block into slot r of all ``c_gathered``."""
+        arr = lambda v: (C.c_uint64 * len(v))(*v)
+        _check(lib().t0_mg_gemm_sharded_gathered(self._h, arr(x), arr(b_slice), arr(c_gathered), m, n, k))
 
     def all_gather_c(self, c_gathered: list[int], m: int, n: int) -> None:
         _check(lib().t0_mg_all_gather_c(self._h, (C.c_uint64 * len(c_gathered))(*c_gathered), m, n))
@@ -935,6 +963,11 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_synchronize", i32, vp)
     sig("t0_rt_wait_idle", i32, vp)
     sig("t0_rt_set_wait_limit_ns", i32, vp, u64)
+    sig("t0_gemm_launch_gather", i32, vp, C.POINTER(GemmArgs), C.POINTER(C.c_uint64), u32)
+    sig("t0_buf_ipc_export", i32, vp, C.POINTER(C.c_uint8))
+    sig("t0_rt_ipc_open", i32, vp, C.POINTER(C.c_uint8), C.POINTER(C.c_uint64))
+    sig("t0_rt_ipc_close", i32, vp, u64)
+    sig("t0_mg_gemm_sharded_gathered", i32, vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), u32, u32, u32)
     sig("t0_rt_reserve_scratch", i32, vp, i32, sz)
     sig("t0_rt_w4_fused_scratch_bytes", sz, vp)
     sig("t0_rt_selftest_drop_one_load", i32, vp)

@@ -33,6 +33,8 @@ struct KParams {
     uint32_t out_bf16, epilogue, n_ops;
     uint32_t tma_store;          // full f32 chunks leave through the output tensor map
     uint32_t drop_load;          // self-test of the failure path: the producer of CTA 0 leaves out its first operand load
+    uint32_t n_peers;            // gathered output: every TMA-stored chunk also goes to this many other buffers (other GPUs' memory)
+    const CUtensorMap* peer_maps; // their output tensor maps, in global memory (written by the host before the launch)
     float scale, clamp_min, clamp_max;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
 };
@@ -161,6 +163,10 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
             __syncwarp();
             if (lane == 0) {
                 ptx::tma_store_3d(map_y, sb, (int32_t)col0, (int32_t)row_base, (int32_t)split);
+                // gathered output: the same block to the other GPUs' buffers (plain TMA stores to peer memory over NVLink),
+                // in the same bulk group, so the block is reused only after all of them have read it
+                for (uint32_t i = 0; i < p.n_peers; ++i)
+                    ptx::tma_store_3d(p.peer_maps + i, sb, (int32_t)col0, (int32_t)row_base, (int32_t)split);
                 ptx::bulk_commit_group();
             }
             ++n_stores;
@@ -299,6 +305,30 @@ inline int make_map_out_f32(CUtensorMap* map, const void* base, uint32_t M, uint
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (f32 output %u x %u) failed: %d", M, N, (int)r);
+    return T0_OK;
+}
+
+// Gathered output: one output tensor map per extra destination, copied to `g.peer_map_slot` on the launch stream (a small
+// pageable-source copy, staged by the driver before the call returns), unless the caller says the slot already holds them.
+inline int stage_peer_maps(const GemmLaunch& g, KParams& p, uint32_t split, cudaStream_t stream) {
+    p.n_peers = 0;
+    p.peer_maps = nullptr;
+    if (g.n_peer_y == 0) return T0_OK;
+    if (g.n_peer_y > 7 || !g.peer_map_slot) return fail(T0_ERR_INVALID, "gathered output: %u destinations (at most 7) or no slot for their tensor maps", g.n_peer_y);
+    if (!p.tma_store || split != 1 || g.n % 32 != 0)
+        return fail(T0_ERR_UNSUPPORTED, "a gathered output needs the TMA-store epilogue on every chunk: f32 output, N %% 32 == 0 (N=%u), 16-byte aligned buffers, no split-K", g.n);
+    if (!g.peer_maps_staged) {
+        CUtensorMap maps[7];
+        for (uint32_t i = 0; i < g.n_peer_y; ++i) {
+            if (!g.peer_y[i] || ((uintptr_t)g.peer_y[i] & 15)) return fail(T0_ERR_INVALID, "gathered output: destination %u is null or not 16-byte aligned", i);
+            int rc = make_map_out_f32(&maps[i], g.peer_y[i], g.m, g.n, 1, 0);
+            if (rc != T0_OK) return rc;
+        }
+        cudaError_t e = cudaMemcpyAsync(g.peer_map_slot, maps, g.n_peer_y * sizeof(CUtensorMap), cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return fail(T0_ERR_CUDA, "gathered output: copying the tensor maps failed: %s", cudaGetErrorString(e));
+    }
+    p.peer_maps = (const CUtensorMap*)g.peer_map_slot;
+    p.n_peers = g.n_peer_y;
     return T0_OK;
 }
 

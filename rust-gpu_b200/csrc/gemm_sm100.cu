@@ -275,6 +275,8 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
         if (rc != T0_OK) return rc;
         p.tma_store = 1;
     }
+    rc = stage_peer_maps(g, p, split, stream);
+    if (rc != T0_OK) return rc;
 
     if (g.nn) {
         switch (bn) {

@@ -345,6 +345,8 @@ int launch_gemm_sm100_pair(const GemmLaunch& g, cudaStream_t stream) {
         if (rc != T0_OK) return rc;
         p.tma_store = 1;
     }
+    rc = stage_peer_maps(g, p, split, stream);
+    if (rc != T0_OK) return rc;
     const uint32_t n_sms = g.n_sms ? g.n_sms : 148;
     if (g.nn)
         return pair_n == 256 ? launch_pair_instance<256, true>(ma, mb, mb_half, my, p, total, n_sms, stream)

@@ -31,7 +31,16 @@ struct GemmLaunch {
     uint32_t n_sms;
     uint64_t wait_limit_ns;      // 0 = the default limit (ptx::kWaitLimitNs)
     bool drop_load;              // self-test: CTA 0's producer leaves out its first load, so a bounded wait must run out
+    // Gathered output (multi-GPU): the product is also stored to n_peer_y other f32 [M,N] buffers, normally other GPUs'
+    // memory mapped into this process.  Needs the TMA-store epilogue for every chunk: f32 output, N % 32 == 0, 16-byte aligned
+    // bases, no split-K.  peer_map_slot = device memory for kMaxPeerY tensor maps (128-byte aligned) that stays untouched
+    // until the launch has finished.
+    void* peer_y[7];
+    uint32_t n_peer_y;
+    void* peer_map_slot;
+    bool peer_maps_staged;       // the slot already holds the maps of exactly these destinations and this shape
 };
+constexpr uint32_t kMaxPeerY = 7;
 
 // Launches the tcgen05 GEMM. Requirements (checked): x and b 16-byte aligned, row strides and
 // K / split_k multiples of 8 elements, K % split_k == 0.  Returns a T0_* code.

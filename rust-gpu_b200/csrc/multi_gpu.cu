@@ -133,6 +133,43 @@ int t0_mg_gemm_sharded(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, co
     return T0_OK;
 }
 
+int t0_mg_gemm_sharded_gathered(t0_mg* mg, const uint64_t* x, const uint64_t* b_slice, const uint64_t* c_gathered, uint32_t m, uint32_t n,
+                                uint32_t k) {
+    if (!mg || !x || !b_slice || !c_gathered) return fail(T0_ERR_INVALID, "null argument");
+    const uint32_t g = (uint32_t)mg->rts.size();
+    if (g > kMaxPeerY + 1) return fail(T0_ERR_UNSUPPORTED, "at most %u GPUs", kMaxPeerY + 1);
+    uint32_t first = 0, n_local = 0;
+    int rc = t0_shard_columns(n, g, 0, &first, &n_local);
+    if (rc != T0_OK) return rc;
+    // every GPU must be able to store into every other GPU's buffer
+    for (uint32_t r = 0; r < g; ++r) {
+        DeviceGuard guard(mg->rts[r]->device);
+        for (uint32_t d = 0; d < g; ++d) {
+            if (d == r) continue;
+            int can = 0;
+            cudaDeviceCanAccessPeer(&can, mg->rts[r]->device, mg->rts[d]->device);
+            if (!can) return fail(T0_ERR_UNSUPPORTED, "GPU %d cannot address GPU %d's memory: use t0_mg_gemm_sharded and t0_mg_all_gather_c", mg->rts[r]->device, mg->rts[d]->device);
+            cudaError_t e = cudaDeviceEnablePeerAccess(mg->rts[d]->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) return fail(T0_ERR_CUDA, "cudaDeviceEnablePeerAccess: %s", cudaGetErrorString(e));
+            cudaGetLastError();
+        }
+    }
+    const size_t slot = (size_t)m * n_local * sizeof(float);
+    for (uint32_t r = 0; r < g; ++r) {
+        t0_gemm_args a;
+        memset(&a, 0, sizeof a);
+        a.x = x[r]; a.b = b_slice[r]; a.y = c_gathered[r] + r * slot;
+        a.m = m; a.n = n_local; a.k = k; a.transpose = T0_NT; a.swap_grid = 1;
+        uint64_t peers[kMaxPeerY];
+        uint32_t np = 0;
+        for (uint32_t d = 0; d < g; ++d)
+            if (d != r) peers[np++] = c_gathered[d] + r * slot;      // slot r of GPU d's buffer
+        rc = t0_gemm_launch_gather(mg->rts[r], &a, peers, np);
+        if (rc != T0_OK) return rc;
+    }
+    return T0_OK;
+}
+
 int t0_mg_gemm_sharded_host(t0_mg* mg, const void* x_host, const void* wt_host, void* y_host, uint32_t m, uint32_t n, uint32_t k) {
     if (!mg || !x_host || !wt_host || !y_host) return fail(T0_ERR_INVALID, "null argument");
     const uint32_t g = (uint32_t)mg->rts.size();

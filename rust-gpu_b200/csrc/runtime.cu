@@ -19,6 +19,8 @@ struct GemmRequest {
     uint8_t epilogue, n_ops;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
     float scale, clamp_min, clamp_max;
+    uint64_t peer_y[kMaxPeerY];   // gathered output: further f32 [M,N] destinations (other GPUs' memory), see t0_gemm_launch_gather
+    uint32_t n_peer_y;
 };
 
 uint32_t choose_tile_n(const t0_runtime* rt, uint32_t m, uint32_t n, uint32_t k, uint32_t split) {
@@ -58,6 +60,8 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q_in) {
                                     : q.epilogue != T0_EPI_STORE_F32;
     if (needs_bias && !q.bias) return fail(T0_ERR_INVALID, "epilogue needs a bias vector but bias is null");
     uint32_t split = q.split_k > 1 ? q.split_k : 1;
+    if (q.n_peer_y && (split > 1 || q.k == 0 || q.out_bf16 || q.planes))
+        return fail(T0_ERR_UNSUPPORTED, "a gathered output takes a plain f32 product: no split-K, no bf16 output, K > 0");
     if (q.k == 0) {
         // empty contraction: the sum is zero, the epilogue still applies
         int rc0 = launch_splitk_reduce(nullptr, (void*)q.y, (const float*)q.bias, q.m, q.n, 0, q.out_bf16, q.epilogue, q.n_ops,
@@ -153,6 +157,18 @@ int run_gemm(t0_runtime* rt, const GemmRequest& q_in) {
         if (rc != T0_OK) return rc;
         rt->launches.fetch_add(1);
         return T0_OK;
+    }
+    if (q.n_peer_y) {
+        // the destinations' tensor maps live in a per-runtime device slot; they are rewritten (stream-ordered) only when the
+        // destinations or the shape differ from the launch before
+        std::vector<uint64_t> key(q.peer_y, q.peer_y + q.n_peer_y);
+        key.push_back(((uint64_t)q.m << 32) | q.n);
+        if (!rt->d_peer_maps) T0_CUDA(cudaMalloc(&rt->d_peer_maps, kMaxPeerY * 128));
+        g.n_peer_y = q.n_peer_y;
+        for (uint32_t i = 0; i < q.n_peer_y; ++i) g.peer_y[i] = (void*)q.peer_y[i];
+        g.peer_map_slot = rt->d_peer_maps;
+        g.peer_maps_staged = key == rt->peer_maps_key;
+        rt->peer_maps_key = key;
     }
     g.y = (void*)q.y;
     g.plane_stride = split > 1 ? (q.plane_stride ? q.plane_stride : (uint64_t)q.m * q.n) : 0;
@@ -323,6 +339,7 @@ void t0_rt_free(t0_runtime* rt) {
         if (s->ptr) cudaFree(s->ptr);
     if (rt->d_status) cudaFree(rt->d_status);
     if (rt->d_probe) cudaFree(rt->d_probe);
+    if (rt->d_peer_maps) cudaFree(rt->d_peer_maps);
     if (rt->h_status) cudaFreeHost(rt->h_status);
     if (rt->ev_start) cudaEventDestroy(rt->ev_start);
     if (rt->ev_stop) cudaEventDestroy(rt->ev_stop);
@@ -731,6 +748,67 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* a) {
     memcpy(q.ops, a->tile_epilogue, sizeof q.ops);
     q.scale = a->scale; q.clamp_min = a->clamp_min; q.clamp_max = a->clamp_max;
     return run_gemm(rt, q);
+}
+
+int t0_gemm_launch_gather(t0_runtime* rt, const t0_gemm_args* a, const uint64_t* peer_y, uint32_t n_peers) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!a || (n_peers && !peer_y)) return fail(T0_ERR_INVALID, "null arguments");
+    if (n_peers > kMaxPeerY) return fail(T0_ERR_INVALID, "at most %u further destinations (got %u)", kMaxPeerY, n_peers);
+    if (a->transpose > T0_NN || a->epilogue > T0_EPI_BIAS_ADD_RELU_STORE_F32 || a->n_tile_epilogue > T0_TILE_MAX_EPILOGUE)
+        return fail(T0_ERR_INVALID, "bad enum value in GEMM arguments");
+    if (a->split_k > 1 || a->planes || a->out_bf16) return fail(T0_ERR_UNSUPPORTED, "a gathered output takes a plain f32 product: no split-K, no bf16 output");
+    DeviceGuard guard(rt->device);
+    GemmRequest q;
+    memset(&q, 0, sizeof q);
+    q.x = a->x; q.b = a->b; q.y = a->y; q.bias = a->bias;
+    q.m = a->m; q.n = a->n; q.k = a->k;
+    q.tile_n = a->tile_n ? a->tile_n : 256; q.split_k = 1;      // a fixed tile: the cost model may not pick split-K here
+    q.nn = a->transpose == T0_NN; q.swap_grid = a->swap_grid;
+    q.plane_stride = (uint64_t)a->m * a->n;
+    q.pair = a->pair_cta;
+    q.epilogue = a->epilogue; q.n_ops = a->n_tile_epilogue;
+    memcpy(q.ops, a->tile_epilogue, sizeof q.ops);
+    q.scale = a->scale; q.clamp_min = a->clamp_min; q.clamp_max = a->clamp_max;
+    q.n_peer_y = n_peers;
+    for (uint32_t i = 0; i < n_peers; ++i) q.peer_y[i] = peer_y[i];
+    return run_gemm(rt, q);
+}
+
+int t0_buf_ipc_export(const t0_buffer* buf, uint8_t handle[64]) {
+    if (!buf || !handle) return fail(T0_ERR_INVALID, "null argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is 64 bytes");
+    cudaIpcMemHandle_t h;
+    DeviceGuard guard(buf->rt->device);
+    cudaError_t e = cudaIpcGetMemHandle(&h, buf->dptr);
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    memcpy(handle, &h, 64);
+    return T0_OK;
+}
+
+int t0_rt_ipc_open(t0_runtime* rt, const uint8_t handle[64], uint64_t* device_ptr) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!handle || !device_ptr) return fail(T0_ERR_INVALID, "null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    DeviceGuard guard(rt->device);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+    *device_ptr = (uint64_t)(uintptr_t)p;
+    return T0_OK;
+}
+
+int t0_rt_ipc_close(t0_runtime* rt, uint64_t device_ptr) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!device_ptr) return T0_OK;
+    DeviceGuard guard(rt->device);
+    cudaError_t e = cudaStreamSynchronize(rt->stream);
+    if (e == cudaSuccess) e = cudaIpcCloseMemHandle((void*)(uintptr_t)device_ptr);
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+    return T0_OK;
 }
 
 // ------------------------------------------------------------------ seeded inputs

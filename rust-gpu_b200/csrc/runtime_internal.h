@@ -52,6 +52,8 @@ struct t0_runtime {
     int* d_status = nullptr;     // device error word written by kernels whose bounded wait expired
     int* h_status = nullptr;     // pinned mirror
     unsigned long long* d_probe = nullptr;   // {cycles, ns} of the last GEMM kernel's CTA 0
+    void* d_peer_maps = nullptr;             // gathered output: device slot for the destinations' tensor maps (made on first use)
+    std::vector<uint64_t> peer_maps_key;     // destinations and shape the slot currently describes
     Scratch scratch_a, scratch_b, scratch_planes;
     Scratch scratch_w4;          // W4A16: slab arrival counters + straddling pieces
     Scratch scratch_w;           // W4A16 general path: dequantised weights

@@ -653,6 +653,26 @@ __device__ __forceinline__ void dequant_ref_word(uint32_t word, int32_t zp, floa
     }
 }
 
+// The f32 form for a full warp: a thread's eight values are 32 bytes, so two plain 16-byte stores per thread would each
+// touch half of every 32-byte sector.  Neighbouring lanes swap one half instead (the even lane gives its upper four values
+// and takes the odd lane's lower four), after which each store instruction writes whole sectors.
+__device__ __forceinline__ void dequant_ref_word_f32_paired(uint32_t word, int32_t zp, float sc, float* out, uint64_t e0, uint32_t lane) {
+    uint32_t bits[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bits[i] = __float_as_uint(__fmul_rn((float)((int32_t)((word >> (4 * i)) & 0xFu) - zp), sc));
+    const bool odd = lane & 1;
+    uint32_t got[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) got[i] = __shfl_xor_sync(0xFFFFFFFFu, odd ? bits[i] : bits[4 + i], 1);
+    // even lane: own values 0..3 at e0, the neighbour's 0..3 at e0 + 8; odd lane: the neighbour's 4..7 at e0 - 4, own 4..7 at e0 + 4
+    float* base = out + e0;
+    uint4 v1, v2;
+    v1.x = odd ? got[0] : bits[0]; v1.y = odd ? got[1] : bits[1]; v1.z = odd ? got[2] : bits[2]; v1.w = odd ? got[3] : bits[3];
+    v2.x = odd ? bits[4] : got[0]; v2.y = odd ? bits[5] : got[1]; v2.z = odd ? bits[6] : got[2]; v2.w = odd ? bits[7] : got[3];
+    __stcs((uint4*)(odd ? base - 4 : base), v1);
+    __stcs((uint4*)(odd ? base + 4 : base + 8), v2);
+}
+
 // Reference wire format (quant_kernels.rs:53-171): byte e/2 holds element e in its low nibble for even e, one f32 scale and
 // one i32 zero point per group of 2^group_log2 elements.  One thread per packed 32-bit word (eight elements): a warp reads
 // 128 contiguous bytes and writes 1 KiB (f32) or 512 bytes (bf16) contiguous, 16 bytes per store.
@@ -667,7 +687,9 @@ __global__ void dequant_int4_ref_kernel(const uint8_t* __restrict__ packed, cons
     if (vec) {
         // four independent words per round: all twelve loads are issued before the first is used
         const uint64_t full = total / 8;
-        for (; u + 3 * stride < full; u += 4 * stride) {
+        const uint32_t lane = threadIdx.x & 31;
+        // (the condition is the same for all lanes of a warp: the f32 stores exchange halves between neighbouring lanes)
+        for (; u - lane + 31 + 3 * stride < full; u += 4 * stride) {
             uint32_t word[4];
             int32_t zp[4];
             float sc[4];
@@ -679,7 +701,10 @@ __global__ void dequant_int4_ref_kernel(const uint8_t* __restrict__ packed, cons
                 sc[j] = __ldg(scales + grp);
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) dequant_ref_word(word[j], zp[j], sc[j], out, (u + j * stride) * 8, out_bf16);
+            for (int j = 0; j < 4; ++j) {
+                if (out_bf16) dequant_ref_word(word[j], zp[j], sc[j], out, (u + j * stride) * 8, 1u);
+                else dequant_ref_word_f32_paired(word[j], zp[j], sc[j], (float*)out, (u + j * stride) * 8, lane);
+            }
         }
     }
     for (; u < units; u += stride) {

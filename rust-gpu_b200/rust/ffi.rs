@@ -260,6 +260,10 @@ extern "C" {
     pub fn t0_rt_timer_stop(rt: *mut t0_runtime, ms: *mut f32) -> c_int;
     pub fn t0_gemm_launch(rt: *mut t0_runtime, args: *const t0_gemm_args) -> c_int;
     pub fn t0_gemm_launch_batch(rt: *mut t0_runtime, args: *const t0_gemm_args, count: usize) -> c_int;
+    pub fn t0_gemm_launch_gather(rt: *mut t0_runtime, args: *const t0_gemm_args, peer_y: *const u64, n_peers: u32) -> c_int;
+    pub fn t0_buf_ipc_export(buf: *const t0_buffer, handle: *mut u8) -> c_int;
+    pub fn t0_rt_ipc_open(rt: *mut t0_runtime, handle: *const u8, device_ptr: *mut u64) -> c_int;
+    pub fn t0_rt_ipc_close(rt: *mut t0_runtime, device_ptr: u64) -> c_int;
     pub fn t0_gemm_launch_host_batch(rt: *mut t0_runtime, args: *const t0_gemm_args, count: usize) -> c_int;
     pub fn t0_gemm_launch_host(rt: *mut t0_runtime, args: *const t0_gemm_args) -> c_int;
     pub fn t0_auto_schedule_tile_costs(m: u32, n: u32, k: u32, out: *mut t0_tile_cost, cap: c_int) -> c_int;
@@ -326,6 +330,7 @@ extern "C" {
     pub fn t0_mg_runtime(mg: *mut t0_mg, rank: c_int) -> *mut t0_runtime;
     pub fn t0_mg_synchronize(mg: *mut t0_mg) -> c_int;
     pub fn t0_mg_gemm_sharded(mg: *mut t0_mg, x: *const u64, b_slice: *const u64, y_slice: *const u64, m: u32, n: u32, k: u32, tile_n: u32, pair_cta: c_int) -> c_int;
+    pub fn t0_mg_gemm_sharded_gathered(mg: *mut t0_mg, x: *const u64, b_slice: *const u64, c_gathered: *const u64, m: u32, n: u32, k: u32) -> c_int;
     pub fn t0_mg_gemm_sharded_host(mg: *mut t0_mg, x_host: *const c_void, wt_host: *const c_void, y_host: *mut c_void, m: u32, n: u32, k: u32) -> c_int;
     pub fn t0_mg_all_gather_c(mg: *mut t0_mg, c_gathered: *const u64, m: u32, n: u32) -> c_int;
     pub fn t0_fill_uniform_bf16(rt: *mut t0_runtime, dst: u64, n: u64, seed: u64, first_index: u64) -> c_int;

@@ -108,6 +108,73 @@ def test_multi_device_sharded_gemm_and_gather(t0, oracle):
 
 
 @pytest.mark.gpu
+def test_gather_launch_with_extra_destinations_on_one_gpu(t0, oracle):
+    # the gathered-output launch writes the same product to args.y and to every further destination; on one GPU the further
+    # destinations are ordinary buffers of the same device.  Several tiles per CTA, ragged M (the copies clip rows >= M),
+    # both kernels, and the shapes the entry must refuse.
+    rt = t0.GpuRuntime(0)
+    try:
+        for (M, N, K, pair) in [(300, 512, 256, 2), (1000, 1024, 128, 1), (4096 + 40, 2048, 64, 1)]:
+            a = oracle.fill_uniform_bf16(M * K, 1 + M)
+            b = oracle.fill_uniform_bf16(N * K, 2 + N)
+            xa, xb = rt.upload(a), rt.upload(b)
+            dests = [rt.alloc(M * N * 4 + 4096) for _ in range(4)]
+            for d in dests:
+                d.write(np.full(M * N + 1024, -777.0, np.float32))
+            args = rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), dests[0].gpu_addr(), M, N, K, pair_cta=pair)
+            rt.gemm_gather(args, [d.gpu_addr() for d in dests[1:]])
+            rt.synchronize()
+            ref = oracle.gemm_nt(a, b, M, K, N)
+            first = dests[0].read((M * N + 1024) * 4, np.float32)
+            assert np.abs(first[:M * N].reshape(M, N) - ref).max() <= 5e-3 * np.sqrt(max(K, 256) / 256)
+            assert np.all(first[M * N:] == -777.0), "wrote past the matrix"
+            for d in dests[1:]:
+                assert np.array_equal(d.read((M * N + 1024) * 4, np.float32), first)
+            for buf in [xa, xb] + dests:
+                buf.free()
+        xa, xb, y = rt.alloc(64 * 64 * 2), rt.alloc(80 * 64 * 2), rt.alloc(64 * 80 * 4)
+        with pytest.raises(t0.T0Error):          # N % 32 != 0: some chunks would not go through the TMA store
+            rt.gemm_gather(rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), 64, 80, 64), [y.gpu_addr()])
+        with pytest.raises(t0.T0Error):          # split-K
+            rt.gemm_gather(rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), y.gpu_addr(), 64, 64, 64, split_k=2), [y.gpu_addr()])
+    finally:
+        rt.close()
+
+
+@pytest.mark.gpu
+def test_multi_device_gemm_with_gather_in_the_epilogue(t0, oracle):
+    # GEMM and all-gather in one kernel per GPU: afterwards every GPU holds all of C in C_g[g][M][N/g], equal bit for bit to
+    # what the GEMM + NCCL all-gather pair leaves
+    import torch
+    g = min(torch.cuda.device_count(), 4)
+    if g < 2:
+        pytest.skip("needs at least two GPUs")
+    M, N, K = 1000, 512 * g, 512
+    mg = t0.MultiGpu(g)
+    a = oracle.fill_uniform_bf16(M * K, 42 + M)
+    b = oracle.fill_uniform_bf16(N * K, 137 + N)
+    cnt = N // g
+    xs, bs, cs, cn = [], [], [], []
+    for r in range(g):
+        rt = mg.runtime(r)
+        xs.append(rt.upload(a)); bs.append(rt.upload(b.reshape(N, K)[r * cnt:(r + 1) * cnt]))
+        cs.append(rt.alloc_zero(M * N * 4)); cn.append(rt.alloc_zero(M * N * 4))
+    mg.gemm_sharded_gathered([x.gpu_addr() for x in xs], [x.gpu_addr() for x in bs], [c.gpu_addr() for c in cs], M, N, K)
+    mg.synchronize()
+    mg.gemm_sharded([x.gpu_addr() for x in xs], [x.gpu_addr() for x in bs], [c.gpu_addr() + r * M * cnt * 4 for r, c in enumerate(cn)], M, N, K,
+                    tile_n=256)
+    mg.all_gather_c([c.gpu_addr() for c in cn], M, N)
+    mg.synchronize()
+    full = oracle.gemm_nt(a, b, M, K, N)
+    for r in range(g):
+        got = cs[r].read(M * N * 4, np.float32)
+        rebuilt = np.concatenate(list(got.reshape(g, M, cnt)), axis=1)
+        assert np.abs(rebuilt - full).max() <= 5e-3 * np.sqrt(K / 256)
+        assert np.array_equal(got, cn[r].read(M * N * 4, np.float32)), f"GPU {r}: one-kernel gather differs from GEMM + all-gather"
+    mg.free()
+
+
+@pytest.mark.gpu
 def test_multi_device_host_operands_upload_a_once(t0, oracle):
     # host operands: every GPU uploads 1/g of A, the GPUs complete their copies over NVLink, each returns its column block
     # of C into the caller's row-major matrix; ragged M (rows not a multiple of g) included
