@@ -165,8 +165,12 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
                 ptx::tma_store_3d(map_y, sb, (int32_t)col0, (int32_t)row_base, (int32_t)split);
                 // gathered output: the same block to the other GPUs' buffers (plain TMA stores to peer memory over NVLink),
                 // in the same bulk group, so the block is reused only after all of them have read it
-                for (uint32_t i = 0; i < p.n_peers; ++i)
+                for (uint32_t i = 0; i < p.n_peers; ++i) {
+                    // the maps were written to global memory by a copy before this launch: before the first use, order this
+                    // thread's tensor-map reads after that write (the slot is rewritten when the destinations change)
+                    if (n_stores == 0) ptx::fence_proxy_tensormap_acquire(p.peer_maps + i);
                     ptx::tma_store_3d(p.peer_maps + i, sb, (int32_t)col0, (int32_t)row_base, (int32_t)split);
+                }
                 ptx::bulk_commit_group();
             }
             ++n_stores;
