@@ -535,10 +535,10 @@ def run_lib_ab(t0, rt, torch):
     count, warm-up and CUDA-event timing.  Reported per arm: TFLOP/s, the SM clock (the repo's kernel stamps cycles and
     nanoseconds itself; the library arm uses the NVML median) and time x clock = SM cycles per launch."""
     out = []
-    for size in (2048, 4096, 8192):
-        M = N = K = size
-        n_sets = max(2, min(4, -(-3 * 126 * 2 ** 20 // (M * K * 2 + N * K * 2 + M * N * 4))))
-        steps = 200 if size <= 4096 else 40
+    for (M, N, K) in ((128, 4096, 4096), (64, 4096, 16384), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192)):
+        size = f"{M}x{N}x{K}" if not (M == N == K) else M
+        n_sets = max(2, min(12, -(-3 * 126 * 2 ** 20 // (M * K * 2 + N * K * 2 + M * N * 4))))
+        steps = 200 if M * N * K <= 4096 ** 3 else 40
         sets = []
         for s in range(n_sets):
             xa, xb, y = rt.alloc(M * K * 2), rt.alloc(N * K * 2), rt.alloc(M * N * 4)

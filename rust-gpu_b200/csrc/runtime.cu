@@ -432,6 +432,7 @@ int t0_rt_last_kernel_clock(t0_runtime* rt, double* sm_mhz, double* kernel_us) {
             auto us = [&](int i) { return s[i] ? (double)(s[i] - s[0]) * 1e-3 : -1.0; };
             fprintf(stderr, "[gemm trace] prologue %.2f  dep-wait %.2f  first-load %.2f  first-tile %.2f  last-store %.2f  exit %.2f", us(2), us(1), us(3),
                     us(4), us(5), us(6));
+            if (s[7]) fprintf(stderr, "  aux %.2f", us(7));
             if (k + 1 < order.size()) fprintf(stderr, "  | next entry %+.2f after exit", ((double)t[order[k + 1] * 8] - (double)s[6]) * 1e-3);
             fprintf(stderr, "\n");
         }
