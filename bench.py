@@ -175,7 +175,7 @@ def run_hbm_workload(args, name, rt=None, brief=False):
     xa = alloc(M * K * 2)
     xa.write(a_host)
     # the problems of one batched launch run concurrently, so consecutive steps write distinct outputs
-    n_out = 32 if w4 else 1
+    n_out = 32
     ys = [alloc(M * N * 4) for _ in range(n_out)]
     y = ys[(steps - 1) % n_out]          # the output of the last step, checked against the oracle below
     sets = []
@@ -211,9 +211,16 @@ def run_hbm_workload(args, name, rt=None, brief=False):
         cfg = t0.auto_select(M, K, N)
         sk = w.get("split_k", cfg.split())
         kw = dict(tile_n=cfg.tile_n, split_k=sk, swap_grid=bool(cfg.swap_grid), pair_cta=2)
-        calls = [rt.gemm_args(xa.gpu_addr(), sets[i % n_sets][0].gpu_addr(), y.gpu_addr(), M, N, K, **kw) for i in range(steps)]
-        submit = rt.gemm_batch
-        kernel = cfg.copy(split_k=sk).name()
+        # grouped: tile and split left to the library, which chooses them for the group (32 skinny problems fill the GPU
+        # without split-K); one problem per launch: the configuration auto_select gives the single problem (split-K 4)
+        calls = [rt.gemm_args(xa.gpu_addr(), sets[i % n_sets][0].gpu_addr(), ys[i % n_out].gpu_addr(), M, N, K) for i in range(steps)]
+        calls_single = [rt.gemm_args(xa.gpu_addr(), sets[i % n_sets][0].gpu_addr(), ys[i % n_out].gpu_addr(), M, N, K, **kw) for i in range(steps)]
+
+        def submit(cs):
+            # 32 independent problems per launch (distinct weights and outputs): t0_gemm_launch_grouped
+            for i in range(0, len(cs), 32):
+                rt.gemm_grouped(cs[i:i + 32])
+        kernel = "gemm_bf16_tcgen05_kernel<128> over the tiles of 32 problems per launch (no split-K needed); one problem per launch: " + cfg.copy(split_k=sk).name()
     submit(calls[:warmup])
     rt.synchronize()
     sampler = ClockSampler(0)
@@ -228,6 +235,16 @@ def run_hbm_workload(args, name, rt=None, brief=False):
     launches = (rt.launch_count() - before) // 3
     per_launch_s = best * 1e-3 / steps
     gbs = alg_bytes / per_launch_s / 1e9
+    one_per_launch = None
+    if not w4:
+        # the same problems one launch each (t0_gemm_launch_batch), for comparison
+        single = float("inf")
+        for _ in range(3):
+            rt.timer_start()
+            rt.gemm_batch(calls_single)
+            single = min(single, rt.timer_stop())
+        one_per_launch = {"us_per_problem": single * 1e3 / steps, "value": alg_bytes / (single * 1e-3 / steps) / 1e9, "unit": "GB/s",
+                          "frac": alg_bytes / (single * 1e-3 / steps) / 1e9 / measured_peaks()["hbm_gbs"]}
 
     # parity of the last step against the oracle (full result: these shapes are small)
     s_idx = (steps - 1) % n_sets
@@ -255,6 +272,8 @@ def run_hbm_workload(args, name, rt=None, brief=False):
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
                          "traffic": ncu_traffic(name), "peak_source": f"{peaks['source']} (copy bandwidth)"},
             "clocks": clocks, "gpu_launches": int(launches), "parity": {"max_abs_err": err, "tol": tol}}
+    if one_per_launch:
+        line["one_problem_per_launch"] = one_per_launch
     if w4 and M > 16:
         # above the ridge point both roofs apply: also the tensor-bound fraction
         line["roofline"]["tensor_frac"] = tflops / peaks["bf16_tflops"]
@@ -959,6 +978,8 @@ def main():
                                       "steps": ln["steps"], "kernel": ln["config"]["kernel"], "bytes": ln["config"]["bytes"], "tflops": ln["config"]["tflops"],
                                       "roofline": {k: ln["roofline"][k] for k in ("bound", "frac", "peak", "traffic", "tensor_frac") if k in ln["roofline"]},
                                       "gpu_launches": ln["gpu_launches"], "parity": ln["parity"]})
+                    if "one_problem_per_launch" in ln:
+                        sec_lines[-1]["one_problem_per_launch"] = ln["one_problem_per_launch"]
                 else:
                     sec_lines.append(run_square_brief(t0, rt, sname))
             for sname in AUX_WORKLOADS:

@@ -299,6 +299,18 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* args);
 /* `count` launches from an array, submitted back to back from native code (the batch form of the above; the reference's
  * timing loops submit N dispatches and wait once, src/t0/tile_ir.rs:5704-5717). */
 int t0_gemm_launch_batch(t0_runtime* rt, const t0_gemm_args* args, size_t count);
+/* Several independent GEMMs in ONE launch (the reference's nearest item is DispatchQueue::submit / flush, src/kfd/aql.rs, which
+ * batches independent dispatches behind one doorbell).  Where all the problems have one shape and one configuration and that
+ * configuration is the one-launch split-K (the skinny shapes: the CTAs of a tile form a cluster), the clusters of a single
+ * persistent launch walk the tiles of all the problems (up to 32 per launch): launch, prologue and drain are paid once and
+ * the exchange of one tile overlaps the main loop of the next.  With tile_n and split_k given, every y is the same, bit for
+ * bit, as from t0_gemm_launch with those values.  With both left at 0 the split is chosen for the group, not for one
+ * problem: several skinny problems fill the GPU with fewer splits (often none, which then runs the plain kernel over all the
+ * problems' tiles), so y agrees with t0_gemm_launch to rounding (another order of the fp32 sums along K), not bit for bit.
+ * The problems run at the same time, so no y may overlap an operand or the y of another problem: that is checked
+ * (T0_ERR_INVALID).  Other shapes (NN layout, CTA-pair tiles), or problems that differ, are launched back to back as by
+ * t0_gemm_launch_batch. */
+int t0_gemm_launch_grouped(t0_runtime* rt, const t0_gemm_args* args, size_t count);
 /* GEMM with a gathered output (no counterpart in the reference, which is single-GPU; it is the compute step and the
  * all-gather of the sharded GEMM in one kernel).  The product goes to args->y and, in the same epilogue, to n_peers further
  * f32 [M,N] buffers (at most 7), normally slot `rank` of the other GPUs' rank-major result C_g[g][M][N/g]: the epilogue

@@ -667,6 +667,12 @@ class GpuRuntime:
         arr = (GemmArgs * len(args_list))(*args_list)
         _check(lib().t0_gemm_launch_batch(self._h, arr, len(args_list)))
 
+    def gemm_grouped(self, args_list: list[GemmArgs]) -> None:
+        """``t0_gemm_launch_grouped``: independent problems of one shape in one launch where the shape's configuration is the
+        one-launch split-K; otherwise the same as ``gemm_batch``."""
+        arr = (GemmArgs * len(args_list))(*args_list)
+        _check(lib().t0_gemm_launch_grouped(self._h, arr, len(args_list)))
+
     def gemm_gather(self, args: GemmArgs, peer_y: list[int]) -> None:
         """``t0_gemm_launch_gather``: the product goes to ``args.y`` and, in the same epilogue, to every address of
         ``peer_y`` (other GPUs' memory mapped into this process)."""
@@ -963,6 +969,7 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_rt_synchronize", i32, vp)
     sig("t0_rt_wait_idle", i32, vp)
     sig("t0_rt_set_wait_limit_ns", i32, vp, u64)
+    sig("t0_gemm_launch_grouped", i32, vp, C.POINTER(GemmArgs), sz)
     sig("t0_gemm_launch_gather", i32, vp, C.POINTER(GemmArgs), C.POINTER(C.c_uint64), u32)
     sig("t0_buf_ipc_export", i32, vp, C.POINTER(C.c_uint8))
     sig("t0_rt_ipc_open", i32, vp, C.POINTER(C.c_uint8), C.POINTER(C.c_uint64))

@@ -33,11 +33,16 @@ struct KParams {
     uint32_t out_bf16, epilogue, n_ops;
     uint32_t tma_store;          // full f32 chunks leave through the output tensor map
     uint32_t drop_load;          // self-test of the failure path: the producer of CTA 0 leaves out its first operand load
+    uint32_t n_problems;         // split-K cluster kernel, grouped launch: problems of one shape in this launch (0 or 1 = a single problem)
     uint32_t n_peers;            // gathered output: every TMA-stored chunk also goes to this many other buffers (other GPUs' memory)
     const CUtensorMap* peer_maps; // their output tensor maps, in global memory (written by the host before the launch)
     float scale, clamp_min, clamp_max;
     uint8_t ops[T0_TILE_MAX_EPILOGUE];
 };
+
+// Grouped launch (several problems of one shape in one launch): the problems' tensor maps and outputs ride in the kernel
+// parameters; the kernels that are not grouped take the empty record.
+struct NoGroup { uint32_t unused; };
 
 struct WorkItem { uint32_t m_blk, n_blk, split; };
 
@@ -124,7 +129,9 @@ constexpr uint32_t kEpiStageBytes = 4096;   // per epilogue warp: one 32 x 32 f3
 // an odd number of full chunks, a single chunk, or rows the copy would clip entirely.  The caller waits for its stores
 // (ptx::bulk_wait_group_all by lane 0) before shared memory goes away.
 __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r)[32], uint32_t row_base, uint32_t lane, uint32_t col0,
-                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage, uint32_t& n_stores, const CUtensorMap* map_y = nullptr) {
+                                            uint32_t split, bool vec32, bool vec16, uint8_t* stage, uint32_t& n_stores, const CUtensorMap* map_y = nullptr,
+                                            void* y_base = nullptr) {
+    void* const y_out = y_base ? y_base : p.y;       // a grouped launch names the problem's output
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -183,7 +190,7 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
             const uint32_t rr = i * 4 + (lane >> 3), row = row_base + rr;
             float4 q;
             asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(q.x), "=f"(q.y), "=f"(q.z), "=f"(q.w) : "r"(sb + (rr * 8 + (slot ^ (rr & 7))) * 16) : "memory");
-            if (row < p.M) *(float4*)((float*)p.y + plane + (size_t)row * p.N + col0 + 4 * slot) = q;
+            if (row < p.M) *(float4*)((float*)y_out + plane + (size_t)row * p.N + col0 + 4 * slot) = q;
         }
         __syncwarp();
         return;
@@ -206,7 +213,7 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
         for (uint32_t i = 0; i < 4; ++i) {
             const uint32_t rr = i * 8 + (lane >> 2), row = row_base + rr;
             const uint4 q = s4[rr * 4 + (slot ^ ((rr >> 1) & 3))];
-            if (row < p.M) *(uint4*)((__nv_bfloat16*)p.y + plane + (size_t)row * p.N + col0 + 8 * slot) = q;
+            if (row < p.M) *(uint4*)((__nv_bfloat16*)y_out + plane + (size_t)row * p.N + col0 + 8 * slot) = q;
         }
         __syncwarp();
         return;
@@ -215,11 +222,11 @@ __device__ __forceinline__ void store_chunk(const KParams& p, const uint32_t (&r
     if (row >= p.M) return;
     const size_t off = plane + (size_t)row * p.N + col0;
     if (!p.out_bf16) {
-        float* dst = (float*)p.y + off;
+        float* dst = (float*)y_out + off;
         for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) dst[j] = v[j];
     } else {
-        __nv_bfloat16* dst = (__nv_bfloat16*)p.y + off;
+        __nv_bfloat16* dst = (__nv_bfloat16*)y_out + off;
         for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) dst[j] = __float2bfloat16_rn(v[j]);
     }

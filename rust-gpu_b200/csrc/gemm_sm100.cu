@@ -16,6 +16,7 @@
 // error word the host turns into an error (no trap, no unbounded spin).
 #include "kernels.h"
 #include "ptx_sm100.cuh"
+#include <type_traits>
 #include "gemm_common.cuh"
 
 
@@ -28,10 +29,18 @@ constexpr uint32_t kThreads = 192;
 
 __host__ __device__ constexpr uint32_t stages_for(uint32_t bn) { return bn == 256 ? 4 : bn == 128 ? 6 : 8; }
 
-template <uint32_t BN, bool B_MN>
+// Grouped launch: operand and output maps and the output addresses of up to kMaxGroupedGemms problems of one shape (12.5 KB
+// of kernel parameters).
+struct GroupOperands3 {
+    CUtensorMap maps[3 * kMaxGroupedGemms];     // A, B, Y of problem i at 3i, 3i + 1, 3i + 2
+    void* y[kMaxGroupedGemms];
+};
+
+template <uint32_t BN, bool B_MN, bool kGrouped = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const __grid_constant__ CUtensorMap map_y, const KParams p) {
+                         const __grid_constant__ CUtensorMap map_y, const KParams p,
+                         const __grid_constant__ std::conditional_t<kGrouped, GroupOperands3, NoGroup> group) {
     constexpr uint32_t kStages = stages_for(BN);
     constexpr uint32_t kBStageBytes = BN * BK * 2;
     constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;
@@ -54,7 +63,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
-    const uint32_t total_work = p.tiles_m * p.tiles_n * p.split_k;
+    const uint32_t work_per_problem = p.tiles_m * p.tiles_n * p.split_k;
+    uint32_t total_work = work_per_problem;                 // a grouped launch walks the tiles of all its problems, problem-major
+    if constexpr (kGrouped) total_work = work_per_problem * p.n_problems;
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -92,7 +103,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; ok && w < total_work; w += gridDim.x) {
-                const WorkItem wi = decode_work(w, p);
+                uint32_t prob = 0, item = w;
+                if constexpr (kGrouped) { prob = w / work_per_problem; item = w - prob * work_per_problem; }
+                const WorkItem wi = decode_work(item, p);
+                const CUtensorMap* ma = &map_a;
+                const CUtensorMap* mb = &map_b;
+                if constexpr (kGrouped) { ma = &group.maps[3 * prob]; mb = &group.maps[3 * prob + 1]; }
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.wait_limit_ns)) {
                         atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(w & 0xFFFFFF));
@@ -103,16 +119,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     // self-test of the failure path: this stage is never filled, so the issuer's bounded wait must run out
                     if (p.drop_load && blockIdx.x == 0 && w == 0 && kb == 0) { if (++stage == kStages) { stage = 0; phase ^= 1; } continue; }
                     ptx::mbar_arrive_expect_tx(fb, kStageBytes);
-                    ptx::tma_load_3d(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
+                    ptx::tma_load_3d(ptx::smem_u32(a_tiles + stage * kAStageBytes), ma, fb,
                                      (int32_t)(kb * BK), (int32_t)(wi.m_blk * BM), (int32_t)wi.split);
                     if constexpr (!B_MN) {
-                        ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b, fb,
+                        ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes), mb, fb,
                                          (int32_t)(kb * BK), (int32_t)(wi.n_blk * BN), (int32_t)wi.split);
                     } else {
                         // B[K,N]: one 64(k) x 64(n) box per 64 columns; each box is an [k][128 B] block
 #pragma unroll
                         for (uint32_t j = 0; j < BN / 64; ++j)
-                            ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes + j * (BK * 128)), &map_b, fb,
+                            ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes + j * (BK * 128)), mb, fb,
                                              (int32_t)(wi.n_blk * BN + j * 64), (int32_t)(kb * BK), (int32_t)wi.split);
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -159,11 +175,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const uint32_t quarter = warp & 3;   // tensor-memory lanes 32*quarter .. +31 belong to this warp
-        const bool vec32 = (p.N % 4 == 0) && (((uintptr_t)p.y & 15) == 0);
-        const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)p.y & 15) == 0);
         uint32_t iter = 0, n_stores = 0;     // n_stores: this warp's committed TMA stores, see store_chunk
         for (uint32_t w = blockIdx.x; w < total_work; w += gridDim.x, ++iter) {
-            const WorkItem wi = decode_work(w, p);
+            uint32_t prob = 0, item = w;
+            if constexpr (kGrouped) { prob = w / work_per_problem; item = w - prob * work_per_problem; }
+            const WorkItem wi = decode_work(item, p);
+            void* y_out = p.y;
+            const CUtensorMap* my = &map_y;
+            if constexpr (kGrouped) { y_out = group.y[prob]; my = &group.maps[3 * prob + 2]; }
+            const bool vec32 = (p.N % 4 == 0) && (((uintptr_t)y_out & 15) == 0);
+            const bool vec16 = (p.N % 8 == 0) && (((uintptr_t)y_out & 15) == 0);
             const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
             if (!ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag, p.wait_limit_ns)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(w & 0xFFFFFF));
@@ -179,7 +200,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                 ptx::tmem_ld_32x32b_x32(tmem_base + ((quarter * 32) << 16) + buf * BN + c * 32, r);
                 ptx::tmem_ld_wait();
                 store_chunk(p, r, row_base, lane, col0, wi.split, vec32, vec16, epi_stage + quarter * 2 * kEpiStageBytes, n_stores,
-                            p.tma_store ? &map_y : nullptr);
+                            p.tma_store ? my : nullptr, y_out);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -205,9 +226,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
 // ------------------------------------------------------------------ host side
 
-template <uint32_t BN, bool B_MN>
-int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const KParams& p, uint32_t grid, cudaStream_t stream) {
-    auto kern = gemm_bf16_tcgen05_kernel<BN, B_MN>;
+template <uint32_t BN, bool B_MN, bool kGrouped = false>
+int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& my, const KParams& p, uint32_t grid, cudaStream_t stream,
+                    const std::conditional_t<kGrouped, GroupOperands3, NoGroup>& group = {}) {
+    auto kern = gemm_bf16_tcgen05_kernel<BN, B_MN, kGrouped>;
     const uint32_t smem = gemm_smem_bytes(BN);
     static bool attr_set[64] = {};   // per instantiation, per device
     int dev = 0;
@@ -217,7 +239,7 @@ int launch_instance(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensor
         if (e != cudaSuccess) return fail(T0_ERR_CUDA, "cudaFuncSetAttribute(smem=%u): %s", smem, cudaGetErrorString(e));
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
-    cudaError_t e = launch_pdl(kern, grid, kThreads, smem, stream, ma, mb, my, p);
+    cudaError_t e = launch_pdl(kern, grid, kThreads, smem, stream, ma, mb, my, p, group);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
 }
@@ -291,6 +313,63 @@ int launch_gemm_sm100(const GemmLaunch& g, cudaStream_t stream) {
         case 128: return launch_instance<128, false>(ma, mb, my, p, grid, stream);
         default: return launch_instance<256, false>(ma, mb, my, p, grid, stream);
     }
+}
+
+// Several problems of one shape, no split-K, NT layout, 64- or 128-wide tiles, in one launch: the persistent CTAs walk the
+// tiles of all the problems (see kernels.h).  Every problem must qualify for the TMA path (16-byte aligned operands, K % 8).
+int launch_gemm_sm100_grouped(const GemmLaunch* gs, uint32_t count, cudaStream_t stream) {
+    if (!gs || count == 0) return T0_OK;
+    if (count > kMaxGroupedGemms) return fail(T0_ERR_INVALID, "at most %u problems per grouped launch (got %u)", kMaxGroupedGemms, count);
+    const GemmLaunch& g0 = gs[0];
+    if (g0.m == 0 || g0.n == 0) return T0_OK;
+    const uint32_t bn = snap_tile_n(g0.tile_n);
+    if (g0.nn || (g0.split_k > 1) || (bn != 64 && bn != 128) || g0.k == 0 || g0.k % 8 || g0.n_peer_y)
+        return fail(T0_ERR_UNSUPPORTED, "grouped launch: NT layout, no split-K, tile width 64 or 128, K a positive multiple of 8");
+    const uint32_t ldx = g0.ldx ? g0.ldx : g0.k, ldb = g0.ldb ? g0.ldb : g0.k;
+    if ((ldx % 8) || (ldb % 8)) return fail(T0_ERR_UNSUPPORTED, "grouped launch: row strides must be multiples of 8");
+    KParams p;
+    memset(&p, 0, sizeof p);
+    p.wait_limit_ns = g0.wait_limit_ns ? g0.wait_limit_ns : ptx::kWaitLimitNs;
+    p.y = g0.y; p.bias = g0.bias; p.status = g0.status; p.probe = g0.probe;
+    p.M = g0.m; p.N = g0.n; p.K = g0.k;
+    p.tiles_m = ceil_div(g0.m, BM); p.tiles_n = ceil_div(g0.n, bn); p.split_k = 1;
+    p.kb_per_split = ceil_div(g0.k, BK);
+    p.swap_grid = g0.swap_grid ? 1 : 0; p.raster_group = 8;
+    p.out_bf16 = g0.out_bf16 ? 1 : 0; p.epilogue = g0.epilogue; p.n_ops = g0.n_ops;
+    p.scale = g0.scale; p.clamp_min = g0.clamp_min; p.clamp_max = g0.clamp_max;
+    memcpy(p.ops, g0.ops, sizeof p.ops);
+    p.n_problems = count;
+    static const bool no_tma_store = getenv("T0_NO_TMA_STORE") != nullptr;
+    bool tma_store = !no_tma_store && !g0.out_bf16 && g0.n % 4 == 0;
+    for (uint32_t i = 0; i < count; ++i) tma_store = tma_store && (((uintptr_t)gs[i].y & 15) == 0);
+    p.tma_store = tma_store ? 1 : 0;
+    static GroupOperands3 group;         // 12.5 KB: kept off the stack, filled under the lock, copied by the launch
+    static std::mutex group_mu;
+    std::lock_guard<std::mutex> lock(group_mu);
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemmLaunch& g = gs[i];
+        if (g.m != g0.m || g.n != g0.n || g.k != g0.k || g.ldx != g0.ldx || g.ldb != g0.ldb || g.tile_n != g0.tile_n || g.split_k != g0.split_k ||
+            g.nn != g0.nn || g.out_bf16 != g0.out_bf16 || g.swap_grid != g0.swap_grid || g.epilogue != g0.epilogue || g.n_ops != g0.n_ops ||
+            memcmp(g.ops, g0.ops, sizeof g.ops) != 0 || g.scale != g0.scale || g.clamp_min != g0.clamp_min || g.clamp_max != g0.clamp_max ||
+            g.bias != g0.bias)
+            return fail(T0_ERR_INVALID, "grouped launch: problem %u differs from problem 0 in shape or configuration", i);
+        if (!g.x || !g.b || !g.y) return fail(T0_ERR_INVALID, "grouped launch: null pointer in problem %u", i);
+        if (((uintptr_t)g.x & 15) || ((uintptr_t)g.b & 15)) return fail(T0_ERR_UNSUPPORTED, "grouped launch: operands of problem %u are not 16-byte aligned", i);
+        int rc = make_map_kmajor(&group.maps[3 * i], g.x, g.m, ldx, g.k, 1, BM);
+        if (rc == T0_OK) rc = make_map_kmajor(&group.maps[3 * i + 1], g.b, g.n, ldb, g.k, 1, bn);
+        if (rc != T0_OK) return rc;
+        group.maps[3 * i + 2] = group.maps[3 * i];          // a valid map either way; only read when p.tma_store is set
+        if (tma_store) {
+            rc = make_map_out_f32(&group.maps[3 * i + 2], g.y, g.m, g.n, 1, 0);
+            if (rc != T0_OK) return rc;
+        }
+        group.y[i] = g.y;
+    }
+    const uint64_t total = (uint64_t)p.tiles_m * p.tiles_n * count;
+    if (total > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(total, g0.n_sms ? g0.n_sms : 148);
+    return bn == 128 ? launch_instance<128, false, true>(group.maps[0], group.maps[1], group.maps[2], p, grid, stream, group)
+                     : launch_instance<64, false, true>(group.maps[0], group.maps[1], group.maps[2], p, grid, stream, group);
 }
 
 }  // namespace t0

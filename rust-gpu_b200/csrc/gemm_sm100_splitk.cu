@@ -19,6 +19,7 @@
 // Every wait is bounded; a wait that runs out raises the abort flag and writes the status word the host reads.
 #include "kernels.h"
 #include "ptx_sm100.cuh"
+#include <type_traits>
 #include "gemm_common.cuh"
 
 namespace t0 {
@@ -82,9 +83,17 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
     return v;
 }
 
-template <uint32_t BN>
+// Grouped launch: the tensor maps and outputs of up to kMaxGroupedGemms problems of one shape ride in the kernel parameters
+// (8.4 KB; parameters may be 32 KB).  The single-problem kernel takes an empty record instead.
+struct GroupOperands {
+    CUtensorMap maps[2 * kMaxGroupedGemms];     // A, B of problem i at 2i, 2i + 1
+    void* y[kMaxGroupedGemms];
+};
+
+template <uint32_t BN, bool kGrouped>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p) {
+gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const KParams p,
+                                const __grid_constant__ std::conditional_t<kGrouped, GroupOperands, NoGroup> group) {
     const uint32_t kStages = p.sk_stages;                  // 4 (6) with a parking area of its own, 7 (9) when the accumulator is parked over the ring
     constexpr uint32_t kBStageBytes = BN * BK * 2;
     constexpr uint32_t kStageBytes = kAStageBytes + kBStageBytes;
@@ -111,7 +120,9 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t split = ptx::cluster_ctarank();          // this CTA's part of K
-    const uint32_t n_tiles = p.tiles_m * p.tiles_n;
+    const uint32_t n_tiles = p.tiles_m * p.tiles_n;                                   // of one problem
+    uint32_t n_items = n_tiles;                                                        // tiles of all the problems of the launch, problem-major
+    if constexpr (kGrouped) n_items = n_tiles * p.n_problems;
 
     if (threadIdx.x == 0) {
         trace_stamp(p, 0);
@@ -152,8 +163,13 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (uint32_t w = cluster_id_x(); ok && w < n_tiles; w += n_clusters_x()) {
-                const WorkItem wi = decode_work(w * p.split_k, p);     // (the tile list carries no split: the rank is the split)
+            for (uint32_t w = cluster_id_x(); ok && w < n_items; w += n_clusters_x()) {
+                uint32_t prob = 0, tile = w;
+                if constexpr (kGrouped) { prob = w / n_tiles; tile = w - prob * n_tiles; }
+                const WorkItem wi = decode_work(tile * p.split_k, p);  // (the tile list carries no split: the rank is the split)
+                const CUtensorMap* ma = &map_a;
+                const CUtensorMap* mb = &map_b;
+                if constexpr (kGrouped) { ma = &group.maps[2 * prob]; mb = &group.maps[2 * prob + 1]; }
                 for (uint32_t kb = 0; kb < p.kb_per_split; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_u32(&empty_bar[stage]), phase ^ 1, abort_flag, p.wait_limit_ns)) {
                         atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(w & 0xFFFFFF));
@@ -162,9 +178,9 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
                     }
                     const uint32_t fb = ptx::smem_u32(&full_bar[stage]);
                     ptx::mbar_arrive_expect_tx(fb, kStageBytes);
-                    ptx::tma_load_3d(ptx::smem_u32(a_tiles + stage * kAStageBytes), &map_a, fb,
+                    ptx::tma_load_3d(ptx::smem_u32(a_tiles + stage * kAStageBytes), ma, fb,
                                      (int32_t)(kb * BK), (int32_t)(wi.m_blk * BM), (int32_t)split);
-                    ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes), &map_b, fb,
+                    ptx::tma_load_3d(ptx::smem_u32(b_tiles + stage * kBStageBytes), mb, fb,
                                      (int32_t)(kb * BK), (int32_t)(wi.n_blk * BN), (int32_t)split);
                     if (++stage == kStages) { stage = 0; phase ^= 1; }
                 }
@@ -175,7 +191,7 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
-            for (uint32_t w = cluster_id_x(); ok && w < n_tiles; w += n_clusters_x(), ++iter) {
+            for (uint32_t w = cluster_id_x(); ok && w < n_items; w += n_clusters_x(), ++iter) {
                 const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
                 if (!ptx::mbar_wait(ptx::smem_u32(&tmem_empty_bar[buf]), acc_phase ^ 1, abort_flag, p.wait_limit_ns)) {
                     atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(w & 0xFFFFFF));
@@ -212,12 +228,17 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
         const uint32_t quarter = warp & 3;
         const uint32_t n_split = p.split_k;
         const uint32_t cols_per = BN / n_split;             // columns of the tile this CTA reduces and stores
-        const bool vec = (p.N % 4 == 0) && (((uintptr_t)p.y & 15) == 0) && !p.out_bf16;
+        const bool vec_shape = (p.N % 4 == 0) && !p.out_bf16;
         const uint32_t parked = ptx::smem_u32(parked_bar), readb = ptx::smem_u32(read_bar);
         bool ok = true;
         uint32_t iter = 0;
-        for (uint32_t w = cluster_id_x(); w < n_tiles; w += n_clusters_x(), ++iter) {
-            const WorkItem wi = decode_work(w * p.split_k, p);
+        for (uint32_t w = cluster_id_x(); w < n_items; w += n_clusters_x(), ++iter) {
+            uint32_t prob = 0, tile = w;
+            if constexpr (kGrouped) { prob = w / n_tiles; tile = w - prob * n_tiles; }
+            const WorkItem wi = decode_work(tile * p.split_k, p);
+            void* y_out = p.y;
+            if constexpr (kGrouped) y_out = group.y[prob];
+            const bool vec = vec_shape && (((uintptr_t)y_out & 15) == 0);
             const uint32_t buf = iter & 1, acc_phase = (iter >> 1) & 1;
             if (ok && !ptx::mbar_wait(ptx::smem_u32(&tmem_full_bar[buf]), acc_phase, abort_flag, p.wait_limit_ns)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(w & 0xFFFFFF));
@@ -300,12 +321,12 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
                         }
                         const size_t off = (size_t)row * p.N + col;
                         if (vec && col + 4 <= p.N) {
-                            *(float4*)((float*)p.y + off) = make_float4(o[0], o[1], o[2], o[3]);
+                            *(float4*)((float*)y_out + off) = make_float4(o[0], o[1], o[2], o[3]);
                         } else {
                             for (int j = 0; j < 4; ++j) {
                                 if (col + j >= p.N) break;
-                                if (p.out_bf16) ((__nv_bfloat16*)p.y)[off + j] = __float2bfloat16_rn(o[j]);
-                                else ((float*)p.y)[off + j] = o[j];
+                                if (p.out_bf16) ((__nv_bfloat16*)y_out)[off + j] = __float2bfloat16_rn(o[j]);
+                                else ((float*)y_out)[off + j] = o[j];
                             }
                         }
                     }
@@ -336,9 +357,10 @@ gemm_bf16_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const
 
 uint32_t splitk_smem_bytes(uint32_t bn) { return sk_bars_offset(bn) + 256 + 1024; }
 
-template <uint32_t BN>
-int launch_splitk_instance(const CUtensorMap& ma, const CUtensorMap& mb, KParams p, uint32_t n_sms, cudaStream_t stream) {
-    auto kern = gemm_bf16_tcgen05_splitk_kernel<BN>;
+template <uint32_t BN, bool kGrouped>
+int launch_splitk_instance(const CUtensorMap& ma, const CUtensorMap& mb, KParams p, uint32_t n_sms, cudaStream_t stream,
+                           const std::conditional_t<kGrouped, GroupOperands, NoGroup>& group) {
+    auto kern = gemm_bf16_tcgen05_splitk_kernel<BN, kGrouped>;
     const uint32_t smem = splitk_smem_bytes(BN);
     static bool attr_set[64] = {};
     static int max_clusters[64][9] = {};
@@ -371,13 +393,13 @@ int launch_splitk_instance(const CUtensorMap& ma, const CUtensorMap& mb, KParams
         max_clusters[dev][split] = std::max(n, 1);
     }
     static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
-    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    const uint32_t tiles = p.tiles_m * p.tiles_n * (kGrouped ? p.n_problems : 1u);
     const uint32_t clusters = std::min<uint32_t>(tiles, (uint32_t)max_clusters[dev][split]);
     p.sk_alias = tiles <= clusters ? 1 : 0;                 // one tile per cluster: the accumulator is parked over the idle ring
     p.sk_stages = sk_stages(BN, p.sk_alias != 0);
     cfg.gridDim = dim3(clusters * split, 1, 1);
     cfg.numAttrs = use_pdl ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, p, group);
     if (e != cudaSuccess) return fail(T0_ERR_CUDA, "split-K GEMM kernel launch failed: %s", cudaGetErrorString(e));
     return T0_OK;
 }
@@ -397,9 +419,10 @@ bool gemm_splitk_cluster_supported(const GemmLaunch& g) {
     return true;
 }
 
-int launch_gemm_sm100_splitk(const GemmLaunch& g, cudaStream_t stream) {
-    if (g.m == 0 || g.n == 0) return T0_OK;
-    if (!gemm_splitk_cluster_supported(g)) return fail(T0_ERR_UNSUPPORTED, "the cluster split-K kernel does not take this request");
+namespace {
+
+// The launch parameters and the two operand maps of one problem (shape already accepted by gemm_splitk_cluster_supported).
+int splitk_params(const GemmLaunch& g, KParams* out, CUtensorMap* ma, CUtensorMap* mb) {
     const uint32_t split = g.split_k, kps = g.k / split;
     const uint32_t ldx = g.ldx ? g.ldx : g.k, ldb = g.ldb ? g.ldb : g.k;
     const uint32_t bn = snap_tile_n(g.tile_n);
@@ -420,14 +443,61 @@ int launch_gemm_sm100_splitk(const GemmLaunch& g, cudaStream_t stream) {
     p.out_bf16 = g.out_bf16 ? 1 : 0; p.epilogue = g.epilogue; p.n_ops = g.n_ops;
     p.scale = g.scale; p.clamp_min = g.clamp_min; p.clamp_max = g.clamp_max;
     memcpy(p.ops, g.ops, sizeof p.ops);
-    CUtensorMap ma, mb;
-    int rc = make_map_kmajor(&ma, g.x, g.m, ldx, kps, split, BM);
+    int rc = make_map_kmajor(ma, g.x, g.m, ldx, kps, split, BM);
     if (rc != T0_OK) return rc;
-    rc = make_map_kmajor(&mb, g.b, g.n, ldb, kps, split, bn);
+    rc = make_map_kmajor(mb, g.b, g.n, ldb, kps, split, bn);
+    if (rc != T0_OK) return rc;
+    *out = p;
+    return T0_OK;
+}
+
+}  // namespace
+
+int launch_gemm_sm100_splitk(const GemmLaunch& g, cudaStream_t stream) {
+    if (g.m == 0 || g.n == 0) return T0_OK;
+    if (!gemm_splitk_cluster_supported(g)) return fail(T0_ERR_UNSUPPORTED, "the cluster split-K kernel does not take this request");
+    KParams p;
+    CUtensorMap ma, mb;
+    int rc = splitk_params(g, &p, &ma, &mb);
     if (rc != T0_OK) return rc;
     if ((uint64_t)p.tiles_m * p.tiles_n > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
     const uint32_t n_sms = g.n_sms ? g.n_sms : 148;
-    return bn == 128 ? launch_splitk_instance<128>(ma, mb, p, n_sms, stream) : launch_splitk_instance<64>(ma, mb, p, n_sms, stream);
+    const NoGroup none = {0};
+    return snap_tile_n(g.tile_n) == 128 ? launch_splitk_instance<128, false>(ma, mb, p, n_sms, stream, none)
+                                        : launch_splitk_instance<64, false>(ma, mb, p, n_sms, stream, none);
+}
+
+int launch_gemm_sm100_splitk_grouped(const GemmLaunch* gs, uint32_t count, cudaStream_t stream) {
+    if (!gs || count == 0) return T0_OK;
+    if (count > kMaxGroupedGemms) return fail(T0_ERR_INVALID, "at most %u problems per grouped launch (got %u)", kMaxGroupedGemms, count);
+    const GemmLaunch& g0 = gs[0];
+    if (g0.m == 0 || g0.n == 0) return T0_OK;
+    if (!gemm_splitk_cluster_supported(g0)) return fail(T0_ERR_UNSUPPORTED, "the cluster split-K kernel does not take this request");
+    static GroupOperands group;          // 8.4 KB: kept off the stack; launches are issued under the caller's lock
+    static std::mutex group_mu;
+    std::lock_guard<std::mutex> lock(group_mu);
+    KParams p0;
+    for (uint32_t i = 0; i < count; ++i) {
+        const GemmLaunch& g = gs[i];
+        // one shape and one configuration: only the operand and output addresses differ
+        if (g.m != g0.m || g.n != g0.n || g.k != g0.k || g.ldx != g0.ldx || g.ldb != g0.ldb || g.tile_n != g0.tile_n || g.split_k != g0.split_k ||
+            g.nn != g0.nn || g.out_bf16 != g0.out_bf16 || g.swap_grid != g0.swap_grid || g.epilogue != g0.epilogue || g.n_ops != g0.n_ops ||
+            memcmp(g.ops, g0.ops, sizeof g.ops) != 0 || g.scale != g0.scale || g.clamp_min != g0.clamp_min || g.clamp_max != g0.clamp_max ||
+            g.bias != g0.bias)
+            return fail(T0_ERR_INVALID, "grouped launch: problem %u differs from problem 0 in shape or configuration", i);
+        if (!g.x || !g.b || !g.y) return fail(T0_ERR_INVALID, "grouped launch: null pointer in problem %u", i);
+        if (((uintptr_t)g.x & 15) || ((uintptr_t)g.b & 15)) return fail(T0_ERR_UNSUPPORTED, "grouped launch: operands of problem %u are not 16-byte aligned", i);
+        KParams pi;
+        int rc = splitk_params(g, &pi, &group.maps[2 * i], &group.maps[2 * i + 1]);
+        if (rc != T0_OK) return rc;
+        if (i == 0) p0 = pi;
+        group.y[i] = g.y;
+    }
+    p0.n_problems = count;
+    if ((uint64_t)p0.tiles_m * p0.tiles_n * count > 0x7FFFFFFFull) return fail(T0_ERR_UNSUPPORTED, "too many tiles");
+    const uint32_t n_sms = g0.n_sms ? g0.n_sms : 148;
+    return snap_tile_n(g0.tile_n) == 128 ? launch_splitk_instance<128, true>(group.maps[0], group.maps[1], p0, n_sms, stream, group)
+                                         : launch_splitk_instance<64, true>(group.maps[0], group.maps[1], p0, n_sms, stream, group);
 }
 
 }  // namespace t0

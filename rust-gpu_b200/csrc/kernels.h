@@ -54,6 +54,13 @@ uint32_t gemm_pair_smem_bytes(uint32_t pair_n);
 // distributed shared memory (same sum, in split order, as planes + reduction).  NT layout, split_k 2 / 4 / 8, tile_n 64 / 128.
 bool gemm_splitk_cluster_supported(const GemmLaunch& g);
 int launch_gemm_sm100_splitk(const GemmLaunch& g, cudaStream_t stream);
+// Several problems of ONE shape and configuration (only x, b and y differ) in one launch of the same kernel: the clusters walk
+// the tiles of all the problems, so launch, prologue and drain are paid once and the exchange of one tile overlaps the main
+// loop of the next.  The problems run concurrently: no y may be an input of another.  At most kMaxGroupedGemms per launch.
+constexpr uint32_t kMaxGroupedGemms = 32;
+int launch_gemm_sm100_splitk_grouped(const GemmLaunch* gs, uint32_t count, cudaStream_t stream);
+// The same for shapes that need no split-K once several problems fill the GPU: the single-CTA kernel, NT, tile width 64 / 128.
+int launch_gemm_sm100_grouped(const GemmLaunch* gs, uint32_t count, cudaStream_t stream);
 
 // y[i] = sum_s planes[s][i] in split order, then the epilogue; K4.
 int launch_splitk_reduce(const float* planes, void* y, const float* bias, uint32_t m, uint32_t n, uint32_t split_k,

@@ -751,6 +751,94 @@ int t0_gemm_launch(t0_runtime* rt, const t0_gemm_args* a) {
     return run_gemm(rt, q);
 }
 
+int t0_gemm_launch_grouped(t0_runtime* rt, const t0_gemm_args* args, size_t count) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
+    if (count == 0) return T0_OK;
+    const t0_gemm_args& a0 = args[0];
+    // the problems run at the same time: none may write what another reads or writes
+    struct Range { uint64_t lo, hi; };
+    auto overlaps = [](Range a, Range b) { return a.lo < b.hi && b.lo < a.hi; };
+    std::vector<Range> ins, outs;
+    bool same = true;
+    for (size_t i = 0; i < count; ++i) {
+        const t0_gemm_args& a = args[i];
+        if (a.m != a0.m || a.n != a0.n || a.k != a0.k || a.tile_n != a0.tile_n || a.split_k != a0.split_k || a.transpose != a0.transpose ||
+            a.epilogue != a0.epilogue || a.out_bf16 != a0.out_bf16 || a.planes != a0.planes || a.swap_grid != a0.swap_grid || a.pair_cta != a0.pair_cta ||
+            a.n_tile_epilogue != a0.n_tile_epilogue || memcmp(a.tile_epilogue, a0.tile_epilogue, sizeof a.tile_epilogue) != 0 || a.scale != a0.scale ||
+            a.clamp_min != a0.clamp_min || a.clamp_max != a0.clamp_max || a.bias != a0.bias)
+            same = false;
+        const uint64_t out_bytes = (uint64_t)a.m * a.n * (a.out_bf16 ? 2 : 4) * ((a.planes && a.split_k > 1) ? a.split_k : 1);
+        outs.push_back({a.y, a.y + out_bytes});
+        ins.push_back({a.x, a.x + (uint64_t)a.m * a.k * 2});
+        ins.push_back({a.b, a.b + (uint64_t)a.n * a.k * 2});
+    }
+    for (size_t i = 0; i < count; ++i) {
+        for (size_t j = 0; j < count; ++j) {
+            if (i == j) continue;
+            if (overlaps(outs[i], outs[j]) || overlaps(outs[i], ins[2 * j]) || overlaps(outs[i], ins[2 * j + 1]))
+                return fail(T0_ERR_INVALID, "grouped launch: the output of problem %zu overlaps an operand or the output of problem %zu (the problems run concurrently)", i, j);
+        }
+    }
+    // one launch where the problems share a shape whose configuration is the one-launch split-K; otherwise back to back
+    DeviceGuard guard(rt->device);
+    uint32_t tile_n = a0.tile_n, split = a0.split_k > 1 ? a0.split_k : 1;
+    int pair = a0.pair_cta;
+    if (a0.tile_n == 0 && a0.pair_cta == 0 && split == 1 && a0.k >= 64) {
+        t0_gemm_config c;
+        if (t0_cached_auto_select(a0.m, a0.k, a0.n, &c) == T0_OK) {
+            tile_n = c.tile_n; split = c.split_k > 1 ? c.split_k : 1; pair = c.wgp_mode ? 1 : 2;
+        }
+    }
+    static const bool no_cluster = getenv("T0_NO_CLUSTER_SPLITK") != nullptr;
+    GemmLaunch g;
+    memset(&g, 0, sizeof g);
+    g.m = a0.m; g.n = a0.n; g.k = a0.k; g.tile_n = tile_n; g.split_k = split;
+    g.nn = a0.transpose == T0_NN; g.out_bf16 = a0.out_bf16 != 0; g.swap_grid = a0.swap_grid != 0;
+    g.epilogue = a0.epilogue; g.n_ops = a0.n_tile_epilogue;
+    memcpy(g.ops, a0.tile_epilogue, sizeof g.ops);
+    g.scale = a0.scale; g.clamp_min = a0.clamp_min; g.clamp_max = a0.clamp_max;
+    g.bias = (const float*)a0.bias;
+    g.status = rt->d_status; g.probe = rt->d_probe; g.n_sms = (uint32_t)rt->sm_count;
+    g.wait_limit_ns = rt->wait_limit_ns.load(std::memory_order_relaxed);
+    g.x = (const void*)a0.x; g.b = (const void*)a0.b; g.y = (void*)a0.y;
+    const bool needs_bias = g.n_ops ? std::find(g.ops, g.ops + g.n_ops, (uint8_t)T0_TEPI_BIAS_ADD) != g.ops + g.n_ops : g.epilogue != T0_EPI_STORE_F32;
+    const bool basics = same && count > 1 && !a0.planes && pair != 1 && a0.k >= 64 && a0.k % 8 == 0 && !g.nn && (!needs_bias || a0.bias);
+    // Where the caller fixed neither tile nor split, the split is chosen for the GROUP: a single skinny problem needs split-K to
+    // fill the GPU, several of them may not, and every split costs an exchange between the CTAs of a tile.  The smallest split
+    // (none, 2, 4, 8) with which the tiles of min(count, 32) problems give every SM at least two work items is taken.
+    bool plain = false;                                    // no split-K: the single-CTA kernel, grouped
+    if (basics && a0.tile_n == 0 && a0.pair_cta == 0 && (a0.split_k <= 1) && split > 1) {
+        const uint32_t bn = a0.n <= 64 ? 64u : 128u;
+        const uint64_t tiles = (uint64_t)ceil_div(a0.m, 128) * ceil_div(a0.n, bn) * std::min<size_t>(count, kMaxGroupedGemms);
+        uint32_t s = 1;
+        while (s < split && tiles * s < 2ull * (uint64_t)rt->sm_count) s *= 2;
+        while (s > 1 && (a0.k % s || (a0.k / s) % 8)) s /= 2;
+        g.tile_n = bn; g.split_k = split = s;
+        plain = s == 1;
+    } else if (basics && split == 1 && pair != 1 && (snap_tile_n(tile_n) == 64 || snap_tile_n(tile_n) == 128)) {
+        plain = true;                                      // the caller (or the model) asked for no split and a tile this kernel has
+    }
+    const bool grouped = basics && (plain || (!no_cluster && split > 1 && gemm_splitk_cluster_supported(g)));
+    if (!grouped) return t0_gemm_launch_batch(rt, args, count);
+    std::vector<GemmLaunch> gs;
+    for (size_t i = 0; i < count; i += kMaxGroupedGemms) {
+        const size_t n = std::min<size_t>(kMaxGroupedGemms, count - i);
+        gs.assign(n, g);
+        for (size_t j = 0; j < n; ++j) {
+            const t0_gemm_args& a = args[i + j];
+            if (!a.x || !a.b || !a.y) return fail(T0_ERR_INVALID, "null device pointer in GEMM arguments");
+            if ((a.x & 15) || (a.b & 15)) return t0_gemm_launch_batch(rt, args + i, count - i);     // the staged path takes these one by one
+            gs[j].x = (const void*)a.x; gs[j].b = (const void*)a.b; gs[j].y = (void*)a.y;
+        }
+        rc = plain ? launch_gemm_sm100_grouped(gs.data(), (uint32_t)n, rt->stream) : launch_gemm_sm100_splitk_grouped(gs.data(), (uint32_t)n, rt->stream);
+        if (rc != T0_OK) return rc;
+        rt->launches.fetch_add(1);
+    }
+    return T0_OK;
+}
+
 int t0_gemm_launch_gather(t0_runtime* rt, const t0_gemm_args* a, const uint64_t* peer_y, uint32_t n_peers) {
     int rc = check_rt(rt);
     if (rc != T0_OK) return rc;

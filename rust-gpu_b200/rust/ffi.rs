@@ -260,6 +260,7 @@ extern "C" {
     pub fn t0_rt_timer_stop(rt: *mut t0_runtime, ms: *mut f32) -> c_int;
     pub fn t0_gemm_launch(rt: *mut t0_runtime, args: *const t0_gemm_args) -> c_int;
     pub fn t0_gemm_launch_batch(rt: *mut t0_runtime, args: *const t0_gemm_args, count: usize) -> c_int;
+    pub fn t0_gemm_launch_grouped(rt: *mut t0_runtime, args: *const t0_gemm_args, count: usize) -> c_int;
     pub fn t0_gemm_launch_gather(rt: *mut t0_runtime, args: *const t0_gemm_args, peer_y: *const u64, n_peers: u32) -> c_int;
     pub fn t0_buf_ipc_export(buf: *const t0_buffer, handle: *mut u8) -> c_int;
     pub fn t0_rt_ipc_open(rt: *mut t0_runtime, handle: *const u8, device_ptr: *mut u64) -> c_int;

@@ -767,3 +767,43 @@ def test_reserve_scratch_then_padded_and_planes_paths(t0, oracle):
         assert_gemm_close(got, oracle.gemm_nt(a, b, m, k, n), k)
     finally:
         rt.close()
+
+
+@pytest.mark.parametrize("m,n,k,kw,count", [(128, 4096, 4096, {}, 5), (64, 1024, 2048, dict(tile_n=64, split_k=2, pair_cta=2), 40),
+                                            (16, 512, 1024, dict(tile_n=128, split_k=8, pair_cta=2), 3), (200, 384, 512, dict(tile_n=128, split_k=4, pair_cta=2), 7),
+                                            (300, 512, 256, {}, 4), (16, 4096, 4096, {}, 33), (128, 1024, 512, dict(tile_n=128), 6), (70, 200, 136, dict(tile_n=64, pair_cta=2), 5)])
+def test_grouped_launch_equals_one_launch_per_problem(t0, oracle, rt, m, n, k, kw, count):
+    # independent problems of one shape in one launch (the clusters walk the tiles of all of them): every y equals the y of
+    # its own launch bit for bit, and the oracle within tolerance; more than 32 problems take two launches; a shape whose
+    # configuration is not the one-launch split-K (the last case) runs back to back
+    xs = [rt.upload(oracle.fill_uniform_bf16(m * k, 10 + i)) for i in range(count)]
+    bs = [rt.upload(oracle.fill_uniform_bf16(n * k, 500 + i)) for i in range(count)]
+    y_one = [rt.alloc(m * n * 4) for _ in range(count)]
+    y_grp = [rt.alloc(m * n * 4) for _ in range(count)]
+    for y in y_one + y_grp:
+        y.write(np.full(m * n, SENTINEL, np.float32))
+    for i in range(count):
+        rt.gemm(xs[i].gpu_addr(), bs[i].gpu_addr(), y_one[i].gpu_addr(), m, n, k, **kw)
+    rt.gemm_grouped([rt.gemm_args(xs[i].gpu_addr(), bs[i].gpu_addr(), y_grp[i].gpu_addr(), m, n, k, **kw) for i in range(count)])
+    rt.synchronize()
+    for i in range(count):
+        one, grp = rt.read_f32(y_one[i], m * n), rt.read_f32(y_grp[i], m * n)
+        if kw:
+            assert np.array_equal(one, grp), f"problem {i}"            # the same tile and split: the same sums in the same order
+        else:
+            assert not np.any(grp == SENTINEL) and np.abs(one - grp).max() <= tol_abs(k), f"problem {i}"   # the split is chosen for the group
+        if i in (0, count - 1):
+            a, b = oracle.fill_uniform_bf16(m * k, 10 + i), oracle.fill_uniform_bf16(n * k, 500 + i)
+            assert_gemm_close(grp.reshape(m, n), oracle.gemm_nt(a, b, m, k, n), k)
+    for buf in xs + bs + y_one + y_grp:
+        rt.recycle(buf)
+
+
+def test_grouped_launch_refuses_dependent_problems(t0, rt):
+    m, n, k = 128, 4096, 4096
+    x, b, y = rt.alloc(m * k * 2), rt.alloc(n * k * 2), rt.alloc(m * n * 4)
+    same_y = [rt.gemm_args(x.gpu_addr(), b.gpu_addr(), y.gpu_addr(), m, n, k) for _ in range(2)]
+    with pytest.raises(t0.T0Error):
+        rt.gemm_grouped(same_y)
+    for buf in (x, b, y):
+        rt.recycle(buf)
