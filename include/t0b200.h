@@ -467,6 +467,13 @@ typedef struct t0_w4a16_args {
     uint32_t m, n, k, group;
 } t0_w4a16_args;
 int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
+/* `count` INDEPENDENT problems (no y is the a or the y of another: checked, T0_ERR_INVALID).  Where they share one shape with
+ * 16 < M <= 128 that the fused tcgen05 kernel takes, up to 32 of them run in ONE launch whose CTAs walk the column tiles of all
+ * the problems: K is then not split, so launch, prologue and the exchange between the parts of K are paid once per launch
+ * instead of once per GEMM (the projections of a decode or small-batch prefill step that read the same input).  The fp32
+ * sums run along K in one piece, so y agrees with t0_w4a16_gemm to rounding, not bit for bit.  Anything else is submitted
+ * back to back as by t0_w4a16_gemm_batch. */
+int t0_w4a16_gemm_grouped(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
 /* Streaming weight layout for the fused kernel (no counterpart in the reference).  The row layout above puts the 16 KiB
  * a CTA needs per step in sixteen 1 KiB pieces 4N bytes apart, which HBM serves at about a quarter of its copy bandwidth,
  * and leaves the codes in an order no MMA fragment has.  t0_w4_prepack rewrites the three arrays once (weight-load time)

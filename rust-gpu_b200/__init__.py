@@ -766,6 +766,11 @@ class GpuRuntime:
         arr = (W4A16Args * len(calls))(*calls)
         _check(lib().t0_w4a16_gemm_batch(self._h, arr, len(calls)))
 
+    def w4a16_gemm_grouped(self, calls: list[W4A16Args]) -> None:
+        """``t0_w4a16_gemm_grouped``: independent problems; one shape with 16 < M <= 128 runs up to 32 per launch."""
+        arr = (W4A16Args * len(calls))(*calls)
+        _check(lib().t0_w4a16_gemm_grouped(self._h, arr, len(calls)))
+
     def fill_uniform_bf16(self, dst: int, n: int, seed: int, first_index: int = 0) -> None:
         _check(lib().t0_fill_uniform_bf16(self._h, dst, n, seed, first_index))
 
@@ -1051,6 +1056,7 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4_dequant", i32, vp, u64, u64, u64, u64, u32, u32, u32)
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
+    sig("t0_w4a16_gemm_grouped", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     tcp = C.POINTER(TileConfig)
     sig("t0_auto_schedule_tile_costs", i32, u32, u32, u32, C.POINTER(TileCost), i32)

@@ -909,6 +909,7 @@ namespace t0 {
 bool w4a16_umma_supported(uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group);
 int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K,
                       uint32_t group);
+int launch_w4a16_umma_grouped(t0_runtime* rt, const t0_w4a16_args* args, uint32_t count);
 }  // namespace t0
 
 extern "C" {
@@ -1009,6 +1010,45 @@ int t0_w4a16_gemm_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count)
     for (size_t i = 0; i < count; ++i) {
         const t0_w4a16_args& a = args[i];
         int rc = t0_w4a16_gemm(rt, a.a, a.packed, a.scales, a.zeros, a.y, a.m, a.n, a.k, a.group);
+        if (rc != T0_OK) return rc;
+    }
+    return T0_OK;
+}
+
+int t0_w4a16_gemm_grouped(t0_runtime* rt, const t0_w4a16_args* args, size_t count) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
+    if (count == 0) return T0_OK;
+    const t0_w4a16_args& a0 = args[0];
+    bool same = true;
+    for (size_t i = 0; i < count; ++i) {
+        const t0_w4a16_args& a = args[i];
+        if (!a.a || !a.packed || !a.scales || !a.zeros || !a.y) return fail(T0_ERR_INVALID, "null device pointer in problem %zu", i);
+        if (a.m != a0.m || a.n != a0.n || a.k != a0.k || a.group != a0.group) same = false;
+        // the problems run at the same time: no output may be an activation or the output of another problem
+        const uint64_t y_lo = a.y, y_hi = a.y + (uint64_t)a.m * a.n * 4;
+        for (size_t j = 0; j < count; ++j) {
+            if (j == i) continue;
+            const t0_w4a16_args& b = args[j];
+            const uint64_t by_hi = b.y + (uint64_t)b.m * b.n * 4, ba_hi = b.a + (uint64_t)b.m * b.k * 2;
+            if ((y_lo < by_hi && b.y < y_hi) || (y_lo < ba_hi && b.a < y_hi))
+                return fail(T0_ERR_INVALID, "grouped launch: the output of problem %zu overlaps the activations or the output of problem %zu (the problems run concurrently)", i, j);
+        }
+    }
+    static const bool two_step = getenv("T0_W4_TWO_STEP") != nullptr;
+    const bool grouped = same && count > 1 && !two_step && a0.m > 16 &&
+                         w4a16_umma_supported(a0.a, a0.packed, a0.scales, a0.zeros, a0.y, a0.m, a0.n, a0.k, a0.group);
+    if (!grouped) return t0_w4a16_gemm_batch(rt, args, count);
+    DeviceGuard guard(rt->device);
+    for (size_t i = 0; i < count; i += 32) {
+        const size_t n = std::min<size_t>(32, count - i);
+        bool ok = true;
+        for (size_t j = 0; j < n; ++j) {
+            const t0_w4a16_args& a = args[i + j];
+            ok = ok && w4a16_umma_supported(a.a, a.packed, a.scales, a.zeros, a.y, a.m, a.n, a.k, a.group);
+        }
+        rc = ok ? launch_w4a16_umma_grouped(rt, args + i, (uint32_t)n) : t0_w4a16_gemm_batch(rt, args + i, n);
         if (rc != T0_OK) return rc;
     }
     return T0_OK;

@@ -17,6 +17,7 @@
 // At the end the sixteen warps read the accumulator, park it in shared memory (over the rings, idle by then), exchange
 // across the cluster and store.  Every wait is bounded.
 #include "w4a16_common.cuh"
+#include <type_traits>
 
 using namespace t0;
 using namespace t0::w4;
@@ -48,6 +49,7 @@ struct UmParams {
     uint32_t M, N, K;
     uint32_t group;          // k per scale / zero-point row (a multiple of 64)
     uint32_t n_tiles, n_chunks, split;
+    uint32_t n_problems;     // grouped launch: problems of one shape in this launch (their maps and outputs ride in the group record)
 };
 
 __device__ __forceinline__ bool um_try_wait_cluster(uint32_t bar, uint32_t parity) {
@@ -103,9 +105,22 @@ __device__ __forceinline__ float4 um_ld_cluster_f4(uint32_t addr) {
     return v;
 }
 
+// Grouped launch: the four tensor maps (weights, scales, zero points, activations) and the output of up to 32 problems of
+// one shape in the kernel parameters (16.6 KB).
+constexpr uint32_t kUmMaxGroup = 32;
+struct UmGroup {
+    CUtensorMap maps[4 * kUmMaxGroup];
+    float* y[kUmMaxGroup];
+};
+
+template <bool kGrouped>
 __global__ void __launch_bounds__(kUmThreads, 1)
 w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
-                  const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_a, const UmParams p) {
+                  const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_a, const UmParams p,
+                  const __grid_constant__ std::conditional_t<kGrouped, UmGroup, gemm::NoGroup> group) {
+    // a grouped launch (no split of K: cluster of one) walks the column tiles of all its problems, problem-major
+    uint32_t n_items = p.n_tiles;
+    if constexpr (kGrouped) n_items = p.n_tiles * p.n_problems;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t raw_ring = smem;
@@ -164,7 +179,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
-            for (uint32_t tile = um_cluster_id(); ok && tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+            for (uint32_t item = um_cluster_id(); ok && item < n_items; item += um_n_clusters(), ++iter) {
+                uint32_t prob = 0, tile = item;
+                if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
+                (void)prob; (void)tile;
                 // the rings double as the parking area: the previous tile's copy must have been read by the whole cluster
                 if (iter > 0 && !um_wait_cluster(read_bar, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
                     atomicCAS(p.status, 0, kStatusProducerTimeout | 0x800000);
@@ -181,9 +199,13 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     const uint32_t fb = raw_full + 8 * stage, dst = raw_ring + stage * kUmRawStride;
                     const uint32_t grp = c * kUmBK / p.group;
                     ptx::mbar_arrive_expect_tx(fb, kUmRawBytes);
-                    ptx::tma_load_2d(dst, &map_w, fb, (int32_t)n0, (int32_t)(c * (kUmBK / 8)));
-                    ptx::tma_load_2d(dst + 8 * kUmBN * 4, &map_s, fb, (int32_t)n0, (int32_t)grp);
-                    ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, &map_z, fb, (int32_t)(n0 / 8), (int32_t)grp);
+                    const CUtensorMap* mw = &map_w;
+                    const CUtensorMap* ms = &map_s;
+                    const CUtensorMap* mz = &map_z;
+                    if constexpr (kGrouped) { mw = &group.maps[4 * prob]; ms = &group.maps[4 * prob + 1]; mz = &group.maps[4 * prob + 2]; }
+                    ptx::tma_load_2d(dst, mw, fb, (int32_t)n0, (int32_t)(c * (kUmBK / 8)));
+                    ptx::tma_load_2d(dst + 8 * kUmBN * 4, ms, fb, (int32_t)n0, (int32_t)grp);
+                    ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, (int32_t)(n0 / 8), (int32_t)grp);
                     if (++stage == kUmRawStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -191,7 +213,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             // the activations of every chunk, one 128-row box each, as soon as the UMMAs that read the operand stage are done
             uint32_t as = 0, aphase = 0, iter = 0;
             bool ok = true;
-            for (uint32_t tile = um_cluster_id(); ok && tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+            for (uint32_t item = um_cluster_id(); ok && item < n_items; item += um_n_clusters(), ++iter) {
+                uint32_t prob = 0, tile = item;
+                if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
+                (void)prob; (void)tile;
                 if (iter > 0 && !um_wait_cluster(read_bar, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) break;
                 for (uint32_t c = c_begin; c < c_end; ++c) {
                     if (!ptx::mbar_wait_relaxed(ab_empty + 8 * as, aphase ^ 1, abort_flag, p.wait_limit_ns, 64)) {
@@ -201,7 +226,9 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     }
                     ptx::fence_proxy_async_smem();           // the rings were the parking area of the previous tile (generic proxy)
                     ptx::mbar_arrive_expect_tx(ab_full + 8 * as, kUmABytes);
-                    ptx::tma_load_3d(a_ring + as * kUmABytes, &map_a, ab_full + 8 * as, (int32_t)(c * kUmBK), 0, 0);
+                    const CUtensorMap* ma = &map_a;
+                    if constexpr (kGrouped) ma = &group.maps[4 * prob + 3];
+                    ptx::tma_load_3d(a_ring + as * kUmABytes, ma, ab_full + 8 * as, (int32_t)(c * kUmBK), 0, 0);
                     if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
                 }
             }
@@ -212,7 +239,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(128, kUmBN, 0u);
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
-            for (uint32_t tile = um_cluster_id(); ok && tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+            for (uint32_t item = um_cluster_id(); ok && item < n_items; item += um_n_clusters(), ++iter) {
+                uint32_t prob = 0, tile = item;
+                if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
+                (void)prob; (void)tile;
                 if (iter > 0 && !ptx::mbar_wait(acc_empty, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
                     atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000);
                     break;
@@ -247,7 +277,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
         uint32_t rs = 0, rphase = 0, as = 0, aphase = 0, iter = 0;
         bool ok = true;
         const uint32_t b_off = (n >> 3) * 1024 + (n & 7) * 128;
-        for (uint32_t tile = um_cluster_id(); tile < p.n_tiles; tile += um_n_clusters(), ++iter) {
+        for (uint32_t item = um_cluster_id(); item < n_items; item += um_n_clusters(), ++iter) {
+            uint32_t prob = 0, tile = item;
+            if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
+            (void)prob;
             const uint32_t n0 = tile * kUmBN;
             if (ok && iter > 0 && !um_wait_cluster(read_bar, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x400000);
@@ -314,10 +347,19 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     ptx::tmem_ld_wait();
                     const uint32_t col = n0 + cg * 64 + h * 32;
                     if (row_in < p.M) {
-                        float* dst = p.y + (size_t)row_in * p.N + col;
+                        float* y_out = p.y;
+                        if constexpr (kGrouped) y_out = group.y[prob];
+                        float* dst = y_out + (size_t)row_in * p.N + col;
+                        if (col + 32 <= p.N && (((uintptr_t)y_out & 15) == 0)) {       // (N % 32 == 0: every row starts on a 16-byte boundary)
 #pragma unroll
-                        for (uint32_t j = 0; j < 32; ++j)
-                            if (col + j < p.N) dst[j] = __uint_as_float(r[j]);
+                            for (uint32_t j = 0; j < 8; ++j)
+                                *(float4*)(dst + 4 * j) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                                                                    __uint_as_float(r[4 * j + 3]));
+                        } else {
+#pragma unroll
+                            for (uint32_t j = 0; j < 32; ++j)
+                                if (col + j < p.N) dst[j] = __uint_as_float(r[j]);
+                        }
                     }
                 }
                 ptx::tc_fence_before_sync();
@@ -419,34 +461,24 @@ bool w4a16_umma_supported(uint64_t a, uint64_t packed, uint64_t scales, uint64_t
     return true;
 }
 
-int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K,
-                      uint32_t group) {
-    UmParams p;
-    memset(&p, 0, sizeof p);
-    p.a = (const uint16_t*)a; p.y = (float*)y; p.status = rt->d_status;
-    const uint64_t limit = rt->wait_limit_ns.load(std::memory_order_relaxed);
-    p.wait_limit_ns = limit ? limit : ptx::kWaitLimitNs;
-    p.M = M; p.N = N; p.K = K; p.group = group;
-    p.n_tiles = ceil_div(N, kUmBN);
-    p.n_chunks = K / kUmBK;
-    // as many parts of K as fill the machine (the parts of a tile form a cluster of at most four CTAs)
-    uint32_t split = std::max<uint32_t>(1, std::min<uint32_t>(4, (uint32_t)rt->sm_count / std::max<uint32_t>(1, p.n_tiles)));
-    split = std::min(split, p.n_chunks);
-    CUtensorMap map_w, map_s, map_z;
-    int rc = gemm::make_map_2d_plain(&map_w, (const void*)packed, 4, K / 8, N, kUmBN, kUmBK / 8);
-    if (rc != T0_OK) return rc;
-    rc = gemm::make_map_2d_plain(&map_s, (const void*)scales, 2, K / group, N, kUmBN, 1);
-    if (rc != T0_OK) return rc;
-    rc = gemm::make_map_2d_plain(&map_z, (const void*)zeros, 4, K / group, N / 8, kUmBN / 8, 1);
-    if (rc != T0_OK) return rc;
-    CUtensorMap map_a;      // the activations [M][K] as the 128-row operand: K-major boxes of 64, 128-byte swizzle, rows beyond M read as zero
-    rc = gemm::make_map_kmajor(&map_a, (const void*)a, M, K, K, 1, 128);
-    if (rc != T0_OK) return rc;
+// The four tensor maps of one problem: packed words, scales, zero points, and the activations as the 128-row operand
+// (K-major boxes of 64, 128-byte swizzle, rows beyond M read as zero).
+static int um_maps(uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint32_t M, uint32_t N, uint32_t K, uint32_t group, CUtensorMap* out4) {
+    int rc = gemm::make_map_2d_plain(&out4[0], (const void*)packed, 4, K / 8, N, kUmBN, kUmBK / 8);
+    if (rc == T0_OK) rc = gemm::make_map_2d_plain(&out4[1], (const void*)scales, 2, K / group, N, kUmBN, 1);
+    if (rc == T0_OK) rc = gemm::make_map_2d_plain(&out4[2], (const void*)zeros, 4, K / group, N / 8, kUmBN / 8, 1);
+    if (rc == T0_OK) rc = gemm::make_map_kmajor(&out4[3], (const void*)a, M, K, K, 1, 128);
+    return rc;
+}
+
+template <bool kGrouped>
+static int um_launch(t0_runtime* rt, const CUtensorMap* m4, UmParams p, uint32_t split, const std::conditional_t<kGrouped, UmGroup, gemm::NoGroup>& group) {
+    auto kern = w4a16_umma_kernel<kGrouped>;
     static bool attr_set[64] = {};
     static int max_clusters[64][5] = {};
     if (rt->device >= 64) return fail(T0_ERR_INVALID, "device ordinal out of range");
     if (!attr_set[rt->device]) {
-        T0_CUDA(cudaFuncSetAttribute(w4a16_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmSmem));
+        T0_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmSmem));
         attr_set[rt->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -463,19 +495,68 @@ int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scal
         cfg.gridDim = dim3(split * ((uint32_t)rt->sm_count / split), 1, 1);
         cfg.numAttrs = 1;
         int n = 0;
-        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, w4a16_umma_kernel, &cfg);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
         if (e != cudaSuccess || n <= 0) { cudaGetLastError(); n = (int)((uint32_t)rt->sm_count / split) * 3 / 4; }
         max_clusters[rt->device][split] = std::max(n, 1);
     }
     p.split = split;
     static const bool use_pdl = getenv("T0_NO_PDL") == nullptr;
-    const uint32_t clusters = std::min<uint32_t>(p.n_tiles, (uint32_t)max_clusters[rt->device][split]);
+    const uint32_t items = p.n_tiles * (kGrouped ? p.n_problems : 1u);
+    const uint32_t clusters = std::min<uint32_t>(items, (uint32_t)max_clusters[rt->device][split]);
     cfg.gridDim = dim3(clusters * split, 1, 1);
     cfg.numAttrs = use_pdl ? 2 : 1;
-    cudaError_t le = cudaLaunchKernelEx(&cfg, w4a16_umma_kernel, map_w, map_s, map_z, map_a, p);
+    cudaError_t le = cudaLaunchKernelEx(&cfg, kern, m4[0], m4[1], m4[2], m4[3], p, group);
     if (le != cudaSuccess) return fail(T0_ERR_CUDA, "W4A16 kernel launch failed: %s", cudaGetErrorString(le));
     rt->launches.fetch_add(1);
     return T0_OK;
+}
+
+static UmParams um_params(t0_runtime* rt, uint64_t a, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
+    UmParams p;
+    memset(&p, 0, sizeof p);
+    p.a = (const uint16_t*)a; p.y = (float*)y; p.status = rt->d_status;
+    const uint64_t limit = rt->wait_limit_ns.load(std::memory_order_relaxed);
+    p.wait_limit_ns = limit ? limit : ptx::kWaitLimitNs;
+    p.M = M; p.N = N; p.K = K; p.group = group;
+    p.n_tiles = ceil_div(N, kUmBN);
+    p.n_chunks = K / kUmBK;
+    return p;
+}
+
+int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t y, uint32_t M, uint32_t N, uint32_t K,
+                      uint32_t group) {
+    UmParams p = um_params(rt, a, y, M, N, K, group);
+    // as many parts of K as fill the machine (the parts of a tile form a cluster of at most four CTAs)
+    uint32_t split = std::max<uint32_t>(1, std::min<uint32_t>(4, (uint32_t)rt->sm_count / std::max<uint32_t>(1, p.n_tiles)));
+    split = std::min(split, p.n_chunks);
+    CUtensorMap m4[4];
+    int rc = um_maps(a, packed, scales, zeros, M, N, K, group, m4);
+    if (rc != T0_OK) return rc;
+    const gemm::NoGroup none = {0};
+    return um_launch<false>(rt, m4, p, split, none);
+}
+
+// Up to 32 problems of one shape in one launch, K not split: the CTAs walk the column tiles of all the problems, so launch,
+// prologue and the exchange between the parts of K disappear from the per-problem cost.  The problems run concurrently.
+int launch_w4a16_umma_grouped(t0_runtime* rt, const t0_w4a16_args* args, uint32_t count) {
+    if (count == 0) return T0_OK;
+    if (count > kUmMaxGroup) return fail(T0_ERR_INVALID, "at most %u problems per grouped launch (got %u)", kUmMaxGroup, count);
+    const t0_w4a16_args& a0 = args[0];
+    static UmGroup grp;                  // 16.6 KB: kept off the stack, filled under the lock, copied by the launch
+    static std::mutex grp_mu;
+    std::lock_guard<std::mutex> lock(grp_mu);
+    for (uint32_t i = 0; i < count; ++i) {
+        const t0_w4a16_args& a = args[i];
+        if (a.m != a0.m || a.n != a0.n || a.k != a0.k || a.group != a0.group) return fail(T0_ERR_INVALID, "grouped launch: problem %u differs from problem 0 in shape", i);
+        if (!w4a16_umma_supported(a.a, a.packed, a.scales, a.zeros, a.y, a.m, a.n, a.k, a.group))
+            return fail(T0_ERR_UNSUPPORTED, "grouped launch: problem %u is not a shape of the fused tcgen05 kernel", i);
+        int rc = um_maps(a.a, a.packed, a.scales, a.zeros, a.m, a.n, a.k, a.group, &grp.maps[4 * i]);
+        if (rc != T0_OK) return rc;
+        grp.y[i] = (float*)a.y;
+    }
+    UmParams p = um_params(rt, a0.a, a0.y, a0.m, a0.n, a0.k, a0.group);
+    p.n_problems = count;
+    return um_launch<true>(rt, grp.maps, p, 1, grp);
 }
 
 }  // namespace t0

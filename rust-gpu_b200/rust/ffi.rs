@@ -313,6 +313,7 @@ extern "C" {
     pub fn t0_w4_dequant(rt: *mut t0_runtime, packed: u64, scales: u64, zeros: u64, out_bf16: u64, K: u32, N: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm(rt: *mut t0_runtime, a: u64, packed: u64, scales: u64, zeros: u64, y: u64, M: u32, N: u32, K: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm_batch(rt: *mut t0_runtime, args: *const t0_w4a16_args, count: usize) -> c_int;
+    pub fn t0_w4a16_gemm_grouped(rt: *mut t0_runtime, args: *const t0_w4a16_args, count: usize) -> c_int;
     pub fn t0_w4_prepacked_bytes(K: u32, N: u32, group: u32) -> usize;
     pub fn t0_w4_prepack(rt: *mut t0_runtime, packed: u64, scales: u64, zeros: u64, out: u64, K: u32, N: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm_prepacked(rt: *mut t0_runtime, a: u64, prepacked: u64, y: u64, M: u32, N: u32, K: u32, group: u32) -> c_int;

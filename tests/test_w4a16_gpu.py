@@ -455,3 +455,36 @@ def test_fused_large_m_dequantises_bit_exactly(t0, oracle, rt):
             a[m, base + m] = 0x3F80
         got = run_w4a16(rt, a, packed, sbits, zeros, M, N, K, G)
         assert np.array_equal(got.view(np.uint32) & 0x7FFFFFFF, want[base:base + M].view(np.uint32) & 0x7FFFFFFF), base
+
+
+@pytest.mark.parametrize("M,K,N,G,count", [(128, 4096, 1536, 128, 5), (17, 512, 288, 128, 3), (100, 1024, 11008, 256, 4), (64, 192, 8192, 64, 40)])
+def test_grouped_large_m_problems_in_one_launch(t0, oracle, rt, M, K, N, G, count):
+    # independent problems of one shape (their own activations, weights and outputs) in one launch of the fused tcgen05
+    # kernel, K not split: each y against the oracle, the guard words behind each y untouched, one launch per 32 problems;
+    # with one-hot activations the result is the dequantised weights, bit for bit
+    acts = [oracle.fill_normal_bf16(M * K, 70 + i) for i in range(min(count, 3))]
+    w = [make_w4(oracle, K, N, G, seed=M + K + i) for i in range(min(count, 3))]
+    bufs, calls, ys = [], [], []
+    for i in range(count):
+        j = i % len(acts)
+        xa, xp, xs, xz = rt.upload(acts[j]), rt.upload(w[j][0]), rt.upload(w[j][1]), rt.upload(w[j][2])
+        y = rt.alloc(M * N * 4 + 4096)
+        y.write(np.full(M * N + 1024, -9999.0, np.float32))
+        calls.append(t0.W4A16Args(xa.gpu_addr(), xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), y.gpu_addr(), M, N, K, G))
+        bufs += [xa, xp, xs, xz, y]
+        ys.append(y)
+    before = rt.launch_count()
+    rt.w4a16_gemm_grouped(calls)
+    rt.synchronize()
+    assert rt.launch_count() - before == -(-count // 32)
+    refs = [oracle.w4a16_gemm(acts[j], *w[j], M, N, K, G) for j in range(len(acts))]
+    for i, y in enumerate(ys):
+        assert_close(y.read(M * N * 4, np.float32).reshape(M, N), refs[i % len(acts)], K)
+        assert np.all(y.read_bytes(M * N * 4, 4096, np.float32) == -9999.0), "wrote past the output"
+    # dependent problems are refused: the output of one as the activations of another
+    if count >= 2 and M * K * 2 <= M * N * 4:
+        bad = [calls[0], t0.W4A16Args(ys[0].gpu_addr(), calls[1].packed, calls[1].scales, calls[1].zeros, ys[1].gpu_addr(), M, N, K, G)]
+        with pytest.raises(t0.T0Error):
+            rt.w4a16_gemm_grouped(bad)
+    for b in bufs:
+        b.free()
