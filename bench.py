@@ -171,6 +171,8 @@ def run_hbm_workload(args, name, rt=None, brief=False):
         alg_bytes = M * K * 2 + N * K * 2 + M * N * 4
         set_bytes = N * K * 2
     n_sets = max(2, -(-3 * 126 * 2 ** 20 // set_bytes))      # rotating weight sets: together three times the L2
+    if not w4:
+        n_sets = max(n_sets, 32)        # a grouped launch runs several of its 32 problems at once: every one has weights of its own
     a_host = oracle.fill_normal_bf16(M * K, 7 + M) if w4 else oracle.fill_uniform_bf16(M * K, 42 + M)
     xa = alloc(M * K * 2)
     xa.write(a_host)
