@@ -502,8 +502,8 @@ def run_square_brief(t0, rt, name):
     tf = 2.0 * M * N * K * steps / (best * 1e-3) / 1e12
     peak, src = tensor_peak(peaks, best)
     return {"workload": name, "metric": "bf16_gemm_tflops", "value": tf, "unit": "TFLOP/s", "ms_per_step": best / steps, "steps": steps,
-            "roofline": {"bound": "tensor", "frac": tf / peak, "peak": peak, "peak_source": src},
-            "parity": {"sampled_rows": rows, "max_abs_err": worst, "tol": tol}}
+            "roofline": {"bound": "tensor", "frac": tf / peak, "peak": peak, "traffic": ncu_traffic(name), "peak_source": src},
+            "gpu_launches": steps, "parity": {"sampled_rows": rows, "max_abs_err": worst, "tol": tol}}
 
 
 def cpu_baseline(oracle, m, n, k, rows, threads=0):
