@@ -494,6 +494,20 @@ size_t t0_w4_prepacked_bytes(uint32_t K, uint32_t N, uint32_t group);
 int t0_w4_prepack(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group);
 int t0_w4a16_gemm_prepacked(t0_runtime* rt, uint64_t a, uint64_t prepacked, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group);
 int t0_w4a16_gemm_prepacked_batch(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
+/* Tile-major weight layout for 16 < M <= 128 (no counterpart in the reference).  In the row layout the 8 KB of packed words
+ * a CTA needs per 64-deep chunk are eight 1 KB pieces 4N bytes apart, which HBM serves at about a third of its copy
+ * bandwidth; that, not the arithmetic, then bounds the fused tcgen05 kernel.  t0_w4_to_tiled rewrites the three arrays
+ * once (weight-load time) into one buffer of t0_w4_tiled_bytes(K, N, group) bytes in which every 256-column tile is a matrix
+ * of its own:  words [T][K/8][256] u32, then scales [T][K/group][256] bf16, then zero points [T][K/group][32] u32,
+ * T = ceil(N / 256), columns past N zero.  K % 64 == 0, group % 64 == 0, group | K; any N.
+ * t0_w4a16_gemm_tiled computes the same product as t0_w4a16_gemm from that buffer (M <= 128; y f32 [M,N]);
+ * t0_w4a16_gemm_tiled_grouped takes INDEPENDENT problems (checked) whose .packed is the tile-major buffer (.scales / .zeros are
+ * ignored) and runs consecutive problems of one shape up to 32 per launch: K is then not split, and the dequantised weights
+ * are the tensor-memory operand of the UMMAs (they never pass through shared memory). */
+size_t t0_w4_tiled_bytes(uint32_t K, uint32_t N, uint32_t group);
+int t0_w4_to_tiled(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group);
+int t0_w4a16_gemm_tiled(t0_runtime* rt, uint64_t a, uint64_t tiled, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group);
+int t0_w4a16_gemm_tiled_grouped(t0_runtime* rt, const t0_w4a16_args* args, size_t count);
 /* The fused W4A16 GEMM for callers that may not allocate device memory (no counterpart in the reference, which has no
  * fused INT4 GEMM).  Same arguments and result as t0_w4a16_gemm, bit for bit, but the scratch the kernel needs lives in a
  * fixed array inside the library (t0_w4a16_gemm_static_scratch_bytes() bytes per device), so the call never allocates or

@@ -232,6 +232,26 @@ def w4_prepack(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, K: int
     return out
 
 
+def w4_to_tiled(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, K: int, N: int, group: int = 128) -> np.ndarray:
+    """Tile-major layout of the B200 W4A16 kernel for 16 < M <= 128 (one uint8 buffer): every 256-column tile a matrix of its
+    own, words [T][K/8][256] u32, then scales [T][K/group][256] bf16, then zero points [T][K/group][32] u32, columns past N
+    zero.  (No counterpart in the reference: a pure index remap of the B200 row layout.)"""
+    T = -(-N // 256)
+    npad = T * 256
+    pk = np.zeros((K // 8, npad), np.uint32)
+    pk[:, :N] = np.asarray(packed, np.uint32).reshape(K // 8, N)
+    sc = np.zeros((K // group, npad), np.uint16)
+    sc[:, :N] = np.asarray(scales, np.uint16).reshape(K // group, N)
+    zsrc = np.asarray(zeros, np.uint32).reshape(K // group, -1)
+    zp = np.zeros((K // group, npad // 8), np.uint32)
+    zp[:, :zsrc.shape[1]] = zsrc
+    words = pk.reshape(K // 8, T, 256).transpose(1, 0, 2)
+    sct = sc.reshape(K // group, T, 256).transpose(1, 0, 2)
+    zpt = zp.reshape(K // group, T, 32).transpose(1, 0, 2)
+    return np.concatenate([np.ascontiguousarray(words).view(np.uint8).reshape(-1), np.ascontiguousarray(sct).view(np.uint8).reshape(-1),
+                           np.ascontiguousarray(zpt).view(np.uint8).reshape(-1)])
+
+
 def gptq_parse(raw: bytes):
     """GptqWeight::from_bytes wire format (quant_kernels.rs:242-286) -> dict of arrays."""
     buf = np.frombuffer(raw, dtype=np.uint8)

@@ -766,6 +766,23 @@ class GpuRuntime:
         arr = (W4A16Args * len(calls))(*calls)
         _check(lib().t0_w4a16_gemm_batch(self._h, arr, len(calls)))
 
+    def w4_to_tiled(self, packed: int, scales: int, zeros: int, K: int, N: int, group: int = 128) -> "GpuBuffer":
+        """``t0_w4_to_tiled``: the weights rewritten into the tile-major layout (a new buffer)."""
+        n = int(lib().t0_w4_tiled_bytes(K, N, group))
+        if n == 0:
+            raise T0Error(f"the tile-major layout does not take K={K} group={group}")
+        out = self.alloc(n)
+        _check(lib().t0_w4_to_tiled(self._h, packed, scales, zeros, out.gpu_addr(), K, N, group))
+        return out
+
+    def w4a16_gemm_tiled(self, a: int, tiled: int, y: int, M: int, N: int, K: int, group: int = 128) -> None:
+        _check(lib().t0_w4a16_gemm_tiled(self._h, a, tiled, y, M, N, K, group))
+
+    def w4a16_gemm_tiled_grouped(self, calls: list[W4A16Args]) -> None:
+        """``t0_w4a16_gemm_tiled_grouped``: independent problems on tile-major weights, up to 32 of one shape per launch."""
+        arr = (W4A16Args * len(calls))(*calls)
+        _check(lib().t0_w4a16_gemm_tiled_grouped(self._h, arr, len(calls)))
+
     def w4a16_gemm_grouped(self, calls: list[W4A16Args]) -> None:
         """``t0_w4a16_gemm_grouped``: independent problems; one shape with 16 < M <= 128 runs up to 32 per launch."""
         arr = (W4A16Args * len(calls))(*calls)
@@ -1057,6 +1074,10 @@ def _declare(L: C.CDLL) -> None:
     sig("t0_w4a16_gemm", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_batch", i32, vp, C.POINTER(W4A16Args), sz)
     sig("t0_w4a16_gemm_grouped", i32, vp, C.POINTER(W4A16Args), sz)
+    sig("t0_w4a16_gemm_tiled_grouped", i32, vp, C.POINTER(W4A16Args), sz)
+    sig("t0_w4_tiled_bytes", sz, u32, u32, u32)
+    sig("t0_w4_to_tiled", i32, vp, u64, u64, u64, u64, u32, u32, u32)
+    sig("t0_w4a16_gemm_tiled", i32, vp, u64, u64, u64, u32, u32, u32, u32)
     sig("t0_w4a16_gemm_static", i32, vp, u64, u64, u64, u64, u64, u32, u32, u32, u32)
     tcp = C.POINTER(TileConfig)
     sig("t0_auto_schedule_tile_costs", i32, u32, u32, u32, C.POINTER(TileCost), i32)

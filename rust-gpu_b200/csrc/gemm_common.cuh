@@ -304,6 +304,22 @@ inline int make_map_2d_plain(CUtensorMap* map, const void* base, uint32_t elem_b
     return T0_OK;
 }
 
+// Plain (unswizzled) 3-D view [d2][d1][d0] with byte strides for d1 and d2, box d0 x d1 x 1 (u32 or u16 elements).
+inline int make_map_3d_plain(CUtensorMap* map, const void* base, uint32_t elem_bytes, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                             uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {d0, d1, d2};
+    cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+    cuuint32_t box[3] = {box0, box1, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims,
+                     strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(T0_ERR_CUDA, "cuTensorMapEncodeTiled (plain 3-D, %llu x %llu x %llu) failed: %d", (unsigned long long)d2, (unsigned long long)d1, (unsigned long long)d0, (int)r);
+    return T0_OK;
+}
+
 // 3-D view [planes][M][N] of the f32 output (or of split-K planes `plane_stride` elements apart), box 32 x 32, 128-byte
 // swizzle: what the epilogue's TMA store writes through.  Needs a 16-byte aligned base and N % 4 == 0.
 inline int make_map_out_f32(CUtensorMap* map, const void* base, uint32_t M, uint32_t N, uint32_t planes, uint64_t plane_stride) {

@@ -49,6 +49,8 @@ struct UmParams {
     uint32_t M, N, K;
     uint32_t group;          // k per scale / zero-point row (a multiple of 64)
     uint32_t n_tiles, n_chunks, split;
+    uint32_t tiled;          // the weights are in the tile-major layout (3-D maps: column in tile, row, tile) instead of the row layout
+    uint32_t probe;          // measurement switch (T0_W4_UMMA_PROBE, results are wrong): 1 = no UMMAs, 2 = no dequantisation arithmetic
     uint32_t n_problems;     // grouped launch: problems of one shape in this launch (their maps and outputs ride in the group record)
 };
 
@@ -144,10 +146,10 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     if (tid == 0) {
         for (uint32_t s = 0; s < kUmRawStages; ++s) {
             ptx::mbar_init(raw_full + 8 * s, 1);
-            ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps);
+            ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps / 2);    // the eight warps of the group that dequantises the chunk
         }
         for (uint32_t s = 0; s < kUmAbStages; ++s) {
-            ptx::mbar_init(ab_full + 8 * s, kUmDqWarps + 1);      // sixteen warps' weights + the activations' bytes (producer)
+            ptx::mbar_init(ab_full + 8 * s, kUmDqWarps / 2 + 1);  // eight warps' weights + the activations' bytes (producer)
             ptx::mbar_init(ab_empty + 8 * s, 1);
         }
         ptx::mbar_init(acc_full, 1);
@@ -203,9 +205,16 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     const CUtensorMap* ms = &map_s;
                     const CUtensorMap* mz = &map_z;
                     if constexpr (kGrouped) { mw = &group.maps[4 * prob]; ms = &group.maps[4 * prob + 1]; mz = &group.maps[4 * prob + 2]; }
-                    ptx::tma_load_2d(dst, mw, fb, (int32_t)n0, (int32_t)(c * (kUmBK / 8)));
-                    ptx::tma_load_2d(dst + 8 * kUmBN * 4, ms, fb, (int32_t)n0, (int32_t)grp);
-                    ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, (int32_t)(n0 / 8), (int32_t)grp);
+                    if (p.tiled) {
+                        // tile-major layout: the chunk's 8 KB of words are contiguous, as are its scales and zero points
+                        ptx::tma_load_3d(dst, mw, fb, 0, (int32_t)(c * (kUmBK / 8)), (int32_t)tile);
+                        ptx::tma_load_3d(dst + 8 * kUmBN * 4, ms, fb, 0, (int32_t)grp, (int32_t)tile);
+                        ptx::tma_load_3d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, 0, (int32_t)grp, (int32_t)tile);
+                    } else {
+                        ptx::tma_load_2d(dst, mw, fb, (int32_t)n0, (int32_t)(c * (kUmBK / 8)));
+                        ptx::tma_load_2d(dst + 8 * kUmBN * 4, ms, fb, (int32_t)n0, (int32_t)grp);
+                        ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, (int32_t)(n0 / 8), (int32_t)grp);
+                    }
                     if (++stage == kUmRawStages) { stage = 0; phase ^= 1; }
                 }
             }
@@ -269,15 +278,18 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------ sixteen warps: dequantise, stage activations, then the epilogue
-        const uint32_t n = tid & 255, jh = tid >> 8;               // this thread's column of the tile and half of a chunk's eight words
+        // ------------------------------------------------------------ sixteen warps: dequantise, then the epilogue
+        // Two groups of eight warps take alternate chunks: a warp's chain per chunk (wait, loads, arithmetic, stores, proxy
+        // fence, arrive) is longer than the UMMAs of a chunk, so with all sixteen warps on the same chunk that chain, not any
+        // unit, set the pace; two chunks in flight hide it.  A thread owns one column of the tile and all eight word rows.
+        const uint32_t grp = warp >> 3, n = (warp & 7) * 32 + lane;
         uint32_t mask, magic;
         asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
         asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
-        uint32_t rs = 0, rphase = 0, as = 0, aphase = 0, iter = 0;
+        uint32_t iter = 0, t_base = 0;                              // t_base: chunks of earlier tiles (ring positions run on across tiles)
         bool ok = true;
         const uint32_t b_off = (n >> 3) * 1024 + (n & 7) * 128;
-        for (uint32_t item = um_cluster_id(); item < n_items; item += um_n_clusters(), ++iter) {
+        for (uint32_t item = um_cluster_id(); item < n_items; item += um_n_clusters(), ++iter, t_base += my_chunks) {
             uint32_t prob = 0, tile = item;
             if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
             (void)prob;
@@ -286,29 +298,32 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                 if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x400000);
                 ok = false;
             }
-            for (uint32_t c = c_begin; ok && c < c_end; ++c) {
+            for (uint32_t ci = 0; ok && ci < my_chunks; ++ci) {
+                const uint32_t t = t_base + ci;
+                if ((t & 1u) != grp) continue;
+                const uint32_t rs = t % kUmRawStages, rphase = (t / kUmRawStages) & 1u, as = t % kUmAbStages, aphase = (t / kUmAbStages) & 1u;
                 if (!ptx::mbar_wait(raw_full + 8 * rs, rphase, abort_flag, p.wait_limit_ns)) {
-                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(c & 0x3FFFFF));
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(ci & 0x3FFFFF));
                     ok = false;
                     break;
                 }
                 const uint32_t raw = raw_ring + rs * kUmRawStride;
-                uint32_t words[4];
+                uint32_t words[8];
 #pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) words[i] = um_lds32(raw + (jh * 4 + i) * (kUmBN * 4) + n * 4);
+                for (uint32_t i = 0; i < 8; ++i) words[i] = um_lds32(raw + i * (kUmBN * 4) + n * 4);
                 const uint32_t sbits = um_lds16(raw + 8 * kUmBN * 4 + n * 2);
                 const uint32_t zword = um_lds32(raw + 8 * kUmBN * 4 + kUmBN * 2 + (n >> 3) * 4);
                 const uint32_t zz = ((zword >> ((n & 7) * 4)) & 0xFu) * 0x00010001u + 0x43004300u;     // bf16x2 (128+z, 128+z)
                 const uint32_t ss = sbits * 0x00010001u;                                               // (s, s)
                 if (!ptx::mbar_wait(ab_empty + 8 * as, aphase ^ 1, abort_flag, p.wait_limit_ns)) {
-                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x800000 | (int)(c & 0x3FFFFF));
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x800000 | (int)(ci & 0x3FFFFF));
                     ok = false;
                     break;
                 }
                 const uint32_t b_stage = b_ring + as * kUmBBytes + b_off;
 #pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                    const uint32_t wd = words[i], j = jh * 4 + i;
+                for (uint32_t j = 0; j < 8; ++j) {
+                    const uint32_t wd = words[j];
                     const uint32_t v0 = bf16x2_mul(bf16x2_sub(and_or(wd, mask, magic), zz), ss);            // k 0, 4
                     const uint32_t v1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz), ss);       // k 1, 5
                     const uint32_t v2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz), ss);       // k 2, 6
@@ -326,8 +341,6 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     ptx::mbar_arrive(raw_empty + 8 * rs);
                     ptx::mbar_arrive(ab_full + 8 * as);
                 }
-                if (++rs == kUmRawStages) { rs = 0; rphase ^= 1; }
-                if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
             }
             // ---- epilogue: the accumulator of this CTA's part of K
             if (ok && !ptx::mbar_wait(acc_full, iter & 1, abort_flag, p.wait_limit_ns)) {
@@ -350,7 +363,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                         float* y_out = p.y;
                         if constexpr (kGrouped) y_out = group.y[prob];
                         float* dst = y_out + (size_t)row_in * p.N + col;
-                        if (col + 32 <= p.N && (((uintptr_t)y_out & 15) == 0)) {       // (N % 32 == 0: every row starts on a 16-byte boundary)
+                        if (col + 32 <= p.N && (p.N % 4 == 0) && (((uintptr_t)y_out & 15) == 0)) {       // every row starts on a 16-byte boundary
 #pragma unroll
                             for (uint32_t j = 0; j < 8; ++j)
                                 *(float4*)(dst + 4 * j) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
@@ -450,6 +463,335 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     }
 }
 
+// ------------------------------------------------------------------ the same GEMM with the weights as the TENSOR-MEMORY operand
+//
+// For launches that do not split K (the grouped launches).  The shared-memory form above moves 114 KB through an SM's shared
+// memory per 64-deep chunk (32 KB of dequantised weights written, then read again by the UMMAs, on top of the raw weights and
+// the activations), which is what bounds it.  Here the roles of the operands are swapped: the dequantised weights are the
+// 128-row A operand and go from registers straight into tensor memory (tcgen05.st; a warp writes the 32 lanes of its
+// quadrant), the activations are the 128-column B operand in shared memory, exactly as TMA delivers them.  The accumulator is
+// y transposed: lane = column of y, tensor-memory column = row of y; a tile of 256 columns is two 128-lane accumulators.
+// Shared-memory traffic per chunk falls to 66 KB (raw weights in and out 18, activations in 16, read by eight UMMAs 32).
+//
+// Tensor memory (512 columns): accumulators 2 x 128 columns, then three A stages of 2 halves x 4 k-steps x 8 columns.
+constexpr uint32_t kTsTmemCols = 512;
+constexpr uint32_t kTsABase = 256;                         // first column of the A stages
+constexpr uint32_t kTsAStageCols = 64;
+// (the request is padded past half an SM's shared memory: the kernel takes all 512 tensor-memory columns, so two of its CTAs
+// must never share an SM)
+constexpr uint32_t kTsXStages = 8;                         // activation stages: a 16 KB box from L2 takes about a microsecond, several chunk periods
+constexpr uint32_t kTsSmemUsed = kUmRawStages * kUmRawStride + kTsXStages * kUmABytes + 512 + 1024;
+constexpr uint32_t kTsSmem = kTsSmemUsed > 120 * 1024 ? kTsSmemUsed : 120 * 1024;
+
+template <bool kGrouped>
+__global__ void __launch_bounds__(kUmThreads, 1)
+w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
+                     const __grid_constant__ CUtensorMap map_z, const __grid_constant__ CUtensorMap map_a, const UmParams p,
+                     const __grid_constant__ std::conditional_t<kGrouped, UmGroup, gemm::NoGroup> group) {
+    uint32_t n_items = p.n_tiles;
+    if constexpr (kGrouped) n_items = p.n_tiles * p.n_problems;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t raw_ring = smem;
+    const uint32_t x_ring = smem + kUmRawStages * kUmRawStride;           // activations: [128 rows][64 k] bf16, 128-byte swizzle, per stage
+    const uint32_t bars = x_ring + kTsXStages * kUmABytes;
+    const uint32_t raw_full = bars, raw_empty = bars + 8 * kUmRawStages;
+    const uint32_t ab_full = raw_empty + 8 * kUmRawStages, ab_empty = ab_full + 8 * kUmAbStages;
+    const uint32_t acc_full = ab_empty + 8 * kUmAbStages, acc_empty = acc_full + 8;
+    const uint32_t x_full = acc_empty + 8, x_empty = x_full + 8 * kTsXStages;
+    __shared__ uint32_t tmem_holder;
+    __shared__ int s_abort;
+    volatile int* abort_flag = &s_abort;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t n_chunks = p.n_chunks;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kUmRawStages; ++s) {
+            ptx::mbar_init(raw_full + 8 * s, 1);
+            ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps);
+        }
+        for (uint32_t s = 0; s < kUmAbStages; ++s) {
+            ptx::mbar_init(ab_full + 8 * s, kUmDqWarps);          // sixteen warps' weights in tensor memory
+            ptx::mbar_init(ab_empty + 8 * s, 1);
+        }
+        for (uint32_t s = 0; s < kTsXStages; ++s) {
+            ptx::mbar_init(x_full + 8 * s, 1);
+            ptx::mbar_init(x_empty + 8 * s, 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        ptx::mbar_init(acc_empty, kUmDqWarps);
+        s_abort = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+        ptx::tma_prefetch_desc(&map_w);
+        ptx::tma_prefetch_desc(&map_s);
+        ptx::tma_prefetch_desc(&map_z);
+        ptx::tma_prefetch_desc(&map_a);
+    }
+    if (warp == kUmDqWarps + 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&tmem_holder), kTsTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_holder;
+    ptx::grid_launch_dependents();
+    ptx::grid_dependency_wait();
+
+    if (warp == kUmDqWarps) {
+        if (lane == 0) {
+            // ---------------------------------------------------------- raw weights, scales, zero points: three TMA boxes per chunk
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                uint32_t prob = 0, tile = item;
+                if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
+                const CUtensorMap* mw = &map_w;
+                const CUtensorMap* ms = &map_s;
+                const CUtensorMap* mz = &map_z;
+                if constexpr (kGrouped) { mw = &group.maps[4 * prob]; ms = &group.maps[4 * prob + 1]; mz = &group.maps[4 * prob + 2]; }
+                const uint32_t n0 = tile * kUmBN;
+                for (uint32_t c = 0; c < n_chunks; ++c) {
+                    if (!ptx::mbar_wait_relaxed(raw_empty + 8 * stage, phase ^ 1, abort_flag, p.wait_limit_ns, 64)) {
+                        atomicCAS(p.status, 0, kStatusProducerTimeout | (int)(c & 0xFFFFFF));
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = raw_full + 8 * stage, dst = raw_ring + stage * kUmRawStride;
+                    const uint32_t grp = c * kUmBK / p.group;
+                    ptx::mbar_arrive_expect_tx(fb, kUmRawBytes);
+                    if (p.tiled) {
+                        // tile-major layout: the chunk's 8 KB of words are contiguous, as are its scales and zero points
+                        ptx::tma_load_3d(dst, mw, fb, 0, (int32_t)(c * (kUmBK / 8)), (int32_t)tile);
+                        ptx::tma_load_3d(dst + 8 * kUmBN * 4, ms, fb, 0, (int32_t)grp, (int32_t)tile);
+                        ptx::tma_load_3d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, 0, (int32_t)grp, (int32_t)tile);
+                    } else {
+                        ptx::tma_load_2d(dst, mw, fb, (int32_t)n0, (int32_t)(c * (kUmBK / 8)));
+                        ptx::tma_load_2d(dst + 8 * kUmBN * 4, ms, fb, (int32_t)n0, (int32_t)grp);
+                        ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, (int32_t)(n0 / 8), (int32_t)grp);
+                    }
+                    if (++stage == kUmRawStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        } else if (lane == 1) {
+            // ---------------------------------------------------------- activations: one 128-row box per chunk (rows beyond M are zero)
+            uint32_t as = 0, aphase = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+                uint32_t prob = 0;
+                if constexpr (kGrouped) prob = item / p.n_tiles;
+                const CUtensorMap* ma = &map_a;
+                if constexpr (kGrouped) ma = &group.maps[4 * prob + 3];
+                for (uint32_t c = 0; c < n_chunks; ++c) {
+                    if (!ptx::mbar_wait_relaxed(x_empty + 8 * as, aphase ^ 1, abort_flag, p.wait_limit_ns, 64)) {
+                        atomicCAS(p.status, 0, kStatusProducerTimeout | 0x400000 | (int)(c & 0x3FFFFF));
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(x_full + 8 * as, kUmABytes);
+                    ptx::tma_load_3d(x_ring + as * kUmABytes, ma, x_full + 8 * as, (int32_t)(c * kUmBK), 0, 0);
+                    if (++as == kTsXStages) { as = 0; aphase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == kUmDqWarps + 1) {
+        // -------------------------------------------------------------- UMMA issuer: per chunk 2 halves x 4 k-steps of M 128 x N 128 x K 16
+        if (lane == 0) {
+            constexpr uint32_t kIdesc = ptx::make_idesc_bf16_f32(128, 128, 0u);
+            uint32_t stage = 0, phase = 0, iter = 0, xs = 0, xphase = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++iter) {
+                if (iter > 0 && !ptx::mbar_wait(acc_empty, (iter - 1) & 1, abort_flag, p.wait_limit_ns)) {
+                    atomicCAS(p.status, 0, kStatusMmaTimeout | 0x800000);
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                for (uint32_t c = 0; c < n_chunks; ++c) {
+                    if (!ptx::mbar_wait(ab_full + 8 * stage, phase, abort_flag, p.wait_limit_ns) ||
+                        !ptx::mbar_wait(x_full + 8 * xs, xphase, abort_flag, p.wait_limit_ns)) {
+                        atomicCAS(p.status, 0, kStatusMmaTimeout | (int)(c & 0x7FFFFF));
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t x_addr = x_ring + xs * kUmABytes;
+                    const uint32_t a_cols = tmem_base + kTsABase + stage * kTsAStageCols;
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < kUmBK / 16; ++k4) {
+                        if (p.probe == 1 && (c | k4) != 0) break;
+                        const uint64_t db = ptx::make_smem_desc(x_addr + k4 * 32, 16, 1024);
+#pragma unroll
+                        for (uint32_t t = 0; t < 2; ++t)
+                            ptx::umma_bf16_ts(tmem_base + t * 128, a_cols + t * 32 + k4 * 8, db, kIdesc, (c | k4) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(ab_empty + 8 * stage);
+                    ptx::umma_commit(x_empty + 8 * xs);
+                    if (++stage == kUmAbStages) { stage = 0; phase ^= 1; }
+                    if (++xs == kTsXStages) { xs = 0; xphase ^= 1; }
+                }
+                if (ok) ptx::umma_commit(acc_full);
+            }
+        }
+    } else {
+        // -------------------------------------------------------------- sixteen warps: dequantise into tensor memory, then the epilogue
+        const uint32_t q = warp & 3, t = (warp >> 2) & 1, h = warp >> 3;   // lane quadrant, 128-column half of the tile, k half of a chunk
+        const uint32_t n = t * 128 + q * 32 + lane;                          // this thread's column of the tile
+        const uint32_t lane_base = (q * 32) << 16;
+        uint32_t mask, magic;
+        asm volatile("mov.b32 %0, 0x000F000F;" : "=r"(mask));
+        asm volatile("mov.b32 %0, 0x43004300;" : "=r"(magic));
+        uint32_t rs = 0, rphase = 0, as = 0, aphase = 0, iter = 0;
+        bool ok = true;
+        for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
+            uint32_t prob = 0, tile = item;
+            if constexpr (kGrouped) { prob = item / p.n_tiles; tile = item - prob * p.n_tiles; }
+            const uint32_t n0 = tile * kUmBN;
+            for (uint32_t c = 0; ok && c < n_chunks; ++c) {
+                if (!ptx::mbar_wait(raw_full + 8 * rs, rphase, abort_flag, p.wait_limit_ns)) {
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | (int)(c & 0x3FFFFF));
+                    ok = false;
+                    break;
+                }
+                const uint32_t raw = raw_ring + rs * kUmRawStride;
+                uint32_t words[4];
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) words[i] = um_lds32(raw + (h * 4 + i) * (kUmBN * 4) + n * 4);
+                const uint32_t sbits = um_lds16(raw + 8 * kUmBN * 4 + n * 2);
+                const uint32_t zword = um_lds32(raw + 8 * kUmBN * 4 + kUmBN * 2 + (n >> 3) * 4);
+                const uint32_t zz = ((zword >> ((n & 7) * 4)) & 0xFu) * 0x00010001u + 0x43004300u;     // bf16x2 (128+z, 128+z)
+                const uint32_t ss = sbits * 0x00010001u;                                               // (s, s)
+                // the A stage is free once the UMMAs of three chunks ago have read it
+                if (!ptx::mbar_wait(ab_empty + 8 * as, aphase ^ 1, abort_flag, p.wait_limit_ns)) {
+                    if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0x800000 | (int)(c & 0x3FFFFF));
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after_sync();
+                const uint32_t a_cols = tmem_base + lane_base + kTsABase + as * kTsAStageCols + t * 32 + h * 16;
+#pragma unroll
+                for (uint32_t jj = 0; jj < 2; ++jj) {          // one k-step of 16 = two packed words = eight columns of bf16 pairs
+                    if (p.probe == 2) break;
+                    uint32_t r8[8];
+#pragma unroll
+                    for (uint32_t half = 0; half < 2; ++half) {
+                        const uint32_t wd = words[2 * jj + half];
+                        const uint32_t v0 = bf16x2_mul(bf16x2_sub(and_or(wd, mask, magic), zz), ss);            // k 0, 4
+                        const uint32_t v1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz), ss);       // k 1, 5
+                        const uint32_t v2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz), ss);       // k 2, 6
+                        const uint32_t v3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz), ss);      // k 3, 7
+                        // k order: (0,1) (2,3) (4,5) (6,7), two consecutive k per tensor-memory column
+                        r8[half * 4 + 0] = __byte_perm(v0, v1, 0x5410);
+                        r8[half * 4 + 1] = __byte_perm(v2, v3, 0x5410);
+                        r8[half * 4 + 2] = __byte_perm(v0, v1, 0x7632);
+                        r8[half * 4 + 3] = __byte_perm(v2, v3, 0x7632);
+                    }
+                    ptx::tmem_st_32x32b_x8(a_cols + jj * 8, r8);
+                }
+                ptx::fence_proxy_async_smem();       // the raw stage was read through the generic proxy and TMA will overwrite it
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    ptx::mbar_arrive(raw_empty + 8 * rs);
+                    ptx::mbar_arrive(ab_full + 8 * as);
+                }
+                if (++rs == kUmRawStages) { rs = 0; rphase ^= 1; }
+                if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
+            }
+            // ---- epilogue: y[m][n0 + n] = D[lane n][column m]; a warp stores 32 consecutive columns of one row per instruction
+            if (ok && !ptx::mbar_wait(acc_full, iter & 1, abort_flag, p.wait_limit_ns)) {
+                if (lane == 0) atomicCAS(p.status, 0, kStatusEpilogueTimeout | 0xC00000);
+                ok = false;
+            }
+            if (!ok) break;
+            ptx::tc_fence_after_sync();
+            float* y_out = p.y;
+            if constexpr (kGrouped) y_out = group.y[prob];
+            const uint32_t col = n0 + n;
+            // this warp: lanes of quadrant q, accumulator half t, rows (columns of the accumulator) h * 64 .. h * 64 + 63
+#pragma unroll 1
+            for (uint32_t mc = 0; mc < 2; ++mc) {
+                const uint32_t m0 = h * 64 + mc * 32;
+                if (m0 >= p.M) break;                 // warp-uniform
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(tmem_base + lane_base + t * 128 + m0, r);
+                ptx::tmem_ld_wait();
+                if (col < p.N) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j)
+                        if (m0 + j < p.M) y_out[(size_t)(m0 + j) * p.N + col] = __uint_as_float(r[j]);
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(acc_empty);
+        }
+    }
+
+    __syncwarp();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == kUmDqWarps + 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTsTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ tile-major weight layout
+//
+// The row layout puts the 8 KB of packed words a CTA needs per chunk in eight 1 KB pieces 4N bytes apart; HBM serves that
+// pattern at about a third of its copy bandwidth, which is then what bounds these kernels (not the arithmetic, not the
+// UMMAs).  The tile-major layout stores every 256-column tile as a matrix of its own, so a chunk's words, scales and zero
+// points are each one contiguous piece:
+//   words  [T][K/8][256] u32, scales [T][K/G][256] bf16, zero points [T][K/G][32] u32, T = ceil(N / 256), columns past N zero.
+struct TiledLayout { size_t off_words, off_scales, off_zeros, total; uint32_t tiles, rows, groups; };
+
+TiledLayout tiled_layout(uint32_t K, uint32_t N, uint32_t group) {
+    TiledLayout L;
+    L.tiles = ceil_div(N, kUmBN); L.rows = K / 8; L.groups = K / group;
+    L.off_words = 0;
+    L.off_scales = (size_t)L.tiles * L.rows * kUmBN * 4;
+    L.off_zeros = L.off_scales + (size_t)L.tiles * L.groups * kUmBN * 2;
+    L.total = L.off_zeros + (size_t)L.tiles * L.groups * (kUmBN / 8) * 4;
+    return L;
+}
+
+// Row layout -> tile-major layout: one thread per output word / scale / zero-point word.
+__global__ void w4_to_tiled_kernel(const uint32_t* __restrict__ packed, const uint16_t* __restrict__ scales, const uint32_t* __restrict__ zeros,
+                                   uint8_t* __restrict__ out, uint32_t N, uint32_t nz, TiledLayout L) {
+    const uint64_t n_words = (uint64_t)L.tiles * L.rows * kUmBN;
+    const uint64_t n_scales = (uint64_t)L.tiles * L.groups * kUmBN;
+    const uint64_t n_zwords = (uint64_t)L.tiles * L.groups * (kUmBN / 8);
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words + n_scales + n_zwords; i += stride) {
+        if (i < n_words) {
+            const uint32_t c = (uint32_t)(i % kUmBN);
+            const uint64_t r = i / kUmBN;
+            const uint32_t row = (uint32_t)(r % L.rows), tile = (uint32_t)(r / L.rows);
+            const uint32_t n = tile * kUmBN + c;
+            ((uint32_t*)(out + L.off_words))[i] = n < N ? packed[(size_t)row * N + n] : 0u;
+        } else if (i < n_words + n_scales) {
+            const uint64_t j = i - n_words;
+            const uint32_t c = (uint32_t)(j % kUmBN);
+            const uint64_t r = j / kUmBN;
+            const uint32_t g = (uint32_t)(r % L.groups), tile = (uint32_t)(r / L.groups);
+            const uint32_t n = tile * kUmBN + c;
+            ((uint16_t*)(out + L.off_scales))[j] = n < N ? scales[(size_t)g * N + n] : (uint16_t)0;
+        } else {
+            const uint64_t j = i - n_words - n_scales;
+            const uint32_t wz = (uint32_t)(j % (kUmBN / 8));
+            const uint64_t r = j / (kUmBN / 8);
+            const uint32_t g = (uint32_t)(r % L.groups), tile = (uint32_t)(r / L.groups);
+            const uint32_t n0 = tile * kUmBN + wz * 8;
+            ((uint32_t*)(out + L.off_zeros))[j] = n0 < N ? zeros[(size_t)g * nz + (n0 >> 3)] : 0u;
+        }
+    }
+}
+
 }  // namespace
 
 namespace t0 {
@@ -471,19 +813,36 @@ static int um_maps(uint64_t a, uint64_t packed, uint64_t scales, uint64_t zeros,
     return rc;
 }
 
-template <bool kGrouped>
+// The same four maps over the tile-major buffer: 3-D views (column in tile, row, tile).
+static int um_maps_tiled(uint64_t a, uint64_t tiled, uint32_t M, uint32_t N, uint32_t K, uint32_t group, CUtensorMap* out4) {
+    const TiledLayout L = tiled_layout(K, N, group);
+    const uint8_t* base = (const uint8_t*)tiled;
+    int rc = gemm::make_map_3d_plain(&out4[0], base + L.off_words, 4, kUmBN, L.rows, L.tiles, kUmBN * 4, (uint64_t)L.rows * kUmBN * 4, kUmBN, kUmBK / 8);
+    if (rc == T0_OK) rc = gemm::make_map_3d_plain(&out4[1], base + L.off_scales, 2, kUmBN, L.groups, L.tiles, kUmBN * 2, (uint64_t)L.groups * kUmBN * 2, kUmBN, 1);
+    if (rc == T0_OK) rc = gemm::make_map_3d_plain(&out4[2], base + L.off_zeros, 4, kUmBN / 8, L.groups, L.tiles, (kUmBN / 8) * 4, (uint64_t)L.groups * (kUmBN / 8) * 4, kUmBN / 8, 1);
+    if (rc == T0_OK) rc = gemm::make_map_kmajor(&out4[3], (const void*)a, M, K, K, 1, 128);
+    return rc;
+}
+
+static bool um_tiled_supported(uint64_t a, uint64_t tiled, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
+    if (M == 0 || M > 128 || N == 0 || K == 0 || K % kUmBK || group == 0 || group % kUmBK || K % group) return false;
+    return ((a | tiled) & 15) == 0 && (y & 3) == 0;
+}
+
+template <bool kGrouped, bool kTs = false>
 static int um_launch(t0_runtime* rt, const CUtensorMap* m4, UmParams p, uint32_t split, const std::conditional_t<kGrouped, UmGroup, gemm::NoGroup>& group) {
-    auto kern = w4a16_umma_kernel<kGrouped>;
+    auto kern = kTs ? w4a16_umma_ts_kernel<kGrouped> : w4a16_umma_kernel<kGrouped>;     // kTs: weights as the tensor-memory operand (K not split)
+    constexpr uint32_t kSmemBytes = kTs ? kTsSmem : kUmSmem;
     static bool attr_set[64] = {};
     static int max_clusters[64][5] = {};
     if (rt->device >= 64) return fail(T0_ERR_INVALID, "device ordinal out of range");
     if (!attr_set[rt->device]) {
-        T0_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kUmSmem));
+        T0_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_set[rt->device] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kUmThreads, 1, 1);
-    cfg.dynamicSmemBytes = kUmSmem;
+    cfg.dynamicSmemBytes = kSmemBytes;
     cfg.stream = rt->stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -520,6 +879,8 @@ static UmParams um_params(t0_runtime* rt, uint64_t a, uint64_t y, uint32_t M, ui
     p.M = M; p.N = N; p.K = K; p.group = group;
     p.n_tiles = ceil_div(N, kUmBN);
     p.n_chunks = K / kUmBK;
+    static const uint32_t probe = getenv("T0_W4_UMMA_PROBE") ? (uint32_t)atoi(getenv("T0_W4_UMMA_PROBE")) : 0u;
+    p.probe = probe;
     return p;
 }
 
@@ -534,6 +895,39 @@ int launch_w4a16_umma(t0_runtime* rt, uint64_t a, uint64_t packed, uint64_t scal
     if (rc != T0_OK) return rc;
     const gemm::NoGroup none = {0};
     return um_launch<false>(rt, m4, p, split, none);
+}
+
+int launch_w4a16_umma_tiled(t0_runtime* rt, uint64_t a, uint64_t tiled, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
+    UmParams p = um_params(rt, a, y, M, N, K, group);
+    p.tiled = 1;
+    uint32_t split = std::max<uint32_t>(1, std::min<uint32_t>(4, (uint32_t)rt->sm_count / std::max<uint32_t>(1, p.n_tiles)));
+    split = std::min(split, p.n_chunks);
+    CUtensorMap m4[4];
+    int rc = um_maps_tiled(a, tiled, M, N, K, group, m4);
+    if (rc != T0_OK) return rc;
+    const gemm::NoGroup none = {0};
+    return split == 1 ? um_launch<false, true>(rt, m4, p, 1, none) : um_launch<false, false>(rt, m4, p, split, none);
+}
+
+int launch_w4a16_umma_tiled_grouped(t0_runtime* rt, const t0_w4a16_args* args, uint32_t count) {
+    if (count == 0) return T0_OK;
+    if (count > kUmMaxGroup) return fail(T0_ERR_INVALID, "at most %u problems per grouped launch (got %u)", kUmMaxGroup, count);
+    const t0_w4a16_args& a0 = args[0];
+    static UmGroup grp;
+    static std::mutex grp_mu;
+    std::lock_guard<std::mutex> lock(grp_mu);
+    for (uint32_t i = 0; i < count; ++i) {
+        const t0_w4a16_args& a = args[i];
+        if (a.m != a0.m || a.n != a0.n || a.k != a0.k || a.group != a0.group) return fail(T0_ERR_INVALID, "grouped launch: problem %u differs from problem 0 in shape", i);
+        if (!um_tiled_supported(a.a, a.packed, a.y, a.m, a.n, a.k, a.group)) return fail(T0_ERR_UNSUPPORTED, "grouped launch: problem %u is not a shape of the fused tcgen05 kernel", i);
+        int rc = um_maps_tiled(a.a, a.packed, a.m, a.n, a.k, a.group, &grp.maps[4 * i]);
+        if (rc != T0_OK) return rc;
+        grp.y[i] = (float*)a.y;
+    }
+    UmParams p = um_params(rt, a0.a, a0.y, a0.m, a0.n, a0.k, a0.group);
+    p.n_problems = count;
+    p.tiled = 1;
+    return um_launch<true, true>(rt, grp.maps, p, 1, grp);
 }
 
 // Up to 32 problems of one shape in one launch, K not split: the CTAs walk the column tiles of all the problems, so launch,
@@ -556,7 +950,81 @@ int launch_w4a16_umma_grouped(t0_runtime* rt, const t0_w4a16_args* args, uint32_
     }
     UmParams p = um_params(rt, a0.a, a0.y, a0.m, a0.n, a0.k, a0.group);
     p.n_problems = count;
-    return um_launch<true>(rt, grp.maps, p, 1, grp);
+    static const bool smem_form = getenv("T0_W4_UMMA_SS") != nullptr;     // comparison switch: dequantised weights through shared memory
+    return smem_form ? um_launch<true, false>(rt, grp.maps, p, 1, grp) : um_launch<true, true>(rt, grp.maps, p, 1, grp);
 }
 
 }  // namespace t0
+
+extern "C" {
+
+size_t t0_w4_tiled_bytes(uint32_t K, uint32_t N, uint32_t group) {
+    if (K == 0 || N == 0 || group == 0 || K % kUmBK || group % kUmBK || K % group) return 0;
+    return tiled_layout(K, N, group).total;
+}
+
+int t0_w4_to_tiled(t0_runtime* rt, uint64_t packed, uint64_t scales, uint64_t zeros, uint64_t out, uint32_t K, uint32_t N, uint32_t group) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!packed || !scales || !zeros || !out) return fail(T0_ERR_INVALID, "null device pointer");
+    if (K == 0 || N == 0 || group == 0 || K % kUmBK || group % kUmBK || K % group)
+        return fail(T0_ERR_UNSUPPORTED, "the tile-major layout needs K %% 64 == 0 and group %% 64 == 0 with group | K (K=%u, group=%u)", K, group);
+    if (out & 127) return fail(T0_ERR_INVALID, "the output buffer must be 128-byte aligned");
+    DeviceGuard guard(rt->device);
+    const TiledLayout L = tiled_layout(K, N, group);
+    const uint64_t n = L.total / 2;
+    const uint32_t grid = (uint32_t)std::min<uint64_t>((n + 255) / 256, 148ull * 16);
+    w4_to_tiled_kernel<<<grid, 256, 0, rt->stream>>>((const uint32_t*)packed, (const uint16_t*)scales, (const uint32_t*)zeros, (uint8_t*)out, N, (N + 7) / 8, L);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(T0_ERR_CUDA, "layout conversion launch failed: %s", cudaGetErrorString(e));
+    rt->launches.fetch_add(1);
+    return T0_OK;
+}
+
+int t0_w4a16_gemm_tiled(t0_runtime* rt, uint64_t a, uint64_t tiled, uint64_t y, uint32_t M, uint32_t N, uint32_t K, uint32_t group) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (M == 0 || N == 0) return T0_OK;
+    if (!a || !tiled || !y) return fail(T0_ERR_INVALID, "null device pointer");
+    if (!um_tiled_supported(a, tiled, y, M, N, K, group))
+        return fail(T0_ERR_UNSUPPORTED, "shape M=%u N=%u K=%u group=%u: needs M <= 128, K %% 64 == 0, group %% 64 == 0, group | K, a and the weights 16-byte aligned", M, N, K, group);
+    DeviceGuard guard(rt->device);
+    return launch_w4a16_umma_tiled(rt, a, tiled, y, M, N, K, group);
+}
+
+int t0_w4a16_gemm_tiled_grouped(t0_runtime* rt, const t0_w4a16_args* args, size_t count) {
+    int rc = check_rt(rt);
+    if (rc != T0_OK) return rc;
+    if (!args && count) return fail(T0_ERR_INVALID, "null arguments");
+    for (size_t i = 0; i < count; ++i) {
+        const t0_w4a16_args& a = args[i];
+        if (a.m == 0 || a.n == 0) return fail(T0_ERR_INVALID, "grouped launch: problem %zu is empty", i);
+        if (!a.a || !a.packed || !a.y) return fail(T0_ERR_INVALID, "null device pointer in problem %zu", i);
+        if (!um_tiled_supported(a.a, a.packed, a.y, a.m, a.n, a.k, a.group))
+            return fail(T0_ERR_UNSUPPORTED, "problem %zu: needs M <= 128, K %% 64 == 0, group %% 64 == 0, group | K, a and the weights 16-byte aligned", i);
+        // the problems run at the same time: no output may be an activation or the output of another problem
+        const uint64_t y_lo = a.y, y_hi = a.y + (uint64_t)a.m * a.n * 4;
+        for (size_t j = 0; j < count; ++j) {
+            if (j == i) continue;
+            const t0_w4a16_args& b = args[j];
+            const uint64_t by_hi = b.y + (uint64_t)b.m * b.n * 4, ba_hi = b.a + (uint64_t)b.m * b.k * 2;
+            if ((y_lo < by_hi && b.y < y_hi) || (y_lo < ba_hi && b.a < y_hi))
+                return fail(T0_ERR_INVALID, "grouped launch: the output of problem %zu overlaps the activations or the output of problem %zu (the problems run concurrently)", i, j);
+        }
+    }
+    DeviceGuard guard(rt->device);
+    // runs of equal shapes share a launch (up to 32 problems each)
+    size_t i = 0;
+    while (i < count) {
+        size_t n = 1;
+        while (i + n < count && n < kUmMaxGroup && args[i + n].m == args[i].m && args[i + n].n == args[i].n && args[i + n].k == args[i].k && args[i + n].group == args[i].group) ++n;
+        rc = n == 1 ? launch_w4a16_umma_tiled(rt, args[i].a, args[i].packed, args[i].y, args[i].m, args[i].n, args[i].k, args[i].group)
+                    : launch_w4a16_umma_tiled_grouped(rt, args + i, (uint32_t)n);
+        if (rc != T0_OK) return rc;
+        i += n;
+    }
+    return T0_OK;
+}
+
+}  // extern "C"
+

@@ -318,6 +318,10 @@ extern "C" {
     pub fn t0_w4_prepack(rt: *mut t0_runtime, packed: u64, scales: u64, zeros: u64, out: u64, K: u32, N: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm_prepacked(rt: *mut t0_runtime, a: u64, prepacked: u64, y: u64, M: u32, N: u32, K: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm_prepacked_batch(rt: *mut t0_runtime, args: *const t0_w4a16_args, count: usize) -> c_int;
+    pub fn t0_w4_tiled_bytes(K: u32, N: u32, group: u32) -> usize;
+    pub fn t0_w4_to_tiled(rt: *mut t0_runtime, packed: u64, scales: u64, zeros: u64, out: u64, K: u32, N: u32, group: u32) -> c_int;
+    pub fn t0_w4a16_gemm_tiled(rt: *mut t0_runtime, a: u64, tiled: u64, y: u64, M: u32, N: u32, K: u32, group: u32) -> c_int;
+    pub fn t0_w4a16_gemm_tiled_grouped(rt: *mut t0_runtime, args: *const t0_w4a16_args, count: usize) -> c_int;
     pub fn t0_w4a16_gemm_static(rt: *mut t0_runtime, a: u64, packed: u64, scales: u64, zeros: u64, y: u64, M: u32, N: u32, K: u32, group: u32) -> c_int;
     pub fn t0_w4a16_gemm_static_scratch_bytes() -> usize;
     pub fn t0_int4_wmma_config_k16(out: *mut t0_int4_wmma_config) -> c_int;

@@ -488,3 +488,88 @@ def test_grouped_large_m_problems_in_one_launch(t0, oracle, rt, M, K, N, G, coun
             rt.w4a16_gemm_grouped(bad)
     for b in bufs:
         b.free()
+
+
+@pytest.mark.parametrize("K,N,G", [(64, 32, 64), (512, 288, 128), (256, 1000, 128), (1024, 11008, 256)])
+def test_tiled_layout_conversion_is_bit_exact(t0, oracle, rt, K, N, G):
+    # the tile-major layout is an index remap of the row layout: the device conversion against the oracle's, byte for byte
+    # (partial last tiles and N that is not a multiple of 8 words of zero points included)
+    if N % 8:
+        pytest.skip("the row layout itself needs N % 8 == 0")
+    packed, scales, zeros = make_w4(oracle, K, N, G, seed=K + N)
+    xp, xs, xz = rt.upload(packed), rt.upload(scales), rt.upload(zeros)
+    tiled = rt.w4_to_tiled(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G)
+    rt.synchronize()
+    want = oracle.w4_to_tiled(packed, scales, zeros, K, N, G)
+    got = tiled.read(len(want), np.uint8)
+    assert np.array_equal(got, want)
+    for b in (xp, xs, xz, tiled):
+        b.free()
+
+
+@pytest.mark.parametrize("M,K,N,G,count", [(128, 4096, 1536, 128, 5), (17, 512, 288, 128, 3), (100, 1024, 11008, 256, 4), (64, 192, 8200, 64, 40),
+                                           (1, 256, 1000, 128, 2), (128, 128, 256, 64, 1)])
+def test_tiled_weights_single_and_grouped(t0, oracle, rt, M, K, N, G, count):
+    # tile-major weights: one problem per launch (K split over a cluster where that fills the GPU) and up to 32 per launch (K
+    # not split, weights as the tensor-memory operand), each y against the oracle, guard words untouched; N with a partial last
+    # tile and N that the row-layout kernel would refuse (N % 32 != 0) included
+    acts = [oracle.fill_normal_bf16(M * K, 170 + i) for i in range(min(count, 3))]
+    w = [make_w4(oracle, K, N, G, seed=M + K + 9 * i) for i in range(min(count, 3))]
+    refs = [oracle.w4a16_gemm(acts[j], *w[j], M, N, K, G) for j in range(len(acts))]
+    tiled = []
+    for j in range(len(acts)):
+        xp, xs, xz = rt.upload(w[j][0]), rt.upload(w[j][1]), rt.upload(w[j][2])
+        tiled.append(rt.w4_to_tiled(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G))
+        rt.synchronize()
+        for b in (xp, xs, xz):
+            b.free()
+    xas = [rt.upload(a) for a in acts]
+    ys, calls = [], []
+    for i in range(count):
+        y = rt.alloc(M * N * 4 + 4096)
+        y.write(np.full(M * N + 1024, -9999.0, np.float32))
+        ys.append(y)
+        calls.append(t0.W4A16Args(xas[i % len(acts)].gpu_addr(), tiled[i % len(acts)].gpu_addr(), 0, 0, y.gpu_addr(), M, N, K, G))
+    rt.w4a16_gemm_tiled(xas[0].gpu_addr(), tiled[0].gpu_addr(), ys[0].gpu_addr(), M, N, K, G)
+    rt.synchronize()
+    assert_close(ys[0].read(M * N * 4, np.float32).reshape(M, N), refs[0], K)
+    ys[0].write(np.full(M * N + 1024, -9999.0, np.float32))
+    before = rt.launch_count()
+    rt.w4a16_gemm_tiled_grouped(calls)
+    rt.synchronize()
+    assert rt.launch_count() - before == -(-count // 32)
+    for i, y in enumerate(ys):
+        assert_close(y.read(M * N * 4, np.float32).reshape(M, N), refs[i % len(acts)], K)
+        assert np.all(y.read_bytes(M * N * 4, 4096, np.float32) == -9999.0), "wrote past the output"
+    for b in tiled + xas + ys:
+        b.free()
+
+
+def test_tiled_grouped_dequantises_bit_exactly(t0, oracle, rt):
+    # one-hot activations through the grouped launch (weights as the tensor-memory operand): row m of y is row base + m of the
+    # dequantised weights, exactly
+    K, G, M, N = 256, 128, 128, 2048
+    rng = np.random.default_rng(12)
+    packed = rng.integers(0, 2 ** 32, size=(K // 8, N), dtype=np.uint64).astype(np.uint32)
+    col = np.arange(N, dtype=np.uint32)
+    sbits = np.stack([(0x3A00 + (col % 0x400)).astype(np.uint16) | ((col // 0x400 % 2) << 15).astype(np.uint16), (0x3B80 + (col % 0x300)).astype(np.uint16)])
+    zeros = rng.integers(0, 2 ** 32, size=(K // G, N // 8), dtype=np.uint64).astype(np.uint32)
+    want = oracle.bf16_to_f32(oracle.dequant_w4_b200(packed, sbits, zeros, K, N, G)).reshape(K, N)
+    xp, xs, xz = rt.upload(packed), rt.upload(sbits), rt.upload(zeros)
+    tiled = rt.w4_to_tiled(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G)
+    bufs, calls, ys = [xp, xs, xz, tiled], [], []
+    for base in (0, 128):
+        a = np.zeros((M, K), np.uint16)
+        for m in range(M):
+            a[m, base + m] = 0x3F80
+        xa, y = rt.upload(a), rt.alloc(M * N * 4)
+        bufs += [xa, y]
+        ys.append(y)
+        calls.append(t0.W4A16Args(xa.gpu_addr(), tiled.gpu_addr(), 0, 0, y.gpu_addr(), M, N, K, G))
+    rt.w4a16_gemm_tiled_grouped(calls)
+    rt.synchronize()
+    for base, y in zip((0, 128), ys):
+        got = y.read(M * N * 4, np.float32).reshape(M, N)
+        assert np.array_equal(got.view(np.uint32) & 0x7FFFFFFF, want[base:base + M].view(np.uint32) & 0x7FFFFFFF), base
+    for b in bufs:
+        b.free()
