@@ -50,7 +50,6 @@ struct UmParams {
     uint32_t group;          // k per scale / zero-point row (a multiple of 64)
     uint32_t n_tiles, n_chunks, split;
     uint32_t tiled;          // the weights are in the tile-major layout (3-D maps: column in tile, row, tile) instead of the row layout
-    uint32_t probe;          // measurement switch (T0_W4_UMMA_PROBE, results are wrong): 1 = no UMMAs, 2 = no dequantisation arithmetic
     uint32_t n_problems;     // grouped launch: problems of one shape in this launch (their maps and outputs ride in the group record)
 };
 
@@ -479,8 +478,9 @@ constexpr uint32_t kTsABase = 256;                         // first column of th
 constexpr uint32_t kTsAStageCols = 64;
 // (the request is padded past half an SM's shared memory: the kernel takes all 512 tensor-memory columns, so two of its CTAs
 // must never share an SM)
-constexpr uint32_t kTsXStages = 8;                         // activation stages: a 16 KB box from L2 takes about a microsecond, several chunk periods
-constexpr uint32_t kTsSmemUsed = kUmRawStages * kUmRawStride + kTsXStages * kUmABytes + 512 + 1024;
+constexpr uint32_t kTsXStages = 4;                         // activation stages (16 KB boxes from L2)
+constexpr uint32_t kTsRawStages = 14;                      // raw weight stages: 124 KB in flight per SM; with six the kernel was bound by bytes in flight x latency
+constexpr uint32_t kTsSmemUsed = kTsRawStages * kUmRawStride + kTsXStages * kUmABytes + 512 + 1024;
 constexpr uint32_t kTsSmem = kTsSmemUsed > 120 * 1024 ? kTsSmemUsed : 120 * 1024;
 
 template <bool kGrouped>
@@ -493,10 +493,10 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t raw_ring = smem;
-    const uint32_t x_ring = smem + kUmRawStages * kUmRawStride;           // activations: [128 rows][64 k] bf16, 128-byte swizzle, per stage
+    const uint32_t x_ring = smem + kTsRawStages * kUmRawStride;           // activations: [128 rows][64 k] bf16, 128-byte swizzle, per stage
     const uint32_t bars = x_ring + kTsXStages * kUmABytes;
-    const uint32_t raw_full = bars, raw_empty = bars + 8 * kUmRawStages;
-    const uint32_t ab_full = raw_empty + 8 * kUmRawStages, ab_empty = ab_full + 8 * kUmAbStages;
+    const uint32_t raw_full = bars, raw_empty = bars + 8 * kTsRawStages;
+    const uint32_t ab_full = raw_empty + 8 * kTsRawStages, ab_empty = ab_full + 8 * kUmAbStages;
     const uint32_t acc_full = ab_empty + 8 * kUmAbStages, acc_empty = acc_full + 8;
     const uint32_t x_full = acc_empty + 8, x_empty = x_full + 8 * kTsXStages;
     __shared__ uint32_t tmem_holder;
@@ -506,7 +506,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const uint32_t n_chunks = p.n_chunks;
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < kUmRawStages; ++s) {
+        for (uint32_t s = 0; s < kTsRawStages; ++s) {
             ptx::mbar_init(raw_full + 8 * s, 1);
             ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps);
         }
@@ -558,6 +558,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         ok = false;
                         break;
                     }
+                    ptx::fence_proxy_async_smem();           // the stage was read through the generic proxy, the copies write it through the async proxy
                     const uint32_t fb = raw_full + 8 * stage, dst = raw_ring + stage * kUmRawStride;
                     const uint32_t grp = c * kUmBK / p.group;
                     ptx::mbar_arrive_expect_tx(fb, kUmRawBytes);
@@ -571,7 +572,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         ptx::tma_load_2d(dst + 8 * kUmBN * 4, ms, fb, (int32_t)n0, (int32_t)grp);
                         ptx::tma_load_2d(dst + 8 * kUmBN * 4 + kUmBN * 2, mz, fb, (int32_t)(n0 / 8), (int32_t)grp);
                     }
-                    if (++stage == kUmRawStages) { stage = 0; phase ^= 1; }
+                    if (++stage == kTsRawStages) { stage = 0; phase ^= 1; }
                 }
             }
         } else if (lane == 1) {
@@ -619,7 +620,6 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     const uint32_t a_cols = tmem_base + kTsABase + stage * kTsAStageCols;
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < kUmBK / 16; ++k4) {
-                        if (p.probe == 1 && (c | k4) != 0) break;
                         const uint64_t db = ptx::make_smem_desc(x_addr + k4 * 32, 16, 1024);
 #pragma unroll
                         for (uint32_t t = 0; t < 2; ++t)
@@ -671,7 +671,6 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                 const uint32_t a_cols = tmem_base + lane_base + kTsABase + as * kTsAStageCols + t * 32 + h * 16;
 #pragma unroll
                 for (uint32_t jj = 0; jj < 2; ++jj) {          // one k-step of 16 = two packed words = eight columns of bf16 pairs
-                    if (p.probe == 2) break;
                     uint32_t r8[8];
 #pragma unroll
                     for (uint32_t half = 0; half < 2; ++half) {
@@ -688,7 +687,6 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     }
                     ptx::tmem_st_32x32b_x8(a_cols + jj * 8, r8);
                 }
-                ptx::fence_proxy_async_smem();       // the raw stage was read through the generic proxy and TMA will overwrite it
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -696,7 +694,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     ptx::mbar_arrive(raw_empty + 8 * rs);
                     ptx::mbar_arrive(ab_full + 8 * as);
                 }
-                if (++rs == kUmRawStages) { rs = 0; rphase ^= 1; }
+                if (++rs == kTsRawStages) { rs = 0; rphase ^= 1; }
                 if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
             }
             // ---- epilogue: y[m][n0 + n] = D[lane n][column m]; a warp stores 32 consecutive columns of one row per instruction
@@ -879,8 +877,6 @@ static UmParams um_params(t0_runtime* rt, uint64_t a, uint64_t y, uint32_t M, ui
     p.M = M; p.N = N; p.K = K; p.group = group;
     p.n_tiles = ceil_div(N, kUmBN);
     p.n_chunks = K / kUmBK;
-    static const uint32_t probe = getenv("T0_W4_UMMA_PROBE") ? (uint32_t)atoi(getenv("T0_W4_UMMA_PROBE")) : 0u;
-    p.probe = probe;
     return p;
 }
 
