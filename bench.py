@@ -654,6 +654,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-secondary", action="store_true", help="default single-GPU run: leave out the short runs of the other workloads")
     ap.add_argument("--layout", default="nt", choices=["nt", "nn"], help="B as WT[N,K] (the reference's native layout) or as B[K,N]")
+    ap.add_argument("--no-gather", action="store_true", help="sharded workload: leave out the gathered-C legs")
     ap.add_argument("--gather", action="store_true", help="sharded workload: also time GEMM + in-place NCCL all-gather of C, and the one-kernel form whose epilogue stores to every rank (reported under \"gather\")")
     ap.add_argument("--row-layout", action="store_true", help="W4A16 workloads: weights in the row layout instead of the streaming layout")
     ap.add_argument("--lib-ab", action="store_true", help="measurement only: time the vendor library's bf16 GEMM beside the repo's kernel (single GPU)")
@@ -763,7 +764,7 @@ def main():
     # optional: the gathered C.  Every rank's GEMM stores straight into slot `rank` of C_g[g][M][N/g]; one in-place
     # all-gather over NVLink completes it.  NCCL is issued on the runtime's own stream, so the device timer covers both.
     gather = None
-    if args.gather and sharded and world > 1:
+    if (args.gather or (default_run and not args.no_gather)) and sharded and world > 1:
         c_g = torch.empty((world, M, N), dtype=torch.float32, device="cuda")
         ext = torch.cuda.ExternalStream(rt.stream())
         xa, xb, _ = sets[0]
