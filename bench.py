@@ -800,8 +800,27 @@ def main():
         # ranks' buffers (its own and, over NVLink, the others' mapped through CUDA IPC).  No collective call at all.
         c_buf = rt.alloc(world * M * N * 4)
         handles = [None] * world
-        dist.all_gather_object(handles, c_buf.ipc_export())
-        mapped = {d: rt.ipc_open(handles[d]) for d in range(world) if d != rank}
+        mapped, why = {}, None
+        try:
+            mine = c_buf.ipc_export()
+        except Exception as exc:                    # every rank goes on to the agreement below
+            mine, why = None, str(exc)
+        dist.all_gather_object(handles, mine)
+        if all(h is not None for h in handles):
+            try:
+                mapped = {d: rt.ipc_open(handles[d]) for d in range(world) if d != rank}
+            except Exception as exc:
+                why = str(exc)
+        agree = torch.tensor([0.0 if why or len(mapped) != world - 1 else 1.0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+        if agree.item() != 1.0:
+            # some rank cannot map its peers' memory (no peer access between these GPUs, or no IPC in this container)
+            for ptr in mapped.values():
+                rt.ipc_close(ptr)
+            c_buf.free()
+            gather["fused"] = {"unavailable": why or "another rank could not map the peers' buffers"}
+            mapped = None
+    if gather is not None and "fused" not in gather:
         slot = rank * M * N * 4
         f_args = rt.gemm_args(xa.gpu_addr(), xb.gpu_addr(), c_buf.gpu_addr() + slot, M, N, K, **gemm_kw)
         peers = [mapped[d] + slot for d in sorted(mapped)]
