@@ -476,6 +476,7 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 constexpr uint32_t kTsTmemCols = 512;
 constexpr uint32_t kTsABase = 256;                         // first column of the A stages
 constexpr uint32_t kTsAStageCols = 64;
+constexpr uint32_t kTsAStages = 3;                         // (a fourth stage, which fills the 512 columns, measured no faster)
 // (the request is padded past half an SM's shared memory: the kernel takes all 512 tensor-memory columns, so two of its CTAs
 // must never share an SM)
 constexpr uint32_t kTsXStages = 4;                         // activation stages (16 KB boxes from L2)
@@ -496,8 +497,8 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
     const uint32_t x_ring = smem + kTsRawStages * kUmRawStride;           // activations: [128 rows][64 k] bf16, 128-byte swizzle, per stage
     const uint32_t bars = x_ring + kTsXStages * kUmABytes;
     const uint32_t raw_full = bars, raw_empty = bars + 8 * kTsRawStages;
-    const uint32_t ab_full = raw_empty + 8 * kTsRawStages, ab_empty = ab_full + 8 * kUmAbStages;
-    const uint32_t acc_full = ab_empty + 8 * kUmAbStages, acc_empty = acc_full + 8;
+    const uint32_t ab_full = raw_empty + 8 * kTsRawStages, ab_empty = ab_full + 8 * kTsAStages;
+    const uint32_t acc_full = ab_empty + 8 * kTsAStages, acc_empty = acc_full + 8;
     const uint32_t x_full = acc_empty + 8, x_empty = x_full + 8 * kTsXStages;
     __shared__ uint32_t tmem_holder;
     __shared__ int s_abort;
@@ -510,7 +511,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
             ptx::mbar_init(raw_full + 8 * s, 1);
             ptx::mbar_init(raw_empty + 8 * s, kUmDqWarps);
         }
-        for (uint32_t s = 0; s < kUmAbStages; ++s) {
+        for (uint32_t s = 0; s < kTsAStages; ++s) {
             ptx::mbar_init(ab_full + 8 * s, kUmDqWarps);          // sixteen warps' weights in tensor memory
             ptx::mbar_init(ab_empty + 8 * s, 1);
         }
@@ -627,7 +628,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     }
                     ptx::umma_commit(ab_empty + 8 * stage);
                     ptx::umma_commit(x_empty + 8 * xs);
-                    if (++stage == kUmAbStages) { stage = 0; phase ^= 1; }
+                    if (++stage == kTsAStages) { stage = 0; phase ^= 1; }
                     if (++xs == kTsXStages) { xs = 0; xphase ^= 1; }
                 }
                 if (ok) ptx::umma_commit(acc_full);
@@ -695,7 +696,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     ptx::mbar_arrive(ab_full + 8 * as);
                 }
                 if (++rs == kTsRawStages) { rs = 0; rphase ^= 1; }
-                if (++as == kUmAbStages) { as = 0; aphase ^= 1; }
+                if (++as == kTsAStages) { as = 0; aphase ^= 1; }
             }
             // ---- epilogue: y[m][n0 + n] = D[lane n][column m]; a warp stores 32 consecutive columns of one row per instruction
             if (ok && !ptx::mbar_wait(acc_full, iter & 1, abort_flag, p.wait_limit_ns)) {
