@@ -807,3 +807,35 @@ def test_grouped_launch_refuses_dependent_problems(t0, rt):
         rt.gemm_grouped(same_y)
     for buf in (x, b, y):
         rt.recycle(buf)
+
+
+@pytest.mark.parametrize("m,n,k,kw", [(128, 2048, 1024, dict(tile_n=128, split_k=4, pair_cta=2)), (64, 4096, 512, {}), (100, 1000, 256, dict(tile_n=64, pair_cta=2))])
+def test_grouped_launch_with_epilogues_and_bf16_output(t0, oracle, rt, m, n, k, kw):
+    # the grouped launch carries the same epilogues as the single launch: gemm_gen bias + ReLU, a TileIR chain, bf16 output;
+    # through the cluster split-K kernel (first case), the plain kernel chosen for the group (second) and ragged N (third)
+    count = 6
+    bias = (np.arange(n) % 11 - 5).astype(np.float32) * 0.25
+    xb_bias = rt.upload(bias)
+    a = [oracle.fill_uniform_bf16(m * k, 20 + i) for i in range(2)]
+    b = [oracle.fill_uniform_bf16(n * k, 600 + i) for i in range(2)]
+    xa, xb = [rt.upload(v) for v in a], [rt.upload(v) for v in b]
+    plain = [oracle.gemm_nt(a[i], b[i], m, k, n) for i in range(2)]
+    for what, extra, want_fn, out_bf16 in [("bias+relu", dict(bias=xb_bias.gpu_addr(), epilogue=2), lambda y: oracle.epilogue_gemm_gen(y, bias, 2), False),
+                                           ("chain", dict(bias=xb_bias.gpu_addr(), tile_epilogue=["bias", "scale", "silu"], scale=0.5),
+                                            lambda y: oracle.epilogue_tile(y, ["bias", "scale", "silu"], bias, 0.5, 0.0, 0.0), False),
+                                           ("bf16", dict(out_bf16=True), lambda y: y, True)]:
+        ys = [rt.alloc(m * n * 4) for _ in range(count)]
+        calls = [rt.gemm_args(xa[i % 2].gpu_addr(), xb[i % 2].gpu_addr(), ys[i].gpu_addr(), m, n, k, **kw, **extra) for i in range(count)]
+        rt.gemm_grouped(calls)
+        rt.synchronize()
+        for i in (0, 1, count - 1):
+            want = want_fn(plain[i % 2])
+            if out_bf16:
+                got = oracle.bf16_to_f32(ys[i].read(m * n * 2, np.uint16)).reshape(m, n)
+                assert np.abs(got - want).max() <= tol_abs(k) + np.abs(want).max() * 2.0 ** -8, what
+            else:
+                assert_gemm_close(rt.read_f32(ys[i], m * n).reshape(m, n), want, k)
+        for y in ys:
+            rt.recycle(y)
+    for buf in xa + xb + [xb_bias]:
+        rt.recycle(buf)
