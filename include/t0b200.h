@@ -499,7 +499,8 @@ int t0_w4a16_gemm_prepacked_batch(t0_runtime* rt, const t0_w4a16_args* args, siz
  * bandwidth; that, not the arithmetic, then bounds the fused tcgen05 kernel.  t0_w4_to_tiled rewrites the three arrays
  * once (weight-load time) into one buffer of t0_w4_tiled_bytes(K, N, group) bytes in which every 256-column tile is a matrix
  * of its own:  words [T][K/8][256] u32, then scales [T][K/group][256] bf16, then zero points [T][K/group][32] u32,
- * T = ceil(N / 256), columns past N zero.  K % 64 == 0, group % 64 == 0, group | K; any N.
+ * T = ceil(N / 256), columns past N zero; within a word code k (k = 0..7) sits in nibble (k >> 1) + 4 (k & 1), the order in
+ * which the kernels' pairwise extraction yields consecutive k.  K % 64 == 0, group % 64 == 0, group | K; any N.
  * t0_w4a16_gemm_tiled computes the same product as t0_w4a16_gemm from that buffer (M <= 128; y f32 [M,N]);
  * t0_w4a16_gemm_tiled_grouped takes INDEPENDENT problems (checked) whose .packed is the tile-major buffer (.scales / .zeros are
  * ignored) and runs consecutive problems of one shape up to 32 per launch: K is then not split, and the dequantised weights

@@ -234,12 +234,16 @@ def w4_prepack(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, K: int
 
 def w4_to_tiled(packed: np.ndarray, scales: np.ndarray, zeros: np.ndarray, K: int, N: int, group: int = 128) -> np.ndarray:
     """Tile-major layout of the B200 W4A16 kernel for 16 < M <= 128 (one uint8 buffer): every 256-column tile a matrix of its
-    own, words [T][K/8][256] u32, then scales [T][K/group][256] bf16, then zero points [T][K/group][32] u32, columns past N
-    zero.  (No counterpart in the reference: a pure index remap of the B200 row layout.)"""
+    own, words [T][K/8][256] u32 (code k of a word in nibble (k >> 1) + 4 (k & 1)), then scales [T][K/group][256] bf16, then zero
+    points [T][K/group][32] u32, columns past N zero.  (No counterpart in the reference: a pure index remap of the B200 row layout.)"""
     T = -(-N // 256)
     npad = T * 256
     pk = np.zeros((K // 8, npad), np.uint32)
-    pk[:, :N] = np.asarray(packed, np.uint32).reshape(K // 8, N)
+    src = np.asarray(packed, np.uint32).reshape(K // 8, N)
+    perm = np.zeros_like(src)
+    for k in range(8):                      # code k of a word moves to nibble (k >> 1) + 4 (k & 1)
+        perm |= ((src >> np.uint32(4 * k)) & np.uint32(0xF)) << np.uint32(4 * ((k >> 1) + 4 * (k & 1)))
+    pk[:, :N] = perm
     sc = np.zeros((K // group, npad), np.uint16)
     sc[:, :N] = np.asarray(scales, np.uint16).reshape(K // group, N)
     zsrc = np.asarray(zeros, np.uint32).reshape(K // group, -1)

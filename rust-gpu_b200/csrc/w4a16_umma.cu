@@ -50,6 +50,9 @@ struct UmParams {
     uint32_t group;          // k per scale / zero-point row (a multiple of 64)
     uint32_t n_tiles, n_chunks, split;
     uint32_t tiled;          // the weights are in the tile-major layout (3-D maps: column in tile, row, tile) instead of the row layout
+#ifdef T0_UM_TRACE
+    unsigned long long* trace;   // debugging build only: nanosecond stamps of CTA 0's roles, 6 x 64 chunks
+#endif
     uint32_t n_problems;     // grouped launch: problems of one shape in this launch (their maps and outputs ride in the group record)
 };
 
@@ -327,9 +330,14 @@ w4a16_umma_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
                     const uint32_t v1 = bf16x2_mul(bf16x2_sub(and_or(wd >> 4, mask, magic), zz), ss);       // k 1, 5
                     const uint32_t v2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz), ss);       // k 2, 6
                     const uint32_t v3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz), ss);      // k 3, 7
-                    // back into k order: (0,1) (2,3) (4,5) (6,7)
-                    um_sts128(b_stage + ((j ^ (n & 7)) << 4), __byte_perm(v0, v1, 0x5410), __byte_perm(v2, v3, 0x5410),
-                              __byte_perm(v0, v1, 0x7632), __byte_perm(v2, v3, 0x7632));
+                    if (p.tiled) {
+                        // tile-major words hold their codes so that the four pairs come out as (0,1) (2,3) (4,5) (6,7)
+                        um_sts128(b_stage + ((j ^ (n & 7)) << 4), v0, v1, v2, v3);
+                    } else {
+                        // row layout: pairs (0,4) (1,5) (2,6) (3,7); back into k order
+                        um_sts128(b_stage + ((j ^ (n & 7)) << 4), __byte_perm(v0, v1, 0x5410), __byte_perm(v2, v3, 0x5410),
+                                  __byte_perm(v0, v1, 0x7632), __byte_perm(v2, v3, 0x7632));
+                    }
                 }
                 // The UMMAs read these bytes through the async proxy.  The warp's writes are ordered before lane 0 by the warp
                 // barrier; lane 0's proxy fence and release-arrive then publish them (one fence per warp instead of 32:
@@ -484,6 +492,12 @@ constexpr uint32_t kTsRawStages = 14;                      // raw weight stages:
 constexpr uint32_t kTsSmemUsed = kTsRawStages * kUmRawStride + kTsXStages * kUmABytes + 512 + 1024;
 constexpr uint32_t kTsSmem = kTsSmemUsed > 120 * 1024 ? kTsSmemUsed : 120 * 1024;
 
+#ifdef T0_UM_TRACE
+#define UM_STAMP(row, t) do { if (p.trace && blockIdx.x == 0 && (t) < 64) p.trace[(row) * 64 + (t)] = ptx::globaltimer_ns(); } while (0)
+#else
+#define UM_STAMP(row, t) do { } while (0)
+#endif
+
 template <bool kGrouped>
 __global__ void __launch_bounds__(kUmThreads, 1)
 w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_s,
@@ -559,6 +573,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         ok = false;
                         break;
                     }
+                    UM_STAMP(0, c);
                     ptx::fence_proxy_async_smem();           // the stage was read through the generic proxy, the copies write it through the async proxy
                     const uint32_t fb = raw_full + 8 * stage, dst = raw_ring + stage * kUmRawStride;
                     const uint32_t grp = c * kUmBK / p.group;
@@ -616,6 +631,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         ok = false;
                         break;
                     }
+                    UM_STAMP(4, c);
                     ptx::tc_fence_after_sync();
                     const uint32_t x_addr = x_ring + xs * kUmABytes;
                     const uint32_t a_cols = tmem_base + kTsABase + stage * kTsAStageCols;
@@ -628,6 +644,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     }
                     ptx::umma_commit(ab_empty + 8 * stage);
                     ptx::umma_commit(x_empty + 8 * xs);
+                    UM_STAMP(5, c);
                     if (++stage == kTsAStages) { stage = 0; phase ^= 1; }
                     if (++xs == kTsXStages) { xs = 0; xphase ^= 1; }
                 }
@@ -654,6 +671,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     ok = false;
                     break;
                 }
+                if (tid == 0) UM_STAMP(1, c);
                 const uint32_t raw = raw_ring + rs * kUmRawStride;
                 uint32_t words[4];
 #pragma unroll
@@ -668,6 +686,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     ok = false;
                     break;
                 }
+                if (tid == 0) UM_STAMP(2, c);
                 ptx::tc_fence_after_sync();
                 const uint32_t a_cols = tmem_base + lane_base + kTsABase + as * kTsAStageCols + t * 32 + h * 16;
 #pragma unroll
@@ -681,10 +700,14 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                         const uint32_t v2 = bf16x2_mul(bf16x2_sub(and_or(wd >> 8, mask, magic), zz), ss);       // k 2, 6
                         const uint32_t v3 = bf16x2_mul(bf16x2_sub(and_or(wd >> 12, mask, magic), zz), ss);      // k 3, 7
                         // k order: (0,1) (2,3) (4,5) (6,7), two consecutive k per tensor-memory column
-                        r8[half * 4 + 0] = __byte_perm(v0, v1, 0x5410);
-                        r8[half * 4 + 1] = __byte_perm(v2, v3, 0x5410);
-                        r8[half * 4 + 2] = __byte_perm(v0, v1, 0x7632);
-                        r8[half * 4 + 3] = __byte_perm(v2, v3, 0x7632);
+                        if (p.tiled) {                     // tile-major words are stored so that the pairs come out in that order
+                            r8[half * 4 + 0] = v0; r8[half * 4 + 1] = v1; r8[half * 4 + 2] = v2; r8[half * 4 + 3] = v3;
+                        } else {                           // row layout: pairs (0,4) (1,5) (2,6) (3,7)
+                            r8[half * 4 + 0] = __byte_perm(v0, v1, 0x5410);
+                            r8[half * 4 + 1] = __byte_perm(v2, v3, 0x5410);
+                            r8[half * 4 + 2] = __byte_perm(v0, v1, 0x7632);
+                            r8[half * 4 + 3] = __byte_perm(v2, v3, 0x7632);
+                        }
                     }
                     ptx::tmem_st_32x32b_x8(a_cols + jj * 8, r8);
                 }
@@ -695,6 +718,7 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
                     ptx::mbar_arrive(raw_empty + 8 * rs);
                     ptx::mbar_arrive(ab_full + 8 * as);
                 }
+                if (tid == 0) UM_STAMP(3, c);
                 if (++rs == kTsRawStages) { rs = 0; rphase ^= 1; }
                 if (++as == kTsAStages) { as = 0; aphase ^= 1; }
             }
@@ -746,7 +770,8 @@ w4a16_umma_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 // pattern at about a third of its copy bandwidth, which is then what bounds these kernels (not the arithmetic, not the
 // UMMAs).  The tile-major layout stores every 256-column tile as a matrix of its own, so a chunk's words, scales and zero
 // points are each one contiguous piece:
-//   words  [T][K/8][256] u32, scales [T][K/G][256] bf16, zero points [T][K/G][32] u32, T = ceil(N / 256), columns past N zero.
+//   words  [T][K/8][256] u32, scales [T][K/G][256] bf16, zero points [T][K/G][32] u32, T = ceil(N / 256), columns past N zero;
+//   within a word code k sits in nibble (k >> 1) + 4 (k & 1).
 struct TiledLayout { size_t off_words, off_scales, off_zeros, total; uint32_t tiles, rows, groups; };
 
 TiledLayout tiled_layout(uint32_t K, uint32_t N, uint32_t group) {
@@ -772,7 +797,12 @@ __global__ void w4_to_tiled_kernel(const uint32_t* __restrict__ packed, const ui
             const uint64_t r = i / kUmBN;
             const uint32_t row = (uint32_t)(r % L.rows), tile = (uint32_t)(r / L.rows);
             const uint32_t n = tile * kUmBN + c;
-            ((uint32_t*)(out + L.off_words))[i] = n < N ? packed[(size_t)row * N + n] : 0u;
+            // code k of the word moves to nibble (k >> 1) + 4 (k & 1): the kernels pull nibbles i and i + 4 out together as one
+            // bf16 pair, which is then (k, k + 1) with k = 2i, the order the UMMA operand wants, with no byte permutes
+            uint32_t w = n < N ? packed[(size_t)row * N + n] : 0u, v = 0;
+#pragma unroll
+            for (uint32_t kk = 0; kk < 8; ++kk) v |= ((w >> (4 * kk)) & 0xFu) << (4 * ((kk >> 1) + 4 * (kk & 1)));
+            ((uint32_t*)(out + L.off_words))[i] = v;
         } else if (i < n_words + n_scales) {
             const uint64_t j = i - n_words;
             const uint32_t c = (uint32_t)(j % kUmBN);
@@ -924,6 +954,26 @@ int launch_w4a16_umma_tiled_grouped(t0_runtime* rt, const t0_w4a16_args* args, u
     UmParams p = um_params(rt, a0.a, a0.y, a0.m, a0.n, a0.k, a0.group);
     p.n_problems = count;
     p.tiled = 1;
+#ifdef T0_UM_TRACE
+    {
+        static unsigned long long* d_trace = nullptr;
+        static int calls = 0;
+        if (!d_trace) { cudaMalloc(&d_trace, 6 * 64 * 8); cudaMemset(d_trace, 0, 6 * 64 * 8); }
+        p.trace = d_trace;
+        int rc2 = um_launch<true, true>(rt, grp.maps, p, 1, grp);
+        if (++calls == 6) {
+            cudaStreamSynchronize(rt->stream);
+            unsigned long long h[6 * 64];
+            cudaMemcpy(h, d_trace, sizeof h, cudaMemcpyDeviceToHost);
+            const unsigned long long t0 = h[0];
+            fprintf(stderr, "[um trace] chunk: producer-free raw-seen stage-free arrived | mma-ready committed   (us after the first)\n");
+            for (int c = 0; c < 64; ++c)
+                fprintf(stderr, "[um trace] %2d: %7.2f %7.2f %7.2f %7.2f | %7.2f %7.2f\n", c, (h[c] - t0) * 1e-3, (h[64 + c] - t0) * 1e-3, (h[128 + c] - t0) * 1e-3,
+                        (h[192 + c] - t0) * 1e-3, (h[256 + c] - t0) * 1e-3, (h[320 + c] - t0) * 1e-3);
+        }
+        return rc2;
+    }
+#endif
     return um_launch<true, true>(rt, grp.maps, p, 1, grp);
 }
 
