@@ -5,10 +5,14 @@
 N = 1   workload `gemm_bf16_4096`: bf16 4096^3 GEMM, fp32 accumulate and output (the configuration the
         headline metric is quoted on).  A step is one GEMM over one of several resident input sets.  The line also
         carries, under "secondary", short runs of the other single-GPU workloads of the metric (the skinny GEMMs and
-        the W4A16 shapes, HBM-bound, reported in GB/s against the measured copy bandwidth; the other square sizes).
+        the W4A16 shapes, HBM-bound, reported in GB/s against the measured copy bandwidth; the other square sizes; the
+        stand-alone dequantisation, the weight prepack and the f32 matmul entry).  A step of a skinny-GEMM or W4A16
+        workload is one of 32 independent problems of a grouped launch; the same problems launched one at a time are
+        reported beside it as `one_problem_per_launch`.
 N > 1   workload `gemm_bf16_16384_sharded`: the 16384^3 GEMM sharded by N-column blocks, A replicated,
         each rank computes C[:, N/g slice]; no data-path collective (strong scaling).  Rank 0 then runs the whole
-        16384^3 on its one GPU, so the line carries the single-GPU time and the speed-up over it.
+        16384^3 on its one GPU, so the line carries the single-GPU time and the speed-up over it; `gather` holds the
+        step with the gathered C (GEMM + NCCL all-gather, and the one-kernel form whose epilogue stores to every rank).
 `value` is whole-job TFLOP/s with inputs resident in HBM, timed with CUDA events on the launching
 stream, max over ranks.  `e2e` is the same metric through the C-ABI call with pinned HOST buffers:
 host->device copies of the step's operands and the device->host read of its result are inside the
