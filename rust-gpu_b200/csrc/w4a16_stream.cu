@@ -499,34 +499,42 @@ PrepackLayout prepack_layout(uint32_t K, uint32_t N, uint32_t group) {
     return L;
 }
 
-// Row layout -> streaming layout.  One thread per output element: a tile word (eight codes in mma.sync fragment order),
-// a scale, or a word of eight zero points.  Columns past N are written as zero.
+// Row layout -> streaming layout.  One thread per four tile words (the four words that draw on the same four source words),
+// per scale, or per word of eight zero points.  Columns past N are written as zero.
 __global__ void w4_prepack_kernel(const uint32_t* __restrict__ packed, const uint16_t* __restrict__ scales, const uint32_t* __restrict__ zeros,
                                   uint8_t* __restrict__ out, uint32_t K, uint32_t N, uint32_t nz, PrepackLayout L) {
-    const uint64_t n_words = (uint64_t)L.bands * L.ksteps * 16 * kBandCols;
+    const uint64_t n_words = (uint64_t)L.bands * L.ksteps * 16 * kBandCols / 4;      // units of four words
     const uint64_t n_scales = (uint64_t)L.bands * L.groups * kBandCols;
     const uint64_t n_zwords = (uint64_t)L.bands * L.groups * (kBandCols / 8);
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words + n_scales + n_zwords; i += stride) {
         if (i < n_words) {
-            // word (tile, w, j, lane, e) of the fragment order: k step s = 4j + e of column tile w, lane (g, t);
-            // nibble c / c+4 = codes (k, k+1) of column n = 16w + g + 8(c & 1) at k = 16s + 2t + 8(c >> 1)
-            const uint32_t e = (uint32_t)(i & 3), ln = (uint32_t)((i >> 2) & 31), j = (uint32_t)((i >> 7) & 1), w = (uint32_t)((i >> 8) & 15);
-            const uint64_t tile = i >> 12;
+            // Word (tile, w, j, lane, e) of the fragment order: k step s = 4j + e of column tile w, lane (g, t); nibble c / c+4 =
+            // codes (k, k+1) of column n = 16w + g + 8(c & 1) at k = 16s + 2t + 8(c >> 1).  The four words t = 0..3 of one
+            // (tile, w, j, g, e) take nibble pair t of the same four source words (two rows x two columns).
+            const uint32_t e = (uint32_t)(i & 3), g = (uint32_t)((i >> 2) & 7), j = (uint32_t)((i >> 5) & 1), w = (uint32_t)((i >> 6) & 15);
+            const uint64_t tile = i >> 10;
             const uint32_t ks = (uint32_t)(tile % L.ksteps), band = (uint32_t)(tile / L.ksteps);
-            const uint32_t g = ln >> 2, t = ln & 3, sstep = 4 * j + e;
-            uint32_t v = 0;
+            const uint32_t sstep = 4 * j + e;
+            const uint32_t n0 = band * kBandCols + w * 16 + g, n1 = n0 + 8;
+            const size_t r0 = (size_t)(ks * (kUnitK / 8) + 2 * sstep) * N;
+            uint32_t src[4];
+            src[0] = n0 < N ? __ldg(packed + r0 + n0) : 0u;
+            src[1] = n1 < N ? __ldg(packed + r0 + n1) : 0u;
+            src[2] = n0 < N ? __ldg(packed + r0 + N + n0) : 0u;
+            src[3] = n1 < N ? __ldg(packed + r0 + N + n1) : 0u;
+            uint32_t* dst = (uint32_t*)(out + L.off_tiles) + ((tile << 12) | ((uint64_t)w << 8) | ((uint64_t)j << 7) | ((uint64_t)g << 4) | e);
 #pragma unroll
-            for (uint32_t c = 0; c < 4; ++c) {
-                const uint32_t n = band * kBandCols + w * 16 + g + 8 * (c & 1);
-                const uint32_t k = ks * kUnitK + sstep * 16 + 2 * t + 8 * (c >> 1);
-                if (n < N) {
-                    const uint32_t src = packed[(size_t)(k >> 3) * N + n] >> (4 * (k & 7));
-                    v |= (src & 0xFu) << (4 * c);
-                    v |= ((src >> 4) & 0xFu) << (4 * (c + 4));
+            for (uint32_t t = 0; t < 4; ++t) {
+                uint32_t v = 0;
+#pragma unroll
+                for (uint32_t c = 0; c < 4; ++c) {
+                    const uint32_t pair = src[c] >> (8 * t);
+                    v |= (pair & 0xFu) << (4 * c);
+                    v |= ((pair >> 4) & 0xFu) << (4 * (c + 4));
                 }
+                dst[t * 4] = v;                       // lane 4g + t: sixteen bytes further on
             }
-            ((uint32_t*)(out + L.off_tiles))[i] = v;
         } else if (i < n_words + n_scales) {
             const uint64_t j = i - n_words;
             const uint32_t c = (uint32_t)(j % kBandCols);
