@@ -839,3 +839,32 @@ def test_grouped_launch_with_epilogues_and_bf16_output(t0, oracle, rt, m, n, k, 
             rt.recycle(y)
     for buf in xa + xb + [xb_bias]:
         rt.recycle(buf)
+
+
+def test_grouped_launch_random_shapes(t0, oracle, rt):
+    # a seeded sweep over shapes and configurations of the grouped entry (ragged M and N, K that is and is not a multiple of the
+    # split, explicit and library-chosen tile and split): every problem against the oracle, rows and bytes beyond untouched
+    rng = np.random.default_rng(2026)
+    for case in range(14):
+        m = int(rng.integers(1, 300))
+        n = int(rng.integers(1, 190)) * 8
+        k = int(rng.integers(1, 33)) * 64
+        count = int(rng.integers(2, 6))
+        choice = int(rng.integers(0, 4))
+        kw = [{}, dict(tile_n=128, split_k=2, pair_cta=2), dict(tile_n=64, split_k=4, pair_cta=2), dict(tile_n=128, pair_cta=2)][choice]
+        if kw.get("split_k", 1) > 1 and (k // 64) % kw["split_k"]:
+            kw = {}
+        a = [oracle.fill_uniform_bf16(m * k, 1000 + 10 * case + i) for i in range(count)]
+        b = [oracle.fill_uniform_bf16(n * k, 5000 + 10 * case + i) for i in range(count)]
+        xa, xb = [rt.upload(v) for v in a], [rt.upload(v) for v in b]
+        ys = [rt.alloc(m * n * 4 + 4096) for _ in range(count)]
+        for y in ys:
+            y.write(np.full(m * n + 1024, SENTINEL, np.float32))
+        rt.gemm_grouped([rt.gemm_args(xa[i].gpu_addr(), xb[i].gpu_addr(), ys[i].gpu_addr(), m, n, k, **kw) for i in range(count)])
+        rt.synchronize()
+        for i in range(count):
+            got = ys[i].read((m * n + 1024) * 4, np.float32)
+            assert_gemm_close(got[:m * n].reshape(m, n), oracle.gemm_nt(a[i], b[i], m, k, n), k), (case, m, n, k, kw)
+            assert np.all(got[m * n:] == SENTINEL), ("wrote past the matrix", case, m, n, k, kw)
+        for buf in xa + xb + ys:
+            buf.free()

@@ -573,3 +573,31 @@ def test_tiled_grouped_dequantises_bit_exactly(t0, oracle, rt):
         assert np.array_equal(got.view(np.uint32) & 0x7FFFFFFF, want[base:base + M].view(np.uint32) & 0x7FFFFFFF), base
     for b in bufs:
         b.free()
+
+
+def test_tiled_grouped_random_shapes(t0, oracle, rt):
+    # a seeded sweep over M (1..128), N (multiples of 8, partial last tiles), K (multiples of the group) and both group sizes of
+    # the tile-major entries: every problem of a grouped call against the oracle, the words behind each y untouched
+    rng = np.random.default_rng(77)
+    for case in range(10):
+        G = int(rng.choice([64, 128, 256]))
+        M = int(rng.integers(1, 129))
+        N = int(rng.integers(1, 160)) * 8
+        K = int(rng.integers(1, 9)) * G
+        count = int(rng.integers(1, 5))
+        w = make_w4(oracle, K, N, G, seed=300 + case)
+        xp, xs, xz = rt.upload(w[0]), rt.upload(w[1]), rt.upload(w[2])
+        tiled = rt.w4_to_tiled(xp.gpu_addr(), xs.gpu_addr(), xz.gpu_addr(), K, N, G)
+        acts = [oracle.fill_normal_bf16(M * K, 900 + 7 * case + i) for i in range(count)]
+        xas = [rt.upload(a) for a in acts]
+        ys = [rt.alloc(M * N * 4 + 4096) for _ in range(count)]
+        for y in ys:
+            y.write(np.full(M * N + 1024, -9999.0, np.float32))
+        rt.w4a16_gemm_tiled_grouped([t0.W4A16Args(xas[i].gpu_addr(), tiled.gpu_addr(), 0, 0, ys[i].gpu_addr(), M, N, K, G) for i in range(count)])
+        rt.synchronize()
+        for i in range(count):
+            got = ys[i].read((M * N + 1024) * 4, np.float32)
+            assert_close(got[:M * N].reshape(M, N), oracle.w4a16_gemm(acts[i], *w, M, N, K, G), K)
+            assert np.all(got[M * N:] == -9999.0), ("wrote past the output", case, M, N, K, G)
+        for b in [xp, xs, xz, tiled] + xas + ys:
+            b.free()
